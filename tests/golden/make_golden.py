@@ -1,0 +1,100 @@
+"""Generates tests/golden/*.npz from the reference's own dense PyTorch path.
+
+Run in a container that has the reference checkout (default /root/reference); the
+fixtures it writes are committed, this script is how they were made:
+
+    python tests/golden/make_golden.py [--reference /path/to/FlashBEV]
+
+What is recorded, per case: the inputs, the forward output of
+``sampling_vt_pytorch`` fed by ``project_coords`` (flashbev/flashbevpool/sampling_vt.py:36-123,
+449-466), and the gradients autograd produces through that path for a seeded upstream
+gradient.  The reference package imports its compiled extensions at import time; they
+are replaced by empty stand-in modules because only the pure-PyTorch functions are used.
+One case takes its camera rig from the reference's calibration fixture
+(inputs/calib_nuscenes.json) through the reference's ``create_projection_matrix``.
+"""
+import argparse
+import json
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+from flashbev_b200 import synth  # noqa: E402
+
+
+def load_reference(root):
+    for n in ("flashbevpool.flashbevpool_ext", "flashbevpool.sampling_vt_ext", "flashbevpool_ext", "sampling_vt_ext"):
+        sys.modules[n] = types.ModuleType(n)
+    sys.path.insert(0, os.path.join(root, "flashbev"))
+    import flashbevpool.sampling_vt as R
+    return R
+
+
+def dense_reference(R, feats, depth, proj, image_size, roi, grid, dist, threshold, grad_out):
+    """feats [B,N,H,W,C], depth [B,N,H,W,2] -> out [B,Y,X,C] and autograd gradients."""
+    B, N = feats.shape[:2]
+    X, Y, Z = grid
+    r = torch.tensor(roi, dtype=torch.float32).view(3, 2)
+    vs = [(r[i, 1] - r[i, 0]) / g for i, g in enumerate(grid)]
+    # SamplingVT._calculate_coords_3d (sampling_vt.py:364-378)
+    axes = [torch.linspace(float(r[i, 0]), float(r[i, 1]), g + 1)[:-1] + vs[i] / 2.0 for i, g in enumerate(grid)]
+    coords = torch.stack(torch.meshgrid(*axes, indexing="ij"), dim=-1)
+    coords = coords.unsqueeze(0).unsqueeze(0).expand(B, N, -1, -1, -1, -1)
+    uvd = R.project_coords(coords_xyz=coords, projection_matrices=proj)
+    f = feats.clone().requires_grad_(True)
+    d = depth.clone().requires_grad_(True)
+    out = R.sampling_vt_pytorch(
+        image_uvd=uvd, features_pv=f.flatten(0, 1).movedim(-1, 1), depths=d.flatten(0, 1).movedim(-1, 1),
+        B=B, N=N, image_size=image_size, depth_weight_threshold=threshold, depth_distribution=dist, epsilon=1e-6)
+    out = out.movedim(1, -1)  # [B,C,Y,X] -> [B,Y,X,C]
+    out.backward(grad_out)
+    return out.detach(), f.grad, d.grad
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    args = ap.parse_args()
+    R = load_reference(args.reference)
+    torch.manual_seed(0)
+
+    small = synth.Workload("golden_small", B=2, N=6, C=8, H=8, W=22, D=16, X=24, Y=20, Z=4, xy_extent=25.6,
+                           d0=1.0, delta=2.0, dtype="fp32", seed=11, jitter=True)
+    cases = []
+    inp = synth.make_inputs(small, "parametric")
+    for dist in ("laplace", "gaussian"):
+        for thr in (0.0, 2e-2):
+            cases.append((f"synthetic_{dist}_thr{thr:g}", inp, small, dist, thr))
+
+    # second rig: the reference's calibration record through its own matrix builder
+    with open(os.path.join(args.reference, "inputs", "calib_nuscenes.json")) as fh:
+        calib = {k: torch.tensor(v, dtype=torch.float32) for k, v in json.load(fh).items()}
+    nus = synth.Workload("golden_nuscenes", B=1, N=6, C=6, H=16, W=44, D=16, X=40, Y=36, Z=6, xy_extent=50.0,
+                         z_range=(-4.0, 2.0), d0=1.0, delta=3.0, dtype="fp32", seed=12)
+    inp_n = synth.make_inputs(nus, "parametric")
+    inp_n["projection_matrices"] = R.create_projection_matrix(
+        calib["sensor2ego"], calib["ego2global"], calib["camera2imgs"], calib["post_rots"], calib["post_trans"],
+        calib["bda"]).contiguous()
+    cases.append(("nuscenes_laplace_thr0", inp_n, nus, "laplace", 0.0))
+
+    for name, inp, w, dist, thr in cases:
+        go = synth.upstream_grad(w)
+        out, dfe, dde = dense_reference(R, inp["image_feats"], inp["depth_params"], inp["projection_matrices"],
+                                        w.image_size, w.roi, w.grid, dist, thr, go)
+        path = os.path.join(HERE, f"{name}.npz")
+        np.savez_compressed(
+            path, feats=inp["image_feats"].numpy(), depth=inp["depth_params"].numpy(),
+            proj=inp["projection_matrices"].numpy(), image_size=np.array(w.image_size, np.int32),
+            roi=np.array(w.roi, np.float32), grid=np.array(w.grid, np.int32), threshold=np.float32(thr),
+            laplace=np.int32(dist == "laplace"), grad_out=go.numpy(), out=out.numpy(), d_feats=dfe.numpy(),
+            d_depth=dde.numpy(), torch_version=np.array(torch.__version__))
+        print(name, out.shape, "nonzero cells", int((out.abs().sum(-1) > 0).sum()), os.path.getsize(path), "bytes")
+
+
+if __name__ == "__main__":
+    main()
