@@ -1,0 +1,380 @@
+#!/usr/bin/env python
+"""Benchmark of the fused BEV pooling forward (and forward+backward) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg2]
+
+One "step" is one operator call over one batch of synthetic input of the headline
+configuration (cfg2, Z = 8: 6 cameras, 16x44x80 bfloat16 features, 118 depth bins,
+200x200 BEV grid, categorical depth, sum pooling).  With N > 1 every rank runs its own
+sample(s) of the batch (weak scaling, no collective on the data path).  Rank 0 prints one
+JSON line:
+
+  value        BEV cells/s over all ranks, inputs resident in HBM, device time from CUDA events
+               around every launch, L2 flushed (256 MiB write) between steps
+  e2e          the same through the public Python call with pinned host inputs and a host read-back
+               of the result inside the timed region
+  roofline     algorithmic HBM bytes / kernel time against the measured copy bandwidth, plus the
+               same for the gather traffic against a measured L2-resident read bandwidth
+  cpu_baseline the CPU oracle (a port of the reference arithmetic) on the host cores, N = 1 only
+  extra        forward+backward time and other context
+
+`--impl reference` times the CPU implementation alone (the reference publishes no CPU build that
+can travel; the port in oracle/ is used, all host threads).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+from flashbev_b200 import synth  # noqa: E402
+
+METRIC = "bev_pool_forward_cells_per_s"
+UNIT = "BEV cells/s"
+
+
+def workload_description(w, B_local, mode):
+    return (f"{w.name}: B={B_local}/GPU, {w.N} cams, {w.H}x{w.W}x{w.C} {w.dtype} features, D={w.D}, "
+            f"BEV {w.X}x{w.Y}x{w.Z}, {mode} depth, forward")
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as fh:
+            return float(json.load(fh)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and clock-event reasons of one GPU through NVML while the benchmark runs."""
+    BITS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz, self.ok = [], set(), None, False
+        self._stop = threading.Event()
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+            self.ok = True
+        except Exception:
+            self.ok = False
+        self.t = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM)))
+                try:
+                    r = int(self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
+                except Exception:
+                    r = int(self.nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+                for bit, name in self.BITS.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.01)
+
+    def __enter__(self):
+        if self.ok:
+            self.t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self.ok:
+            self.t.join(timeout=1.0)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def physical_gpu_index(local_rank):
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except Exception:
+            return local_rank
+    return local_rank
+
+
+def cpu_forward_rate(w, mode, threads, min_seconds, min_reps=2):
+    """Times the CPU oracle's forward on the same workload (one sample); returns cells/s and the run's facts."""
+    from oracle import oracle as O
+    inp = synth.make_inputs(w, mode, batch_slice=(0, 1))
+    p = O.Problem(
+        feats=inp["image_feats"].float().numpy(), depth=inp["depth_params"].float().numpy(),
+        proj=inp["projection_matrices"].numpy(), image_size=w.image_size, roi=w.roi, grid=w.grid,
+        mode=O.MODE_CATEGORICAL if mode == "categorical" else O.MODE_LAPLACE, threshold=0.0, d0=w.d0, delta=w.delta)
+    O.forward(p, threads=threads)  # warm-up
+    times = []
+    t_end = time.perf_counter() + min_seconds
+    while len(times) < min_reps or time.perf_counter() < t_end:
+        t0 = time.perf_counter()
+        O.forward(p, threads=threads)
+        times.append(time.perf_counter() - t0)
+    return times
+
+
+def reference_arm(args, rank):
+    """CPU implementation of the path on the host cores (the oracle port, OpenMP over BEV rows)."""
+    if rank != 0:
+        return
+    from oracle import oracle as O
+    w = synth.workload(args.workload)
+    threads = O.host_threads()
+    O.forward  # noqa: B018  (import check)
+    inp = synth.make_inputs(w, args.mode, batch_slice=(0, 1))
+    p = O.Problem(
+        feats=inp["image_feats"].float().numpy(), depth=inp["depth_params"].float().numpy(),
+        proj=inp["projection_matrices"].numpy(), image_size=w.image_size, roi=w.roi, grid=w.grid,
+        mode=O.MODE_CATEGORICAL if args.mode == "categorical" else O.MODE_LAPLACE, threshold=0.0, d0=w.d0,
+        delta=w.delta)
+    for _ in range(args.warmup):
+        O.forward(p, threads=threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        O.forward(p, threads=threads)
+    dt = (time.perf_counter() - t0) / args.steps
+    cells = w.X * w.Y
+    value = cells / dt
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_description(w, 1, args.mode), "l2": "n/a (CPU)"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": f"one whole forward of one sample per step, {args.steps} steps, "
+                                   f"float32 oracle, OpenMP over BEV rows; host has {os.cpu_count()} logical CPUs"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=None)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg2")
+    ap.add_argument("--mode", default="categorical", choices=["categorical", "parametric"])
+    ap.add_argument("--batch-per-gpu", type=int, default=1)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip backward / e2e / L2 probe (for profiler runs)")
+    ap.add_argument("--tune", default=None, help="tile_x,tile_y,chunks_per_lane,warps (0 = automatic)")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        args.steps = args.steps if args.steps is not None else 20
+        args.warmup = args.warmup if args.warmup is not None else 3
+        reference_arm(args, rank)
+        return
+    args.steps = args.steps if args.steps is not None else 500
+    args.warmup = max(args.warmup if args.warmup is not None else 20, 3)
+
+    import torch.distributed as dist
+    from flashbev_b200 import _lib, flash_bevpool
+    from flashbev_b200.flash_bevpool import DepthSpec, forward_with_count, make_problem
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU path for the product arm")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    lib = _lib.load()
+    if args.tune:
+        lib.fbev_set_tuning(*[int(v) for v in args.tune.split(",")])
+
+    w = synth.workload(args.workload)
+    Bl = args.batch_per_gpu
+    w_all = synth.workload(args.workload, B=Bl * world)
+    inp_cpu = synth.make_inputs(w_all, args.mode, batch_slice=(rank * Bl, (rank + 1) * Bl))
+    inp = {k: v.to(device) for k, v in inp_cpu.items()}
+    mode_int = 2 if args.mode == "categorical" else 1
+    extra_kw = {"depth_bin_range": (w.d0, w.delta)} if args.mode == "categorical" else {}
+    spec = DepthSpec(mode_int, **extra_kw)
+    prob, keep = make_problem(inp["depth_params"], inp["image_feats"], inp["projection_matrices"],
+                              inp["feature_size"], inp["image_size"], inp["roi_range"], inp["grid_size"], spec,
+                              1e-6, 0.0)
+    out = torch.empty(Bl, w.Y, w.X, w.C, dtype=inp["image_feats"].dtype, device=device)
+    stream = torch.cuda.current_stream().cuda_stream
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=device)  # larger than the 126 MB L2
+
+    def flush():
+        flush_buf.zero_()
+
+    def fwd_raw():
+        rc = lib.fbev_forward(ctypes.byref(prob), out.data_ptr(), None, stream)
+        if rc:
+            raise RuntimeError(_lib.strerror(rc))
+
+    def timed(fn, steps, warmup):
+        """Device time of `steps` calls of fn, each bracketed by its own events, L2 flushed before each."""
+        for _ in range(warmup):
+            flush()
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        for i in range(steps):
+            flush()
+            starts[i].record()
+            fn()
+            ends[i].record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
+        return sum(ms) / steps, ms
+
+    with ClockSampler(physical_gpu_index(local_rank)) as clocks:
+        ms_fwd, ms_list = timed(fwd_raw, args.steps, args.warmup)
+        extra = {"fwd_us_median": statistics.median(ms_list) * 1e3, "fwd_us_min": min(ms_list) * 1e3}
+        e2e = None
+        l2_gbs = None
+        if not args.no_extras:
+            # forward + backward through the C ABI, upstream gradient and gradient buffers resident
+            go = synth.upstream_grad(w, B=Bl).to(device=device, dtype=inp["image_feats"].dtype)
+            kw = dict(depth_distribution=mode_int, depth_weight_threshold=0.0, **extra_kw)
+            g_feats = torch.empty_like(keep[0])
+            g_depth = torch.empty_like(keep[1])
+            flags = _lib.BWD_FEATS | _lib.BWD_DEPTH
+            nbytes = lib.fbev_backward_scratch_bytes(ctypes.byref(prob), flags)
+            scratch = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=device)
+
+            def fwd_bwd():
+                fwd_raw()
+                rc = lib.fbev_backward(ctypes.byref(prob), go.data_ptr(), g_feats.data_ptr(), g_depth.data_ptr(),
+                                       scratch.data_ptr() if nbytes else None, nbytes, flags, stream)
+                if rc:
+                    raise RuntimeError(_lib.strerror(rc))
+
+            nb = max(10, args.steps // 5)
+            ms_fb, _ = timed(fwd_bwd, nb, 5)
+            extra["fwd_bwd_us"] = ms_fb * 1e3
+            extra["fwd_bwd_note"] = "forward + backward (gradients for features and depth), device time, L2 flushed"
+
+            # back-to-back launches with warm L2 (what a model sees when the features were just produced)
+            for _ in range(20):
+                fwd_raw()
+            torch.cuda.synchronize()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            for _ in range(200):
+                fwd_raw()
+            e.record()
+            torch.cuda.synchronize()
+            extra["fwd_us_warm_l2_back_to_back"] = s.elapsed_time(e) / 200 * 1e3
+
+            # end to end: pinned host inputs -> device, operator, result -> pinned host
+            host = {k: inp_cpu[k].pin_memory() for k in ("image_feats", "depth_params", "projection_matrices")}
+            host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+            const = {k: inp[k] for k in ("feature_size", "image_size", "roi_range", "grid_size")}
+            h2d = sum(t.numel() * t.element_size() for t in host.values())
+            d2h = host_out.numel() * host_out.element_size()
+
+            def e2e_step():
+                with torch.no_grad():
+                    dev_in = {k: t.to(device, non_blocking=True) for k, t in host.items()}
+                    o = flash_bevpool(**dev_in, **const, **kw)
+                    host_out.copy_(o, non_blocking=True)
+
+            ne = max(10, args.steps // 5)
+            ms_e2e, _ = timed(e2e_step, ne, 5)
+            e2e_ms_max = ms_e2e
+
+            # L2-resident read bandwidth: 32 MiB buffer read 50 times
+            buf = torch.empty(32 << 20, dtype=torch.uint8, device=device)
+            sink = torch.zeros(1, dtype=torch.int32, device=device)
+            lib.fbev_probe_read(buf.data_ptr(), buf.numel(), 5, sink.data_ptr(), stream)
+            best = None
+            for _ in range(5):
+                s.record()
+                lib.fbev_probe_read(buf.data_ptr(), buf.numel(), 50, sink.data_ptr(), stream)
+                e.record()
+                torch.cuda.synchronize()
+                t = s.elapsed_time(e)
+                best = t if best is None else min(best, t)
+            l2_gbs = buf.numel() * 50 / (best * 1e-3) / 1e9
+        # accepted samples (exact, from the kernel's per-cell counts) for the gather figure
+        _, cnt = forward_with_count(**inp, depth_distribution=mode_int, depth_weight_threshold=0.0, **extra_kw)
+        s_valid = int(cnt.sum().item())
+    clk = clocks.summary()
+
+    # max over ranks
+    t = torch.tensor([ms_fwd, e2e_ms_max if not args.no_extras else 0.0], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_fwd_max, ms_e2e_max = float(t[0]), float(t[1])
+
+    cells_total = Bl * w.X * w.Y * world
+    value = cells_total / (ms_fwd_max * 1e-3)
+    hbm_peak, peak_kind = measured_peaks()
+    alg_bytes = synth.algorithmic_bytes(w, args.mode, B=Bl)
+    achieved = alg_bytes / (ms_fwd * 1e-3) / 1e9
+    es = 4 if w.dtype == "fp32" else 2
+    gather_bytes = s_valid * (4 * w.C * es + 4 * (1 if args.mode == "categorical" else 2) * es)
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_fwd_max, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": w.dtype, "data": "synthetic",
+        "config": {"workload": workload_description(w, Bl, args.mode),
+                   "l2": "flushed between steps (256 MiB write)", "timing": "CUDA events around every launch",
+                   "parallelism": f"batch samples sharded over {world} GPU(s), no data-path collective"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                     "frac": achieved / hbm_peak, "traffic": None, "peak_kind": f"of {peak_kind}",
+                     "algorithmic_bytes_per_launch": alg_bytes, "kernel": "fwd_kernel"},
+        "roofline_gather": {"bound": "l2", "achieved": gather_bytes / (ms_fwd * 1e-3) / 1e9, "peak": l2_gbs,
+                            "unit": "GB/s", "frac": (gather_bytes / (ms_fwd * 1e-3) / 1e9 / l2_gbs) if l2_gbs else None,
+                            "algorithmic_bytes_per_launch": gather_bytes, "accepted_samples": s_valid,
+                            "peak_kind": "L2-resident 16-byte loads of a 32 MiB buffer, measured in this run"},
+        "clocks": clk, "gpu_launches": args.steps, "extra": extra,
+    }
+    if not args.no_extras:
+        line["e2e"] = {"value": cells_total / (ms_e2e_max * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
+                       "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e_max}
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        from oracle import oracle as O
+        threads = O.host_threads()
+        times = cpu_forward_rate(w, args.mode, threads, min_seconds=8.0)
+        line["cpu_baseline"] = {
+            "value": w.X * w.Y / statistics.median(times), "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"{len(times)} whole forwards of one sample (median), float32 oracle, OpenMP over BEV rows"}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,287 @@
+"""``FlashBEVPool`` / ``flash_bevpool``: the operator of the reference package, on libfbev.so.
+
+Mirrors flashbev/flashbevpool/flash_bevpool.py of the reference:
+  * ``FlashBEVPool.forward`` keeps the 14 positional slots of flash_bevpool.py:22-23 and
+    ``backward`` returns the 14-tuple of :135-136 (gradients for depth and features only);
+  * ``flash_bevpool`` keeps names, order and defaults of :139-140 and reorders its first
+    two arguments exactly as :163-166 does.
+
+Differences, all additive or host-side:
+  * no host synchronisation per call: sizes come from a cached host copy of ``grid_size``;
+    ``roi_range``, ``image_size`` and ``feature_size`` are read on the device, as the
+    reference's backward kernel already does (flash_bevpool_cuda.cu:465-470);
+  * launches go to the caller's current stream (the reference uses the legacy default
+    stream, flash_bevpool_cuda.cu:807);
+  * float32, bfloat16 and float16 features are processed natively (float32 accumulation)
+    and the output has the feature dtype; the reference up-casts to float32 (:47-49);
+  * ``depth_distribution=2`` selects the categorical depth mode (depth = probabilities
+    [B,N,H,W,D]); ``pool``, ``depth_bin_range``, ``legacy_depth_grad`` and ``y_range``
+    are keyword-only extras of the wrapper;
+  * the kernel-variant flags (``use_shared_memory``, ``optimize_z_precompute``,
+    ``use_warp_kernel``, ``use_vectorized_load``) are accepted and ignored: they select
+    between reference kernels that compute the same thing;
+  * ``projection_matrices`` may be [B,N,3,4] or [B,N,4,4] (rows 0-2 are used).
+
+There is no CPU path: tensors must live on a CUDA device and libfbev.so must load.
+"""
+from __future__ import annotations
+
+import ctypes
+import weakref
+from typing import Optional, Tuple
+
+import numpy as np
+import torch
+
+from . import _lib
+
+_DTYPES = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16, torch.float16: _lib.F16}
+
+
+class DepthSpec(int):
+    """``depth_distribution`` with the extra options riding along.
+
+    It is an ``int`` (0 gaussian, 1 laplace, 2 categorical), so it fits the reference's
+    positional slot; the attributes carry what the reference has no slot for.
+    """
+
+    def __new__(cls, mode: int, pool: Optional[str] = None, depth_bin_range: Optional[Tuple[float, float]] = None,
+                legacy_depth_grad: bool = False, y_range: Optional[Tuple[int, int]] = None):
+        mode = int(mode)
+        if mode not in (0, 1, 2):
+            raise ValueError(f"depth_distribution must be 0 (gaussian), 1 (laplace) or 2 (categorical), got {mode}")
+        self = super().__new__(cls, mode)
+        if pool is None:
+            pool = "sum" if mode == 2 else "mean"
+        if pool not in ("mean", "sum"):
+            raise ValueError(f"pool must be 'mean' or 'sum', got {pool!r}")
+        self.pool = pool
+        if mode == 2:
+            if depth_bin_range is None:
+                raise ValueError("depth_distribution=2 needs depth_bin_range=(first_edge, bin_width)")
+            d0, delta = float(depth_bin_range[0]), float(depth_bin_range[1])
+            if not delta > 0:
+                raise ValueError("depth_bin_range: bin width must be positive")
+        else:
+            d0, delta = 0.0, 1.0
+        self.d0, self.delta = d0, delta
+        self.legacy_depth_grad = bool(legacy_depth_grad)
+        self.y_range = None if y_range is None else (int(y_range[0]), int(y_range[1]))
+        return self
+
+
+# host copies of small device tensors, keyed by the tensor object and its version
+_host_cache: "weakref.WeakKeyDictionary[torch.Tensor, tuple]" = weakref.WeakKeyDictionary()
+
+
+def _host_values(t: torch.Tensor) -> tuple:
+    """Values of a small tensor on the host.  Synchronises only the first time a given
+    (tensor, version) is seen; the reference synchronises on every call (flash_bevpool.py:58-67)."""
+    if t.device.type == "cpu":
+        return tuple(t.tolist())
+    hit = _host_cache.get(t)
+    if hit is not None and hit[0] == t._version:
+        return hit[1]
+    vals = tuple(t.tolist())
+    _host_cache[t] = (t._version, vals)
+    return vals
+
+
+_status_words = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """Per-device int32 word the kernels OR FBEV_DEV_* flags into (never read on the hot path)."""
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    w = _status_words.get(key)
+    if w is None:
+        w = torch.zeros(1, dtype=torch.int32, device=device)
+        _status_words[key] = w
+    return w
+
+
+def _on(t: torch.Tensor, device: torch.device, dtype: torch.dtype) -> torch.Tensor:
+    if t.device != device or t.dtype != dtype:
+        t = t.to(device=device, dtype=dtype)
+    return t.contiguous()
+
+
+def make_problem(depth_params, image_feats, projection_matrices, feature_size, image_size, roi_range, grid_size,
+                 spec: DepthSpec, epsilon: float, threshold: float):
+    """Builds the FbevProblem for a call and returns it with the tensors that must stay alive."""
+    if not image_feats.is_cuda:
+        raise RuntimeError("flash_bevpool runs on CUDA tensors only (there is no CPU path)")
+    dev = image_feats.device
+    dtype = image_feats.dtype if image_feats.dtype in _DTYPES else torch.float32
+    feats = _on(image_feats, dev, dtype)
+    depth = _on(depth_params, dev, dtype)
+    proj = _on(projection_matrices, dev, torch.float32)
+    fsize = _on(feature_size, dev, torch.int32)
+    isize = _on(image_size, dev, torch.int32)
+    roi = _on(roi_range, dev, torch.float32)
+    if feats.dim() != 5 or depth.dim() != 5 or feats.shape[:4] != depth.shape[:4]:
+        raise ValueError(f"image_feats must be [B,N,H,W,C] and depth_params [B,N,H,W,D]; got "
+                         f"{tuple(image_feats.shape)} and {tuple(depth_params.shape)}")
+    B, N, H, W, C = feats.shape
+    if proj.dim() != 4 or tuple(proj.shape[:2]) != (B, N) or tuple(proj.shape[2:]) not in ((3, 4), (4, 4)):
+        raise ValueError(f"projection_matrices must be [B,N,3,4] or [B,N,4,4]; got {tuple(proj.shape)}")
+    if fsize.numel() != B * N * 2 or isize.numel() != 2 or roi.numel() != 6:
+        raise ValueError("feature_size must be [B,N,2], image_size [2], roi_range [6]")
+    grid = _host_values(grid_size)
+    if len(grid) != 3:
+        raise ValueError("grid_size must hold [grid_x, grid_y, grid_z]")
+    X, Y, Z = (int(v) for v in grid)
+    p = _lib.FbevProblem()
+    p.struct_size = ctypes.sizeof(_lib.FbevProblem)
+    p.dtype = _DTYPES[dtype]
+    p.B, p.N, p.H, p.W, p.C = B, N, H, W, C
+    p.D = depth.shape[-1]
+    p.X, p.Y, p.Z = X, Y, Z
+    p.proj_stride = proj.shape[2] * proj.shape[3]
+    p.mode = int(spec)
+    p.pool = _lib.POOL_SUM if spec.pool == "sum" else _lib.POOL_MEAN
+    p.epsilon, p.threshold = float(epsilon), float(threshold)
+    p.depth_d0, p.depth_delta = spec.d0, spec.delta
+    yb, ye = spec.y_range if spec.y_range is not None else (0, Y)
+    p.y_begin, p.y_end = yb, ye
+    p.image_feats, p.depth, p.projection = feats.data_ptr(), depth.data_ptr(), proj.data_ptr()
+    p.feature_size, p.image_size, p.roi_range = fsize.data_ptr(), isize.data_ptr(), roi.data_ptr()
+    p.status = status_word(dev).data_ptr()
+    return p, (feats, depth, proj, fsize, isize, roi)
+
+
+class FlashBEVPool(torch.autograd.Function):
+    """Fused BEV pooling: projection, depth weight, bilinear sampling and the reduction over
+    cameras and height bins in one kernel; see the module docstring for the contract."""
+
+    @staticmethod
+    def forward(ctx, depth_params, image_feats, projection_matrices, feature_size, image_size, roi_range,
+                grid_size, depth_distribution=0, use_shared_memory=True, optimize_z_precompute=True,
+                use_warp_kernel=False, use_vectorized_load=False, epsilon=1e-6, depth_weight_threshold=1e-6):
+        spec = depth_distribution if isinstance(depth_distribution, DepthSpec) else DepthSpec(depth_distribution)
+        p, keep = make_problem(depth_params, image_feats, projection_matrices, feature_size, image_size,
+                               roi_range, grid_size, spec, epsilon, depth_weight_threshold)
+        feats = keep[0]
+        shape = (p.B, p.Y, p.X, p.C)
+        partial = (p.y_begin, p.y_end) != (0, p.Y)
+        out = (torch.zeros if partial else torch.empty)(shape, dtype=feats.dtype, device=feats.device)
+        with torch.cuda.device(feats.device):
+            stream = torch.cuda.current_stream().cuda_stream
+            rc = _lib.load().fbev_forward(ctypes.byref(p), out.data_ptr(), None, stream)
+        _lib.check(rc, "fbev_forward")
+        ctx.save_for_backward(*keep)
+        ctx.spec = spec
+        ctx.grid = (p.X, p.Y, p.Z)
+        ctx.epsilon = float(epsilon)
+        ctx.depth_weight_threshold = float(depth_weight_threshold)
+        ctx.in_dtypes = (depth_params.dtype, image_feats.dtype)
+        return out
+
+    @staticmethod
+    def backward(ctx, out_grad):
+        feats, depth, proj, fsize, isize, roi = ctx.saved_tensors
+        spec = ctx.spec
+        grid = torch.tensor(ctx.grid, dtype=torch.int32)  # host tensor: no synchronisation
+        p, keep = make_problem(depth, feats, proj, fsize, isize, roi, grid, spec, ctx.epsilon,
+                               ctx.depth_weight_threshold)
+        flags = 0
+        if ctx.needs_input_grad[1]:
+            flags |= _lib.BWD_FEATS
+        if ctx.needs_input_grad[0]:
+            flags |= _lib.BWD_DEPTH
+        if spec.legacy_depth_grad:
+            flags |= _lib.BWD_LEGACY_DEPTH
+        grad_feats = grad_depth = None
+        if flags & (_lib.BWD_FEATS | _lib.BWD_DEPTH):
+            go = _on(out_grad, feats.device, feats.dtype)
+            lib = _lib.load()
+            if flags & _lib.BWD_FEATS:
+                grad_feats = torch.empty_like(feats)
+            if flags & _lib.BWD_DEPTH:
+                grad_depth = torch.empty_like(depth)
+            nbytes = lib.fbev_backward_scratch_bytes(ctypes.byref(p), flags)
+            scratch = torch.empty(nbytes, dtype=torch.uint8, device=feats.device) if nbytes else None
+            with torch.cuda.device(feats.device):
+                stream = torch.cuda.current_stream().cuda_stream
+                rc = lib.fbev_backward(
+                    ctypes.byref(p), go.data_ptr(),
+                    grad_feats.data_ptr() if grad_feats is not None else None,
+                    grad_depth.data_ptr() if grad_depth is not None else None,
+                    scratch.data_ptr() if scratch is not None else None, nbytes, flags, stream)
+            _lib.check(rc, "fbev_backward")
+            if scratch is not None:
+                scratch.record_stream(torch.cuda.current_stream(feats.device))
+            if grad_depth is not None and grad_depth.dtype != ctx.in_dtypes[0]:
+                grad_depth = grad_depth.to(ctx.in_dtypes[0])
+            if grad_feats is not None and grad_feats.dtype != ctx.in_dtypes[1]:
+                grad_feats = grad_feats.to(ctx.in_dtypes[1])
+        return (grad_depth, grad_feats, None, None, None, None, None, None, None, None, None, None, None, None)
+
+
+def flash_bevpool(image_feats, depth_params, projection_matrices, feature_size, image_size, roi_range, grid_size,
+                  depth_distribution=0, use_shared_memory=True, optimize_z_precompute=True, use_warp_kernel=False,
+                  use_vectorized_load=False, epsilon=1e-6, depth_weight_threshold=1e-6, *, pool=None,
+                  depth_bin_range=None, legacy_depth_grad=False, y_range=None):
+    """Fused BEV pooling; same arguments as the reference wrapper (flash_bevpool.py:139-178).
+
+    Args:
+        image_feats: [B,N,H,W,C] channels-last features (float32 / bfloat16 / float16).
+        depth_params: [B,N,H,W,2] (mean, sigma) for ``depth_distribution`` 0 / 1, or [B,N,H,W,D]
+            probabilities for 2.
+        projection_matrices: [B,N,3,4] or [B,N,4,4].
+        feature_size: [B,N,2] int (h, w).  image_size: [2] int (height, width).
+        roi_range: [6] xmin,xmax,ymin,ymax,zmin,zmax.  grid_size: [3] int grid_x, grid_y, grid_z.
+        depth_distribution: 0 gaussian, 1 laplace, 2 categorical (needs ``depth_bin_range``).
+        pool: "mean" (default for 0/1, the reference's) or "sum" (default for 2).
+        depth_bin_range: (first bin edge, bin width) of the categorical mode.
+        legacy_depth_grad: parametric modes only; reproduce the reference CUDA kernel's depth gradient.
+        y_range: (begin, end) BEV rows to compute; the other rows of the output are zero.
+    Returns:
+        BEV features [B,Y,X,C] in the dtype of ``image_feats``.
+    """
+    spec = DepthSpec(depth_distribution, pool=pool, depth_bin_range=depth_bin_range,
+                     legacy_depth_grad=legacy_depth_grad, y_range=y_range)
+    return FlashBEVPool.apply(depth_params, image_feats, projection_matrices, feature_size, image_size, roi_range,
+                              grid_size, spec, use_shared_memory, optimize_z_precompute, use_warp_kernel,
+                              use_vectorized_load, epsilon, depth_weight_threshold)
+
+
+def debug_indices(image_feats, depth_params, projection_matrices, feature_size, image_size, roi_range, grid_size,
+                  depth_distribution=0, epsilon=1e-6, depth_weight_threshold=1e-6, *, pool=None,
+                  depth_bin_range=None):
+    """Integer decisions of every (b, n, y, x, z) candidate, for bit-exact comparison with a CPU check.
+
+    Returns dict(u0, v0, kbin: int32 [B,N,Y,X,Z]; valid: uint8 [B,N,Y,X,Z]; count: int32 [B,Y,X]).
+    """
+    spec = DepthSpec(depth_distribution, pool=pool, depth_bin_range=depth_bin_range)
+    p, keep = make_problem(depth_params, image_feats, projection_matrices, feature_size, image_size, roi_range,
+                           grid_size, spec, epsilon, depth_weight_threshold)
+    dev = keep[0].device
+    shp = (p.B, p.N, p.Y, p.X, p.Z)
+    u0 = torch.empty(shp, dtype=torch.int32, device=dev)
+    v0 = torch.empty_like(u0)
+    kb = torch.empty_like(u0)
+    va = torch.empty(shp, dtype=torch.uint8, device=dev)
+    cnt = torch.empty((p.B, p.Y, p.X), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.load().fbev_debug_indices(ctypes.byref(p), u0.data_ptr(), v0.data_ptr(), kb.data_ptr(),
+                                            va.data_ptr(), cnt.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc, "fbev_debug_indices")
+    return {"u0": u0, "v0": v0, "kbin": kb, "valid": va, "count": cnt}
+
+
+def forward_with_count(image_feats, depth_params, projection_matrices, feature_size, image_size, roi_range,
+                       grid_size, depth_distribution=0, epsilon=1e-6, depth_weight_threshold=1e-6, *, pool=None,
+                       depth_bin_range=None, y_range=None):
+    """Forward without autograd that also returns the per-cell count of accepted samples [B,Y,X]."""
+    spec = DepthSpec(depth_distribution, pool=pool, depth_bin_range=depth_bin_range, y_range=y_range)
+    p, keep = make_problem(depth_params, image_feats, projection_matrices, feature_size, image_size, roi_range,
+                           grid_size, spec, epsilon, depth_weight_threshold)
+    dev = keep[0].device
+    out = torch.zeros((p.B, p.Y, p.X, p.C), dtype=keep[0].dtype, device=dev)
+    cnt = torch.zeros((p.B, p.Y, p.X), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.load().fbev_forward(ctypes.byref(p), out.data_ptr(), cnt.data_ptr(),
+                                      torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc, "fbev_forward")
+    return out, cnt

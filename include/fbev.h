@@ -1,0 +1,175 @@
+/*
+ * fbev.h - C ABI of the B200 (sm_100a) fused BEV pooling library, libfbev.so.
+ *
+ * The library replaces the native half of the reference operator
+ * flashbevpool.flash_bevpool (yokosyun/FlashBEV): the pybind11 module
+ * flashbevpool_ext (flashbev/flashbevpool/src/flash_bevpool.cpp:79-246) and the
+ * CUDA launchers and kernels behind it (src/flash_bevpool_cuda.cu).  It has no
+ * torch, pybind or C++ types in its interface: plain pointers, sizes, a stream.
+ *
+ * Conventions
+ *  - Every pointer marked "device" is device memory the caller owns; the library
+ *    borrows it for the duration of the asynchronous launch and never allocates
+ *    or frees device memory in these calls.
+ *  - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream).
+ *  - Every function returns an FBEV_* status (0 = success) and never throws,
+ *    aborts or traps.  Launch errors are collected with cudaGetLastError, without
+ *    synchronising.
+ *  - Layouts are the reference's (flash_bevpool.py:28-34,44): features
+ *    [B,N,H,W,C] channels-last, depth [B,N,H,W,Dd], output [B,Y,X,C].
+ */
+#ifndef FBEV_H_
+#define FBEV_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FBEV_ABI_VERSION 1
+
+/* element type of features, depth, output and gradients */
+enum { FBEV_F32 = 0, FBEV_BF16 = 1, FBEV_F16 = 2 };
+
+/* depth model.  0 and 1 are the reference's (flash_bevpool.py:35,
+ * flash_bevpool_cuda.cu:178-184); 2 is the depth-bin lookup into a softmaxed
+ * distribution, depth tensor [B,N,H,W,D], which the reference does not have. */
+enum { FBEV_DEPTH_GAUSSIAN = 0, FBEV_DEPTH_LAPLACE = 1, FBEV_DEPTH_CATEGORICAL = 2 };
+
+/* reduction over cameras and height bins: mean over accepted samples
+ * (reference, flash_bevpool_cuda.cu:212-216) or plain sum */
+enum { FBEV_POOL_MEAN = 0, FBEV_POOL_SUM = 1 };
+
+/* status codes */
+enum {
+  FBEV_OK = 0,
+  FBEV_ERR_NULL = 1,        /* a required pointer is NULL */
+  FBEV_ERR_STRUCT = 2,      /* struct_size does not match this library */
+  FBEV_ERR_SHAPE = 3,       /* a size is non-positive or inconsistent */
+  FBEV_ERR_DTYPE = 4,       /* unknown element type */
+  FBEV_ERR_MODE = 5,        /* unknown depth model / pooling, or bad bin parameters */
+  FBEV_ERR_ALIGN = 6,       /* a pointer is not aligned to its element size */
+  FBEV_ERR_RANGE = 7,       /* sizes exceed what the kernels index (see fbev_strerror) */
+  FBEV_ERR_SCRATCH = 8,     /* scratch buffer missing or too small */
+  FBEV_ERR_LAUNCH = 9,      /* the CUDA runtime refused a launch or a memset */
+  FBEV_ERR_NO_DEVICE = 10   /* no usable sm_100 device / wrong architecture */
+};
+
+/* bits a kernel may OR into the optional device status word */
+enum {
+  FBEV_DEV_BAD_FEATURE_SIZE = 1 /* a feature_size entry is <= 0 or larger than H x W; that camera was skipped */
+};
+
+/* flags of fbev_backward */
+enum {
+  FBEV_BWD_FEATS = 1,        /* compute grad_feats */
+  FBEV_BWD_DEPTH = 2,        /* compute grad_depth */
+  FBEV_BWD_LEGACY_DEPTH = 4  /* parametric modes: reproduce the reference kernel's depth gradient
+                                (same value into mean and sigma, flash_bevpool_cuda.cu:665-674)
+                                instead of the analytic one */
+};
+
+/*
+ * One operator call.  Replaces the 21 positional arguments of
+ * flash_bevpool_forward (flash_bevpool.cpp:79-101) and the 14 of
+ * flash_bevpool_backward (:168-183); both calls share this description.
+ */
+typedef struct FbevProblem {
+  uint32_t struct_size;        /* sizeof(FbevProblem) */
+  int32_t dtype;               /* FBEV_F32 / FBEV_BF16 / FBEV_F16 */
+  int32_t B, N, H, W, C;       /* features [B,N,H,W,C] */
+  int32_t D;                   /* last dimension of the depth tensor: 2 (mean, sigma) or the bin count */
+  int32_t X, Y, Z;             /* grid_size = [X, Y, Z]; output [B,Y,X,C] */
+  int32_t proj_stride;         /* floats per camera matrix: 12 ([B,N,3,4]) or 16 ([B,N,4,4], rows 0-2 used) */
+  int32_t mode;                /* FBEV_DEPTH_* */
+  int32_t pool;                /* FBEV_POOL_* */
+  float epsilon;               /* flash_bevpool.py:23, default 1e-6 */
+  float threshold;             /* depth_weight_threshold, samples with weight < threshold are dropped */
+  float depth_d0, depth_delta; /* categorical: first bin edge and bin width, bin k covers [d0+k*delta, d0+(k+1)*delta) */
+  int32_t y_begin, y_end;      /* BEV rows computed by this call (row sharding); 0, Y for all */
+  float voxel_size[3];         /* used when roi_range is NULL: (max-min)/grid, flash_bevpool.py:62-64 */
+  float voxel_min[3];          /* used when roi_range is NULL: xmin, ymin, zmin, flash_bevpool.py:65-67 */
+  const void* image_feats;     /* device [B,N,H,W,C] */
+  const void* depth;           /* device [B,N,H,W,D] */
+  const float* projection;     /* device [B,N,proj_stride] float32 */
+  const int32_t* feature_size; /* device [B,N,2] (h, w), as the reference reads it in-kernel (:134-135) */
+  const int32_t* image_size;   /* device [2] (image_h, image_w) (:48-49) */
+  const float* roi_range;      /* device [6] xmin,xmax,ymin,ymax,zmin,zmax, or NULL (then voxel_size/voxel_min) */
+  int32_t* status;             /* optional device word for FBEV_DEV_* flags; NULL to ignore */
+} FbevProblem;
+
+/* Forward.  Replaces flash_bevpool_forward (flash_bevpool.cpp:79-166) ->
+ * flash_bevpool() (flash_bevpool_cuda.cu:757-865).  Writes every element of
+ * out[:, y_begin:y_end] (no zero fill needed); valid_count (optional, device
+ * int32 [B,Y,X]) receives the number of accepted samples per cell. */
+int fbev_forward(const FbevProblem* p, void* out, int32_t* valid_count, void* stream);
+
+/* Bytes of float32 scratch fbev_backward needs for this problem and flags:
+ * 0 for float32 tensors (gradients accumulate in place), otherwise room for
+ * float32 copies of the requested gradients. */
+size_t fbev_backward_scratch_bytes(const FbevProblem* p, int flags);
+
+/* Backward.  Replaces flash_bevpool_backward (flash_bevpool.cpp:168-241) ->
+ * flash_bevpool_grad() (flash_bevpool_cuda.cu:867-938).  grad_out device
+ * [B,Y,X,C]; grad_feats device [B,N,H,W,C]; grad_depth device [B,N,H,W,D]; all
+ * of the problem's dtype.  The requested gradients are overwritten (the
+ * library clears them itself).  scratch: device, 256-byte aligned, at least
+ * fbev_backward_scratch_bytes(); may be NULL when that is 0. */
+int fbev_backward(const FbevProblem* p, const void* grad_out, void* grad_feats, void* grad_depth,
+                  void* scratch, size_t scratch_bytes, int flags, void* stream);
+
+/* Integer decisions of every (b, n, y, x, z) candidate, for bit-exact checks:
+ * texel indices after clamping (:147-154), depth bin (categorical, else -1),
+ * final acceptance, each device [B,N,Y,X,Z]; count device int32 [B,Y,X].
+ * Rejected candidates hold -1 / 0.  The reference keeps these values internal. */
+int fbev_debug_indices(const FbevProblem* p, int32_t* u0, int32_t* v0, int32_t* kbin, uint8_t* valid,
+                       int32_t* count, void* stream);
+
+/* Drop-in for the reference launcher
+ *   void flash_bevpool(int total_threads, ...)   flash_bevpool_cuda.cu:757-786
+ * same arguments in the same order (float32, parametric depth, mean pooling),
+ * plus the stream.  The variant flags only chose between reference kernels
+ * with the same result and are ignored.  Addressing follows feature_size, as
+ * in the reference. */
+int fbev_flash_bevpool(int total_threads, int num_channels, int num_cameras, int batch_size,
+                       int num_extrinsic_params, int num_intrinsic_params, int depth_distribution,
+                       int use_shared_memory, int optimize_z_precompute, int use_warp_kernel,
+                       int use_vectorized_load, float epsilon, float depth_weight_threshold,
+                       const float* depth_params, const float* image_feats, const float* projection_matrices,
+                       const int* feature_size, const int* image_size, int grid_x, int grid_y, int grid_z,
+                       float voxel_size_x, float voxel_size_y, float voxel_size_z, float voxel_x_min,
+                       float voxel_y_min, float voxel_z_min, float* out, void* stream);
+
+/* Drop-in for the reference launcher
+ *   void flash_bevpool_grad(int total_threads, ...)   flash_bevpool_cuda.cu:867-889
+ * same arguments in the same order plus the tensor's H and W (the reference
+ * relies on the caller having zero-filled both gradients; this call clears
+ * them, which needs their size) and the stream.  Produces the reference
+ * kernel's depth gradient (FBEV_BWD_LEGACY_DEPTH). */
+int fbev_flash_bevpool_grad(int total_threads, int num_channels, int num_cameras, int batch_size,
+                            int num_extrinsic_params, int num_intrinsic_params, int depth_distribution,
+                            float epsilon, float depth_weight_threshold, const float* out_grad,
+                            const float* depth_params, const float* image_feats,
+                            const float* projection_matrices, const int* feature_size, const int* image_size,
+                            const float* roi_range, int grid_x, int grid_y, int grid_z,
+                            float* depth_params_grad, float* image_feats_grad, int feat_h, int feat_w,
+                            void* stream);
+
+/* Process-wide launch tuning for experiments: cells per tile in x and y,
+ * 16-byte chunks per lane, warps per block; 0 = choose automatically. */
+void fbev_set_tuning(int tile_x, int tile_y, int chunks_per_lane, int warps);
+
+/* Reads `bytes` of device memory `repeats` times with 16-byte loads (a bandwidth
+ * probe for roofline denominators: L2-resident when bytes fits the L2).  sink:
+ * device, >= 4 bytes. */
+int fbev_probe_read(const void* buf, size_t bytes, int repeats, void* sink, void* stream);
+
+const char* fbev_strerror(int status);
+int fbev_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FBEV_H_ */

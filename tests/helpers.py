@@ -1,0 +1,83 @@
+"""Shared pieces of the parity tests: problem construction for the CPU oracle and the CUDA
+operator from the same seeded inputs, and the error measure the tolerances refer to."""
+import glob
+import os
+
+import numpy as np
+import torch
+
+from flashbev_b200 import synth
+from oracle import oracle as O
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+# Tolerances (relative error = max|a-b| / max|b| per tensor):
+TOL_F32 = 1e-5       # float32 kernels vs the float32/float64 oracle
+TOL_LOWP = 2e-3      # bfloat16 / float16 kernels vs the oracle on the same rounded inputs
+TOL_DENSE = 5e-5     # oracle vs the reference's dense PyTorch path (grid_sample re-normalises coordinates)
+
+
+def rel_err(a, b):
+    a = np.asarray(a, dtype=np.float64)
+    b = np.asarray(b, dtype=np.float64)
+    denom = np.abs(b).max()
+    return float(np.abs(a - b).max() / (denom if denom > 0 else 1.0))
+
+
+MODES = {"gaussian": O.MODE_GAUSSIAN, "laplace": O.MODE_LAPLACE, "categorical": O.MODE_CATEGORICAL}
+
+
+def oracle_problem(inp, w, mode, threshold=0.0, pool=None, y_range=None, eps=1e-6):
+    """Oracle problem from operator inputs (tensors of any float dtype are widened exactly)."""
+    return O.Problem(
+        feats=inp["image_feats"].float().cpu().numpy(), depth=inp["depth_params"].float().cpu().numpy(),
+        proj=inp["projection_matrices"].float().cpu().numpy(),
+        image_size=tuple(int(v) for v in inp["image_size"].tolist()),
+        roi=[float(v) for v in inp["roi_range"].tolist()], grid=tuple(int(v) for v in inp["grid_size"].tolist()),
+        mode=MODES[mode], pool=None if pool is None else (O.POOL_SUM if pool == "sum" else O.POOL_MEAN),
+        eps=eps, threshold=threshold, d0=w.d0, delta=w.delta,
+        feature_size=inp["feature_size"].cpu().numpy(), y_range=y_range)
+
+
+def op_kwargs(w, mode, threshold=0.0, pool=None, y_range=None):
+    kw = dict(depth_distribution={"gaussian": 0, "laplace": 1, "categorical": 2}[mode],
+              depth_weight_threshold=threshold, epsilon=1e-6)
+    if mode == "categorical":
+        kw["depth_bin_range"] = (w.d0, w.delta)
+    if pool is not None:
+        kw["pool"] = pool
+    if y_range is not None:
+        kw["y_range"] = y_range
+    return kw
+
+
+def to_device(inp, device):
+    return {k: v.to(device) for k, v in inp.items()}
+
+
+def inputs_for(w, mode):
+    return synth.make_inputs(w, "categorical" if mode == "categorical" else "parametric")
+
+
+def golden_files():
+    return sorted(glob.glob(os.path.join(GOLDEN, "*.npz")))
+
+
+def golden_problem(g):
+    return O.Problem(g["feats"], g["depth"], g["proj"], tuple(int(v) for v in g["image_size"]),
+                     [float(v) for v in g["roi"]], tuple(int(v) for v in g["grid"]),
+                     mode=O.MODE_LAPLACE if int(g["laplace"]) else O.MODE_GAUSSIAN, threshold=float(g["threshold"]))
+
+
+def golden_inputs(g, device):
+    B, N, H, W, _ = g["feats"].shape
+    return dict(
+        image_feats=torch.from_numpy(g["feats"]).to(device), depth_params=torch.from_numpy(g["depth"]).to(device),
+        projection_matrices=torch.from_numpy(g["proj"]).to(device),
+        feature_size=torch.tensor([[H, W]], dtype=torch.int32).repeat(B * N, 1).view(B, N, 2).to(device),
+        image_size=torch.from_numpy(g["image_size"]).to(device), roi_range=torch.from_numpy(g["roi"]).to(device),
+        grid_size=torch.from_numpy(g["grid"]).to(device))
+
+
+SMALL = synth.Workload("small", B=2, N=6, C=16, H=8, W=22, D=24, X=40, Y=36, Z=5, xy_extent=30.0,
+                       d0=1.0, delta=1.5, dtype="fp32", seed=21, jitter=True)

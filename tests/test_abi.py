@@ -1,0 +1,121 @@
+"""CPU checks of the C ABI: libfbev.so loads, exports every symbol include/fbev.h declares, and
+its host-side validation returns status codes (no kernel is launched here)."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+from flashbev_b200 import _lib, build
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def header_functions():
+    text = open(os.path.join(ROOT, "include", "fbev.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(fbev_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_header_and_binding_list_the_same_functions():
+    assert header_functions() == sorted(_lib.EXPORTS)
+
+
+def test_library_builds_and_exports_every_symbol():
+    build.build()
+    lib = ctypes.CDLL(build.LIB_PATH)
+    for name in header_functions():
+        assert hasattr(lib, name), name
+    assert _lib.load().fbev_version() == 1
+
+
+def test_struct_layout_matches_the_header():
+    # uint32 + 19 int32/float words, 6 floats, 7 pointers; no padding on LP64
+    assert ctypes.sizeof(_lib.FbevProblem) == 4 * 20 + 4 * 6 + 8 * 7
+
+
+def _problem():
+    p = _lib.FbevProblem()
+    p.struct_size = ctypes.sizeof(_lib.FbevProblem)
+    p.dtype = _lib.F32
+    p.B, p.N, p.H, p.W, p.C, p.D = 1, 2, 4, 4, 8, 2
+    p.X, p.Y, p.Z = 8, 8, 2
+    p.proj_stride = 12
+    p.mode, p.pool = _lib.DEPTH_LAPLACE, _lib.POOL_MEAN
+    p.y_begin, p.y_end = 0, 8
+    for f in ("image_feats", "depth", "projection", "feature_size", "image_size"):
+        setattr(p, f, 256)  # never dereferenced: validation fails first in every case below
+    return p
+
+
+def test_validation_status_codes():
+    lib = _lib.load()
+    fwd = lambda p: lib.fbev_forward(ctypes.byref(p), 256, None, None)
+    assert lib.fbev_forward(None, 256, None, None) == 1          # FBEV_ERR_NULL
+    p = _problem(); p.struct_size = 8
+    assert fwd(p) == 2                                            # FBEV_ERR_STRUCT
+    p = _problem(); p.C = 0
+    assert fwd(p) == 3                                            # FBEV_ERR_SHAPE
+    p = _problem(); p.proj_stride = 9
+    assert fwd(p) == 3
+    p = _problem(); p.y_end = 9
+    assert fwd(p) == 3
+    p = _problem(); p.D = 5                                       # parametric depth must have 2 channels
+    assert fwd(p) == 3
+    p = _problem(); p.dtype = 7
+    assert fwd(p) == 4                                            # FBEV_ERR_DTYPE
+    p = _problem(); p.mode = 3
+    assert fwd(p) == 5                                            # FBEV_ERR_MODE
+    p = _problem(); p.mode = _lib.DEPTH_CATEGORICAL; p.depth_delta = 0.0
+    assert fwd(p) == 5
+    p = _problem(); p.image_feats = 258
+    assert fwd(p) == 6                                            # FBEV_ERR_ALIGN
+    p = _problem(); p.B = 1 << 20; p.H = 1 << 10; p.W = 1 << 10
+    assert fwd(p) == 7                                            # FBEV_ERR_RANGE
+    p = _problem(); p.image_feats = None
+    assert fwd(p) == 1
+    p = _problem()
+    assert lib.fbev_forward(ctypes.byref(p), None, None, None) == 1
+    assert _lib.strerror(99) == "unknown status"
+    for code in range(0, 11):
+        assert _lib.strerror(code) != "unknown status"
+
+
+def test_backward_scratch_size_and_checks():
+    lib = _lib.load()
+    p = _problem()
+    assert lib.fbev_backward_scratch_bytes(ctypes.byref(p), 3) == 0            # float32: in place
+    p.dtype = _lib.BF16
+    tex = 1 * 2 * 4 * 4
+    assert lib.fbev_backward_scratch_bytes(ctypes.byref(p), 3) == tex * 8 * 4 + tex * 2 * 4
+    assert lib.fbev_backward_scratch_bytes(ctypes.byref(p), 1) == tex * 8 * 4
+    # 16-bit gradients without scratch are refused before anything is launched
+    assert lib.fbev_backward(ctypes.byref(p), 256, 256, 256, None, 0, 3, None) == 8   # FBEV_ERR_SCRATCH
+    assert lib.fbev_backward(ctypes.byref(p), 256, 256, 256, None, 0, 0, None) == 0   # nothing requested
+
+
+def test_operator_refuses_cpu_tensors():
+    from flashbev_b200 import flash_bevpool
+    from flashbev_b200 import synth
+    inp = synth.make_inputs(synth.Workload("t", 1, 2, 8, 4, 4, 4, 8, 8, 2, 10.0, dtype="fp32"), "parametric")
+    with pytest.raises(RuntimeError, match="CUDA"):
+        flash_bevpool(**inp, depth_distribution=1)
+
+
+def test_depth_spec_rules():
+    from flashbev_b200 import DepthSpec
+    assert int(DepthSpec(1)) == 1 and DepthSpec(1).pool == "mean"
+    s = DepthSpec(2, depth_bin_range=(1.0, 0.5))
+    assert s.pool == "sum" and (s.d0, s.delta) == (1.0, 0.5)
+    with pytest.raises(ValueError):
+        DepthSpec(2)
+    with pytest.raises(ValueError):
+        DepthSpec(3)
+    with pytest.raises(ValueError):
+        DepthSpec(0, pool="max")
+
+
+def test_drop_in_package_name_exports_the_reference_names():
+    import flashbevpool
+    assert sorted(flashbevpool.__all__) == ["FlashBEVPool", "SamplingVT", "flash_bevpool"]

@@ -1,0 +1,364 @@
+"""GPU parity tests: the CUDA operator (through ctypes -> the C ABI of libfbev.so) against the
+CPU oracle on the same seeded inputs, against the golden fixtures of the reference's dense
+path, and, where a built copy exists, against the reference's own CUDA kernels.
+
+Bars: integer outputs bit-exact; float32 within 1e-5 and bfloat16/float16 within 2e-3, both as
+max|a-b| / max|b| per tensor.
+"""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from flashbev_b200 import _lib, debug_indices, flash_bevpool, forward_with_count, synth
+from flashbev_b200.flash_bevpool import status_word
+from oracle import oracle as O
+from tests.helpers import (SMALL, TOL_DENSE, TOL_F32, TOL_LOWP, golden_files, golden_inputs, golden_problem,
+                           inputs_for, op_kwargs, oracle_problem, rel_err, to_device)
+
+pytestmark = pytest.mark.gpu
+
+CFG1 = synth.workload("cfg1")
+CFG2 = synth.workload("cfg2")
+CFG3S = synth.workload("cfg3", B=2, X=96, Y=80)          # training shapes, reduced grid
+CFG5S = synth.workload("cfg5", X=96, Y=64, Z=16)         # 256 channels, 32x88 map, reduced grid
+
+
+def run_case(w, mode, device, threshold=0.0, pool=None, tol=None, dtype=None, y_range=None):
+    inp = synth.make_inputs(w, "categorical" if mode == "categorical" else "parametric", dtype=dtype)
+    p = oracle_problem(inp, w, mode, threshold=threshold, pool=pool, y_range=y_range)
+    ref, ref_cnt = O.forward(p, with_count=True)
+    out, cnt = forward_with_count(**to_device(inp, device), **op_kwargs(w, mode, threshold, pool, y_range))
+    torch.cuda.synchronize()
+    lowp = (dtype or w.dtype) != "fp32"
+    tol = tol if tol is not None else (TOL_LOWP if lowp else TOL_F32)
+    assert out.dtype == inp["image_feats"].dtype
+    yb, ye = y_range if y_range else (0, w.Y)
+    assert np.array_equal(cnt.cpu().numpy()[:, yb:ye], ref_cnt[:, yb:ye]), "per-cell sample counts differ"
+    err = rel_err(out.float().cpu().numpy(), ref)
+    assert err < tol, f"{w.name} {mode}: rel err {err:.3e} >= {tol}"
+    return err
+
+
+@pytest.mark.parametrize("mode", ["gaussian", "laplace", "categorical"])
+@pytest.mark.parametrize("threshold", [0.0, 1e-3])
+def test_forward_small_fp32(cuda_device, mode, threshold):
+    run_case(SMALL, mode, cuda_device, threshold=threshold)
+
+
+@pytest.mark.parametrize("pool", ["mean", "sum"])
+@pytest.mark.parametrize("mode", ["laplace", "categorical"])
+def test_forward_pooling_modes(cuda_device, mode, pool):
+    run_case(SMALL, mode, cuda_device, pool=pool)
+
+
+@pytest.mark.parametrize("mode", ["laplace", "categorical"])
+def test_forward_cfg1_fp32(cuda_device, mode):
+    run_case(CFG1, mode, cuda_device)
+
+
+@pytest.mark.parametrize("Z", [4, 8, 12, 16])
+def test_forward_cfg2_bf16_inference_sweep(cuda_device, Z):
+    run_case(synth.workload("cfg2", Z=Z), "categorical", cuda_device)
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "fp16"])
+def test_forward_cfg2_other_dtypes(cuda_device, dtype):
+    run_case(CFG2, "categorical", cuda_device, dtype=dtype)
+    run_case(CFG2, "laplace", cuda_device, dtype=dtype)
+
+
+def test_forward_training_and_wide_channel_shapes(cuda_device):
+    run_case(CFG3S, "categorical", cuda_device)
+    run_case(CFG3S, "gaussian", cuda_device)
+    run_case(CFG5S, "categorical", cuda_device)
+
+
+@pytest.mark.parametrize("C,dtype", [(7, "fp32"), (10, "bf16"), (3, "fp16"), (1, "fp32"), (4, "fp32"), (8, "bf16"),
+                                     (24, "bf16"), (48, "fp32"), (160, "fp32"), (264, "bf16"), (1040, "bf16")])
+def test_forward_channel_counts(cuda_device, C, dtype):
+    """Chunked layouts of several widths and the scalar path (channel rows that are not 16-byte multiples,
+    more than 128 chunks)."""
+    w = synth.Workload("chan", B=1, N=3, C=C, H=6, W=10, D=12, X=33, Y=17, Z=3, xy_extent=20.0, d0=1.0, delta=2.0,
+                       dtype=dtype, seed=31)
+    run_case(w, "categorical", cuda_device)
+    run_case(w, "laplace", cuda_device, pool="mean")
+
+
+def test_forward_many_height_bins_takes_several_passes(cuda_device):
+    w = synth.Workload("tall", B=1, N=6, C=16, H=8, W=22, D=24, X=30, Y=30, Z=40, xy_extent=30.0, d0=1.0, delta=1.5,
+                       dtype="fp32", seed=32)
+    run_case(w, "categorical", cuda_device, pool="mean")
+    run_case(w, "laplace", cuda_device)
+
+
+def test_forward_row_ranges_compose(cuda_device):
+    w = CFG1
+    inp = inputs_for(w, "categorical")
+    dev = to_device(inp, cuda_device)
+    full = flash_bevpool(**dev, **op_kwargs(w, "categorical"))
+    parts = [flash_bevpool(**dev, **op_kwargs(w, "categorical", y_range=r)) for r in ((0, 37), (37, 38), (38, w.Y))]
+    assert torch.equal(parts[0] + parts[1] + parts[2], full)
+    assert torch.count_nonzero(parts[1][:, :37]) == 0 and torch.count_nonzero(parts[1][:, 38:]) == 0
+    run_case(w, "categorical", cuda_device, y_range=(37, 90))
+
+
+def test_forward_batch_samples_are_independent(cuda_device):
+    """Batch sharding property at the multi-GPU configuration's shapes: a slice of the batch run alone
+    equals the same rows of the whole batch, bit for bit."""
+    w = synth.workload("cfg4", B=6)
+    inp = synth.make_inputs(w, "categorical")
+    dev = to_device(inp, cuda_device)
+    kw = op_kwargs(w, "categorical")
+    full = flash_bevpool(**dev, **kw)
+    part = synth.make_inputs(w, "categorical", batch_slice=(2, 5))
+    out = flash_bevpool(**to_device(part, cuda_device), **kw)
+    assert torch.equal(out, full[2:5])
+    assert not torch.equal(full[0], full[1])  # per-sample rigs differ
+
+
+def test_forward_is_linear_in_features_at_full_size(cuda_device):
+    w = CFG2
+    inp = to_device(synth.make_inputs(w, "categorical", dtype="fp32"), cuda_device)
+    kw = op_kwargs(w, "categorical")
+    a = flash_bevpool(**inp, **kw)
+    other = dict(inp)
+    other["image_feats"] = torch.flip(inp["image_feats"], dims=[-1]) * 0.5
+    b = flash_bevpool(**other, **kw)
+    both = dict(inp)
+    both["image_feats"] = inp["image_feats"] + other["image_feats"]
+    c = flash_bevpool(**both, **kw)
+    assert rel_err((a + b).cpu().numpy(), c.cpu().numpy()) < TOL_F32
+
+
+@pytest.mark.parametrize("mode,wname", [("categorical", "cfg2"), ("laplace", "cfg2"), ("categorical", "cfg1")])
+def test_integer_outputs_are_bit_exact(cuda_device, mode, wname):
+    w = synth.workload(wname)
+    inp = inputs_for(w, mode)
+    ref = O.indices(oracle_problem(inp, w, mode))
+    kw = op_kwargs(w, mode)
+    got = debug_indices(**to_device(inp, cuda_device), **kw)
+    for k in ("u0", "v0", "kbin", "valid", "count"):
+        assert np.array_equal(got[k].cpu().numpy(), ref[k]), k
+    assert ref["valid"].sum() > 100000
+
+
+def test_integer_outputs_nuscenes_rig_and_jitter(cuda_device):
+    for path in golden_files():
+        g = np.load(path)
+        if int(g["laplace"]) != 1:
+            continue
+        ref = O.indices(golden_problem(g))
+        got = debug_indices(**golden_inputs(g, cuda_device), depth_distribution=1,
+                            depth_weight_threshold=float(g["threshold"]))
+        mism = sum(int((got[k].cpu().numpy() != ref[k]).sum()) for k in ("u0", "v0", "valid", "count"))
+        # the laplace weight goes through expf, whose last bit may differ between libm and CUDA: only a
+        # sample whose weight sits exactly on the threshold could flip, and none does in these fixtures
+        assert mism == 0, path
+
+
+@pytest.mark.parametrize("path", golden_files(), ids=lambda p: p.split("/")[-1][:-4])
+def test_kernel_matches_reference_dense_path_fixtures(cuda_device, path):
+    g = np.load(path)
+    inp = golden_inputs(g, cuda_device)
+    inp["image_feats"].requires_grad_(True)
+    inp["depth_params"].requires_grad_(True)
+    out = flash_bevpool(**inp, depth_distribution=int(g["laplace"]), depth_weight_threshold=float(g["threshold"]))
+    out.backward(torch.from_numpy(g["grad_out"]).to(cuda_device))
+    assert rel_err(out.detach().cpu().numpy(), g["out"]) < TOL_DENSE
+    assert rel_err(inp["image_feats"].grad.cpu().numpy(), g["d_feats"]) < TOL_DENSE
+    assert rel_err(inp["depth_params"].grad.cpu().numpy(), g["d_depth"]) < TOL_DENSE
+    diff = out.detach().cpu().numpy().astype(np.float64) - g["out"]
+    assert (diff ** 2).mean() < 1e-6 and np.abs(diff).mean() < 1e-6     # tools/profile_differences.py:75-77
+
+
+def backward_case(w, mode, device, pool=None, dtype=None, legacy=False, threshold=0.0):
+    inp = synth.make_inputs(w, "categorical" if mode == "categorical" else "parametric", dtype=dtype)
+    go = synth.upstream_grad(w)
+    if (dtype or w.dtype) != "fp32":
+        go = go.to(inp["image_feats"].dtype)
+    p = oracle_problem(inp, w, mode, pool=pool, threshold=threshold)
+    rf, rd = O.backward(p, go.float().numpy(), dtype=np.float64, legacy_depth_grad=legacy)
+    dev = to_device(inp, device)
+    dev["image_feats"].requires_grad_(True)
+    dev["depth_params"].requires_grad_(True)
+    out = flash_bevpool(**dev, **op_kwargs(w, mode, threshold, pool), legacy_depth_grad=legacy)
+    out.backward(go.to(device))
+    torch.cuda.synchronize()
+    tol = TOL_F32 if (dtype or w.dtype) == "fp32" else TOL_LOWP
+    gf, gd = dev["image_feats"].grad, dev["depth_params"].grad
+    assert gf.dtype == dev["image_feats"].dtype and gd.dtype == dev["depth_params"].dtype
+    ef, ed = rel_err(gf.float().cpu().numpy(), rf), rel_err(gd.float().cpu().numpy(), rd)
+    assert ef < tol and ed < tol, f"{w.name} {mode}: d_feats {ef:.3e} d_depth {ed:.3e} tol {tol}"
+
+
+@pytest.mark.parametrize("mode", ["gaussian", "laplace", "categorical"])
+@pytest.mark.parametrize("pool", ["mean", "sum"])
+def test_backward_small_fp32(cuda_device, mode, pool):
+    backward_case(SMALL, mode, cuda_device, pool=pool)
+
+
+def test_backward_legacy_depth_gradient(cuda_device):
+    backward_case(SMALL, "laplace", cuda_device, legacy=True)
+    backward_case(SMALL, "gaussian", cuda_device, legacy=True, threshold=1e-3)
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "fp16"])
+def test_backward_low_precision_uses_scratch(cuda_device, dtype):
+    backward_case(CFG3S, "categorical", cuda_device, dtype=dtype)
+    backward_case(SMALL, "laplace", cuda_device, dtype=dtype)
+
+
+def test_backward_training_shapes_fp32(cuda_device):
+    backward_case(CFG3S, "categorical", cuda_device)
+    backward_case(CFG3S, "laplace", cuda_device)
+    backward_case(CFG5S, "categorical", cuda_device, dtype="fp32")
+
+
+def test_backward_many_height_bins_mean_pool(cuda_device):
+    w = synth.Workload("tall", B=1, N=6, C=16, H=8, W=22, D=24, X=30, Y=30, Z=40, xy_extent=30.0, d0=1.0, delta=1.5,
+                       dtype="fp32", seed=32)
+    backward_case(w, "categorical", cuda_device, pool="mean")
+    backward_case(w, "gaussian", cuda_device)
+
+
+def test_backward_only_requested_gradients(cuda_device):
+    w = SMALL
+    inp = to_device(inputs_for(w, "categorical"), cuda_device)
+    go = synth.upstream_grad(w).to(cuda_device)
+    inp["image_feats"].requires_grad_(True)
+    flash_bevpool(**inp, **op_kwargs(w, "categorical")).backward(go)
+    assert inp["image_feats"].grad is not None and inp["depth_params"].grad is None
+    only_f = inp["image_feats"].grad.clone()
+    inp["image_feats"].grad = None
+    inp["depth_params"].requires_grad_(True)
+    flash_bevpool(**inp, **op_kwargs(w, "categorical")).backward(go)
+    assert rel_err(inp["image_feats"].grad.cpu().numpy(), only_f.cpu().numpy()) < TOL_F32
+
+
+def test_edge_cases(cuda_device):
+    # one camera, one height bin, 1x1 grid
+    w = synth.Workload("one", B=1, N=1, C=4, H=4, W=6, D=8, X=1, Y=1, Z=1, xy_extent=8.0, z_range=(0.0, 2.0),
+                       d0=0.5, delta=4.0, dtype="fp32", seed=41)
+    run_case(w, "categorical", cuda_device)
+    # nothing accepted: a threshold above every weight -> zeros, zero counts, zero gradients
+    inp = to_device(inputs_for(SMALL, "laplace"), cuda_device)
+    inp["image_feats"].requires_grad_(True)
+    inp["depth_params"].requires_grad_(True)
+    out = flash_bevpool(**inp, depth_distribution=1, depth_weight_threshold=1e9)
+    assert torch.count_nonzero(out) == 0
+    out.backward(torch.ones_like(out))
+    assert torch.count_nonzero(inp["image_feats"].grad) == 0 and torch.count_nonzero(inp["depth_params"].grad) == 0
+    # every cell behind or outside all cameras (grid far below the rig looking at a shifted roi)
+    w2 = synth.Workload("behind", B=1, N=1, C=8, H=4, W=6, D=8, X=9, Y=7, Z=2, xy_extent=5.0, dtype="fp32", seed=42)
+    inp2 = to_device(inputs_for(w2, "categorical"), cuda_device)
+    inp2["roi_range"] = torch.tensor([-60.0, -50.0, -5.0, 5.0, -5.0, 3.0], device=cuda_device)
+    out2, cnt2 = forward_with_count(**inp2, **op_kwargs(w2, "categorical"))
+    assert torch.count_nonzero(out2) == 0 and torch.count_nonzero(cnt2) == 0
+    # 4x4 projection matrices: rows 0-2 are used (the reference's kernel-only benchmark passes [B,N,4,4])
+    inp3 = inputs_for(SMALL, "laplace")
+    p44 = torch.zeros(SMALL.B, SMALL.N, 4, 4)
+    p44[:, :, :3] = inp3["projection_matrices"]
+    p44[:, :, 3, 3] = 1.0
+    a = flash_bevpool(**to_device(inp3, cuda_device), depth_distribution=1)
+    inp3["projection_matrices"] = p44
+    b = flash_bevpool(**to_device(inp3, cuda_device), depth_distribution=1)
+    assert torch.equal(a, b)
+
+
+def test_bad_feature_size_sets_the_status_word_and_skips_the_camera(cuda_device):
+    inp = to_device(inputs_for(SMALL, "laplace"), cuda_device)
+    word = status_word(cuda_device)
+    word.zero_()
+    fs = inp["feature_size"].clone()
+    fs[0, 1] = torch.tensor([SMALL.H * 4, SMALL.W], dtype=torch.int32)   # larger than the tensor
+    inp["feature_size"] = fs
+    out = flash_bevpool(**inp, depth_distribution=1)
+    torch.cuda.synchronize()
+    assert int(word.item()) & _lib.DEV_BAD_FEATURE_SIZE
+    assert torch.isfinite(out).all()
+    word.zero_()
+
+
+def test_flat_launcher_entry_points(cuda_device):
+    """fbev_flash_bevpool / fbev_flash_bevpool_grad take the reference launchers' argument lists."""
+    w = SMALL
+    inp = to_device(inputs_for(w, "laplace"), cuda_device)
+    lib = _lib.load()
+    roi = [float(v) for v in inp["roi_range"].tolist()]
+    f32 = np.float32
+    vs = [float((f32(roi[2 * i + 1]) - f32(roi[2 * i])) / f32(g)) for i, g in enumerate(w.grid)]
+    out = torch.empty(w.B, w.Y, w.X, w.C, device=cuda_device)
+    rc = lib.fbev_flash_bevpool(out.numel(), w.C, w.N, w.B, 12, 12, 1, 0, 0, 0, 0, 1e-6, 0.0,
+                                inp["depth_params"].data_ptr(), inp["image_feats"].data_ptr(),
+                                inp["projection_matrices"].data_ptr(), inp["feature_size"].data_ptr(),
+                                inp["image_size"].data_ptr(), w.X, w.Y, w.Z, vs[0], vs[1], vs[2], roi[0], roi[2],
+                                roi[4], out.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    ref = flash_bevpool(**inp, depth_distribution=1, depth_weight_threshold=0.0)
+    assert torch.equal(out, ref)
+    go = synth.upstream_grad(w).to(cuda_device)
+    gd = torch.empty_like(inp["depth_params"])
+    gf = torch.empty_like(inp["image_feats"])
+    rc = lib.fbev_flash_bevpool_grad(out.numel(), w.C, w.N, w.B, 12, 12, 1, 1e-6, 0.0, go.data_ptr(),
+                                     inp["depth_params"].data_ptr(), inp["image_feats"].data_ptr(),
+                                     inp["projection_matrices"].data_ptr(), inp["feature_size"].data_ptr(),
+                                     inp["image_size"].data_ptr(), inp["roi_range"].data_ptr(), w.X, w.Y, w.Z,
+                                     gd.data_ptr(), gf.data_ptr(), w.H, w.W, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    p = oracle_problem(inputs_for(w, "laplace"), w, "laplace")
+    rf, rd = O.backward(p, go.cpu().numpy(), dtype=np.float64, legacy_depth_grad=True)
+    assert rel_err(gf.cpu().numpy(), rf) < TOL_F32 and rel_err(gd.cpu().numpy(), rd) < TOL_F32
+
+
+# ---- the reference's own CUDA kernels, built from its checkout (oracle/Makefile, target `ref`) ----
+REF_LIB = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref",
+                       "libflashbev_ref.so")
+
+
+@pytest.mark.skipif(not os.path.exists(REF_LIB), reason="reference CUDA library was not built")
+@pytest.mark.parametrize("dist", [0, 1])
+@pytest.mark.parametrize("zpre", [0, 1])
+def test_against_reference_cuda_kernels(cuda_device, dist, zpre):
+    ref = ctypes.CDLL(REF_LIB)
+    vp, i32, f32c = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+    ref.flashbev_ref_forward.argtypes = [i32] * 7 + [f32c, f32c] + [vp] * 5 + [i32] * 3 + [f32c] * 6 + [vp]
+    ref.flashbev_ref_backward.argtypes = [i32] * 5 + [f32c, f32c] + [vp] * 7 + [i32] * 3 + [vp, vp]
+    w = synth.workload("cfg1")
+    mode = "laplace" if dist == 1 else "gaussian"
+    inp = to_device(inputs_for(w, mode), cuda_device)
+    roi = [float(v) for v in inp["roi_range"].tolist()]
+    f32 = np.float32
+    vs = [float((f32(roi[2 * i + 1]) - f32(roi[2 * i])) / f32(g)) for i, g in enumerate(w.grid)]
+    out_ref = torch.zeros(w.B, w.Y, w.X, w.C, device=cuda_device)
+    torch.cuda.synchronize()
+    rc = ref.flashbev_ref_forward(out_ref.numel(), w.C, w.N, w.B, dist, 0, zpre, 1e-6, 1e-6,
+                                  inp["depth_params"].data_ptr(), inp["image_feats"].data_ptr(),
+                                  inp["projection_matrices"].data_ptr(), inp["feature_size"].data_ptr(),
+                                  inp["image_size"].data_ptr(), w.X, w.Y, w.Z, vs[0], vs[1], vs[2], roi[0], roi[2],
+                                  roi[4], out_ref.data_ptr())
+    assert rc == 0
+    torch.cuda.synchronize()
+    out = flash_bevpool(**inp, depth_distribution=dist, depth_weight_threshold=1e-6)
+    err = rel_err(out.cpu().numpy(), out_ref.cpu().numpy())
+    assert err < TOL_F32, f"forward vs reference kernel: {err:.3e}"
+    go = synth.upstream_grad(w).to(cuda_device)
+    gd_ref = torch.zeros_like(inp["depth_params"])
+    gf_ref = torch.zeros_like(inp["image_feats"])
+    torch.cuda.synchronize()
+    rc = ref.flashbev_ref_backward(out_ref.numel(), w.C, w.N, w.B, dist, 1e-6, 1e-6, go.data_ptr(),
+                                   inp["depth_params"].data_ptr(), inp["image_feats"].data_ptr(),
+                                   inp["projection_matrices"].data_ptr(), inp["feature_size"].data_ptr(),
+                                   inp["image_size"].data_ptr(), inp["roi_range"].data_ptr(), w.X, w.Y, w.Z,
+                                   gd_ref.data_ptr(), gf_ref.data_ptr())
+    assert rc == 0
+    torch.cuda.synchronize()
+    inp["image_feats"].requires_grad_(True)
+    inp["depth_params"].requires_grad_(True)
+    out = flash_bevpool(**inp, depth_distribution=dist, depth_weight_threshold=1e-6, legacy_depth_grad=True)
+    out.backward(go)
+    ef = rel_err(inp["image_feats"].grad.cpu().numpy(), gf_ref.cpu().numpy())
+    ed = rel_err(inp["depth_params"].grad.cpu().numpy(), gd_ref.cpu().numpy())
+    assert ef < TOL_F32 and ed < TOL_F32, f"backward vs reference kernel: feats {ef:.3e} depth {ed:.3e}"
