@@ -15,6 +15,7 @@ DEPTH_GAUSSIAN, DEPTH_LAPLACE, DEPTH_CATEGORICAL = 0, 1, 2
 POOL_MEAN, POOL_SUM = 0, 1
 BWD_FEATS, BWD_DEPTH, BWD_LEGACY_DEPTH = 1, 2, 4
 DEV_BAD_FEATURE_SIZE = 1
+WORKSPACE_BYTES = 16
 
 # every symbol include/fbev.h declares
 EXPORTS = (
@@ -29,6 +30,7 @@ class FbevProblem(ctypes.Structure):
     _fields_ = [
         ("struct_size", ctypes.c_uint32),
         ("dtype", ctypes.c_int32),
+        ("out_dtype", ctypes.c_int32),
         ("B", ctypes.c_int32), ("N", ctypes.c_int32), ("H", ctypes.c_int32), ("W", ctypes.c_int32),
         ("C", ctypes.c_int32),
         ("D", ctypes.c_int32),
@@ -49,6 +51,7 @@ class FbevProblem(ctypes.Structure):
         ("image_size", ctypes.c_void_p),
         ("roi_range", ctypes.c_void_p),
         ("status", ctypes.c_void_p),
+        ("workspace", ctypes.c_void_p),
     ]
 
 

@@ -42,6 +42,8 @@ struct Dev {
   int CPW;    // cells a warp works on at once = 32 / GL
   int cap;    // sample records per cell per pass
   int flags;  // FBEV_BWD_*
+  int out_f32;        // output / upstream gradient are float32 although the features are 16-bit
+  unsigned* sched;    // tile scheduler words {next tile, blocks done}, or null for one tile per block
 };
 
 __device__ __forceinline__ float to_float(float v) { return v; }

@@ -46,7 +46,8 @@ class DepthSpec(int):
     """
 
     def __new__(cls, mode: int, pool: Optional[str] = None, depth_bin_range: Optional[Tuple[float, float]] = None,
-                legacy_depth_grad: bool = False, y_range: Optional[Tuple[int, int]] = None):
+                legacy_depth_grad: bool = False, y_range: Optional[Tuple[int, int]] = None,
+                out_dtype: Optional[torch.dtype] = None):
         mode = int(mode)
         if mode not in (0, 1, 2):
             raise ValueError(f"depth_distribution must be 0 (gaussian), 1 (laplace) or 2 (categorical), got {mode}")
@@ -67,11 +68,15 @@ class DepthSpec(int):
         self.d0, self.delta = d0, delta
         self.legacy_depth_grad = bool(legacy_depth_grad)
         self.y_range = None if y_range is None else (int(y_range[0]), int(y_range[1]))
+        if out_dtype not in (None, torch.float32):
+            raise ValueError("out_dtype must be None (the feature dtype) or torch.float32")
+        self.out_dtype = out_dtype
         return self
 
 
-# host copies of small device tensors, keyed by the tensor object and its version
-_host_cache: "weakref.WeakKeyDictionary[torch.Tensor, tuple]" = weakref.WeakKeyDictionary()
+# host copies of small device tensors, keyed by the identity of the tensor object; the weak
+# reference drops the entry when the tensor dies, the version catches in-place changes
+_host_cache = {}
 
 
 def _host_values(t: torch.Tensor) -> tuple:
@@ -79,11 +84,12 @@ def _host_values(t: torch.Tensor) -> tuple:
     (tensor, version) is seen; the reference synchronises on every call (flash_bevpool.py:58-67)."""
     if t.device.type == "cpu":
         return tuple(t.tolist())
-    hit = _host_cache.get(t)
-    if hit is not None and hit[0] == t._version:
-        return hit[1]
+    key = id(t)
+    hit = _host_cache.get(key)
+    if hit is not None and hit[0]() is t and hit[1] == t._version:
+        return hit[2]
     vals = tuple(t.tolist())
-    _host_cache[t] = (t._version, vals)
+    _host_cache[key] = (weakref.ref(t, lambda _r, k=key: _host_cache.pop(k, None)), t._version, vals)
     return vals
 
 
@@ -97,6 +103,20 @@ def status_word(device: torch.device) -> torch.Tensor:
     if w is None:
         w = torch.zeros(1, dtype=torch.int32, device=device)
         _status_words[key] = w
+    return w
+
+
+_workspaces = {}
+
+
+def workspace(device: torch.device, stream_ptr: int) -> torch.Tensor:
+    """Zero-initialised scheduler words for calls on (device, stream).  Calls on one stream run in
+    order and each leaves the words zero, so one buffer per stream is enough."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(), int(stream_ptr))
+    w = _workspaces.get(key)
+    if w is None:
+        w = torch.zeros(_lib.WORKSPACE_BYTES // 4, dtype=torch.int32, device=device)
+        _workspaces[key] = w
     return w
 
 
@@ -134,6 +154,7 @@ def make_problem(depth_params, image_feats, projection_matrices, feature_size, i
     p = _lib.FbevProblem()
     p.struct_size = ctypes.sizeof(_lib.FbevProblem)
     p.dtype = _DTYPES[dtype]
+    p.out_dtype = _lib.F32 if spec.out_dtype == torch.float32 else p.dtype
     p.B, p.N, p.H, p.W, p.C = B, N, H, W, C
     p.D = depth.shape[-1]
     p.X, p.Y, p.Z = X, Y, Z
@@ -147,7 +168,13 @@ def make_problem(depth_params, image_feats, projection_matrices, feature_size, i
     p.image_feats, p.depth, p.projection = feats.data_ptr(), depth.data_ptr(), proj.data_ptr()
     p.feature_size, p.image_size, p.roi_range = fsize.data_ptr(), isize.data_ptr(), roi.data_ptr()
     p.status = status_word(dev).data_ptr()
+    with torch.cuda.device(dev):
+        p.workspace = workspace(dev, torch.cuda.current_stream().cuda_stream).data_ptr()
     return p, (feats, depth, proj, fsize, isize, roi)
+
+
+def _out_dtype(spec: DepthSpec, feats: torch.Tensor) -> torch.dtype:
+    return torch.float32 if spec.out_dtype == torch.float32 else feats.dtype
 
 
 class FlashBEVPool(torch.autograd.Function):
@@ -164,7 +191,7 @@ class FlashBEVPool(torch.autograd.Function):
         feats = keep[0]
         shape = (p.B, p.Y, p.X, p.C)
         partial = (p.y_begin, p.y_end) != (0, p.Y)
-        out = (torch.zeros if partial else torch.empty)(shape, dtype=feats.dtype, device=feats.device)
+        out = (torch.zeros if partial else torch.empty)(shape, dtype=_out_dtype(spec, feats), device=feats.device)
         with torch.cuda.device(feats.device):
             stream = torch.cuda.current_stream().cuda_stream
             rc = _lib.load().fbev_forward(ctypes.byref(p), out.data_ptr(), None, stream)
@@ -193,7 +220,7 @@ class FlashBEVPool(torch.autograd.Function):
             flags |= _lib.BWD_LEGACY_DEPTH
         grad_feats = grad_depth = None
         if flags & (_lib.BWD_FEATS | _lib.BWD_DEPTH):
-            go = _on(out_grad, feats.device, feats.dtype)
+            go = _on(out_grad, feats.device, _out_dtype(spec, feats))
             lib = _lib.load()
             if flags & _lib.BWD_FEATS:
                 grad_feats = torch.empty_like(feats)
@@ -221,7 +248,7 @@ class FlashBEVPool(torch.autograd.Function):
 def flash_bevpool(image_feats, depth_params, projection_matrices, feature_size, image_size, roi_range, grid_size,
                   depth_distribution=0, use_shared_memory=True, optimize_z_precompute=True, use_warp_kernel=False,
                   use_vectorized_load=False, epsilon=1e-6, depth_weight_threshold=1e-6, *, pool=None,
-                  depth_bin_range=None, legacy_depth_grad=False, y_range=None):
+                  depth_bin_range=None, legacy_depth_grad=False, y_range=None, out_dtype=None):
     """Fused BEV pooling; same arguments as the reference wrapper (flash_bevpool.py:139-178).
 
     Args:
@@ -236,11 +263,13 @@ def flash_bevpool(image_feats, depth_params, projection_matrices, feature_size, 
         depth_bin_range: (first bin edge, bin width) of the categorical mode.
         legacy_depth_grad: parametric modes only; reproduce the reference CUDA kernel's depth gradient.
         y_range: (begin, end) BEV rows to compute; the other rows of the output are zero.
+        out_dtype: None (output in the feature dtype) or torch.float32 (what the reference returns for
+            any input dtype).
     Returns:
-        BEV features [B,Y,X,C] in the dtype of ``image_feats``.
+        BEV features [B,Y,X,C] in the dtype of ``image_feats`` (or float32, see ``out_dtype``).
     """
     spec = DepthSpec(depth_distribution, pool=pool, depth_bin_range=depth_bin_range,
-                     legacy_depth_grad=legacy_depth_grad, y_range=y_range)
+                     legacy_depth_grad=legacy_depth_grad, y_range=y_range, out_dtype=out_dtype)
     return FlashBEVPool.apply(depth_params, image_feats, projection_matrices, feature_size, image_size, roi_range,
                               grid_size, spec, use_shared_memory, optimize_z_precompute, use_warp_kernel,
                               use_vectorized_load, epsilon, depth_weight_threshold)
@@ -272,13 +301,14 @@ def debug_indices(image_feats, depth_params, projection_matrices, feature_size, 
 
 def forward_with_count(image_feats, depth_params, projection_matrices, feature_size, image_size, roi_range,
                        grid_size, depth_distribution=0, epsilon=1e-6, depth_weight_threshold=1e-6, *, pool=None,
-                       depth_bin_range=None, y_range=None):
+                       depth_bin_range=None, y_range=None, out_dtype=None):
     """Forward without autograd that also returns the per-cell count of accepted samples [B,Y,X]."""
-    spec = DepthSpec(depth_distribution, pool=pool, depth_bin_range=depth_bin_range, y_range=y_range)
+    spec = DepthSpec(depth_distribution, pool=pool, depth_bin_range=depth_bin_range, y_range=y_range,
+                     out_dtype=out_dtype)
     p, keep = make_problem(depth_params, image_feats, projection_matrices, feature_size, image_size, roi_range,
                            grid_size, spec, epsilon, depth_weight_threshold)
     dev = keep[0].device
-    out = torch.zeros((p.B, p.Y, p.X, p.C), dtype=keep[0].dtype, device=dev)
+    out = torch.zeros((p.B, p.Y, p.X, p.C), dtype=_out_dtype(spec, keep[0]), device=dev)
     cnt = torch.zeros((p.B, p.Y, p.X), dtype=torch.int32, device=dev)
     with torch.cuda.device(dev):
         rc = _lib.load().fbev_forward(ctypes.byref(p), out.data_ptr(), cnt.data_ptr(),

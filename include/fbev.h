@@ -78,7 +78,9 @@ enum {
  */
 typedef struct FbevProblem {
   uint32_t struct_size;        /* sizeof(FbevProblem) */
-  int32_t dtype;               /* FBEV_F32 / FBEV_BF16 / FBEV_F16 */
+  int32_t dtype;               /* FBEV_F32 / FBEV_BF16 / FBEV_F16: features, depth and both gradients */
+  int32_t out_dtype;           /* output and upstream gradient: same as dtype, or FBEV_F32 (the reference
+                                  always returns float32, flash_bevpool.py:47-49,69) */
   int32_t B, N, H, W, C;       /* features [B,N,H,W,C] */
   int32_t D;                   /* last dimension of the depth tensor: 2 (mean, sigma) or the bin count */
   int32_t X, Y, Z;             /* grid_size = [X, Y, Z]; output [B,Y,X,C] */
@@ -98,7 +100,14 @@ typedef struct FbevProblem {
   const int32_t* image_size;   /* device [2] (image_h, image_w) (:48-49) */
   const float* roi_range;      /* device [6] xmin,xmax,ymin,ymax,zmin,zmax, or NULL (then voxel_size/voxel_min) */
   int32_t* status;             /* optional device word for FBEV_DEV_* flags; NULL to ignore */
+  void* workspace;             /* optional device memory, FBEV_WORKSPACE_BYTES, 16-byte aligned, zero before its
+                                  first use; every call leaves it zero again.  With it the kernels balance
+                                  their tiles through an atomic counter; without it (NULL) every thread block
+                                  owns one fixed tile.  Calls that may overlap on the device need a workspace
+                                  each. */
 } FbevProblem;
+
+#define FBEV_WORKSPACE_BYTES 16
 
 /* Forward.  Replaces flash_bevpool_forward (flash_bevpool.cpp:79-166) ->
  * flash_bevpool() (flash_bevpool_cuda.cu:757-865).  Writes every element of

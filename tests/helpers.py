@@ -24,6 +24,21 @@ def rel_err(a, b):
     return float(np.abs(a - b).max() / (denom if denom > 0 else 1.0))
 
 
+_MANTISSA_BITS = {"bf16": 7, "fp16": 10}
+
+
+def rel_err_quantised(a, b, dtype_name):
+    """Relative error of a result that was rounded to a 16-bit type, after setting aside that one
+    rounding: max(|a-b| - half_ulp(b), 0) / max|b|.  A bfloat16 result cannot be closer than half an ulp
+    (up to 2^-8 = 3.9e-3 of its value) to an unrounded reference, so that part is not an error of the kernel."""
+    a = np.asarray(a, dtype=np.float64)
+    b = np.asarray(b, dtype=np.float64)
+    mag = np.maximum(np.abs(b), 2.0 ** -24)
+    half_ulp = 2.0 ** (np.floor(np.log2(mag)) - _MANTISSA_BITS[dtype_name] - 1)
+    denom = np.abs(b).max()
+    return float(np.maximum(np.abs(a - b) - half_ulp, 0.0).max() / (denom if denom > 0 else 1.0))
+
+
 MODES = {"gaussian": O.MODE_GAUSSIAN, "laplace": O.MODE_LAPLACE, "categorical": O.MODE_CATEGORICAL}
 
 

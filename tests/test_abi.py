@@ -31,14 +31,16 @@ def test_library_builds_and_exports_every_symbol():
 
 
 def test_struct_layout_matches_the_header():
-    # uint32 + 19 int32/float words, 6 floats, 7 pointers; no padding on LP64
-    assert ctypes.sizeof(_lib.FbevProblem) == 4 * 20 + 4 * 6 + 8 * 7
+    # uint32 + 20 int32/float words + 6 floats = 27 words, padded to 8 bytes, then 8 pointers (LP64)
+    assert ctypes.sizeof(_lib.FbevProblem) == 4 * 28 + 8 * 8
+    assert _lib.FbevProblem.image_feats.offset == 112 and _lib.FbevProblem.workspace.offset == 168
 
 
 def _problem():
     p = _lib.FbevProblem()
     p.struct_size = ctypes.sizeof(_lib.FbevProblem)
     p.dtype = _lib.F32
+    p.out_dtype = _lib.F32
     p.B, p.N, p.H, p.W, p.C, p.D = 1, 2, 4, 4, 8, 2
     p.X, p.Y, p.Z = 8, 8, 2
     p.proj_stride = 12
@@ -64,12 +66,16 @@ def test_validation_status_codes():
     p = _problem(); p.D = 5                                       # parametric depth must have 2 channels
     assert fwd(p) == 3
     p = _problem(); p.dtype = 7
+    assert fwd(p) == 4
+    p = _problem(); p.out_dtype = _lib.BF16                       # output narrower than the features
     assert fwd(p) == 4                                            # FBEV_ERR_DTYPE
     p = _problem(); p.mode = 3
     assert fwd(p) == 5                                            # FBEV_ERR_MODE
     p = _problem(); p.mode = _lib.DEPTH_CATEGORICAL; p.depth_delta = 0.0
     assert fwd(p) == 5
     p = _problem(); p.image_feats = 258
+    assert fwd(p) == 6
+    p = _problem(); p.workspace = 264
     assert fwd(p) == 6                                            # FBEV_ERR_ALIGN
     p = _problem(); p.B = 1 << 20; p.H = 1 << 10; p.W = 1 << 10
     assert fwd(p) == 7                                            # FBEV_ERR_RANGE
@@ -86,7 +92,7 @@ def test_backward_scratch_size_and_checks():
     lib = _lib.load()
     p = _problem()
     assert lib.fbev_backward_scratch_bytes(ctypes.byref(p), 3) == 0            # float32: in place
-    p.dtype = _lib.BF16
+    p.dtype = p.out_dtype = _lib.BF16
     tex = 1 * 2 * 4 * 4
     assert lib.fbev_backward_scratch_bytes(ctypes.byref(p), 3) == tex * 8 * 4 + tex * 2 * 4
     assert lib.fbev_backward_scratch_bytes(ctypes.byref(p), 1) == tex * 8 * 4
