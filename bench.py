@@ -182,7 +182,7 @@ def main():
     ap.add_argument("--batch-per-gpu", type=int, default=1)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip backward / e2e / L2 probe (for profiler runs)")
-    ap.add_argument("--tune", default=None, help="tile_x,tile_y,chunks_per_lane,warps (0 = automatic)")
+    ap.add_argument("--tune", default=None, help="tile_x,tile_y,chunks_per_lane,warps,min_blocks (0 = automatic)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))

@@ -88,7 +88,7 @@ def load(build_if_missing: bool = True) -> ctypes.CDLL:
     lib.fbev_flash_bevpool.restype = i32
     lib.fbev_flash_bevpool_grad.argtypes = [i32] * 7 + [f32, f32] + [vp] * 7 + [i32] * 3 + [vp, vp, i32, i32, vp]
     lib.fbev_flash_bevpool_grad.restype = i32
-    lib.fbev_set_tuning.argtypes = [i32] * 4
+    lib.fbev_set_tuning.argtypes = [i32] * 5
     lib.fbev_set_tuning.restype = None
     lib.fbev_probe_read.argtypes = [vp, ctypes.c_size_t, i32, vp, vp]
     lib.fbev_probe_read.restype = i32

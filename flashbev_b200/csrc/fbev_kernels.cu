@@ -162,6 +162,38 @@ __device__ __forceinline__ void block_prologue(const Dev& p, const Tile& t, cons
   __syncthreads();
 }
 
+// Forward-kernel prologue for up to 32 cameras.  The matrices are (re)loaded only when the tile
+// belongs to another sample than the one in shared memory (block barriers then); the camera cull is
+// evaluated by every warp for itself and returned as a bit mask, so the steady state has no barrier.
+__device__ __forceinline__ unsigned tile_visibility(const Dev& p, const Tile& t, const BlockHeader& h,
+                                                    const float vs[3], const float vmin[3], int image_h, int image_w,
+                                                    int& loaded_b) {
+  if (loaded_b != t.b) {  // uniform over the block
+    __syncthreads();      // nobody still reads the matrices of the sample before
+    for (int i = threadIdx.x; i < p.N * 12; i += blockDim.x) {
+      const int n = i / 12, k = i - n * 12;
+      h.P[i] = __ldg(p.proj + ((size_t)t.b * p.N + n) * p.pstride + k);
+    }
+    for (int i = threadIdx.x; i < p.N * 2; i += blockDim.x) h.fs[i] = __ldg(p.fsize + (size_t)t.b * p.N * 2 + i);
+    loaded_b = t.b;
+    __syncthreads();
+  }
+  const int lane = threadIdx.x & 31;
+  bool see = false;
+  if (lane < p.N) {
+    const int fh = h.fs[lane * 2], fw = h.fs[lane * 2 + 1];
+    if (fh > 0 && fw > 0 && (long long)fh * fw <= (long long)p.H * p.W) {
+      const float bx0 = centre(t.x0, vs[0], vmin[0]), bx1 = centre(t.x1 - 1, vs[0], vmin[0]);
+      const float by0 = centre(t.y0, vs[1], vmin[1]), by1 = centre(t.y1 - 1, vs[1], vmin[1]);
+      const float bz0 = centre(0, vs[2], vmin[2]), bz1 = centre(p.Z - 1, vs[2], vmin[2]);
+      see = camera_may_see(p, h.P + lane * 12, bx0, bx1, by0, by1, bz0, bz1, image_h, image_w);
+    } else if (p.status != nullptr && threadIdx.x < 32) {
+      atomicOr(p.status, (int)FBEV_DEV_BAD_FEATURE_SIZE);
+    }
+  }
+  return __ballot_sync(kFull, see);
+}
+
 // List phase for one group of cells and one pass over candidates [r0, r1) of
 // every cell (candidate r = visible-camera index * Z + z).
 //   t0      first tile-linear cell of the group; cell = t0 + c, c < CPW
@@ -282,7 +314,7 @@ __host__ __device__ inline size_t fwd_warp_bytes(int CPW, int cap) { return 256 
 // four per sample, which is some 2.5 to 5 times fewer gathers for the benchmark shapes.  Runs do not
 // extend across the 32 candidates of one round; that only costs merges, never correctness.
 template <typename T>
-__device__ __forceinline__ void row_list_phase(const Dev& p, const Tile& t, const BlockHeader& h, int t0, int r0,
+__device__ __forceinline__ void row_list_phase(const Dev& p, const Tile& t, const BlockHeader& h, unsigned vis, unsigned cpt, int t0, int r0,
                                                int r1, const float vs[3], const float vmin[3], int image_h,
                                                int image_w, int* sLen, int* sCnt, uint4* recs, int lane) {
   const int per = r1 - r0;
@@ -306,7 +338,7 @@ __device__ __forceinline__ void row_list_phase(const Dev& p, const Tile& t, cons
       const int ly = fast_div(tc, inv_tx), lx = tc - ly * p.TX;
       const int x = t.x0 + lx, y = t.y0 + ly;
       if (tc < tile_cells && x < t.x1 && y < t.y1) {
-        const int n = h.vis[ci];
+        const int n = (int)__fns(vis, 0u, ci + 1);  // ci-th visible camera
         const int fh = h.fs[n * 2];
         fw = h.fs[n * 2 + 1];
         const float vx = centre(x, vs[0], vmin[0]), vy = centre(y, vs[1], vmin[1]), vz = centre(z, vs[2], vmin[2]);
@@ -376,9 +408,10 @@ __device__ __forceinline__ void row_list_phase(const Dev& p, const Tile& t, cons
       int pos = before + __popc(m1 & seg & lt) + __popc(m2 & seg & lt);
       uint4* rec = recs + (size_t)cl * rstride;
       const unsigned du = (kk >> 28) & 1u;
-      if (emit_a) rec[pos++] = make_uint4(tex, du, __float_as_uint(A0), __float_as_uint(A1));
+      // chunk index of texel (row, u0), chunk distance to (row, u1), weights
+      if (emit_a) rec[pos++] = make_uint4(tex * cpt, du * cpt, __float_as_uint(A0), __float_as_uint(A1));
       if (emit_b)
-        rec[pos] = make_uint4(tex + (unsigned)fw, du, __float_as_uint(B0 + (absorb_prev ? pA0 : 0.0f)),
+        rec[pos] = make_uint4((tex + (unsigned)fw) * cpt, du * cpt, __float_as_uint(B0 + (absorb_prev ? pA0 : 0.0f)),
                               __float_as_uint(B1 + (absorb_prev ? pA1 : 0.0f)));
     }
     if (q < total && lane == lo) {
@@ -389,8 +422,8 @@ __device__ __forceinline__ void row_list_phase(const Dev& p, const Tile& t, cons
   }
 }
 
-template <typename T, int V>
-__global__ void __launch_bounds__(kMaxWarps * 32, 3) fwd_kernel(const __grid_constant__ Dev p) {
+template <typename T, int V, int MINB>
+__global__ void __launch_bounds__(kMaxWarps * 32, MINB) fwd_kernel(const __grid_constant__ Dev p) {
   constexpr int E = Chunk<T>::E;
   extern __shared__ __align__(16) unsigned char smem[];
   const BlockHeader h = carve(smem, p.N);
@@ -411,14 +444,14 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) fwd_kernel(const __grid_con
   const int cpt = p.GL * V;  // 16-byte chunks per texel
   const int tile_cells = p.TX * p.TY;
   const int ngroups = (tile_cells + p.CPW - 1) / p.CPW;
-  const uint4* fbase = reinterpret_cast<const uint4*>(p.feats);
+  const uint4* fl = reinterpret_cast<const uint4*>(p.feats) + lg;  // this lane's chunk of texel 0
   int loaded_b = -1;
   TileLoop loop;
   loop.begin(p, s_tile);
   for (int tile; (tile = loop.current(p)) >= 0; loop.advance()) {
     const Tile t = tile_of(p, tile);
-    block_prologue(p, t, h, vs, vmin, image_h, image_w, loaded_b);
-    const int nvis = *h.nvis;
+    const unsigned vis = tile_visibility(p, t, h, vs, vmin, image_h, image_w, loaded_b);
+    const int nvis = __popc(vis);
     const int ncand = nvis * p.Z;
 
     for (int grp = warp; grp < ngroups; grp += nwarps) {
@@ -436,7 +469,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) fwd_kernel(const __grid_con
       for (int r0 = 0; r0 < ncand; r0 += p.cap) {
         if (lane < p.CPW) sLen[lane] = 0;
         __syncwarp();
-        row_list_phase<T>(p, t, h, t0, r0, min(r0 + p.cap, ncand), vs, vmin, image_h, image_w, sLen, sCnt, recs,
+        row_list_phase<T>(p, t, h, vis, (unsigned)cpt, t0, r0, min(r0 + p.cap, ncand), vs, vmin, image_h, image_w, sLen, sCnt, recs,
                           lane);
         const int n = cell_ok ? sLen[g] : 0;
         const uint4* rec = recs + (size_t)g * rstride;
@@ -444,12 +477,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) fwd_kernel(const __grid_con
         for (int i = 0; i < n; ++i) {
           const uint4 r = rec[i];
           const float wa0 = __uint_as_float(r.z), wa1 = __uint_as_float(r.w);
-          const uint4* c0 = fbase + (size_t)r.x * cpt + lg;
-          const uint4* c1 = c0 + (size_t)r.y * cpt;
 #pragma unroll
           for (int j = 0; j < V; ++j) {
-            const uint4 q0 = ldg16(c0 + j * p.GL);
-            const uint4 q1 = ldg16(c1 + j * p.GL);
+            const uint4 q0 = ldg16(fl + (r.x + j * p.GL));
+            const uint4 q1 = ldg16(fl + (r.x + r.y + j * p.GL));
             float f0[E], f1[E];
             Chunk<T>::unpack(q0, f0);
             Chunk<T>::unpack(q1, f1);
@@ -937,9 +968,9 @@ __global__ void probe_read_kernel(const uint4* __restrict__ buf, size_t n16, int
 // Host side
 // ---------------------------------------------------------------------------
 struct Tuning {
-  int tx, ty, v, warps;
+  int tx, ty, v, warps, minb;
 };
-static Tuning g_tuning = {0, 0, 0, 0};
+static Tuning g_tuning = {0, 0, 0, 0, 0};
 
 static size_t elem_size(int dtype) { return dtype == FBEV_F32 ? 4 : 2; }
 
@@ -1011,7 +1042,7 @@ static Plan make_plan(const FbevProblem* p, Dev& d, bool bwd, const void* a, con
                        ((uintptr_t)c % 16 == 0);
   const int chunks = aligned ? (int)(row / 16) : 0;
   pl.chunked = aligned && chunks <= 128;
-  pl.warps = g_tuning.warps > 0 ? (g_tuning.warps > kMaxWarps ? kMaxWarps : g_tuning.warps) : 8;
+  pl.warps = g_tuning.warps > 0 ? (g_tuning.warps > kMaxWarps ? kMaxWarps : g_tuning.warps) : (bwd ? 8 : 4);
   pl.cap = 32;
   if (pl.chunked) {
     int bestV = 0;
@@ -1023,10 +1054,9 @@ static Plan make_plan(const FbevProblem* p, Dev& d, bool bwd, const void* a, con
       const int GL = chunks / V;
       if (GL > 32) continue;
       const int CPW = 32 / GL < kMaxCellsPerWarp ? 32 / GL : kMaxCellsPerWarp;
-      // lane utilisation first; then prefer groups of 8..16 lanes (fewer cells per warp
-      // diverge less, more than one chunk per lane amortises the record loads)
+      // lane utilisation first
       double score = (double)(CPW * GL) / 32.0;
-      if (GL >= 8 && GL <= 16) score += 0.02;
+      if (V == 2) score += 0.02;  // two chunks per lane amortise the record handling; four cost registers
       if (score > best) {
         best = score;
         bestV = V;
@@ -1049,17 +1079,33 @@ static Plan make_plan(const FbevProblem* p, Dev& d, bool bwd, const void* a, con
   d.GL = pl.GL;
   d.CPW = pl.CPW;
   d.cap = pl.cap;
-  // tile = 16 groups of CPW cells: two rounds for eight warps, and small enough that the camera cull bites
+  // backward: tile = 16 groups of CPW cells, two rounds for eight warps.  forward: small tiles of about 24
+  // cells for four warps: a single sample has only some 10^4 cells, and the tail of the last tiles is what
+  // a launch waits for.
   int tx = 4 * pl.CPW, ty = 4;
   if (tx > 16) {
     tx /= 2;
     ty *= 2;
+  }
+  if (!bwd && pl.chunked) {
+    tx = pl.CPW * (6 / pl.CPW > 1 ? 6 / pl.CPW : 1);
+    ty = 4;
   }
   d.TX = g_tuning.tx > 0 ? g_tuning.tx : tx;
   d.TY = g_tuning.ty > 0 ? g_tuning.ty : ty;
   d.tiles_x = (p->X + d.TX - 1) / d.TX;
   d.tiles_y = (p->y_end - p->y_begin + d.TY - 1) / d.TY;
   pl.blocks = d.tiles_x * d.tiles_y * p->B;
+  if (!bwd && pl.chunked &&
+      (p->N > 32 ||
+       (unsigned long long)p->B * p->N * p->H * p->W * (unsigned long long)(pl.GL * pl.V) >= (1ull << 32))) {
+    // the forward keeps the visible cameras in a 32-bit mask and 32-bit chunk indices into the feature
+    // tensor in its records: more cameras or a larger tensor take the scalar kernel
+    pl.chunked = false;
+    pl.V = 0;
+    d.GL = pl.GL = 32;
+    d.CPW = pl.CPW = 1;
+  }
   const size_t wb = bwd ? warp_bytes<3>(pl.CPW, pl.cap)
                         : (pl.chunked ? fwd_warp_bytes(pl.CPW, pl.cap) : warp_bytes<2>(pl.CPW, pl.cap));
   pl.smem = header_bytes(p->N) + (size_t)pl.warps * wb;
@@ -1107,10 +1153,11 @@ static int launch(K kernel, const Plan& pl, const Dev& d, cudaStream_t st) {
 template <typename T>
 static int forward_t(const Plan& pl, const Dev& d, cudaStream_t st) {
   if (!pl.chunked) return launch(fwd_generic_kernel<T>, pl, d, st);
+  const bool two = g_tuning.minb == 2;  // compiled for two resident blocks per SM (128 registers) instead of three (80)
   switch (pl.V) {
-    case 1: return launch(fwd_kernel<T, 1>, pl, d, st);
-    case 2: return launch(fwd_kernel<T, 2>, pl, d, st);
-    default: return launch(fwd_kernel<T, 4>, pl, d, st);
+    case 1: return two ? launch(fwd_kernel<T, 1, 2>, pl, d, st) : launch(fwd_kernel<T, 1, 3>, pl, d, st);
+    case 2: return two ? launch(fwd_kernel<T, 2, 2>, pl, d, st) : launch(fwd_kernel<T, 2, 3>, pl, d, st);
+    default: return launch(fwd_kernel<T, 4, 2>, pl, d, st);
   }
 }
 
@@ -1127,6 +1174,27 @@ static int backward_t(const Plan& pl, const Dev& d, cudaStream_t st) {
 }  // namespace fbev
 
 using namespace fbev;
+
+// unknown_hw: the caller could not tell the tensor's H and W (reference launcher signature); the
+// kernels then trust feature_size, as the reference does.
+static int forward_impl(const FbevProblem* p, void* out, int32_t* valid_count, void* stream, bool unknown_hw) {
+  const int rc = validate(p);
+  if (rc != FBEV_OK) return rc;
+  if (out == nullptr) return FBEV_ERR_NULL;
+  if (((uintptr_t)out % elem_size(p->out_dtype)) || ((uintptr_t)valid_count % 4)) return FBEV_ERR_ALIGN;
+  Dev d;
+  fill_dev(p, d);
+  d.out = out;
+  d.count = valid_count;
+  if (unknown_hw) d.H = d.W = 46340;  // feature_size entries up to 2^31 texels pass the in-kernel bound
+  const Plan pl = make_plan(p, d, false, p->image_feats, out, nullptr);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  switch (p->dtype) {
+    case FBEV_F32: return forward_t<float>(pl, d, st);
+    case FBEV_BF16: return forward_t<__nv_bfloat16>(pl, d, st);
+    default: return forward_t<__half>(pl, d, st);
+  }
+}
 
 extern "C" {
 
@@ -1149,26 +1217,12 @@ const char* fbev_strerror(int status) {
   }
 }
 
-void fbev_set_tuning(int tile_x, int tile_y, int chunks_per_lane, int warps) {
-  g_tuning = Tuning{tile_x, tile_y, chunks_per_lane, warps};
+void fbev_set_tuning(int tile_x, int tile_y, int chunks_per_lane, int warps, int min_blocks) {
+  g_tuning = Tuning{tile_x, tile_y, chunks_per_lane, warps, min_blocks};
 }
 
 int fbev_forward(const FbevProblem* p, void* out, int32_t* valid_count, void* stream) {
-  const int rc = validate(p);
-  if (rc != FBEV_OK) return rc;
-  if (out == nullptr) return FBEV_ERR_NULL;
-  if (((uintptr_t)out % elem_size(p->out_dtype)) || ((uintptr_t)valid_count % 4)) return FBEV_ERR_ALIGN;
-  Dev d;
-  fill_dev(p, d);
-  d.out = out;
-  d.count = valid_count;
-  const Plan pl = make_plan(p, d, false, p->image_feats, out, nullptr);
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  switch (p->dtype) {
-    case FBEV_F32: return forward_t<float>(pl, d, st);
-    case FBEV_BF16: return forward_t<__nv_bfloat16>(pl, d, st);
-    default: return forward_t<__half>(pl, d, st);
-  }
+  return forward_impl(p, out, valid_count, stream, false);
 }
 
 size_t fbev_backward_scratch_bytes(const FbevProblem* p, int flags) {
@@ -1282,10 +1336,8 @@ int fbev_flash_bevpool(int total_threads, int num_channels, int num_cameras, int
   p.dtype = FBEV_F32;
   p.out_dtype = FBEV_F32;
   p.B = batch_size; p.N = num_cameras; p.C = num_channels;
-  // The launcher is not told the tensor's H and W; like the reference it addresses
-  // with feature_size alone, so no bound is known here.
-  p.H = 1 << 15; p.W = 1 << 15;
-  if ((unsigned long long)p.B * p.N * p.H * p.W >= (1ull << 31)) { p.H = 1; p.W = (int)(((1ull << 31) - 1) / ((unsigned long long)(p.B > 0 ? p.B : 1) * (p.N > 0 ? p.N : 1))); }
+  // The launcher is not told the tensor's H and W; like the reference it addresses with feature_size alone.
+  p.H = 1; p.W = 1;
   p.D = 2;
   p.X = grid_x; p.Y = grid_y; p.Z = grid_z;
   p.proj_stride = 12;
@@ -1297,7 +1349,7 @@ int fbev_flash_bevpool(int total_threads, int num_channels, int num_cameras, int
   p.voxel_min[0] = voxel_x_min; p.voxel_min[1] = voxel_y_min; p.voxel_min[2] = voxel_z_min;
   p.image_feats = image_feats; p.depth = depth_params; p.projection = projection_matrices;
   p.feature_size = feature_size; p.image_size = image_size;
-  return fbev_forward(&p, out, nullptr, stream);
+  return forward_impl(&p, out, nullptr, stream, true);
 }
 
 int fbev_flash_bevpool_grad(int total_threads, int num_channels, int num_cameras, int batch_size,

@@ -167,8 +167,9 @@ int fbev_flash_bevpool_grad(int total_threads, int num_channels, int num_cameras
                             void* stream);
 
 /* Process-wide launch tuning for experiments: cells per tile in x and y,
- * 16-byte chunks per lane, warps per block; 0 = choose automatically. */
-void fbev_set_tuning(int tile_x, int tile_y, int chunks_per_lane, int warps);
+ * 16-byte chunks per lane, warps per block, resident blocks per SM the forward
+ * kernel is compiled for (2 or 3); 0 = choose automatically. */
+void fbev_set_tuning(int tile_x, int tile_y, int chunks_per_lane, int warps, int min_blocks);
 
 /* Reads `bytes` of device memory `repeats` times with 16-byte loads (a bandwidth
  * probe for roofline denominators: L2-resident when bytes fits the L2).  sink:

