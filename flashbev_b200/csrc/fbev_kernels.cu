@@ -313,7 +313,7 @@ __host__ __device__ inline size_t fwd_warp_bytes(int CPW, int cap) { return 256 
 // already multiplied by the depth weight.  The channel phase reads two texels per record instead of
 // four per sample, which is some 2.5 to 5 times fewer gathers for the benchmark shapes.  Runs do not
 // extend across the 32 candidates of one round; that only costs merges, never correctness.
-template <typename T>
+template <typename T, bool WRITE = true>
 __device__ __forceinline__ void row_list_phase(const Dev& p, const Tile& t, const BlockHeader& h, unsigned vis, unsigned cpt, int t0, int r0,
                                                int r1, const float vs[3], const float vmin[3], int image_h,
                                                int image_w, int* sLen, int* sCnt, uint4* recs, int lane) {
@@ -404,7 +404,7 @@ __device__ __forceinline__ void row_list_phase(const Dev& p, const Tile& t, cons
     const unsigned seg = (hi >= 32 ? kFull : ((1u << hi) - 1u)) & ~((1u << lo) - 1u);
     const int before = sLen[cl];
     __syncwarp();
-    if (tail) {
+    if (WRITE && tail) {
       int pos = before + __popc(m1 & seg & lt) + __popc(m2 & seg & lt);
       uint4* rec = recs + (size_t)cl * rstride;
       const unsigned du = (kk >> 28) & 1u;
@@ -503,6 +503,121 @@ __global__ void __launch_bounds__(kMaxWarps * 32, MINB) fwd_kernel(const __grid_
 #pragma unroll
         for (int j = 0; j < V; ++j) store_chunk<T>(p.out, p.out_f32, cell * cpt + lg + j * p.GL, acc + j * E);
         if (p.count != nullptr && lg == 0) p.count[cell] = cnt;
+      }
+      __syncwarp();
+    }
+  }  // tiles
+  loop.end(p);
+}
+
+// Feature-gradient kernel: the forward kernel run backwards.  It builds the same merged row records
+// (texel pair, summed weights with the depth weight folded in) and, instead of gathering, adds
+//   d_feats[texel, c] += g_c * inv * weight          (flash_bevpool_cuda.cu:665,676-679)
+// with one 16-byte float32 reduction per chunk and texel.  Merging the height bins that share a feature
+// row cuts the number of reductions, which is what bounds this kernel, by the same factor as the
+// forward's gathers; no feature is read at all.  inv = 1/count for mean pooling, 1 for sum.
+__device__ __forceinline__ void red_add4(float* addr, float a, float b, float c, float d);
+
+template <typename T, int V>
+__global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_feats_kernel(const __grid_constant__ Dev p) {
+  constexpr int E = Chunk<T>::E;
+  extern __shared__ __align__(16) unsigned char smem[];
+  const BlockHeader h = carve(smem, p.N);
+  __shared__ int s_tile[2];
+  float vs[3], vmin[3];
+  voxel_frame(p, vs, vmin);
+  const int image_h = __ldg(p.isize), image_w = __ldg(p.isize + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  unsigned char* wa = h.warp_area + (size_t)warp * fwd_warp_bytes(p.CPW, p.cap);
+  int* sLen = reinterpret_cast<int*>(wa);
+  int* sCnt = sLen + 32;
+  uint4* recs = reinterpret_cast<uint4*>(wa + 256);
+  const int rstride = row_stride(p.cap);
+
+  const int g = lane / p.GL, lg = lane - g * p.GL;
+  const bool lane_used = g < p.CPW;
+  const int cpt = p.GL * V;
+  const int tile_cells = p.TX * p.TY;
+  const int ngroups = (tile_cells + p.CPW - 1) / p.CPW;
+  float* gl = p.gfeat + (size_t)lg * E;  // this lane's chunk of texel 0 in the float32 gradient
+  const bool mean_pool = p.pool == FBEV_POOL_MEAN;
+  int loaded_b = -1;
+  TileLoop loop;
+  loop.begin(p, s_tile);
+  for (int tile; (tile = loop.current(p)) >= 0; loop.advance()) {
+    const Tile t = tile_of(p, tile);
+    const unsigned vis = tile_visibility(p, t, h, vs, vmin, image_h, image_w, loaded_b);
+    const int nvis = __popc(vis);
+    const int ncand = nvis * p.Z;
+    const bool single_pass = ncand <= p.cap;
+
+    for (int grp = warp; grp < ngroups; grp += nwarps) {
+      const int t0 = grp * p.CPW;
+      const int tc = t0 + g;
+      const int ly = tc / p.TX, lx = tc - ly * p.TX;
+      const int x = t.x0 + lx, y = t.y0 + ly;
+      const bool cell_ok = lane_used && tc < tile_cells && x < t.x1 && y < t.y1;
+
+      float go[V * E];
+#pragma unroll
+      for (int i = 0; i < V * E; ++i) go[i] = 0.0f;
+      if (cell_ok) {
+        const size_t cell = ((size_t)t.b * p.Y + y) * p.X + x;
+#pragma unroll
+        for (int j = 0; j < V; ++j) load_chunk<T>(p.gout, p.out_f32, cell * cpt + lg + j * p.GL, go + j * E);
+      }
+      if (lane < p.CPW) sCnt[lane] = 0;
+      __syncwarp();
+      if (mean_pool && !single_pass) {
+        // the count of all passes is needed before the first contribution leaves
+        for (int r0 = 0; r0 < ncand; r0 += p.cap) {
+          if (lane < p.CPW) sLen[lane] = 0;
+          __syncwarp();
+          row_list_phase<T, false>(p, t, h, vis, (unsigned)cpt, t0, r0, min(r0 + p.cap, ncand), vs, vmin, image_h,
+                                   image_w, sLen, sCnt, recs, lane);
+        }
+        const int cnt = lane_used ? sCnt[g] : 0;
+        const float inv = cnt > 0 ? __fdiv_rn(1.0f, (float)cnt) : 0.0f;
+#pragma unroll
+        for (int i = 0; i < V * E; ++i) go[i] *= inv;
+        __syncwarp();
+      }
+
+      for (int r0 = 0; r0 < ncand; r0 += p.cap) {
+        if (lane < p.CPW) sLen[lane] = 0;
+        __syncwarp();
+        row_list_phase<T, true>(p, t, h, vis, (unsigned)cpt, t0, r0, min(r0 + p.cap, ncand), vs, vmin, image_h,
+                                image_w, sLen, sCnt, recs, lane);
+        if (mean_pool && single_pass) {
+          const int cnt = lane_used ? sCnt[g] : 0;
+          const float inv = cnt > 0 ? __fdiv_rn(1.0f, (float)cnt) : 0.0f;
+#pragma unroll
+          for (int i = 0; i < V * E; ++i) go[i] *= inv;
+        }
+        const int n = cell_ok ? sLen[g] : 0;
+        const uint4* rec = recs + (size_t)g * rstride;
+        for (int i = 0; i < n; ++i) {
+          const uint4 r = rec[i];
+          const float w0 = __uint_as_float(r.z), w1 = __uint_as_float(r.w);
+#pragma unroll
+          for (int j = 0; j < V; ++j) {
+            float* d0 = gl + (size_t)(r.x + j * p.GL) * E;
+            float* d1 = gl + (size_t)(r.x + r.y + j * p.GL) * E;
+#pragma unroll
+            for (int e4 = 0; e4 < E; e4 += 4) {
+              const float g0 = go[j * E + e4], g1 = go[j * E + e4 + 1], g2 = go[j * E + e4 + 2],
+                          g3 = go[j * E + e4 + 3];
+              red_add4(d0 + e4, g0 * w0, g1 * w0, g2 * w0, g3 * w0);
+              if (r.y != 0u) {
+                red_add4(d1 + e4, g0 * w1, g1 * w1, g2 * w1, g3 * w1);
+              } else {  // u1 == u0 (last column): both weights belong to the same texel
+                red_add4(d0 + e4, g0 * w1, g1 * w1, g2 * w1, g3 * w1);
+              }
+            }
+          }
+        }
+        __syncwarp();
       }
       __syncwarp();
     }
@@ -1162,8 +1277,25 @@ static int forward_t(const Plan& pl, const Dev& d, cudaStream_t st) {
 }
 
 template <typename T>
-static int backward_t(const Plan& pl, const Dev& d, cudaStream_t st) {
+static int backward_feats_t(const Plan& pl, const Dev& d, cudaStream_t st) {
+  switch (pl.V) {
+    case 1: return launch(bwd_feats_kernel<T, 1>, pl, d, st);
+    case 2: return launch(bwd_feats_kernel<T, 2>, pl, d, st);
+    default: return launch(bwd_feats_kernel<T, 4>, pl, d, st);
+  }
+}
+
+// pl / d: plan of the per-sample kernel (depth gradient, or both gradients when the feature-gradient
+// kernel cannot take the shape); plf / df: plan of the feature-gradient kernel.
+template <typename T>
+static int backward_t(const Plan& pl, Dev d, const Plan& plf, const Dev& df, cudaStream_t st) {
   if (!pl.chunked) return launch(bwd_generic_kernel<T>, pl, d, st);
+  if ((d.flags & FBEV_BWD_FEATS) && plf.chunked) {
+    const int rc = backward_feats_t<T>(plf, df, st);
+    if (rc != FBEV_OK) return rc;
+    d.flags &= ~FBEV_BWD_FEATS;
+    if (!(d.flags & FBEV_BWD_DEPTH)) return FBEV_OK;
+  }
   switch (pl.V) {
     case 1: return launch(bwd_kernel<T, 1>, pl, d, st);
     case 2: return launch(bwd_kernel<T, 2>, pl, d, st);
@@ -1274,11 +1406,14 @@ int fbev_backward(const FbevProblem* p, const void* grad_out, void* grad_feats, 
     cudaGetLastError();
     return FBEV_ERR_LAUNCH;
   }
+  // the feature gradient has a kernel of its own, laid out like the forward
+  Dev df = d;
+  const Plan plf = make_plan(p, df, false, p->image_feats, grad_out, d.gfeat);
   int lrc;
   switch (p->dtype) {
-    case FBEV_F32: lrc = backward_t<float>(pl, d, st); break;
-    case FBEV_BF16: lrc = backward_t<__nv_bfloat16>(pl, d, st); break;
-    default: lrc = backward_t<__half>(pl, d, st); break;
+    case FBEV_F32: lrc = backward_t<float>(pl, d, plf, df, st); break;
+    case FBEV_BF16: lrc = backward_t<__nv_bfloat16>(pl, d, plf, df, st); break;
+    default: lrc = backward_t<__half>(pl, d, plf, df, st); break;
   }
   if (lrc != FBEV_OK) return lrc;
   if (!f32) {
