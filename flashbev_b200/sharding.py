@@ -1,0 +1,161 @@
+"""Multi-GPU use of the operator: one process per GPU, ``torch.distributed`` for the plumbing.
+
+The reference has no distributed code.  The operator shards in two ways:
+
+* **batch**: every index of the kernels is prefixed by the batch sample
+  (flash_bevpool_cuda.cu:40,57,144), so ranks take contiguous slices of the batch and nothing
+  crosses GPUs on the data path.  ``gather=True`` assembles the whole output with one
+  ``all_gather_into_tensor`` when a caller needs it on every rank.
+* **BEV rows** (one sample, large grid): output rows are independent too.  Rank r computes rows
+  ``row_slice(Y, world, r)`` of ``[B, Y, X, C]`` through the operator's ``y_range`` and the rows are
+  exchanged with one all-gather.  Inputs are replicated.  In the backward every rank owns the rows
+  of the upstream gradient it produced and holds *partial* gradients of the replicated inputs,
+  which are summed with one all-reduce each.
+
+Collectives are NCCL's (NVLink / NVSwitch); tensors are in local HBM before any kernel reads them.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .flash_bevpool import _host_values, flash_bevpool
+
+
+def even_slice(n: int, world: int, rank: int) -> Tuple[int, int]:
+    """Contiguous [begin, end) share of ``n`` items for ``rank``; the first ``n % world`` ranks get one more."""
+    if world <= 0 or not 0 <= rank < world:
+        raise ValueError(f"rank {rank} outside world of {world}")
+    base, extra = divmod(n, world)
+    begin = rank * base + min(rank, extra)
+    return begin, begin + base + (1 if rank < extra else 0)
+
+
+def batch_slice(batch: int, world: int, rank: int) -> Tuple[int, int]:
+    return even_slice(batch, world, rank)
+
+
+def row_slice(rows: int, world: int, rank: int) -> Tuple[int, int]:
+    return even_slice(rows, world, rank)
+
+
+def _world(group) -> Tuple[int, int]:
+    if not dist.is_available() or not dist.is_initialized():
+        return 1, 0
+    return dist.get_world_size(group), dist.get_rank(group)
+
+
+def gather_batch(local_out: torch.Tensor, batch: int, group=None) -> torch.Tensor:
+    """All ranks' batch slices -> the whole ``[batch, Y, X, C]`` tensor on every rank."""
+    world, rank = _world(group)
+    if world == 1:
+        return local_out
+    per = -(-batch // world)  # slices are padded to the largest one so that one collective suffices
+    pad = local_out.new_zeros((per,) + tuple(local_out.shape[1:]))
+    pad[: local_out.shape[0]] = local_out
+    full = local_out.new_empty((world * per,) + tuple(local_out.shape[1:]))
+    dist.all_gather_into_tensor(full, pad, group=group)
+    parts = []
+    for r in range(world):
+        b0, b1 = batch_slice(batch, world, r)
+        parts.append(full[r * per: r * per + (b1 - b0)])
+    return torch.cat(parts, dim=0)
+
+
+def gather_rows(local_rows: torch.Tensor, rows: int, group=None) -> torch.Tensor:
+    """Row shards ``[B, rows_r, X, C]`` of every rank -> ``[B, rows, X, C]`` on every rank.
+
+    With B = 1 and ``rows`` divisible by the world size the gathered buffer already is the result;
+    otherwise shards are padded to the largest one and stitched together."""
+    world, rank = _world(group)
+    if world == 1:
+        return local_rows
+    B = local_rows.shape[0]
+    per = -(-rows // world)
+    if B == 1 and rows % world == 0:
+        full = local_rows.new_empty((1, rows) + tuple(local_rows.shape[2:]))
+        dist.all_gather_into_tensor(full.view((rows,) + tuple(local_rows.shape[2:])),
+                                    local_rows.reshape((per,) + tuple(local_rows.shape[2:])).contiguous(), group=group)
+        return full
+    pad = local_rows.new_zeros((B, per) + tuple(local_rows.shape[2:]))
+    pad[:, : local_rows.shape[1]] = local_rows
+    full = local_rows.new_empty((world * B, per) + tuple(local_rows.shape[2:]))  # rank-major along dim 0
+    dist.all_gather_into_tensor(full, pad, group=group)
+    full = full.view((world, B, per) + tuple(local_rows.shape[2:]))
+    parts = []
+    for r in range(world):
+        y0, y1 = row_slice(rows, world, r)
+        parts.append(full[r, :, : y1 - y0])
+    return torch.cat(parts, dim=1)
+
+
+class _RowShardedPool(torch.autograd.Function):
+    """Row-sharded operator with the all-gather in the forward and the gradient all-reduce in the backward."""
+
+    @staticmethod
+    def forward(ctx, image_feats, depth_params, local_fn, rows, group):
+        world, rank = _world(group)
+        y0, y1 = row_slice(rows, world, rank)
+        with torch.enable_grad():
+            f = image_feats.detach().requires_grad_(image_feats.requires_grad)
+            d = depth_params.detach().requires_grad_(depth_params.requires_grad)
+            local = local_fn(f, d, (y0, y1))  # [B, Y, X, C] with only rows y0:y1 filled
+        ctx.local, ctx.f, ctx.d, ctx.range, ctx.group = local, f, d, (y0, y1), group
+        return gather_rows(local[:, y0:y1].contiguous(), rows, group)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        y0, y1 = ctx.range
+        mine = torch.zeros_like(ctx.local)
+        mine[:, y0:y1] = grad_out[:, y0:y1]  # rows this rank produced; the other rows belong to other ranks
+        wanted = [t for t in (ctx.f, ctx.d) if t.requires_grad]
+        grads = torch.autograd.grad(ctx.local, wanted, mine, allow_unused=True) if wanted else ()
+        out = []
+        it = iter(grads)
+        for t in (ctx.f, ctx.d):
+            if not t.requires_grad:
+                out.append(None)
+                continue
+            g = next(it)
+            g = torch.zeros_like(t) if g is None else g.contiguous()
+            if _world(ctx.group)[0] > 1:
+                dist.all_reduce(g, group=ctx.group)  # partial gradients of the replicated inputs
+            out.append(g)
+        return out[0], out[1], None, None, None
+
+
+def flash_bevpool_rows(image_feats, depth_params, projection_matrices, feature_size, image_size, roi_range, grid_size,
+                       group=None, local_op: Optional[Callable] = None, **op_kwargs) -> torch.Tensor:
+    """The operator with its BEV rows split over the ranks of ``group``; returns the whole output on every rank.
+
+    ``image_feats`` / ``depth_params`` are replicated on all ranks.  ``local_op`` replaces ``flash_bevpool`` as
+    the per-rank compute (used by CPU tests of the plumbing); it is called as
+    ``local_op(image_feats, depth_params, ..., y_range=(y0, y1), **op_kwargs)``.
+    """
+    op = flash_bevpool if local_op is None else local_op
+    rows = int(_host_values(grid_size)[1])
+
+    def local_fn(f, d, y_range):
+        return op(f, d, projection_matrices, feature_size, image_size, roi_range, grid_size, y_range=y_range,
+                  **op_kwargs)
+
+    return _RowShardedPool.apply(image_feats, depth_params, local_fn, rows, group)
+
+
+def flash_bevpool_batch(image_feats, depth_params, projection_matrices, feature_size, image_size, roi_range,
+                        grid_size, batch: Optional[int] = None, gather: bool = False, group=None,
+                        local_op: Optional[Callable] = None, **op_kwargs) -> torch.Tensor:
+    """The operator on this rank's slice of the batch (the tensors passed in ARE the slice).
+
+    Nothing is exchanged unless ``gather=True``, which returns the whole ``[batch, Y, X, C]`` output on every
+    rank (``batch`` = size of the whole batch; not differentiable through the gather)."""
+    op = flash_bevpool if local_op is None else local_op
+    out = op(image_feats, depth_params, projection_matrices, feature_size, image_size, roi_range, grid_size,
+             **op_kwargs)
+    if not gather:
+        return out
+    if batch is None:
+        raise ValueError("gather=True needs the size of the whole batch")
+    return gather_batch(out.detach(), batch, group)
