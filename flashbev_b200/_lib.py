@@ -16,10 +16,13 @@ POOL_MEAN, POOL_SUM = 0, 1
 BWD_FEATS, BWD_DEPTH, BWD_LEGACY_DEPTH = 1, 2, 4
 DEV_BAD_FEATURE_SIZE = 1
 WORKSPACE_BYTES = 16
+STATIC_SCRATCH_BYTES = 16 << 20
+ERR_STATIC_LIMIT = 11
 
 # every symbol include/fbev.h declares
 EXPORTS = (
-    "fbev_forward", "fbev_backward", "fbev_backward_scratch_bytes", "fbev_debug_indices",
+    "fbev_forward", "fbev_backward", "fbev_backward_scratch_bytes", "fbev_backward_static_scratch",
+    "fbev_debug_indices",
     "fbev_flash_bevpool", "fbev_flash_bevpool_grad", "fbev_set_tuning", "fbev_probe_read",
     "fbev_strerror", "fbev_version",
 )
@@ -82,6 +85,8 @@ def load(build_if_missing: bool = True) -> ctypes.CDLL:
     lib.fbev_backward_scratch_bytes.restype = ctypes.c_size_t
     lib.fbev_backward.argtypes = [ctypes.POINTER(FbevProblem), vp, vp, vp, vp, ctypes.c_size_t, i32, vp]
     lib.fbev_backward.restype = i32
+    lib.fbev_backward_static_scratch.argtypes = [ctypes.POINTER(FbevProblem), vp, vp, vp, i32, vp]
+    lib.fbev_backward_static_scratch.restype = i32
     lib.fbev_debug_indices.argtypes = [ctypes.POINTER(FbevProblem), vp, vp, vp, vp, vp, vp]
     lib.fbev_debug_indices.restype = i32
     lib.fbev_flash_bevpool.argtypes = [i32] * 11 + [f32, f32] + [vp] * 5 + [i32] * 3 + [f32] * 6 + [vp, vp]

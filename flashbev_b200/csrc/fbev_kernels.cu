@@ -1345,6 +1345,7 @@ const char* fbev_strerror(int status) {
     case FBEV_ERR_SCRATCH: return "scratch buffer missing, misaligned or smaller than fbev_backward_scratch_bytes()";
     case FBEV_ERR_LAUNCH: return "the CUDA runtime refused a launch or memset (cudaGetLastError)";
     case FBEV_ERR_NO_DEVICE: return "no usable sm_100 device";
+    case FBEV_ERR_STATIC_LIMIT: return "the problem needs more float32 scratch than fbev_backward_static_scratch holds (FBEV_STATIC_SCRATCH_BYTES); use fbev_backward with caller scratch";
     default: return "unknown status";
   }
 }
@@ -1518,6 +1519,43 @@ int fbev_probe_read(const void* buf, size_t bytes, int repeats, void* sink, void
   probe_read_kernel<<<148 * 8, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const uint4*>(buf), bytes / 16, repeats, reinterpret_cast<unsigned*>(sink));
   return cudaGetLastError() == cudaSuccess ? FBEV_OK : FBEV_ERR_LAUNCH;
+}
+
+// ---------------------------------------------------------------------------
+// Backward without caller scratch
+// ---------------------------------------------------------------------------
+// Float32 accumulation area for 16-bit gradients that lives inside the library image.  Every GPU
+// that loads libfbev.so carries these bytes until the process exits, which is why the size is kept
+// small.  In host code the symbol below is only a handle: the device address must be asked for with
+// cudaGetSymbolAddress on the device in use (done once per device in fbev_backward_static_scratch).
+#define FBEV_STATIC_SCRATCH_LIMIT ((size_t)FBEV_STATIC_SCRATCH_BYTES)
+static __device__ __align__(256) unsigned char g_fbev_static_scratch[FBEV_STATIC_SCRATCH_BYTES];
+static void* g_fbev_static_scratch_addr[64] = {nullptr};  // device address of the array, per device ordinal
+
+int fbev_backward_static_scratch(const FbevProblem* p, const void* grad_out, void* grad_feats, void* grad_depth,
+                                 int flags, void* stream) {
+  const int rc = validate(p);
+  if (rc != FBEV_OK) return rc;
+  const size_t need = fbev_backward_scratch_bytes(p, flags);
+  if (need > FBEV_STATIC_SCRATCH_LIMIT) return FBEV_ERR_STATIC_LIMIT;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    cudaGetLastError();
+    return FBEV_ERR_NO_DEVICE;
+  }
+  if (g_fbev_static_scratch_addr[dev] == nullptr) {
+    // first call on this device: resolve the array's address in this device's copy of the module
+    void* addr = nullptr;
+    if (cudaGetSymbolAddress(&addr, g_fbev_static_scratch) != cudaSuccess || addr == nullptr) {
+      cudaGetLastError();
+      return FBEV_ERR_LAUNCH;
+    }
+    g_fbev_static_scratch_addr[dev] = addr;
+  }
+  // fbev_backward clears the part of the scratch it accumulates into, so what an earlier call left
+  // behind is never read
+  return fbev_backward(p, grad_out, grad_feats, grad_depth, g_fbev_static_scratch_addr[dev],
+                       FBEV_STATIC_SCRATCH_LIMIT, flags, stream);
 }
 
 }  // extern "C"

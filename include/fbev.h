@@ -54,7 +54,8 @@ enum {
   FBEV_ERR_RANGE = 7,       /* sizes exceed what the kernels index (see fbev_strerror) */
   FBEV_ERR_SCRATCH = 8,     /* scratch buffer missing or too small */
   FBEV_ERR_LAUNCH = 9,      /* the CUDA runtime refused a launch or a memset */
-  FBEV_ERR_NO_DEVICE = 10   /* no usable sm_100 device / wrong architecture */
+  FBEV_ERR_NO_DEVICE = 10,  /* no usable sm_100 device / wrong architecture */
+  FBEV_ERR_STATIC_LIMIT = 11 /* fbev_backward_static_scratch: problem larger than the built-in scratch */
 };
 
 /* bits a kernel may OR into the optional device status word */
@@ -128,6 +129,31 @@ size_t fbev_backward_scratch_bytes(const FbevProblem* p, int flags);
  * fbev_backward_scratch_bytes(); may be NULL when that is 0. */
 int fbev_backward(const FbevProblem* p, const void* grad_out, void* grad_feats, void* grad_depth,
                   void* scratch, size_t scratch_bytes, int flags, void* stream);
+
+/* Backward for callers that cannot hand over scratch memory.  (No counterpart in the reference,
+ * which only ever computes in float32 and so never needs a scratch buffer.)
+ *
+ * fbev_backward accumulates 16-bit gradients in float32 scratch the caller allocates.  Some callers
+ * have no way to allocate it: a perception process that reserves its whole device-memory budget at
+ * start-up and forbids cudaMalloc afterwards, or an operator hosted by a framework that owns the
+ * memory pool and gives plug-ins no allocator.  This entry point takes the same arguments minus the
+ * scratch and accumulates in an array that is part of the library image instead.  It allocates
+ * nothing: no cudaMalloc, no cudaFree, no library routine that allocates.
+ *
+ * Limits and rules:
+ *  - the problem's fbev_backward_scratch_bytes() must not exceed FBEV_STATIC_SCRATCH_BYTES, else
+ *    FBEV_ERR_STATIC_LIMIT is returned and nothing is launched (float32 problems need none and
+ *    always fit);
+ *  - the array costs FBEV_STATIC_SCRATCH_BYTES of device memory on every GPU that loads the library,
+ *    for the life of the process;
+ *  - the first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ *    that device current); make that first call outside any stream capture;
+ *  - all calls on a device share the one array.  Each call clears what it accumulates into, so
+ *    leftovers of earlier calls do no harm, but two calls that overlap on the GPU (different
+ *    streams, no ordering between them) corrupt each other's gradients: order them. */
+#define FBEV_STATIC_SCRATCH_BYTES (16u << 20)
+int fbev_backward_static_scratch(const FbevProblem* p, const void* grad_out, void* grad_feats, void* grad_depth,
+                                 int flags, void* stream);
 
 /* Integer decisions of every (b, n, y, x, z) candidate, for bit-exact checks:
  * texel indices after clamping (:147-154), depth bin (categorical, else -1),

@@ -27,14 +27,15 @@ def rel_err(a, b):
 _MANTISSA_BITS = {"bf16": 7, "fp16": 10}
 
 
-def rel_err_quantised(a, b, dtype_name):
+def rel_err_quantised(a, b, dtype_name, ulps=0.5):
     """Relative error of a result that was rounded to a 16-bit type, after setting aside that one
     rounding: max(|a-b| - half_ulp(b), 0) / max|b|.  A bfloat16 result cannot be closer than half an ulp
-    (up to 2^-8 = 3.9e-3 of its value) to an unrounded reference, so that part is not an error of the kernel."""
+    (up to 2^-8 = 3.9e-3 of its value) to an unrounded reference, so that part is not an error of the kernel.
+    ``ulps`` = 0.5 for a rounded result against an unrounded reference, 1.0 for two rounded results."""
     a = np.asarray(a, dtype=np.float64)
     b = np.asarray(b, dtype=np.float64)
     mag = np.maximum(np.abs(b), 2.0 ** -24)
-    half_ulp = 2.0 ** (np.floor(np.log2(mag)) - _MANTISSA_BITS[dtype_name] - 1)
+    half_ulp = ulps * 2.0 ** (np.floor(np.log2(mag)) - _MANTISSA_BITS[dtype_name])
     denom = np.abs(b).max()
     return float(np.maximum(np.abs(a - b) - half_ulp, 0.0).max() / (denom if denom > 0 else 1.0))
 

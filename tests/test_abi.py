@@ -84,7 +84,7 @@ def test_validation_status_codes():
     p = _problem()
     assert lib.fbev_forward(ctypes.byref(p), None, None, None) == 1
     assert _lib.strerror(99) == "unknown status"
-    for code in range(0, 11):
+    for code in range(0, 12):
         assert _lib.strerror(code) != "unknown status"
 
 
