@@ -39,6 +39,9 @@ import torch  # noqa: E402
 
 from flashbev_b200 import synth  # noqa: E402
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one fwd_kernel launch on the default workload, from the ncu
+# capture summarised in profiles/fwd_kernel_cfg2_z8.md (the output stays in L2 until it is evicted later)
+NCU_DRAM_BYTES_PER_LAUNCH = {"cfg2": 1424384}
 METRIC = "bev_pool_forward_cells_per_s"
 UNIT = "BEV cells/s"
 
@@ -135,6 +138,51 @@ def cpu_forward_rate(w, mode, threads, min_seconds, min_reps=2):
     return times
 
 
+def reference_cuda_kernel_us(w):
+    """Device time of the reference's own forward kernel (flash_bevpool_cuda.cu:6, launched through
+    flash_bevpool(), :757) on this box, when a GPU is present and oracle/_ref was built from a reference checkout.
+    Float32, parametric laplace depth, mean pooling: the only mode the reference has.  Informational."""
+    path = os.path.join(ROOT, "oracle", "_ref", "libflashbev_ref.so")
+    if not (os.path.exists(path) and torch.cuda.is_available()):
+        return {"available": False, "why": "no GPU or oracle/_ref not built"}
+    import numpy as np
+    ref = ctypes.CDLL(path)
+    vp, i32, f32c = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+    ref.flashbev_ref_forward.argtypes = [i32] * 7 + [f32c, f32c] + [vp] * 5 + [i32] * 3 + [f32c] * 6 + [vp]
+    dev = torch.device("cuda", 0)
+    wp = synth.workload(w.name, dtype="fp32")
+    inp = {k: v.to(dev) for k, v in synth.make_inputs(wp, "parametric", batch_slice=(0, 1)).items()}
+    roi = [float(v) for v in inp["roi_range"].tolist()]
+    vs = [float((np.float32(roi[2 * i + 1]) - np.float32(roi[2 * i])) / np.float32(g)) for i, g in enumerate(wp.grid)]
+    out = torch.zeros(1, wp.Y, wp.X, wp.C, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def call():  # launches on the legacy default stream, as the reference does
+        rc = ref.flashbev_ref_forward(out.numel(), wp.C, wp.N, 1, 1, 0, 0, 1e-6, 1e-6, inp["depth_params"].data_ptr(),
+                                      inp["image_feats"].data_ptr(), inp["projection_matrices"].data_ptr(),
+                                      inp["feature_size"].data_ptr(), inp["image_size"].data_ptr(), wp.X, wp.Y, wp.Z,
+                                      vs[0], vs[1], vs[2], roi[0], roi[2], roi[4], out.data_ptr())
+        if rc:
+            raise RuntimeError(f"reference launch failed: {rc}")
+
+    null = torch.cuda.default_stream(dev)
+    with torch.cuda.stream(null):
+        for _ in range(5):
+            call()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(50):
+            flush.zero_()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record(null)
+            call()
+            e.record(null)
+            torch.cuda.synchronize()
+            times.append(s.elapsed_time(e) * 1e3)
+    return {"available": True, "forward_us_median": statistics.median(times), "forward_us_min": min(times),
+            "mode": "float32, laplace, mean pooling, optimize_z_precompute=False, L2 flushed between launches"}
+
+
 def reference_arm(args, rank):
     """CPU implementation of the path on the host cores (the oracle port, OpenMP over BEV rows)."""
     if rank != 0:
@@ -157,6 +205,7 @@ def reference_arm(args, rank):
     dt = (time.perf_counter() - t0) / args.steps
     cells = w.X * w.Y
     value = cells / dt
+    ref_gpu = reference_cuda_kernel_us(w)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
@@ -167,6 +216,7 @@ def reference_arm(args, rank):
                                    f"float32 oracle, OpenMP over BEV rows; host has {os.cpu_count()} logical CPUs"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+        "extra": {"reference_cuda_kernel": ref_gpu},
     }
     print(json.dumps(line), flush=True)
 
@@ -284,6 +334,23 @@ def main():
             extra["fwd_bwd_us"] = ms_fb * 1e3
             extra["fwd_bwd_note"] = "forward + backward (gradients for features and depth), device time, L2 flushed"
 
+            # the reference's own mode on the same shapes (float32, parametric laplace depth, mean pooling), for
+            # comparison with the reference CUDA kernel that `--impl reference` times on the same box
+            wp = synth.workload(args.workload, dtype="fp32")
+            inp_p = {k: v.to(device) for k, v in synth.make_inputs(wp, "parametric", batch_slice=(0, Bl)).items()}
+            prob_p, keep_p = make_problem(inp_p["depth_params"], inp_p["image_feats"], inp_p["projection_matrices"],
+                                          inp_p["feature_size"], inp_p["image_size"], inp_p["roi_range"],
+                                          inp_p["grid_size"], DepthSpec(1), 1e-6, 1e-6)
+            out_p = torch.empty(Bl, w.Y, w.X, w.C, dtype=torch.float32, device=device)
+
+            def fwd_param():
+                rc = lib.fbev_forward(ctypes.byref(prob_p), out_p.data_ptr(), None, stream)
+                if rc:
+                    raise RuntimeError(_lib.strerror(rc))
+
+            ms_p, _ = timed(fwd_param, max(10, args.steps // 5), 5)
+            extra["fwd_us_reference_mode_fp32_laplace_mean"] = ms_p * 1e3
+
             # back-to-back launches with warm L2 (what a model sees when the features were just produced)
             for _ in range(20):
                 fwd_raw()
@@ -352,7 +419,8 @@ def main():
                    "l2": "flushed between steps (256 MiB write)", "timing": "CUDA events around every launch",
                    "parallelism": f"batch samples sharded over {world} GPU(s), no data-path collective"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                     "frac": achieved / hbm_peak, "traffic": None, "peak_kind": f"of {peak_kind}",
+                     "frac": achieved / hbm_peak,
+                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(args.workload) if Bl == 1 else None, "peak_kind": f"of {peak_kind}",
                      "algorithmic_bytes_per_launch": alg_bytes, "kernel": "fwd_kernel"},
         "roofline_gather": {"bound": "l2", "achieved": gather_bytes / (ms_fwd * 1e-3) / 1e9, "peak": l2_gbs,
                             "unit": "GB/s", "frac": (gather_bytes / (ms_fwd * 1e-3) / 1e9 / l2_gbs) if l2_gbs else None,

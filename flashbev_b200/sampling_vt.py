@@ -129,8 +129,9 @@ class SamplingVT(nn.Module):
 
     def forward_depth(self, x):
         depth_params = self.depth_network(x)
-        depth_params[:, 1] += 0.1  # keeps sigma away from zero (sampling_vt.py:220-223)
-        return depth_params
+        # sigma + 0.1 keeps it away from zero (sampling_vt.py:220-223); out of place, so that the ReLU output
+        # autograd saved stays intact and the module can be trained
+        return depth_params + depth_params.new_tensor([0.0, 0.1]).view(1, 2, 1, 1)
 
     def forward(self, input, images=None, img_meta=None, lidar_cloud=None, depth_from_lidar=None):
         x = input[0]
