@@ -120,6 +120,15 @@ def physical_gpu_index(local_rank):
     return local_rank
 
 
+def host_thread_count():
+    """Threads for the CPU runs: the cores this process may use.  (torchrun exports OMP_NUM_THREADS=1, which
+    would otherwise pin the OpenMP oracle to one thread; the count is passed to it explicitly.)"""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def cpu_forward_rate(w, mode, threads, min_seconds, min_reps=2):
     """Times the CPU oracle's forward on the same workload (one sample); returns cells/s and the run's facts."""
     from oracle import oracle as O
@@ -189,8 +198,7 @@ def reference_arm(args, rank):
         return
     from oracle import oracle as O
     w = synth.workload(args.workload)
-    threads = O.host_threads()
-    O.forward  # noqa: B018  (import check)
+    threads = host_thread_count()
     inp = synth.make_inputs(w, args.mode, batch_slice=(0, 1))
     p = O.Problem(
         feats=inp["image_feats"].float().numpy(), depth=inp["depth_params"].float().numpy(),
@@ -433,7 +441,7 @@ def main():
                        "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e_max}
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         from oracle import oracle as O
-        threads = O.host_threads()
+        threads = host_thread_count()
         times = cpu_forward_rate(w, args.mode, threads, min_seconds=8.0)
         line["cpu_baseline"] = {
             "value": w.X * w.Y / statistics.median(times), "unit": UNIT, "cores": threads, "kind": "port",

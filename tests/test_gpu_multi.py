@@ -1,0 +1,78 @@
+"""Two-GPU test of row and batch sharding over NCCL (skipped on a single-GPU box): every rank must end up
+with exactly what one GPU computes alone, and the row-sharded backward with the summed partial gradients."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from flashbev_b200 import flash_bevpool, sharding, synth
+        w = synth.workload("cfg5", X=128, Y=96, Z=8, C=64)
+        kw = dict(depth_distribution=2, depth_bin_range=(w.d0, w.delta), depth_weight_threshold=0.0)
+        inp = {k: v.to(dev) for k, v in synth.make_inputs(w, "categorical", dtype="fp32").items()}
+        go = synth.upstream_grad(w).to(dev)
+        # one GPU alone
+        f0 = inp["image_feats"].clone().requires_grad_(True)
+        d0 = inp["depth_params"].clone().requires_grad_(True)
+        alone = flash_bevpool(f0, d0, *[inp[k] for k in ("projection_matrices", "feature_size", "image_size",
+                                                          "roi_range", "grid_size")], **kw)
+        alone.backward(go)
+        # rows over the ranks
+        f1 = inp["image_feats"].clone().requires_grad_(True)
+        d1 = inp["depth_params"].clone().requires_grad_(True)
+        rows = sharding.flash_bevpool_rows(f1, d1, inp["projection_matrices"], inp["feature_size"], inp["image_size"],
+                                           inp["roi_range"], inp["grid_size"], **kw)
+        rows.backward(go)
+        ok_rows = bool(torch.equal(rows, alone))
+        scale = float(f0.grad.abs().max())
+        ok_gf = float((f1.grad - f0.grad).abs().max()) < 1e-5 * scale
+        ok_gd = float((d1.grad - d0.grad).abs().max()) < 1e-5 * float(d0.grad.abs().max())
+        # batch over the ranks
+        wb = synth.workload("cfg4", B=4)
+        whole = {k: v.to(dev) for k, v in synth.make_inputs(wb, "categorical").items()}
+        b0, b1 = sharding.batch_slice(wb.B, world, rank)
+        part = {k: v.to(dev) for k, v in synth.make_inputs(wb, "categorical", batch_slice=(b0, b1)).items()}
+        full = flash_bevpool(**whole, **kw)
+        gathered = sharding.flash_bevpool_batch(part["image_feats"], part["depth_params"], part["projection_matrices"],
+                                                part["feature_size"], part["image_size"], part["roi_range"],
+                                                part["grid_size"], batch=wb.B, gather=True, **kw)
+        ok_batch = bool(torch.equal(gathered, full))
+        torch.cuda.synchronize()
+        results.put((rank, ok_rows, ok_gf, ok_gd, ok_batch))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_row_and_batch_sharding_over_nccl():
+    ctx = mp.get_context("spawn")
+    results = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, results)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = [results.get(timeout=300) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for rank, ok_rows, ok_gf, ok_gd, ok_batch in got:
+        assert ok_rows and ok_gf and ok_gd and ok_batch, (rank, ok_rows, ok_gf, ok_gd, ok_batch)
