@@ -313,10 +313,17 @@ __host__ __device__ inline size_t fwd_warp_bytes(int CPW, int cap) { return 256 
 // already multiplied by the depth weight.  The channel phase reads two texels per record instead of
 // four per sample, which is some 2.5 to 5 times fewer gathers for the benchmark shapes.  Runs do not
 // extend across the 32 candidates of one round; that only costs merges, never correctness.
-template <typename T, bool WRITE = true>
+// SAMPLES (depth-gradient kernel): every accepted sample is also kept, per cell, as three uint4
+//   [0] bilinear weights w00 w01 w10 w11
+//   [1] element index of depth[(v0,u0)][0], element distance to u1, to v1, depth bin (or -1)
+//   [2] positions of the row records holding its v0 and its v1 texels (low / high 16 bits), depth
+//       weight, d weight / d mean, d weight / d sigma
+// in `samp` ([CPW][cap] records), counted in sSmp.
+template <typename T, bool WRITE = true, bool SAMPLES = false>
 __device__ __forceinline__ void row_list_phase(const Dev& p, const Tile& t, const BlockHeader& h, unsigned vis, unsigned cpt, int t0, int r0,
                                                int r1, const float vs[3], const float vmin[3], int image_h,
-                                               int image_w, int* sLen, int* sCnt, uint4* recs, int lane) {
+                                               int image_w, int* sLen, int* sCnt, uint4* recs, int lane,
+                                               uint4* samp = nullptr, int* sSmp = nullptr) {
   const int per = r1 - r0;
   const int total = p.CPW * per;
   const int tile_cells = p.TX * p.TY;
@@ -330,6 +337,8 @@ __device__ __forceinline__ void row_list_phase(const Dev& p, const Tile& t, cons
     unsigned tex = 0, kk = 0;
     int fw = 0;
     float A0 = 0.0f, A1 = 0.0f, B0 = 0.0f, B1 = 0.0f;
+    Sample s;
+    unsigned dep00 = 0;
     if (q < total) {
       cl = fast_div(q, inv_per);
       const int r = r0 + (q - cl * per);
@@ -342,12 +351,12 @@ __device__ __forceinline__ void row_list_phase(const Dev& p, const Tile& t, cons
         const int fh = h.fs[n * 2];
         fw = h.fs[n * 2 + 1];
         const float vx = centre(x, vs[0], vmin[0]), vy = centre(y, vs[1], vmin[1]), vz = centre(z, vs[2], vmin[2]);
-        Sample s;
         if (geometry(h.P + n * 12, vx, vy, vz, image_h, image_w, fh, fw, p.eps, s)) {
           const size_t texbase = ((size_t)t.b * p.N + n) * (size_t)fh * fw;
-          ok = depth_weight<T, false>(p, reinterpret_cast<const T*>(p.depth) + texbase * p.D, fw, s);
+          ok = depth_weight<T, SAMPLES>(p, reinterpret_cast<const T*>(p.depth) + texbase * p.D, fw, s);
           if (ok) {
             tex = (unsigned)(texbase + (size_t)s.v0 * fw + s.u0);
+            dep00 = tex * (unsigned)p.D;
             const unsigned du = (unsigned)(s.u1 - s.u0), dvf = (unsigned)(s.v1 - s.v0);
             kk = (unsigned)cl | ((unsigned)ci << 4) | (du << 28) | (dvf << 29) | (1u << 31);
             A0 = s.w00 * s.wgt;
@@ -404,15 +413,41 @@ __device__ __forceinline__ void row_list_phase(const Dev& p, const Tile& t, cons
     const unsigned seg = (hi >= 32 ? kFull : ((1u << hi) - 1u)) & ~((1u << lo) - 1u);
     const int before = sLen[cl];
     __syncwarp();
+    const int pos0 = before + __popc(m1 & seg & lt) + __popc(m2 & seg & lt);
+    const int pos_a = emit_a ? pos0 : -1;                    // tail lanes: where the run's records go
+    const int pos_b = emit_b ? pos0 + (emit_a ? 1 : 0) : -1;
     if (WRITE && tail) {
-      int pos = before + __popc(m1 & seg & lt) + __popc(m2 & seg & lt);
       uint4* rec = recs + (size_t)cl * rstride;
       const unsigned du = (kk >> 28) & 1u;
       // chunk index of texel (row, u0), chunk distance to (row, u1), weights
-      if (emit_a) rec[pos++] = make_uint4(tex * cpt, du * cpt, __float_as_uint(A0), __float_as_uint(A1));
+      if (emit_a) rec[pos_a] = make_uint4(tex * cpt, du * cpt, __float_as_uint(A0), __float_as_uint(A1));
       if (emit_b)
-        rec[pos] = make_uint4((tex + (unsigned)fw) * cpt, du * cpt, __float_as_uint(B0 + (absorb_prev ? pA0 : 0.0f)),
-                              __float_as_uint(B1 + (absorb_prev ? pA1 : 0.0f)));
+        rec[pos_b] = make_uint4((tex + (unsigned)fw) * cpt, du * cpt, __float_as_uint(B0 + (absorb_prev ? pA0 : 0.0f)),
+                                __float_as_uint(B1 + (absorb_prev ? pA1 : 0.0f)));
+    }
+    if (SAMPLES) {
+      // every sample learns which records hold its texels: its run's tail lane knows
+      const unsigned tailm = __ballot_sync(kFull, tail);
+      const unsigned ahead = tailm >> lane;                  // bit 0: me
+      const int tl = ahead ? lane + __ffs((int)ahead) - 1 : lane;
+      const int run_a = __shfl_sync(kFull, pos_a, tl), run_b = __shfl_sync(kFull, pos_b, tl);
+      // a run whose v0 part was taken over by the next run finds it in that run's v1 record
+      const unsigned after = tl < 31 ? tailm >> (tl + 1) : 0u;
+      const int ntl = after ? tl + 1 + __ffs((int)after) - 1 : tl;
+      const int next_b = __shfl_sync(kFull, pos_b, ntl);
+      if (ok) {
+        const int my_a = run_a >= 0 ? run_a : next_b;
+        const int my_b = has_b ? run_b : my_a;               // v1 == v0: both parts sit in the v0 record
+        const int spos = sSmp[cl] + __popc(okm & seg & lt);
+        uint4* sr = samp + ((size_t)cl * p.cap + spos) * 3;
+        const unsigned du = (kk >> 28) & 1u;
+        sr[0] = make_uint4(__float_as_uint(s.w00), __float_as_uint(s.w01), __float_as_uint(s.w10), __float_as_uint(s.w11));
+        sr[1] = make_uint4(dep00, du * (unsigned)p.D, has_b ? (unsigned)(fw * p.D) : 0u, (unsigned)s.k);
+        sr[2] = make_uint4((unsigned)my_a | ((unsigned)my_b << 16), __float_as_uint(s.wgt), __float_as_uint(s.dmean),
+                           __float_as_uint(s.dsigma));
+      }
+      __syncwarp();
+      if (q < total && lane == lo) sSmp[cl] += __popc(okm & seg);
     }
     if (q < total && lane == lo) {
       sLen[cl] = before + __popc(m1 & seg) + __popc(m2 & seg);
@@ -625,6 +660,304 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_feats_kernel(const __gr
   loop.end(p);
 }
 
+// ---------------------------------------------------------------------------
+// Feature gradient, texel-stationary
+// ---------------------------------------------------------------------------
+// d_feats[texel, c] = sum over the cells that sampled the texel of  g_cell[c] * inv_cell * weight.
+// A scatter with float atomics is bound by the atomic rate of the L2: neighbouring cells hit the same
+// few texels (a 12 x 8 tile of cfg2 makes some 2000 texel updates on fewer than 100 distinct texels
+// per camera).  This kernel therefore turns the scatter of a tile into a gather:
+//   1. list phase as in the forward (merged row records), every record becomes two entries
+//      {texel key, cell of the tile, weight} in a block-wide array;
+//   2. the entries are counting-sorted by texel key (shared-memory integer atomics);
+//   3. one lane group per texel walks that texel's entries, gathers the cells' upstream gradient
+//      chunks (L1-resident: the tile's rows of dO) into float32 registers, and issues ONE 16-byte
+//      reduction per chunk for the whole tile.
+// Keys index the rectangles camera_rect() predicts per visible camera.  An entry outside its
+// rectangle, a camera whose rectangle does not fit the key space, or an entry beyond the array's
+// capacity is added to global memory directly by the lane that found it (slow, rare: only tiles right
+// next to the rig have footprints that large).
+constexpr int kFeatKeys = 3072;     // texel keys per tile (all visible cameras together)
+constexpr int kFeatEntries = 4096;  // entries per tile
+
+__host__ __device__ inline size_t feats_block_bytes() {
+  return (size_t)kFeatEntries * 8 + (size_t)kFeatEntries * 2 + (size_t)(kFeatKeys + 1) * 4 + 64;
+}
+
+// Rectangle of feature texels the cells of a tile can touch in one camera, from the tile's eight box
+// corners: u and v are ratios of affine functions of the voxel centre, so over a box on which the
+// depth stays positive their extremes sit at the corners.  A hint only: every entry is checked.
+__device__ __forceinline__ bool camera_rect(const float* P, int fh, int fw, float bx0, float bx1, float by0, float by1,
+                                            float bz0, float bz1, int image_h, int image_w, int& r0, int& r1,
+                                            int& c0, int& c1) {
+  const float inf = __int_as_float(0x7f800000);
+  float umin = inf, umax = -inf, vmin = inf, vmax = -inf;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const float x = (c & 1) ? bx1 : bx0, y = (c & 2) ? by1 : by0, z = (c & 4) ? bz1 : bz0;
+    const float ld = fmaf(P[10], z, fmaf(P[9], y, P[8] * x)) + P[11];
+    if (!(ld > 1e-2f)) return false;
+    const float u = (fmaf(P[2], z, fmaf(P[1], y, P[0] * x)) + P[3]) / ld / (float)image_w * (float)fw;
+    const float v = (fmaf(P[6], z, fmaf(P[5], y, P[4] * x)) + P[7]) / ld / (float)image_h * (float)fh;
+    umin = fminf(umin, u);
+    umax = fmaxf(umax, u);
+    vmin = fminf(vmin, v);
+    vmax = fmaxf(vmax, v);
+  }
+  if (!(umax >= -2.0f && umin <= (float)fw + 2.0f && vmax >= -2.0f && vmin <= (float)fh + 2.0f)) return false;
+  c0 = max(0, (int)floorf(fmaxf(umin, 0.0f)) - 1);
+  c1 = min(fw - 1, (int)floorf(fminf(umax, (float)fw)) + 2);
+  r0 = max(0, (int)floorf(fmaxf(vmin, 0.0f)) - 1);
+  r1 = min(fh - 1, (int)floorf(fminf(vmax, (float)fh)) + 2);
+  return c0 <= c1 && r0 <= r1;
+}
+
+template <typename T, int V>
+__global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_feats_sorted_kernel(const __grid_constant__ Dev p) {
+  constexpr int E = Chunk<T>::E;
+  extern __shared__ __align__(16) unsigned char smem[];
+  const BlockHeader h = carve(smem, p.N);
+  __shared__ int s_tile[2];
+  __shared__ int4 s_rect[32];        // per camera: first row, first column, columns, first key (-1: no keys)
+  __shared__ int s_rows[32];         // per camera: rows of the rectangle
+  __shared__ unsigned s_texbase[32]; // per camera: texel index of (0, 0)
+  __shared__ int s_nent, s_nkeys;
+  __shared__ int s_wsum[kMaxWarps];
+  float vs[3], vmin[3];
+  voxel_frame(p, vs, vmin);
+  const int image_h = __ldg(p.isize), image_w = __ldg(p.isize + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
+  unsigned char* wa = h.warp_area + (size_t)warp * fwd_warp_bytes(p.CPW, p.cap);
+  int* sLen = reinterpret_cast<int*>(wa);
+  int* sCnt = sLen + 32;
+  uint4* recs = reinterpret_cast<uint4*>(wa + 256);
+  const int rstride = row_stride(p.cap);
+  unsigned char* blk = h.warp_area + (size_t)nwarps * fwd_warp_bytes(p.CPW, p.cap);
+  uint2* ent = reinterpret_cast<uint2*>(blk);                                     // {key | cell << 16, weight}
+  unsigned short* order = reinterpret_cast<unsigned short*>(ent + kFeatEntries);  // entries sorted by key
+  int* hist = reinterpret_cast<int*>(order + kFeatEntries);                       // counts, then offsets / ends
+
+  const int g = lane / p.GL, lg = lane - g * p.GL;
+  const bool lane_used = g < p.CPW;
+  const int cpt = p.GL * V;  // 16-byte chunks per texel
+  const int tile_cells = p.TX * p.TY;
+  const int ngroups = (tile_cells + p.CPW - 1) / p.CPW;
+  const float inv_tx = 1.0f / (float)p.TX;
+  const bool mean_pool = p.pool == FBEV_POOL_MEAN;
+  int loaded_b = -1;
+  TileLoop loop;
+  loop.begin(p, s_tile);
+  for (int tile; (tile = loop.current(p)) >= 0; loop.advance()) {
+    const Tile t = tile_of(p, tile);
+    const unsigned vis = tile_visibility(p, t, h, vs, vmin, image_h, image_w, loaded_b);
+    const int ncand = __popc(vis) * p.Z;
+    const bool single_pass = ncand <= p.cap;
+
+    // ---- key space: one rectangle per visible camera (warp 0); clear the counts ----
+    if (warp == 0) {
+      int r0 = 0, r1 = -1, c0 = 0, c1 = -1;
+      bool have = false;
+      if (lane < p.N && ((vis >> lane) & 1u)) {
+        const float bx0 = centre(t.x0, vs[0], vmin[0]), bx1 = centre(t.x1 - 1, vs[0], vmin[0]);
+        const float by0 = centre(t.y0, vs[1], vmin[1]), by1 = centre(t.y1 - 1, vs[1], vmin[1]);
+        const float bz0 = centre(0, vs[2], vmin[2]), bz1 = centre(p.Z - 1, vs[2], vmin[2]);
+        have = camera_rect(h.P + lane * 12, h.fs[lane * 2], h.fs[lane * 2 + 1], bx0, bx1, by0, by1, bz0, bz1, image_h,
+                           image_w, r0, r1, c0, c1);
+      }
+      const int need = have ? (r1 - r0 + 1) * (c1 - c0 + 1) : 0;
+      int base = 0, mine = -1;
+      for (int n = 0; n < p.N; ++n) {  // cameras take their keys in index order; one that does not fit gets none
+        const int sz = __shfl_sync(kFull, need, n);
+        const bool fits = sz > 0 && base + sz <= kFeatKeys;
+        if (n == lane && fits) mine = base;
+        if (fits) base += sz;
+      }
+      if (lane < p.N) {
+        s_rect[lane] = make_int4(r0, c0, c1 - c0 + 1, mine);
+        s_rows[lane] = r1 - r0 + 1;
+        s_texbase[lane] = (unsigned)(((size_t)t.b * p.N + lane) * (size_t)h.fs[lane * 2] * h.fs[lane * 2 + 1]);
+      }
+      if (lane == 0) {
+        s_nkeys = base;
+        s_nent = 0;
+      }
+    }
+    for (int i = tid; i <= kFeatKeys; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+
+    // ---- list phase per group, records -> entries ----
+    for (int grp = warp; grp < ngroups; grp += nwarps) {
+      const int t0 = grp * p.CPW;
+      if (lane < p.CPW) sCnt[lane] = 0;
+      __syncwarp();
+      float inv_of_lane = 1.0f;  // lane c keeps 1 / count of cell c of the group (mean pooling)
+      if (mean_pool && !single_pass) {
+        for (int r0 = 0; r0 < ncand; r0 += p.cap) {
+          if (lane < p.CPW) sLen[lane] = 0;
+          __syncwarp();
+          row_list_phase<T, false>(p, t, h, vis, 1u, t0, r0, min(r0 + p.cap, ncand), vs, vmin, image_h, image_w, sLen,
+                                   sCnt, recs, lane);
+        }
+        if (lane < p.CPW) inv_of_lane = sCnt[lane] > 0 ? __fdiv_rn(1.0f, (float)sCnt[lane]) : 0.0f;
+      }
+      for (int r0 = 0; r0 < ncand; r0 += p.cap) {
+        if (lane < p.CPW) {
+          sLen[lane] = 0;
+          if (single_pass) sCnt[lane] = 0;
+        }
+        __syncwarp();
+        // cpt = 1: the records hold the texel index and u1 - u0 themselves
+        row_list_phase<T, true>(p, t, h, vis, 1u, t0, r0, min(r0 + p.cap, ncand), vs, vmin, image_h, image_w, sLen,
+                                sCnt, recs, lane);
+        if (mean_pool && single_pass && lane < p.CPW)
+          inv_of_lane = sCnt[lane] > 0 ? __fdiv_rn(1.0f, (float)sCnt[lane]) : 0.0f;
+        for (int c = 0; c < p.CPW; ++c) {
+          const int n = sLen[c];
+          const float inv = mean_pool ? __shfl_sync(kFull, inv_of_lane, c) : 1.0f;
+          const int tc = t0 + c;  // cell of the tile
+          for (int i = lane; i < n; i += 32) {
+            const uint4 r = recs[(size_t)c * rstride + i];
+            const unsigned tex = r.x, du = r.y;
+            float w0 = __uint_as_float(r.z) * inv, w1 = __uint_as_float(r.w) * inv;
+            if (du == 0u) {  // u1 == u0: one texel takes both weights
+              w0 += w1;
+              w1 = 0.0f;
+            }
+            // camera of the texel, its row and column
+            int cam = -1;
+            for (unsigned m = vis; m; m &= m - 1u) {
+              const int n2 = __ffs((int)m) - 1;
+              const unsigned tb = s_texbase[n2];
+              if (tex >= tb && tex - tb < (unsigned)(h.fs[n2 * 2] * h.fs[n2 * 2 + 1])) cam = n2;
+            }
+            int key = -1;
+            if (cam >= 0) {
+              const int fw = h.fs[cam * 2 + 1];
+              const int rel = (int)(tex - s_texbase[cam]);
+              const int row = fast_div(rel, 1.0f / (float)fw), col = rel - row * fw;
+              const int4 rc = s_rect[cam];
+              const int lr = row - rc.x, lc = col - rc.y;
+              if (rc.w >= 0 && lr >= 0 && lr < s_rows[cam] && lc >= 0 && lc + (int)du < rc.z) key = rc.w + lr * rc.z + lc;
+            }
+            const int want = 1 + (int)du;
+            int slot = -1;
+            if (key >= 0) {
+              slot = atomicAdd(&s_nent, want);
+              if (slot + want > kFeatEntries) {
+                // array full: this record goes the direct way; a slot it reserved below the capacity is
+                // marked void so that the sort never reads an unwritten entry
+                if (slot < kFeatEntries) ent[slot] = make_uint2(0xffffu, 0u);
+                slot = -1;
+              }
+            }
+            if (slot >= 0) {
+              ent[slot] = make_uint2((unsigned)key | ((unsigned)tc << 16), __float_as_uint(w0));
+              atomicAdd(&hist[key], 1);
+              if (du) {
+                ent[slot + 1] = make_uint2((unsigned)(key + 1) | ((unsigned)tc << 16), __float_as_uint(w1));
+                atomicAdd(&hist[key + 1], 1);
+              }
+            } else {
+              // direct: this lane alone adds g * w to the record's texel(s), chunk by chunk
+              const int ly = fast_div(tc, inv_tx), lx = tc - ly * p.TX;
+              const size_t cell = ((size_t)t.b * p.Y + t.y0 + ly) * p.X + t.x0 + lx;
+              for (int ch = 0; ch < cpt; ++ch) {
+                float gv[E];
+                load_chunk<T>(p.gout, p.out_f32, cell * cpt + ch, gv);
+                float* d0 = p.gfeat + ((size_t)tex * cpt + ch) * E;
+#pragma unroll
+                for (int e4 = 0; e4 < E; e4 += 4) {
+                  red_add4(d0 + e4, gv[e4] * w0, gv[e4 + 1] * w0, gv[e4 + 2] * w0, gv[e4 + 3] * w0);
+                  if (du)
+                    red_add4(d0 + (size_t)cpt * E + e4, gv[e4] * w1, gv[e4 + 1] * w1, gv[e4 + 2] * w1, gv[e4 + 3] * w1);
+                }
+              }
+            }
+          }
+        }
+        __syncwarp();
+      }
+    }
+    __syncthreads();
+
+    // ---- counting sort of the entries by key ----
+    const int nkeys = s_nkeys;
+    const int nent = min(s_nent, kFeatEntries);
+    {
+      const int chunk = (nkeys + (int)blockDim.x - 1) / (int)blockDim.x;
+      const int k0 = min(tid * chunk, nkeys), k1 = min(k0 + chunk, nkeys);
+      int local = 0;
+      for (int k = k0; k < k1; ++k) local += hist[k];
+      int incl = local;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int o = __shfl_up_sync(kFull, incl, off);
+        if (lane >= off) incl += o;
+      }
+      if (lane == 31) s_wsum[warp] = incl;
+      __syncthreads();
+      int run = incl - local;
+      for (int w2 = 0; w2 < warp; ++w2) run += s_wsum[w2];
+      for (int k = k0; k < k1; ++k) {  // counts -> first position of each key
+        const int c = hist[k];
+        hist[k] = run;
+        run += c;
+      }
+    }
+    __syncthreads();
+    for (int e = tid; e < nent; e += blockDim.x) {
+      const int key = (int)(ent[e].x & 0xffffu);
+      if (key < nkeys) order[atomicAdd(&hist[key], 1)] = (unsigned short)e;  // afterwards hist[key] = end of the key's entries
+    }
+    __syncthreads();
+
+    // ---- one lane group per texel: gather the cells' gradients, one reduction per chunk ----
+    const int G = nwarps * p.CPW;
+    for (int k = warp * p.CPW + g; k < nkeys + G; k += G) {  // same trip count for every lane of a warp
+      if (!(lane_used && k < nkeys)) continue;
+      const int start = k > 0 ? hist[k - 1] : 0, end = hist[k];
+      if (end <= start) continue;
+      float acc[V * E];
+#pragma unroll
+      for (int i = 0; i < V * E; ++i) acc[i] = 0.0f;
+      for (int e = start; e < end; ++e) {
+        const uint2 en = ent[order[e]];
+        const int tc = (int)(en.x >> 16);
+        const float w = __uint_as_float(en.y);
+        const int ly = fast_div(tc, inv_tx), lx = tc - ly * p.TX;
+        const size_t cell = ((size_t)t.b * p.Y + t.y0 + ly) * p.X + t.x0 + lx;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          float gv[E];
+          load_chunk<T>(p.gout, p.out_f32, cell * cpt + lg + j * p.GL, gv);
+#pragma unroll
+          for (int e2 = 0; e2 < E; ++e2) acc[j * E + e2] = fmaf(w, gv[e2], acc[j * E + e2]);
+        }
+      }
+      // texel of the key
+      unsigned tex = 0;
+      for (unsigned m = vis; m; m &= m - 1u) {
+        const int n2 = __ffs((int)m) - 1;
+        const int4 rc = s_rect[n2];
+        if (rc.w >= 0 && k >= rc.w && k < rc.w + s_rows[n2] * rc.z) {
+          const int rel = k - rc.w;
+          const int lr = fast_div(rel, 1.0f / (float)rc.z), lc = rel - lr * rc.z;
+          tex = s_texbase[n2] + (unsigned)((rc.x + lr) * h.fs[n2 * 2 + 1] + rc.y + lc);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        float* d0 = p.gfeat + ((size_t)tex * cpt + lg + j * p.GL) * E;
+#pragma unroll
+        for (int e4 = 0; e4 < E; e4 += 4)
+          red_add4(d0 + e4, acc[j * E + e4], acc[j * E + e4 + 1], acc[j * E + e4 + 2], acc[j * E + e4 + 3]);
+      }
+    }
+  }  // tiles
+  loop.end(p);
+}
+
 // Any channel count and alignment: one cell per warp, lanes stride over channels
 // with scalar loads.  Slow path for shapes the chunked kernel cannot take.
 template <typename T>
@@ -729,6 +1062,180 @@ __device__ __forceinline__ float group_sum(float v, int lg, int GL) {
     if (lg + off < GL) v += o;
   }
   return v;
+}
+
+// Depth-gradient kernel.  For every accepted sample
+//   parametric, analytic:  d_mean_ij  += inv * S * dwgt/dmean  * w_ij,  d_sigma_ij += inv * S * dwgt/dsigma * w_ij
+//   parametric, legacy:    both slots += inv * S * wgt * w_ij                          (flash_bevpool_cuda.cu:667-674)
+//   categorical:           d_prob[corner_ij, k] += inv * S * w_ij
+// with S = sum_c g_c f_c, f the bilinearly interpolated feature.  S is linear in the four corner
+// texels, S = sum_ij w_ij T_ij with T = <g, feature of the texel>, and the samples of a cell share
+// their texels exactly as in the forward.  So the kernel builds the forward's row records, computes T
+// once per record texel (two gathers, a dot product, a shuffle reduction over the group's lanes) and
+// then lets one lane per SAMPLE combine four T values and issue that sample's atomics.  Compared with
+// evaluating S per sample this reads 2.7 times fewer texels and spreads the atomics over all lanes.
+__host__ __device__ inline size_t depth_warp_bytes(int CPW, int cap) {
+  return 512 + (size_t)CPW * row_stride(cap) * 16 + (size_t)CPW * cap * 48;
+}
+
+template <typename T, int V>
+__global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_depth_kernel(const __grid_constant__ Dev p) {
+  constexpr int E = Chunk<T>::E;
+  extern __shared__ __align__(16) unsigned char smem[];
+  const BlockHeader h = carve(smem, p.N);
+  __shared__ int s_tile[2];
+  float vs[3], vmin[3];
+  voxel_frame(p, vs, vmin);
+  const int image_h = __ldg(p.isize), image_w = __ldg(p.isize + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  unsigned char* wa = h.warp_area + (size_t)warp * depth_warp_bytes(p.CPW, p.cap);
+  int* sLen = reinterpret_cast<int*>(wa);  // [32] row records per cell
+  int* sCnt = sLen + 32;                    // [32] accepted samples per cell, all passes
+  int* sSmp = sCnt + 32;                    // [32] sample records per cell, this pass
+  const int rstride = row_stride(p.cap);
+  uint4* recs = reinterpret_cast<uint4*>(wa + 512);
+  uint4* samp = recs + (size_t)p.CPW * rstride;
+
+  const int g = lane / p.GL, lg = lane - g * p.GL;
+  const bool lane_used = g < p.CPW;
+  const int cpt = p.GL * V;
+  const int tile_cells = p.TX * p.TY;
+  const int ngroups = (tile_cells + p.CPW - 1) / p.CPW;
+  const uint4* fl = reinterpret_cast<const uint4*>(p.feats) + lg;
+  const bool legacy = (p.flags & FBEV_BWD_LEGACY_DEPTH) != 0;
+  const bool mean_pool = p.pool == FBEV_POOL_MEAN;
+  int loaded_b = -1;
+  TileLoop loop;
+  loop.begin(p, s_tile);
+  for (int tile; (tile = loop.current(p)) >= 0; loop.advance()) {
+    const Tile t = tile_of(p, tile);
+    const unsigned vis = tile_visibility(p, t, h, vs, vmin, image_h, image_w, loaded_b);
+    const int ncand = __popc(vis) * p.Z;
+    const bool single_pass = ncand <= p.cap;
+
+    for (int grp = warp; grp < ngroups; grp += nwarps) {
+      const int t0 = grp * p.CPW;
+      const int tc = t0 + g;
+      const int ly = tc / p.TX, lx = tc - ly * p.TX;
+      const int x = t.x0 + lx, y = t.y0 + ly;
+      const bool cell_ok = lane_used && tc < tile_cells && x < t.x1 && y < t.y1;
+
+      float go[V * E];
+#pragma unroll
+      for (int i = 0; i < V * E; ++i) go[i] = 0.0f;
+      if (cell_ok) {
+        const size_t cell = ((size_t)t.b * p.Y + y) * p.X + x;
+#pragma unroll
+        for (int j = 0; j < V; ++j) load_chunk<T>(p.gout, p.out_f32, cell * cpt + lg + j * p.GL, go + j * E);
+      }
+      if (lane < p.CPW) sCnt[lane] = 0;
+      __syncwarp();
+      if (mean_pool && !single_pass) {  // the count of all passes is needed before the first contribution
+        for (int r0 = 0; r0 < ncand; r0 += p.cap) {
+          if (lane < p.CPW) sLen[lane] = 0;
+          __syncwarp();
+          row_list_phase<T, false>(p, t, h, vis, (unsigned)cpt, t0, r0, min(r0 + p.cap, ncand), vs, vmin, image_h,
+                                   image_w, sLen, sCnt, recs, lane);
+        }
+      }
+      // inverse count per cell of the group, kept by lane c for cell c
+      float inv_of_lane = 1.0f;
+      if (mean_pool && !single_pass && lane < p.CPW) {
+        const int cnt = sCnt[lane];
+        inv_of_lane = cnt > 0 ? __fdiv_rn(1.0f, (float)cnt) : 0.0f;
+      }
+
+      for (int r0 = 0; r0 < ncand; r0 += p.cap) {
+        if (lane < p.CPW) {
+          sLen[lane] = 0;
+          sSmp[lane] = 0;
+          if (single_pass) sCnt[lane] = 0;
+        }
+        __syncwarp();
+        row_list_phase<T, true, true>(p, t, h, vis, (unsigned)cpt, t0, r0, min(r0 + p.cap, ncand), vs, vmin, image_h,
+                                      image_w, sLen, sCnt, recs, lane, samp, sSmp);
+        if (mean_pool && single_pass && lane < p.CPW) {
+          const int cnt = sCnt[lane];
+          inv_of_lane = cnt > 0 ? __fdiv_rn(1.0f, (float)cnt) : 0.0f;
+        }
+        // ---- T = <g, texel> for the two texels of every row record; stored over the record's weights ----
+        const int n = cell_ok ? sLen[g] : 0;
+        int nmax = n;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) nmax = max(nmax, __shfl_xor_sync(kFull, nmax, off));
+        uint4* rec = recs + (size_t)g * rstride;
+        for (int i = 0; i < nmax; ++i) {
+          float d0 = 0.0f, d1 = 0.0f;
+          if (i < n) {
+            const uint4 r = rec[i];
+#pragma unroll
+            for (int j = 0; j < V; ++j) {
+              float f0[E], f1[E];
+              Chunk<T>::unpack(ldg16(fl + (r.x + j * p.GL)), f0);
+              Chunk<T>::unpack(ldg16(fl + (r.x + r.y + j * p.GL)), f1);
+#pragma unroll
+              for (int e = 0; e < E; ++e) {
+                d0 = fmaf(go[j * E + e], f0[e], d0);
+                d1 = fmaf(go[j * E + e], f1[e], d1);
+              }
+            }
+          }
+          d0 = group_sum(d0, lg, p.GL);
+          d1 = group_sum(d1, lg, p.GL);
+          if (i < n && lg == 0) {
+            rec[i].z = __float_as_uint(d0);
+            rec[i].w = __float_as_uint(d1);
+          }
+        }
+        __syncwarp();
+        // ---- one lane per sample: S from four T values, then the sample's atomics ----
+        for (int c = 0; c < p.CPW; ++c) {
+          const int ns = sSmp[c];
+          const float inv = mean_pool ? __shfl_sync(kFull, inv_of_lane, c) : 1.0f;
+          const uint4* rc = recs + (size_t)c * rstride;
+          for (int idx = lane; idx < ns; idx += 32) {
+            const uint4* sr = samp + ((size_t)c * p.cap + idx) * 3;
+            const uint4 sw = sr[0], sa = sr[1], sp = sr[2];
+            const float w00 = __uint_as_float(sw.x), w01 = __uint_as_float(sw.y), w10 = __uint_as_float(sw.z),
+                        w11 = __uint_as_float(sw.w);
+            const uint4 ra = rc[sp.x & 0xffffu], rb = rc[sp.x >> 16];
+            float S = w00 * __uint_as_float(ra.z);
+            S = fmaf(w10, __uint_as_float(ra.w), S);
+            S = fmaf(w01, __uint_as_float(rb.z), S);
+            S = fmaf(w11, __uint_as_float(rb.w), S);
+            const float sd = S * inv;
+            float* d00 = p.gdepth + sa.x;
+            float* d10 = d00 + sa.y;
+            float* d01 = d00 + sa.z;
+            float* d11 = d01 + sa.y;
+            if (p.mode == FBEV_DEPTH_CATEGORICAL) {
+              const int k = (int)sa.w;
+              atomicAdd(d00 + k, sd * w00);
+              atomicAdd(d01 + k, sd * w01);
+              atomicAdd(d10 + k, sd * w10);
+              atomicAdd(d11 + k, sd * w11);
+            } else {
+              const float wgt = __uint_as_float(sp.y);
+              const float cm = legacy ? wgt : __uint_as_float(sp.z);
+              const float cs = legacy ? wgt : __uint_as_float(sp.w);
+              atomicAdd(d00 + 0, sd * cm * w00);
+              atomicAdd(d00 + 1, sd * cs * w00);
+              atomicAdd(d01 + 0, sd * cm * w01);
+              atomicAdd(d01 + 1, sd * cs * w01);
+              atomicAdd(d10 + 0, sd * cm * w10);
+              atomicAdd(d10 + 1, sd * cs * w10);
+              atomicAdd(d11 + 0, sd * cm * w11);
+              atomicAdd(d11 + 1, sd * cs * w11);
+            }
+          }
+        }
+        __syncwarp();
+      }
+      __syncwarp();
+    }
+  }  // tiles
+  loop.end(p);
 }
 
 // Gradient kernel.  Same decomposition as the forward.  For every accepted sample
@@ -1278,6 +1785,26 @@ static int forward_t(const Plan& pl, const Dev& d, cudaStream_t st) {
 
 template <typename T>
 static int backward_feats_t(const Plan& pl, const Dev& d, cudaStream_t st) {
+  // measured: ahead of the direct kernel on small feature maps with many cells per texel, behind it otherwise
+  if (g_tuning.minb != 1 && (g_tuning.minb == 6 || ((long long)d.H * d.W <= 1024 && (long long)d.X * (d.y1 - d.y0) >= 30000)) &&
+      (long long)d.H * d.W < (1 << 21)) {
+    // texel-stationary kernel: eight warps, 12 x 8 tiles, block-wide entry array
+    Plan ps = pl;
+    Dev ds = d;
+    ps.warps = g_tuning.warps > 0 ? pl.warps : 8;
+    // about 20 (small feature maps) to 35 (large ones) entries per cell: keep a tile within the entry array
+    ds.TX = g_tuning.tx > 0 ? g_tuning.tx : 12;
+    ds.TY = g_tuning.ty > 0 ? g_tuning.ty : 4;
+    ds.tiles_x = (d.X + ds.TX - 1) / ds.TX;
+    ds.tiles_y = (d.y1 - d.y0 + ds.TY - 1) / ds.TY;
+    ps.blocks = ds.tiles_x * ds.tiles_y * d.B;
+    ps.smem = header_bytes(d.N) + (size_t)ps.warps * fwd_warp_bytes(ps.CPW, ps.cap) + feats_block_bytes();
+    switch (ps.V) {
+      case 1: return launch(bwd_feats_sorted_kernel<T, 1>, ps, ds, st);
+      case 2: return launch(bwd_feats_sorted_kernel<T, 2>, ps, ds, st);
+      default: return launch(bwd_feats_sorted_kernel<T, 4>, ps, ds, st);
+    }
+  }
   switch (pl.V) {
     case 1: return launch(bwd_feats_kernel<T, 1>, pl, d, st);
     case 2: return launch(bwd_feats_kernel<T, 2>, pl, d, st);
@@ -1295,6 +1822,22 @@ static int backward_t(const Plan& pl, Dev d, const Plan& plf, const Dev& df, cud
     if (rc != FBEV_OK) return rc;
     d.flags &= ~FBEV_BWD_FEATS;
     if (!(d.flags & FBEV_BWD_DEPTH)) return FBEV_OK;
+  }
+  // (categorical depth only: the parametric modes have two gradient slots per texel, and one lane per sample
+  // firing at them contends more than the per-group issue of the sample kernel below)
+  if (d.flags == (d.flags & (FBEV_BWD_DEPTH | FBEV_BWD_LEGACY_DEPTH)) && plf.chunked &&
+      (d.mode == FBEV_DEPTH_CATEGORICAL || g_tuning.minb == 5) &&
+      (unsigned long long)df.B * df.N * df.H * df.W * (unsigned long long)df.D < (1ull << 32)) {
+    // depth gradient alone: per-texel dot products on the forward's row records
+    Plan pld = plf;
+    Dev dd = df;
+    dd.flags = d.flags;
+    pld.smem = header_bytes(dd.N) + (size_t)pld.warps * depth_warp_bytes(pld.CPW, pld.cap);
+    switch (pld.V) {
+      case 1: return launch(bwd_depth_kernel<T, 1>, pld, dd, st);
+      case 2: return launch(bwd_depth_kernel<T, 2>, pld, dd, st);
+      default: return launch(bwd_depth_kernel<T, 4>, pld, dd, st);
+    }
   }
   switch (pl.V) {
     case 1: return launch(bwd_kernel<T, 1>, pl, d, st);
