@@ -253,6 +253,32 @@ def test_backward_channel_counts_without_16_byte_rows(cuda_device, C, dtype):
     backward_case(w, "laplace", cuda_device)
 
 
+@pytest.mark.parametrize("variant", [1, 5, 6])
+def test_backward_kernel_variants_agree_with_the_oracle(cuda_device, variant):
+    """The library picks between two feature-gradient kernels (direct reductions / texel-stationary gather) and
+    two depth-gradient kernels by shape; the tuning switch forces each of them on shapes it would not get."""
+    lib = _lib.load()
+    tall = synth.Workload("tall", B=1, N=6, C=16, H=8, W=22, D=24, X=30, Y=30, Z=40, xy_extent=30.0, d0=1.0, delta=1.5,
+                          dtype="fp32", seed=32)
+    try:
+        lib.fbev_set_tuning(0, 0, 0, 0, variant)
+        for mode in ("categorical", "laplace", "gaussian"):
+            backward_case(SMALL, mode, cuda_device, pool="mean")
+            backward_case(SMALL, mode, cuda_device, pool="sum", dtype="bf16")
+        backward_case(CFG3S, "categorical", cuda_device)
+        backward_case(tall, "categorical", cuda_device, pool="mean")   # several passes per cell
+        backward_case(tall, "laplace", cuda_device)
+    finally:
+        lib.fbev_set_tuning(0, 0, 0, 0, 0)
+
+
+def test_backward_headline_shape(cuda_device):
+    """cfg2 at full size, the shape on which the texel-stationary feature-gradient kernel is the default."""
+    backward_case(CFG2, "categorical", cuda_device)
+    backward_case(CFG2, "categorical", cuda_device, dtype="fp32")
+    backward_case(CFG2, "laplace", cuda_device, dtype="fp32")
+
+
 def test_backward_only_requested_gradients(cuda_device):
     w = SMALL
     inp = to_device(inputs_for(w, "categorical"), cuda_device)
