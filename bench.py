@@ -240,6 +240,9 @@ def main():
     ap.add_argument("--batch-per-gpu", type=int, default=1)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip backward / e2e / L2 probe (for profiler runs)")
+    ap.add_argument("--only-backward", type=int, default=0, metavar="FLAGS",
+                    help="profiler helper: launch only fbev_backward with these flags (1 features, 2 depth, 3 both) "
+                         "--steps times on the default workload, print the mean device time and exit")
     ap.add_argument("--tune", default=None, help="tile_x,tile_y,chunks_per_lane,warps,min_blocks (0 = automatic)")
     args = ap.parse_args()
 
@@ -314,6 +317,26 @@ def main():
         torch.cuda.synchronize()
         ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
         return sum(ms) / steps, ms
+
+    if args.only_backward:
+        go = synth.upstream_grad(w, B=Bl).to(device=device, dtype=inp["image_feats"].dtype)
+        g_feats, g_depth = torch.empty_like(keep[0]), torch.empty_like(keep[1])
+        nbytes = lib.fbev_backward_scratch_bytes(ctypes.byref(prob), args.only_backward)
+        scratch = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=device)
+
+        def bwd_only():
+            rc = lib.fbev_backward(ctypes.byref(prob), go.data_ptr(), g_feats.data_ptr(), g_depth.data_ptr(),
+                                   scratch.data_ptr() if nbytes else None, nbytes, args.only_backward, stream)
+            if rc:
+                raise RuntimeError(_lib.strerror(rc))
+
+        ms, _ = timed(bwd_only, args.steps, args.warmup)
+        if rank == 0:
+            print(json.dumps({"only_backward_flags": args.only_backward, "us_per_call": ms * 1e3,
+                              "workload": workload_description(w, Bl, args.mode)}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     with ClockSampler(physical_gpu_index(local_rank)) as clocks:
         ms_fwd, ms_list = timed(fwd_raw, args.steps, args.warmup)
