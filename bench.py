@@ -394,6 +394,32 @@ def main():
             torch.cuda.synchronize()
             extra["fwd_us_warm_l2_back_to_back"] = s.elapsed_time(e) / 200 * 1e3
 
+            # calibration -> projection matrices: the one-kernel builder beside the chain of torch ops it replaces
+            from flashbev_b200.sampling_vt import create_projection_matrix
+            eye4 = torch.eye(4, device=device).expand(Bl, w.N, 4, 4).contiguous()
+            eye3 = torch.eye(3, device=device).expand(Bl, w.N, 3, 3).contiguous()
+            zero3 = torch.zeros(Bl, w.N, 3, device=device)
+
+            def torch_chain():
+                k4 = torch.zeros(Bl, w.N, 4, 4, device=device)
+                k4[..., 3, 3] = 1.0
+                k4[..., :3, :3] = eye3 @ eye3
+                k4[..., :3, 2] += zero3
+                return (k4 @ torch.linalg.inv(eye4))[:, :, :3, :]
+
+            for name, fn in (("projection_matrices_us", lambda: create_projection_matrix(eye4, None, eye3, eye3, zero3, None)),
+                             ("projection_matrices_torch_ops_us", torch_chain)):
+                for _ in range(5):
+                    fn()
+                torch.cuda.synchronize()
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record()
+                for _ in range(50):
+                    fn()
+                e.record()
+                torch.cuda.synchronize()
+                extra[name] = s.elapsed_time(e) / 50 * 1e3
+
             # end to end: pinned host inputs -> device, operator, result -> pinned host
             host = {k: inp_cpu[k].pin_memory() for k in ("image_feats", "depth_params", "projection_matrices")}
             host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()

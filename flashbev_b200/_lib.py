@@ -23,7 +23,7 @@ ERR_STATIC_LIMIT = 11
 EXPORTS = (
     "fbev_forward", "fbev_backward", "fbev_backward_scratch_bytes", "fbev_backward_static_scratch",
     "fbev_debug_indices",
-    "fbev_flash_bevpool", "fbev_flash_bevpool_grad", "fbev_set_tuning", "fbev_probe_read",
+    "fbev_flash_bevpool", "fbev_flash_bevpool_grad", "fbev_projection_matrices", "fbev_set_tuning", "fbev_probe_read",
     "fbev_strerror", "fbev_version",
 )
 
@@ -93,6 +93,8 @@ def load(build_if_missing: bool = True) -> ctypes.CDLL:
     lib.fbev_flash_bevpool.restype = i32
     lib.fbev_flash_bevpool_grad.argtypes = [i32] * 7 + [f32, f32] + [vp] * 7 + [i32] * 3 + [vp, vp, i32, i32, vp]
     lib.fbev_flash_bevpool_grad.restype = i32
+    lib.fbev_projection_matrices.argtypes = [vp] * 5 + [i32, vp]
+    lib.fbev_projection_matrices.restype = i32
     lib.fbev_set_tuning.argtypes = [i32] * 5
     lib.fbev_set_tuning.restype = None
     lib.fbev_probe_read.argtypes = [vp, ctypes.c_size_t, i32, vp, vp]

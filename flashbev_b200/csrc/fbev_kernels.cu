@@ -1573,6 +1573,53 @@ __global__ void indices_kernel(const __grid_constant__ Dev p, int* u0, int* v0, 
   p.count[cell] = cnt;
 }
 
+// One thread per camera: P = K4 * inverse(sensor2ego), rows 0-2 (sampling_vt.py:21-33).
+__global__ void projection_kernel(const float* __restrict__ s2e, const float* __restrict__ k33,
+                                  const float* __restrict__ rot, const float* __restrict__ trans,
+                                  float* __restrict__ out, int count) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= count) return;
+  double m[16], inv[16];
+  for (int k = 0; k < 16; ++k) m[k] = (double)s2e[(size_t)i * 16 + k];
+  // adjugate / determinant
+  inv[0] = m[5] * m[10] * m[15] - m[5] * m[11] * m[14] - m[9] * m[6] * m[15] + m[9] * m[7] * m[14] + m[13] * m[6] * m[11] - m[13] * m[7] * m[10];
+  inv[4] = -m[4] * m[10] * m[15] + m[4] * m[11] * m[14] + m[8] * m[6] * m[15] - m[8] * m[7] * m[14] - m[12] * m[6] * m[11] + m[12] * m[7] * m[10];
+  inv[8] = m[4] * m[9] * m[15] - m[4] * m[11] * m[13] - m[8] * m[5] * m[15] + m[8] * m[7] * m[13] + m[12] * m[5] * m[11] - m[12] * m[7] * m[9];
+  inv[12] = -m[4] * m[9] * m[14] + m[4] * m[10] * m[13] + m[8] * m[5] * m[14] - m[8] * m[6] * m[13] - m[12] * m[5] * m[10] + m[12] * m[6] * m[9];
+  inv[1] = -m[1] * m[10] * m[15] + m[1] * m[11] * m[14] + m[9] * m[2] * m[15] - m[9] * m[3] * m[14] - m[13] * m[2] * m[11] + m[13] * m[3] * m[10];
+  inv[5] = m[0] * m[10] * m[15] - m[0] * m[11] * m[14] - m[8] * m[2] * m[15] + m[8] * m[3] * m[14] + m[12] * m[2] * m[11] - m[12] * m[3] * m[10];
+  inv[9] = -m[0] * m[9] * m[15] + m[0] * m[11] * m[13] + m[8] * m[1] * m[15] - m[8] * m[3] * m[13] - m[12] * m[1] * m[11] + m[12] * m[3] * m[9];
+  inv[13] = m[0] * m[9] * m[14] - m[0] * m[10] * m[13] - m[8] * m[1] * m[14] + m[8] * m[2] * m[13] + m[12] * m[1] * m[10] - m[12] * m[2] * m[9];
+  inv[2] = m[1] * m[6] * m[15] - m[1] * m[7] * m[14] - m[5] * m[2] * m[15] + m[5] * m[3] * m[14] + m[13] * m[2] * m[7] - m[13] * m[3] * m[6];
+  inv[6] = -m[0] * m[6] * m[15] + m[0] * m[7] * m[14] + m[4] * m[2] * m[15] - m[4] * m[3] * m[14] - m[12] * m[2] * m[7] + m[12] * m[3] * m[6];
+  inv[10] = m[0] * m[5] * m[15] - m[0] * m[7] * m[13] - m[4] * m[1] * m[15] + m[4] * m[3] * m[13] + m[12] * m[1] * m[7] - m[12] * m[3] * m[5];
+  inv[14] = -m[0] * m[5] * m[14] + m[0] * m[6] * m[13] + m[4] * m[1] * m[14] - m[4] * m[2] * m[13] - m[12] * m[1] * m[6] + m[12] * m[2] * m[5];
+  inv[3] = -m[1] * m[6] * m[11] + m[1] * m[7] * m[10] + m[5] * m[2] * m[11] - m[5] * m[3] * m[10] - m[9] * m[2] * m[7] + m[9] * m[3] * m[6];
+  inv[7] = m[0] * m[6] * m[11] - m[0] * m[7] * m[10] - m[4] * m[2] * m[11] + m[4] * m[3] * m[10] + m[8] * m[2] * m[7] - m[8] * m[3] * m[6];
+  inv[11] = -m[0] * m[5] * m[11] + m[0] * m[7] * m[9] + m[4] * m[1] * m[11] - m[4] * m[3] * m[9] - m[8] * m[1] * m[7] + m[8] * m[3] * m[5];
+  inv[15] = m[0] * m[5] * m[10] - m[0] * m[6] * m[9] - m[4] * m[1] * m[10] + m[4] * m[2] * m[9] + m[8] * m[1] * m[6] - m[8] * m[2] * m[5];
+  const double det = m[0] * inv[0] + m[1] * inv[4] + m[2] * inv[8] + m[3] * inv[12];
+  const double rdet = 1.0 / det;  // a singular pose gives inf / nan, as torch.inverse would complain about
+  for (int k = 0; k < 16; ++k) inv[k] *= rdet;
+  // K4 rows 0-2: (post_rots * camera2imgs) with post_trans added to column 2, fourth column 0
+  double K[12];
+  for (int r = 0; r < 3; ++r) {
+    for (int c = 0; c < 3; ++c) {
+      double a = 0.0;
+      for (int k = 0; k < 3; ++k) a += (double)rot[(size_t)i * 9 + r * 3 + k] * (double)k33[(size_t)i * 9 + k * 3 + c];
+      K[r * 4 + c] = a;
+    }
+    K[r * 4 + 2] += (double)trans[(size_t)i * 3 + r];
+    K[r * 4 + 3] = 0.0;
+  }
+  for (int r = 0; r < 3; ++r)
+    for (int c = 0; c < 4; ++c) {
+      double a = 0.0;
+      for (int k = 0; k < 4; ++k) a += K[r * 4 + k] * inv[k * 4 + c];
+      out[(size_t)i * 12 + r * 4 + c] = (float)a;
+    }
+}
+
 __global__ void probe_read_kernel(const uint4* __restrict__ buf, size_t n16, int repeats, unsigned* sink) {
   unsigned acc = 0;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -2054,6 +2101,17 @@ int fbev_flash_bevpool_grad(int total_threads, int num_channels, int num_cameras
   if (roi_range == nullptr) return FBEV_ERR_NULL;
   return fbev_backward(&p, out_grad, image_feats_grad, depth_params_grad, nullptr, 0,
                        FBEV_BWD_FEATS | FBEV_BWD_DEPTH | FBEV_BWD_LEGACY_DEPTH, stream);
+}
+
+int fbev_projection_matrices(const float* sensor2ego, const float* camera2imgs, const float* post_rots,
+                             const float* post_trans, float* out, int count, void* stream) {
+  if (!sensor2ego || !camera2imgs || !post_rots || !post_trans || !out) return FBEV_ERR_NULL;
+  if (count <= 0) return FBEV_ERR_SHAPE;
+  if (((uintptr_t)sensor2ego | (uintptr_t)camera2imgs | (uintptr_t)post_rots | (uintptr_t)post_trans | (uintptr_t)out) % 4)
+    return FBEV_ERR_ALIGN;
+  projection_kernel<<<(count + 63) / 64, 64, 0, reinterpret_cast<cudaStream_t>(stream)>>>(sensor2ego, camera2imgs, post_rots,
+                                                                                           post_trans, out, count);
+  return cudaGetLastError() == cudaSuccess ? FBEV_OK : FBEV_ERR_LAUNCH;
 }
 
 int fbev_probe_read(const void* buf, size_t bytes, int repeats, void* sink, void* stream) {

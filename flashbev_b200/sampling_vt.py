@@ -30,6 +30,17 @@ def create_projection_matrix(sensor2ego, ego2global, camera2imgs, post_rots, pos
     (sampling_vt.py:21-33).  ``ego2global`` and ``bda`` are accepted and unused, as there.
     """
     B, N = camera2imgs.shape[:2]
+    if camera2imgs.is_cuda and all(t.dtype == torch.float32 for t in (sensor2ego, camera2imgs, post_rots, post_trans)):
+        # one kernel (fbev_projection_matrices) instead of inverse + matmuls + slicing
+        from . import _lib
+        dev = camera2imgs.device
+        args = [t.expand(B, N, *t.shape[2:]).contiguous() for t in (sensor2ego, camera2imgs, post_rots, post_trans)]
+        out = torch.empty(B, N, 3, 4, dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            rc = _lib.load().fbev_projection_matrices(*[a.data_ptr() for a in args], out.data_ptr(), B * N,
+                                                      torch.cuda.current_stream().cuda_stream)
+        _lib.check(rc, "fbev_projection_matrices")
+        return out
     intrinsic = torch.zeros(B, N, 4, 4, device=camera2imgs.device, dtype=camera2imgs.dtype)
     intrinsic[..., 3, 3] = 1.0
     intrinsic[..., :3, :3] = post_rots @ camera2imgs

@@ -192,6 +192,14 @@ int fbev_flash_bevpool_grad(int total_threads, int num_channels, int num_cameras
                             float* depth_params_grad, float* image_feats_grad, int feat_h, int feat_w,
                             void* stream);
 
+/* Projection matrices from the camera calibration, one small kernel instead of the reference's chain of
+ * torch ops (create_projection_matrix, flashbev/flashbevpool/sampling_vt.py:21-33):
+ *   P = [post_rots * camera2imgs, post_trans added to column 2; 0 0 0 1] * inverse(sensor2ego), rows 0-2.
+ * All device float32: sensor2ego [BN,4,4], camera2imgs [BN,3,3], post_rots [BN,3,3], post_trans [BN,3]
+ * -> out [BN,3,4], BN = batch * cameras.  The 4x4 inverse is evaluated in float64 (cofactors). */
+int fbev_projection_matrices(const float* sensor2ego, const float* camera2imgs, const float* post_rots,
+                             const float* post_trans, float* out, int count, void* stream);
+
 /* Process-wide launch tuning for experiments: cells per tile in x and y,
  * 16-byte chunks per lane, warps per block, resident blocks per SM the forward
  * kernel is compiled for (2 or 3); 0 = choose automatically. */

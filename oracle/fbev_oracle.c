@@ -196,6 +196,56 @@ int fbev_oracle_indices(const oracle_args *a, int32_t *u0, int32_t *v0, int32_t 
   return 0;
 }
 
+/* Projection matrices from calibration (create_projection_matrix, flashbev/flashbevpool/sampling_vt.py:21-33):
+ * K4 = identity with K4[:3,:3] = post_rots * camera2imgs and post_trans added to column 2;
+ * out = (K4 * inverse(sensor2ego))[:3, :].  Float64 throughout; the inverse by Gauss-Jordan elimination with
+ * partial pivoting (torch.inverse there is an LU solve).  Returns 1 for a singular pose. */
+int fbev_oracle_projection(const float* s2e, const float* k33, const float* rot, const float* trans, double* out,
+                           int count) {
+  for (int i = 0; i < count; ++i) {
+    double a[4][8];
+    for (int r = 0; r < 4; ++r)
+      for (int c = 0; c < 4; ++c) {
+        a[r][c] = (double)s2e[(size_t)i * 16 + r * 4 + c];
+        a[r][4 + c] = r == c ? 1.0 : 0.0;
+      }
+    for (int col = 0; col < 4; ++col) {
+      int piv = col;
+      for (int r = col + 1; r < 4; ++r)
+        if (fabs(a[r][col]) > fabs(a[piv][col])) piv = r;
+      if (a[piv][col] == 0.0) return 1;
+      if (piv != col)
+        for (int c = 0; c < 8; ++c) {
+          double t = a[col][c];
+          a[col][c] = a[piv][c];
+          a[piv][c] = t;
+        }
+      double inv = 1.0 / a[col][col];
+      for (int c = 0; c < 8; ++c) a[col][c] *= inv;
+      for (int r = 0; r < 4; ++r) {
+        if (r == col) continue;
+        double f = a[r][col];
+        for (int c = 0; c < 8; ++c) a[r][c] -= f * a[col][c];
+      }
+    }
+    double K[4][4] = {{0}};
+    K[3][3] = 1.0;
+    for (int r = 0; r < 3; ++r) {
+      for (int c = 0; c < 3; ++c)
+        for (int k = 0; k < 3; ++k)
+          K[r][c] += (double)rot[(size_t)i * 9 + r * 3 + k] * (double)k33[(size_t)i * 9 + k * 3 + c];
+      K[r][2] += (double)trans[(size_t)i * 3 + r];
+    }
+    for (int r = 0; r < 3; ++r)
+      for (int c = 0; c < 4; ++c) {
+        double acc = 0.0;
+        for (int k = 0; k < 4; ++k) acc += K[r][k] * a[k][4 + c];
+        out[(size_t)i * 12 + r * 4 + c] = acc;
+      }
+  }
+  return 0;
+}
+
 int fbev_oracle_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -74,6 +74,20 @@ def lib() -> ctypes.CDLL:
     return _lib
 
 
+def projection(sensor2ego, camera2imgs, post_rots, post_trans) -> np.ndarray:
+    """[B,N,3,4] float64 matrices from float32 calibration arrays (sampling_vt.py:21-33)."""
+    arrs = [np.ascontiguousarray(a, dtype=np.float32) for a in (sensor2ego, camera2imgs, post_rots, post_trans)]
+    B, N = arrs[1].shape[:2]
+    out = np.empty((B, N, 3, 4), np.float64)
+    f = lib().fbev_oracle_projection
+    f.argtypes = [ctypes.c_void_p] * 5 + [ctypes.c_int]
+    f.restype = ctypes.c_int
+    rc = f(*[a.ctypes.data for a in arrs], out.ctypes.data, B * N)
+    if rc:
+        raise ValueError("singular sensor2ego")
+    return out
+
+
 def host_threads() -> int:
     return int(lib().fbev_oracle_num_threads())
 

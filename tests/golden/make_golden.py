@@ -56,12 +56,61 @@ def dense_reference(R, feats, depth, proj, image_size, roi, grid, dist, threshol
     return out.detach(), f.grad, d.grad
 
 
+def synthetic_calibration(B, N, seed):
+    """Seeded camera calibration with the value ranges of a surround-view rig: rigid sensor-to-ego
+    poses (any yaw, small pitch/roll, metre-scale offsets), pinhole intrinsics, and the image
+    augmentation's scale/flip/rotate matrix and shift."""
+    g = torch.Generator().manual_seed(seed)
+    u = lambda *s: torch.rand(*s, generator=g, dtype=torch.float64)  # noqa: E731
+    yaw, pitch, roll = (u(B, N) * 2 - 1) * np.pi, (u(B, N) * 2 - 1) * 0.05, (u(B, N) * 2 - 1) * 0.05
+    def rot(axis, a):
+        c, s, o, z = torch.cos(a), torch.sin(a), torch.ones_like(a), torch.zeros_like(a)
+        rows = {"z": [c, -s, z, s, c, z, z, z, o], "y": [c, z, s, z, o, z, -s, z, c], "x": [o, z, z, z, c, -s, z, s, c]}[axis]
+        return torch.stack(rows, -1).view(B, N, 3, 3)
+    cam = torch.tensor([[0.0, 0.0, 1.0], [-1.0, 0.0, 0.0], [0.0, -1.0, 0.0]], dtype=torch.float64)  # camera axes -> ego axes
+    s2e = torch.zeros(B, N, 4, 4, dtype=torch.float64)
+    s2e[..., :3, :3] = rot("z", yaw) @ rot("y", pitch) @ rot("x", roll) @ cam
+    s2e[..., :3, 3] = (u(B, N, 3) * 2 - 1) * torch.tensor([1.5, 0.8, 0.3], dtype=torch.float64) + torch.tensor([0.0, 0.0, 1.5], dtype=torch.float64)
+    s2e[..., 3, 3] = 1.0
+    K = torch.zeros(B, N, 3, 3, dtype=torch.float64)
+    K[..., 0, 0] = 1100 + 200 * u(B, N)
+    K[..., 1, 1] = 1100 + 200 * u(B, N)
+    K[..., 0, 2] = 800 + 30 * (u(B, N) * 2 - 1)
+    K[..., 1, 2] = 450 + 30 * (u(B, N) * 2 - 1)
+    K[..., 2, 2] = 1.0
+    scale, ang = 0.4 + 0.1 * u(B, N), (u(B, N) * 2 - 1) * 0.1
+    flip = torch.where(u(B, N) < 0.5, -1.0, 1.0).to(torch.float64)
+    pr = torch.zeros(B, N, 3, 3, dtype=torch.float64)
+    pr[..., 0, 0], pr[..., 0, 1] = scale * flip * torch.cos(ang), -scale * torch.sin(ang)
+    pr[..., 1, 0], pr[..., 1, 1] = scale * flip * torch.sin(ang), scale * torch.cos(ang)
+    pr[..., 2, 2] = 1.0
+    pt = torch.zeros(B, N, 3, dtype=torch.float64)
+    pt[..., :2] = (u(B, N, 2) * 2 - 1) * 60.0
+    return [t.float() for t in (s2e, K, pr, pt)]
+
+
+def projection_case(R):
+    """Calibration -> matrices through the reference's create_projection_matrix (sampling_vt.py:21-33)."""
+    s2e, K, pr, pt = synthetic_calibration(3, 6, seed=21)
+    B, N = s2e.shape[:2]
+    eye = torch.eye(4).expand(B, N, 4, 4)
+    P = R.create_projection_matrix(s2e, eye, K, pr, pt, torch.eye(3).expand(B, 3, 3))
+    path = os.path.join(HERE, "projection_synthetic.npz")
+    np.savez_compressed(path, sensor2ego=s2e.numpy(), camera2imgs=K.numpy(), post_rots=pr.numpy(), post_trans=pt.numpy(),
+                        proj=P.contiguous().numpy(), torch_version=np.array(torch.__version__))
+    print("projection_synthetic", tuple(P.shape), os.path.getsize(path), "bytes")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--only-projection", action="store_true", help="write only projection_synthetic.npz")
     args = ap.parse_args()
     R = load_reference(args.reference)
     torch.manual_seed(0)
+    projection_case(R)
+    if args.only_projection:
+        return
 
     small = synth.Workload("golden_small", B=2, N=6, C=8, H=8, W=22, D=16, X=24, Y=20, Z=4, xy_extent=25.6,
                            d0=1.0, delta=2.0, dtype="fp32", seed=11, jitter=True)

@@ -76,7 +76,13 @@ def inputs_for(w, mode):
 
 
 def golden_files():
-    return sorted(glob.glob(os.path.join(GOLDEN, "*.npz")))
+    """Operator fixtures (the calibration fixture projection_*.npz is read by projection_golden)."""
+    return sorted(f for f in glob.glob(os.path.join(GOLDEN, "*.npz")) if not os.path.basename(f).startswith("projection_"))
+
+
+def projection_golden():
+    """Calibration arrays and the matrices the reference's create_projection_matrix made of them."""
+    return dict(np.load(os.path.join(GOLDEN, "projection_synthetic.npz")))
 
 
 def golden_problem(g):

@@ -78,3 +78,35 @@ def test_reference_state_dict_names():
     m = SamplingVT(GRID, (128, 352), in_channels=8, out_channels=4, fuse_projection=True, use_bev_pool=False)
     assert {"context_network.weight", "context_network.bias", "depth_network.0.weight", "depth_network.0.bias",
             "depth_bins", "roi_ranges", "output_grid_size", "sample_grid_size"} <= set(m.state_dict().keys())
+
+
+def test_projection_kernel_matches_oracle_and_reference_builder(cuda_device):
+    """fbev_projection_matrices against the float64 oracle and the reference's float32 builder output."""
+    from oracle import oracle as O
+    from flashbev_b200.sampling_vt import create_projection_matrix
+    from tests.helpers import projection_golden
+    g = projection_golden()
+    t = {k: torch.from_numpy(g[k]).to(cuda_device) for k in ("sensor2ego", "camera2imgs", "post_rots", "post_trans")}
+    P = create_projection_matrix(t["sensor2ego"], None, t["camera2imgs"], t["post_rots"], t["post_trans"], None)
+    assert P.shape == (3, 6, 3, 4) and P.dtype == torch.float32 and P.is_cuda
+    P = P.cpu().numpy().astype(np.float64)
+    ref = O.projection(g["sensor2ego"], g["camera2imgs"], g["post_rots"], g["post_trans"])
+    scale = np.abs(ref).reshape(-1, 12).max(1)
+    # float32 rounding of the result only: half an ulp of the largest entry per camera
+    assert (np.abs(P - ref).reshape(-1, 12).max(1) / scale).max() < 1.2e-7
+    assert (np.abs(P - g["proj"]).reshape(-1, 12).max(1) / scale).max() < 1e-5
+
+
+def test_projection_kernel_accepts_broadcast_views(cuda_device):
+    """Expanded (stride-0) calibration tensors are materialised before the launch."""
+    from oracle import oracle as O
+    from flashbev_b200.sampling_vt import create_projection_matrix
+    from tests.helpers import projection_golden
+    g = projection_golden()
+    one = {k: torch.from_numpy(g[k][:1, :1]).to(cuda_device) for k in ("sensor2ego", "camera2imgs", "post_rots", "post_trans")}
+    cams = torch.from_numpy(g["camera2imgs"][:1]).to(cuda_device)
+    P = create_projection_matrix(one["sensor2ego"].expand(1, 6, 4, 4), None, cams, one["post_rots"].expand(1, 6, 3, 3),
+                                 one["post_trans"].expand(1, 6, 3), None).cpu().numpy().astype(np.float64)
+    rep = lambda k: np.repeat(g[k][:1, :1], 6, axis=1)  # noqa: E731
+    ref = O.projection(rep("sensor2ego"), g["camera2imgs"][:1], rep("post_rots"), rep("post_trans"))
+    assert (np.abs(P - ref).reshape(-1, 12).max(1) / np.abs(ref).reshape(-1, 12).max(1)).max() < 1.2e-7

@@ -5,6 +5,7 @@ import pytest
 
 from flashbev_b200 import synth
 from oracle import oracle as O
+from tests.helpers import projection_golden  # noqa: E402
 from tests.helpers import (SMALL, TOL_DENSE, TOL_F32, golden_files, golden_problem, inputs_for, oracle_problem,
                            rel_err)
 
@@ -151,3 +152,30 @@ def test_threads_do_not_change_the_forward():
     inp = inputs_for(SMALL, "categorical")
     p = oracle_problem(inp, SMALL, "categorical")
     assert np.array_equal(O.forward(p, threads=1), O.forward(p, threads=4))
+
+
+def test_projection_matrices_match_the_reference_builder():
+    """create_projection_matrix (sampling_vt.py:21-33) on a seeded rig; float32 there, float64 here."""
+    g = projection_golden()
+    P = O.projection(g["sensor2ego"], g["camera2imgs"], g["post_rots"], g["post_trans"])
+    per_cam = np.abs(P - g["proj"]).reshape(-1, 12).max(1) / np.abs(g["proj"]).reshape(-1, 12).max(1)
+    assert per_cam.max() < 1e-5
+
+
+def test_projection_host_fallback_matches_the_oracle():
+    """The torch branch of flashbev_b200.create_projection_matrix (CPU tensors)."""
+    import torch
+    from flashbev_b200.sampling_vt import create_projection_matrix
+    g = projection_golden()
+    t = {k: torch.from_numpy(g[k]) for k in ("sensor2ego", "camera2imgs", "post_rots", "post_trans")}
+    P = create_projection_matrix(t["sensor2ego"], None, t["camera2imgs"], t["post_rots"], t["post_trans"], None).numpy()
+    ref = O.projection(g["sensor2ego"], g["camera2imgs"], g["post_rots"], g["post_trans"])
+    assert np.abs(P - ref).max() / np.abs(ref).max() < 1e-5
+
+
+def test_projection_rejects_a_singular_pose():
+    g = projection_golden()
+    s2e = g["sensor2ego"].copy()
+    s2e[0, 0, 2] = 0.0  # a zero row: the elimination meets an exact zero pivot
+    with pytest.raises(ValueError):
+        O.projection(s2e, g["camera2imgs"], g["post_rots"], g["post_trans"])
