@@ -138,8 +138,24 @@ class SamplingVT(nn.Module):
         # small constant inputs of the operator, built once per (device, B, N, h, w)
         self._const_cache = {}
 
+    @staticmethod
+    def _pointwise_conv(conv, x):
+        """1x1 convolution of x [BN,C,H,W] whose result is laid out [BN,H,W,O] in memory and returned as the
+        [BN,O,H,W] view of it (channels-last strides).  The operator wants channels-last features; the
+        reference converts with movedim + contiguous after the convolution (sampling_vt.py:252-253).  Here
+        the batched GEMM takes x as a transposed operand, so no transpose kernel runs on either side."""
+        BN, C, H, W = x.shape
+        O = conv.out_channels
+        if x.is_contiguous(memory_format=torch.channels_last) and not x.is_contiguous():
+            xm = x.permute(0, 2, 3, 1).reshape(BN, H * W, C)
+        else:
+            xm = x.flatten(2).transpose(1, 2)
+        wt = conv.weight.view(O, C).t().unsqueeze(0).expand(BN, C, O)
+        bias = conv.bias.view(1, 1, O) if conv.bias is not None else xm.new_zeros(1, 1, O)
+        return torch.baddbmm(bias, xm, wt).view(BN, H, W, O).permute(0, 3, 1, 2)
+
     def forward_depth(self, x):
-        depth_params = self.depth_network(x)
+        depth_params = torch.relu(self._pointwise_conv(self.depth_network[0], x))
         # sigma + 0.1 keeps it away from zero (sampling_vt.py:220-223); out of place, so that the ReLU output
         # autograd saved stays intact and the module can be trained
         return depth_params + depth_params.new_tensor([0.0, 0.1]).view(1, 2, 1, 1)
@@ -148,8 +164,9 @@ class SamplingVT(nn.Module):
         x = input[0]
         B, N, C, H, W = x.shape
         x = x.view(B * N, C, H, W)
-        features_pv = self.context_network(x)
+        features_pv = self._pointwise_conv(self.context_network, x)
         depths = self.forward_depth(x)
+        # [B,C,Y,X] with channels-last strides: a channels-last BEV encoder consumes it without a copy
         return self.sampling_vt(input, features_pv, depths), depths
 
     def _constants(self, device, B, N, h, w):
