@@ -496,9 +496,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32, MINB) fwd_kernel(const __grid_
       const int x = t.x0 + lx, y = t.y0 + ly;
       const bool cell_ok = lane_used && tc < tile_cells && x < t.x1 && y < t.y1;
 
-      float acc[V * E];
+      // accumulators as pairs: one packed FFMA2 (two independent IEEE fp32 fmas) per pair of channels
+      float2 acc2[V * E / 2];
 #pragma unroll
-      for (int i = 0; i < V * E; ++i) acc[i] = 0.0f;
+      for (int i = 0; i < V * E / 2; ++i) acc2[i] = make_float2(0.0f, 0.0f);
       if (lane < p.CPW) sCnt[lane] = 0;
 
       for (int r0 = 0; r0 < ncand; r0 += p.cap) {
@@ -511,7 +512,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, MINB) fwd_kernel(const __grid_
 #pragma unroll 2
         for (int i = 0; i < n; ++i) {
           const uint4 r = rec[i];
-          const float wa0 = __uint_as_float(r.z), wa1 = __uint_as_float(r.w);
+          const float2 wa0 = make_float2(__uint_as_float(r.z), __uint_as_float(r.z));
+          const float2 wa1 = make_float2(__uint_as_float(r.w), __uint_as_float(r.w));
 #pragma unroll
           for (int j = 0; j < V; ++j) {
             const uint4 q0 = ldg16(fl + (r.x + j * p.GL));
@@ -520,13 +522,21 @@ __global__ void __launch_bounds__(kMaxWarps * 32, MINB) fwd_kernel(const __grid_
             Chunk<T>::unpack(q0, f0);
             Chunk<T>::unpack(q1, f1);
 #pragma unroll
-            for (int e = 0; e < E; ++e) acc[j * E + e] = fmaf(wa1, f1[e], fmaf(wa0, f0[e], acc[j * E + e]));
+            for (int e = 0; e < E / 2; ++e)
+              acc2[j * E / 2 + e] = __ffma2_rn(wa1, make_float2(f1[2 * e], f1[2 * e + 1]),
+                                               __ffma2_rn(wa0, make_float2(f0[2 * e], f0[2 * e + 1]), acc2[j * E / 2 + e]));
           }
         }
         __syncwarp();
       }
       __syncwarp();
 
+      float acc[V * E];
+#pragma unroll
+      for (int i = 0; i < V * E / 2; ++i) {
+        acc[2 * i] = acc2[i].x;
+        acc[2 * i + 1] = acc2[i].y;
+      }
       if (cell_ok) {
         const int cnt = sCnt[g];
         if (p.pool == FBEV_POOL_MEAN) {

@@ -47,7 +47,7 @@ class DepthSpec(int):
 
     def __new__(cls, mode: int, pool: Optional[str] = None, depth_bin_range: Optional[Tuple[float, float]] = None,
                 legacy_depth_grad: bool = False, y_range: Optional[Tuple[int, int]] = None,
-                out_dtype: Optional[torch.dtype] = None):
+                out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None):
         mode = int(mode)
         if mode not in (0, 1, 2):
             raise ValueError(f"depth_distribution must be 0 (gaussian), 1 (laplace) or 2 (categorical), got {mode}")
@@ -71,6 +71,7 @@ class DepthSpec(int):
         if out_dtype not in (None, torch.float32):
             raise ValueError("out_dtype must be None (the feature dtype) or torch.float32")
         self.out_dtype = out_dtype
+        self.out = out
         return self
 
 
@@ -177,6 +178,26 @@ def _out_dtype(spec: DepthSpec, feats: torch.Tensor) -> torch.dtype:
     return torch.float32 if spec.out_dtype == torch.float32 else feats.dtype
 
 
+def _check_out(out, shape, dtype, device, partial, needs_grad):
+    """A caller-provided result buffer: a tensor on the operator's device, or page-locked host memory that
+    the kernel writes through the bus directly (the device-to-host copy of the result disappears)."""
+    if tuple(out.shape) != tuple(shape) or out.dtype != dtype or not out.is_contiguous():
+        raise ValueError(f"out must be a contiguous {dtype} tensor of shape {tuple(shape)}")
+    if out.is_cuda:
+        if out.device != device:
+            raise ValueError("out is on another device than image_feats")
+        if partial:
+            out.zero_()
+        return out
+    if not out.is_pinned():
+        raise ValueError("a host out tensor must be page-locked (tensor.pin_memory())")
+    if partial:
+        raise ValueError("y_range with a host out tensor is not supported")
+    if needs_grad:
+        raise ValueError("a host out tensor cannot carry gradients; call under torch.no_grad()")
+    return out
+
+
 class FlashBEVPool(torch.autograd.Function):
     """Fused BEV pooling: projection, depth weight, bilinear sampling and the reduction over
     cameras and height bins in one kernel; see the module docstring for the contract."""
@@ -191,7 +212,11 @@ class FlashBEVPool(torch.autograd.Function):
         feats = keep[0]
         shape = (p.B, p.Y, p.X, p.C)
         partial = (p.y_begin, p.y_end) != (0, p.Y)
-        out = (torch.zeros if partial else torch.empty)(shape, dtype=_out_dtype(spec, feats), device=feats.device)
+        if spec.out is not None:
+            out = _check_out(spec.out, shape, _out_dtype(spec, feats), feats.device, partial,
+                             any(t.requires_grad for t in (depth_params, image_feats)))
+        else:
+            out = (torch.zeros if partial else torch.empty)(shape, dtype=_out_dtype(spec, feats), device=feats.device)
         with torch.cuda.device(feats.device):
             stream = torch.cuda.current_stream().cuda_stream
             rc = _lib.load().fbev_forward(ctypes.byref(p), out.data_ptr(), None, stream)
@@ -248,7 +273,7 @@ class FlashBEVPool(torch.autograd.Function):
 def flash_bevpool(image_feats, depth_params, projection_matrices, feature_size, image_size, roi_range, grid_size,
                   depth_distribution=0, use_shared_memory=True, optimize_z_precompute=True, use_warp_kernel=False,
                   use_vectorized_load=False, epsilon=1e-6, depth_weight_threshold=1e-6, *, pool=None,
-                  depth_bin_range=None, legacy_depth_grad=False, y_range=None, out_dtype=None):
+                  depth_bin_range=None, legacy_depth_grad=False, y_range=None, out_dtype=None, out=None):
     """Fused BEV pooling; same arguments as the reference wrapper (flash_bevpool.py:139-178).
 
     Args:
@@ -265,11 +290,14 @@ def flash_bevpool(image_feats, depth_params, projection_matrices, feature_size, 
         y_range: (begin, end) BEV rows to compute; the other rows of the output are zero.
         out_dtype: None (output in the feature dtype) or torch.float32 (what the reference returns for
             any input dtype).
+        out: result buffer to fill and return instead of a new tensor: on the device, or page-locked host
+            memory, which the kernel then writes directly (inference only; the caller synchronises the stream
+            before reading it).
     Returns:
         BEV features [B,Y,X,C] in the dtype of ``image_feats`` (or float32, see ``out_dtype``).
     """
     spec = DepthSpec(depth_distribution, pool=pool, depth_bin_range=depth_bin_range,
-                     legacy_depth_grad=legacy_depth_grad, y_range=y_range, out_dtype=out_dtype)
+                     legacy_depth_grad=legacy_depth_grad, y_range=y_range, out_dtype=out_dtype, out=out)
     return FlashBEVPool.apply(depth_params, image_feats, projection_matrices, feature_size, image_size, roi_range,
                               grid_size, spec, use_shared_memory, optimize_z_precompute, use_warp_kernel,
                               use_vectorized_load, epsilon, depth_weight_threshold)

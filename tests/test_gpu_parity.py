@@ -293,6 +293,28 @@ def test_backward_only_requested_gradients(cuda_device):
     assert rel_err(inp["image_feats"].grad.cpu().numpy(), only_f.cpu().numpy()) < TOL_F32
 
 
+def test_result_buffer_given_by_the_caller(cuda_device):
+    """out= on the device and in page-locked host memory (written by the kernel) equal the default result."""
+    w = SMALL
+    inp = to_device(inputs_for(w, "categorical"), cuda_device)
+    kw = op_kwargs(w, "categorical")
+    with torch.no_grad():
+        ref = flash_bevpool(**inp, **kw)
+        dev_out = torch.full_like(ref, float("nan"))
+        assert flash_bevpool(**inp, **kw, out=dev_out) is dev_out
+        host_out = torch.full(ref.shape, float("nan"), dtype=ref.dtype).pin_memory()
+        flash_bevpool(**inp, **kw, out=host_out)
+        torch.cuda.synchronize()
+    assert torch.equal(dev_out, ref) and torch.equal(host_out, ref.cpu())
+    with pytest.raises(ValueError):
+        flash_bevpool(**inp, **kw, out=torch.empty(ref.shape, dtype=ref.dtype))  # pageable host memory
+    with pytest.raises(ValueError):
+        flash_bevpool(**inp, **kw, out=torch.empty(1, device=cuda_device))
+    inp["image_feats"].requires_grad_(True)
+    with pytest.raises(ValueError):
+        flash_bevpool(**inp, **kw, out=host_out)
+
+
 def test_edge_cases(cuda_device):
     # one camera, one height bin, 1x1 grid
     w = synth.Workload("one", B=1, N=1, C=4, H=4, W=6, D=8, X=1, Y=1, Z=1, xy_extent=8.0, z_range=(0.0, 2.0),
