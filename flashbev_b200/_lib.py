@@ -21,7 +21,7 @@ ERR_STATIC_LIMIT = 11
 
 # every symbol include/fbev.h declares
 EXPORTS = (
-    "fbev_forward", "fbev_backward", "fbev_backward_scratch_bytes", "fbev_backward_static_scratch",
+    "fbev_forward", "fbev_backward", "fbev_backward_scratch_bytes", "fbev_backward_min_scratch_bytes", "fbev_backward_static_scratch",
     "fbev_debug_indices",
     "fbev_flash_bevpool", "fbev_flash_bevpool_grad", "fbev_projection_matrices", "fbev_set_tuning", "fbev_probe_read",
     "fbev_strerror", "fbev_version",
@@ -83,6 +83,8 @@ def load(build_if_missing: bool = True) -> ctypes.CDLL:
     lib.fbev_forward.restype = i32
     lib.fbev_backward_scratch_bytes.argtypes = [ctypes.POINTER(FbevProblem), i32]
     lib.fbev_backward_scratch_bytes.restype = ctypes.c_size_t
+    lib.fbev_backward_min_scratch_bytes.argtypes = [ctypes.POINTER(FbevProblem), i32]
+    lib.fbev_backward_min_scratch_bytes.restype = ctypes.c_size_t
     lib.fbev_backward.argtypes = [ctypes.POINTER(FbevProblem), vp, vp, vp, vp, ctypes.c_size_t, i32, vp]
     lib.fbev_backward.restype = i32
     lib.fbev_backward_static_scratch.argtypes = [ctypes.POINTER(FbevProblem), vp, vp, vp, i32, vp]

@@ -44,6 +44,12 @@ struct Dev {
   int flags;  // FBEV_BWD_*
   int out_f32;        // output / upstream gradient are float32 although the features are 16-bit
   unsigned* sched;    // tile scheduler words {next tile, blocks done}, or null for one tile per block
+  // feature gradient through a global sort by texel (null / 0 when not in use)
+  unsigned* tex_count;   // [texels + 1] entries per texel, then (after the scan) the next free slot per texel
+  unsigned* ent_count;   // [1] entries emitted so far
+  uint4* ent;            // [ent_cap] {texel, cell, weight bits, 0} in emission order
+  uint4* ent_sorted;     // [ent_cap] the same, grouped by texel
+  unsigned ent_cap;
 };
 
 __device__ __forceinline__ float to_float(float v) { return v; }

@@ -561,9 +561,96 @@ __global__ void __launch_bounds__(kMaxWarps * 32, MINB) fwd_kernel(const __grid_
 // with one 16-byte float32 reduction per chunk and texel.  Merging the height bins that share a feature
 // row cuts the number of reductions, which is what bounds this kernel, by the same factor as the
 // forward's gathers; no feature is read at all.  inv = 1/count for mean pooling, 1 for sum.
+
 __device__ __forceinline__ void red_add4(float* addr, float a, float b, float c, float d);
 
+// Adds the contributions of one cell's row records to the float32 feature gradient; go holds this lane's
+// chunks of the cell's upstream gradient, already times 1/count.
 template <typename T, int V>
+__device__ __forceinline__ void add_records_direct(const Dev& p, const uint4* rec, int n, const float* go, float* gl) {
+  constexpr int E = Chunk<T>::E;
+  for (int i = 0; i < n; ++i) {
+    const uint4 r = rec[i];
+    const float w0 = __uint_as_float(r.z), w1 = __uint_as_float(r.w);
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      float* d0 = gl + (size_t)(r.x + j * p.GL) * E;
+      float* d1 = gl + (size_t)(r.x + r.y + j * p.GL) * E;
+#pragma unroll
+      for (int e4 = 0; e4 < E; e4 += 4) {
+        const float g0 = go[j * E + e4], g1 = go[j * E + e4 + 1], g2 = go[j * E + e4 + 2], g3 = go[j * E + e4 + 3];
+        red_add4(d0 + e4, g0 * w0, g1 * w0, g2 * w0, g3 * w0);
+        if (r.y != 0u) {
+          red_add4(d1 + e4, g0 * w1, g1 * w1, g2 * w1, g3 * w1);
+        } else {  // u1 == u0 (last column): both weights belong to the same texel
+          red_add4(d0 + e4, g0 * w1, g1 * w1, g2 * w1, g3 * w1);
+        }
+      }
+    }
+  }
+}
+
+// Entry emission of the sorted feature gradient, for the whole warp: every row record of the warp's cells
+// leaves {texel, cell, weight * inv, position within the texel's segment} for each of its two texels in p.ent.
+// Slots come from p.ent_count (one atomic per call), positions from p.tex_count.  rec / n / cell / inv_cell
+// describe this lane's cell (n = 0 for lanes without one), sLen the list lengths of all cells of the warp.
+// Returns false, having stored nothing, when the list is full.
+__device__ __forceinline__ bool emit_entries(const Dev& p, const uint4* rec, int n, int g, int lg, int lane, unsigned cell,
+                                             float inv_cell, const int* sLen, unsigned ucpt) {
+  int before = 0, total = 0;  // records of the cells before mine in this warp, and of the whole warp
+  for (int c = 0; c < p.CPW; ++c) {
+    const int lc = sLen[c];
+    before += c < g ? lc : 0;
+    total += lc;
+  }
+  unsigned base = 0;
+  if (lane == 0 && total > 0) base = atomicAdd(p.ent_count, 2u * (unsigned)total);
+  base = __shfl_sync(kFull, base, 0);
+  if ((unsigned long long)base + 2ull * (unsigned)total > (unsigned long long)p.ent_cap) {
+    // the slots drawn stay unused: ent_scatter_kernel skips what lies beyond the capacity, and the part of
+    // this reservation below it is marked void
+    if (lane == 0 && base < p.ent_cap)
+      for (unsigned k = base; k < p.ent_cap; ++k) p.ent[k] = make_uint4(0xffffffffu, 0u, 0u, 0u);
+    return false;
+  }
+  uint4* dst = p.ent + base + 2u * (unsigned)before;
+  int nmax = n;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) nmax = max(nmax, __shfl_xor_sync(kFull, nmax, off));
+  const unsigned lt_mask = (1u << lane) - 1u;
+  // lanes with the same group-local index hold the same record of neighbouring cells, which mostly lies on the
+  // same texel: lanes with equal texels draw their positions with one atomic between them
+  for (int i0 = 0; i0 < nmax; i0 += p.GL) {
+    const int i = i0 + lg;
+    const bool valid = i < n;
+    uint4 r = make_uint4(0u, 0u, 0u, 0u);
+    if (valid) r = rec[i];
+    const unsigned tex0 = r.x / ucpt;
+    const bool two = valid && r.y != 0u;
+    const unsigned key0 = valid ? tex0 : 0xffffffffu - (unsigned)lane;
+    const unsigned key1 = two ? tex0 + 1u : 0x7fffffffu - (unsigned)lane;
+    const unsigned peers0 = __match_any_sync(kFull, key0), peers1 = __match_any_sync(kFull, key1);
+    const int lead0 = __ffs((int)peers0) - 1, lead1 = __ffs((int)peers1) - 1;
+    unsigned old0 = 0, old1 = 0;
+    if (valid && lane == lead0) old0 = atomicAdd(p.tex_count + tex0, (unsigned)__popc(peers0));
+    if (two && lane == lead1) old1 = atomicAdd(p.tex_count + tex0 + 1u, (unsigned)__popc(peers1));
+    old0 = __shfl_sync(kFull, old0, lead0) + (unsigned)__popc(peers0 & lt_mask);
+    old1 = __shfl_sync(kFull, old1, lead1) + (unsigned)__popc(peers1 & lt_mask);
+    if (valid) {
+      const float w0 = __uint_as_float(r.z) * inv_cell, w1 = __uint_as_float(r.w) * inv_cell;
+      // u1 == u0 (last column): one entry with both weights, one void slot
+      dst[2 * i] = make_uint4(tex0, cell, __float_as_uint(two ? w0 : w0 + w1), old0);
+      dst[2 * i + 1] = two ? make_uint4(tex0 + 1u, cell, __float_as_uint(w1), old1) : make_uint4(0xffffffffu, 0u, 0u, 0u);
+    }
+  }
+  return true;
+}
+
+// EMIT: instead of adding to global memory, every record leaves two entries {texel, cell, weight * inv} in
+// p.ent (slots drawn from p.ent_count, one atomic per warp and pass) and counts them per texel in
+// p.tex_count; tex_scan_kernel, ent_scatter_kernel and feats_gather_kernel finish the job.  A warp whose
+// entries do not fit the array any more adds its contributions directly, as without EMIT.
+template <typename T, int V, bool EMIT>
 __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_feats_kernel(const __grid_constant__ Dev p) {
   constexpr int E = Chunk<T>::E;
   extern __shared__ __align__(16) unsigned char smem[];
@@ -607,11 +694,12 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_feats_kernel(const __gr
       float go[V * E];
 #pragma unroll
       for (int i = 0; i < V * E; ++i) go[i] = 0.0f;
-      if (cell_ok) {
-        const size_t cell = ((size_t)t.b * p.Y + y) * p.X + x;
+      const size_t cell = ((size_t)t.b * p.Y + y) * p.X + x;
+      if (!EMIT && cell_ok) {
 #pragma unroll
         for (int j = 0; j < V; ++j) load_chunk<T>(p.gout, p.out_f32, cell * cpt + lg + j * p.GL, go + j * E);
       }
+      float inv_cell = 1.0f;  // EMIT: 1 / count of this lane's cell (mean pooling)
       if (lane < p.CPW) sCnt[lane] = 0;
       __syncwarp();
       if (mean_pool && !single_pass) {
@@ -624,6 +712,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_feats_kernel(const __gr
         }
         const int cnt = lane_used ? sCnt[g] : 0;
         const float inv = cnt > 0 ? __fdiv_rn(1.0f, (float)cnt) : 0.0f;
+        inv_cell = inv;
 #pragma unroll
         for (int i = 0; i < V * E; ++i) go[i] *= inv;
         __syncwarp();
@@ -637,37 +726,150 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_feats_kernel(const __gr
         if (mean_pool && single_pass) {
           const int cnt = lane_used ? sCnt[g] : 0;
           const float inv = cnt > 0 ? __fdiv_rn(1.0f, (float)cnt) : 0.0f;
+          inv_cell = inv;
 #pragma unroll
           for (int i = 0; i < V * E; ++i) go[i] *= inv;
         }
         const int n = cell_ok ? sLen[g] : 0;
         const uint4* rec = recs + (size_t)g * rstride;
-        for (int i = 0; i < n; ++i) {
-          const uint4 r = rec[i];
-          const float w0 = __uint_as_float(r.z), w1 = __uint_as_float(r.w);
+        if (EMIT) {
+          if (emit_entries(p, rec, n, g, lg, lane, (unsigned)cell, inv_cell, sLen, (unsigned)cpt)) {
+            __syncwarp();
+            continue;
+          }
+          if (cell_ok) {  // no room left in the entry list: add directly; the upstream gradient was not needed so far
 #pragma unroll
-          for (int j = 0; j < V; ++j) {
-            float* d0 = gl + (size_t)(r.x + j * p.GL) * E;
-            float* d1 = gl + (size_t)(r.x + r.y + j * p.GL) * E;
+            for (int j = 0; j < V; ++j) load_chunk<T>(p.gout, p.out_f32, cell * cpt + lg + j * p.GL, go + j * E);
 #pragma unroll
-            for (int e4 = 0; e4 < E; e4 += 4) {
-              const float g0 = go[j * E + e4], g1 = go[j * E + e4 + 1], g2 = go[j * E + e4 + 2],
-                          g3 = go[j * E + e4 + 3];
-              red_add4(d0 + e4, g0 * w0, g1 * w0, g2 * w0, g3 * w0);
-              if (r.y != 0u) {
-                red_add4(d1 + e4, g0 * w1, g1 * w1, g2 * w1, g3 * w1);
-              } else {  // u1 == u0 (last column): both weights belong to the same texel
-                red_add4(d0 + e4, g0 * w1, g1 * w1, g2 * w1, g3 * w1);
-              }
-            }
+            for (int k = 0; k < V * E; ++k) go[k] *= inv_cell;
           }
         }
+        add_records_direct<T, V>(p, rec, n, go, gl);
         __syncwarp();
       }
       __syncwarp();
     }
   }  // tiles
   loop.end(p);
+}
+
+// ---------------------------------------------------------------------------
+// Feature gradient through a global sort by texel
+// ---------------------------------------------------------------------------
+// d_feats = W^T * dO with W the sparse [cells x texels] matrix of record weights.  bwd_feats_kernel<EMIT>
+// writes W as a list of entries and counts them per texel; tex_scan_kernel turns the counts into start
+// offsets; ent_scatter_kernel moves every entry to its texel's segment; feats_gather_kernel walks the
+// grouped list, gathers the cells' upstream gradient rows from L2 into float32 registers and adds one
+// 16-byte reduction per chunk and texel change -- some 20 times fewer reductions than the scatter, whose
+// rate at the L2 is what bounds the direct kernel.
+
+// Exclusive prefix sum of count[0, n) in place; count[n] receives the total.  One block.
+__global__ void __launch_bounds__(1024) tex_scan_kernel(unsigned* __restrict__ count, unsigned n) {
+  __shared__ unsigned part[1024];
+  const unsigned tid = threadIdx.x, nt = blockDim.x;
+  const unsigned per = (n + nt - 1) / nt;
+  const unsigned lo = min(tid * per, n), hi = min(lo + per, n);
+  unsigned sum = 0;
+  for (unsigned i = lo; i < hi; ++i) sum += count[i];
+  part[tid] = sum;
+  __syncthreads();
+  for (unsigned d = 1; d < nt; d <<= 1) {
+    const unsigned v = tid >= d ? part[tid - d] : 0u;
+    __syncthreads();
+    part[tid] += v;
+    __syncthreads();
+  }
+  unsigned run = part[tid] - sum;
+  for (unsigned i = lo; i < hi; ++i) {
+    const unsigned c = count[i];
+    count[i] = run;
+    run += c;
+  }
+  if (tid == nt - 1) count[n] = part[tid];
+}
+
+// Every emitted entry moves to its place: start of its texel's segment + the position it drew there.
+__global__ void __launch_bounds__(256) ent_scatter_kernel(const uint4* __restrict__ ent, uint4* __restrict__ sorted,
+                                                          const unsigned* __restrict__ start, const unsigned* __restrict__ ent_count,
+                                                          unsigned cap, unsigned texels) {
+  const unsigned n = min(*ent_count, cap);
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const uint4 e = ent[i];
+    if (e.x >= texels) continue;  // void slot
+    sorted[__ldg(start + e.x) + e.w] = e;
+  }
+}
+
+constexpr int kGatherRun = 32;  // entries one lane group walks between two visits of the scheduler
+
+// GF32: the upstream gradient is float32 although the features are 16-bit.
+template <typename T, int V, bool GF32>
+__global__ void __launch_bounds__(256, 2) feats_gather_kernel(const __grid_constant__ Dev p, unsigned texels) {
+  constexpr int E = Chunk<T>::E;
+  constexpr int R = (GF32 && E == 8) ? 2 : 1;  // 16-byte loads per chunk of E channels
+  constexpr int U = V == 4 ? 2 : 4;            // entries in flight per lane
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int g = lane / p.GL, lg = lane - g * p.GL;
+  if (g >= p.CPW) return;
+  const unsigned n = p.tex_count[texels];  // all entries that were counted
+  const unsigned cpt = (unsigned)(p.GL * V);
+  const unsigned groups = gridDim.x * nwarps * p.CPW;
+  const uint4* gl = reinterpret_cast<const uint4*>(p.gout) + (size_t)lg * R;
+  for (unsigned run = (blockIdx.x * nwarps + warp) * p.CPW + g; (unsigned long long)run * kGatherRun < n; run += groups) {
+    const unsigned i0 = run * kGatherRun, i1 = min(i0 + (unsigned)kGatherRun, n);
+    float2 acc[V * E / 2];
+#pragma unroll
+    for (int k = 0; k < V * E / 2; ++k) acc[k] = make_float2(0.0f, 0.0f);
+    unsigned cur = __ldg(&p.ent_sorted[i0].x);
+    auto flush = [&](unsigned tex) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        float* d = p.gfeat + ((size_t)tex * cpt + lg + j * p.GL) * E;
+#pragma unroll
+        for (int e4 = 0; e4 < E; e4 += 4)
+          red_add4(d + e4, acc[(j * E + e4) / 2].x, acc[(j * E + e4) / 2].y, acc[(j * E + e4) / 2 + 1].x,
+                   acc[(j * E + e4) / 2 + 1].y);
+      }
+    };
+    for (unsigned i = i0; i < i1; i += U) {
+      uint4 e[U];
+      uint4 q[U][V][R];
+#pragma unroll
+      for (int u = 0; u < U; ++u) e[u] = i + u < i1 ? __ldg(p.ent_sorted + i + u) : make_uint4(cur, 0u, 0u, 0u);
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int j = 0; j < V; ++j)
+#pragma unroll
+          for (int r = 0; r < R; ++r) q[u][j][r] = ldg16(gl + ((size_t)e[u].y * cpt + j * p.GL) * R + r);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (i + u >= i1) break;
+        if (e[u].x != cur) {
+          flush(cur);
+#pragma unroll
+          for (int k = 0; k < V * E / 2; ++k) acc[k] = make_float2(0.0f, 0.0f);
+          cur = e[u].x;
+        }
+        const float w = __uint_as_float(e[u].z);
+        const float2 w2 = make_float2(w, w);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          float f[E];
+          if (R == 2) {
+            Chunk<float>::unpack(q[u][j][0], f);
+            Chunk<float>::unpack(q[u][j][R - 1], f + 4);
+          } else {
+            Chunk<T>::unpack(q[u][j][0], f);
+          }
+#pragma unroll
+          for (int k = 0; k < E / 2; ++k)
+            acc[j * E / 2 + k] = __ffma2_rn(w2, make_float2(f[2 * k], f[2 * k + 1]), acc[j * E / 2 + k]);
+        }
+      }
+    }
+    flush(cur);
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -1088,7 +1290,9 @@ __host__ __device__ inline size_t depth_warp_bytes(int CPW, int cap) {
   return 512 + (size_t)CPW * row_stride(cap) * 16 + (size_t)CPW * cap * 48;
 }
 
-template <typename T, int V>
+// EMIT: the kernel also leaves the entries of the sorted feature gradient (emit_entries) from the same row
+// records, so that one list phase serves both gradients.
+template <typename T, int V, bool EMIT>
 __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_depth_kernel(const __grid_constant__ Dev p) {
   constexpr int E = Chunk<T>::E;
   extern __shared__ __align__(16) unsigned char smem[];
@@ -1169,8 +1373,20 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_depth_kernel(const __gr
           const int cnt = sCnt[lane];
           inv_of_lane = cnt > 0 ? __fdiv_rn(1.0f, (float)cnt) : 0.0f;
         }
-        // ---- T = <g, texel> for the two texels of every row record; stored over the record's weights ----
         const int n = cell_ok ? sLen[g] : 0;
+        if (EMIT) {
+          const float inv_cell = __shfl_sync(kFull, inv_of_lane, g < p.CPW ? g : 0);
+          const uint4* rec_e = recs + (size_t)g * rstride;
+          const size_t cell = ((size_t)t.b * p.Y + y) * p.X + x;
+          if (!emit_entries(p, rec_e, n, g, lg, lane, (unsigned)cell, inv_cell, sLen, (unsigned)cpt)) {
+            float gs[V * E];
+#pragma unroll
+            for (int k = 0; k < V * E; ++k) gs[k] = go[k] * inv_cell;
+            add_records_direct<T, V>(p, rec_e, n, gs, p.gfeat + (size_t)lg * E);
+          }
+          __syncwarp();
+        }
+        // ---- T = <g, texel> for the two texels of every row record; stored over the record's weights ----
         int nmax = n;
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) nmax = max(nmax, __shfl_xor_sync(kFull, nmax, off));
@@ -1841,7 +2057,48 @@ static int forward_t(const Plan& pl, const Dev& d, cudaStream_t st) {
 }
 
 template <typename T>
+static int sort_finish_t(const Plan& pl, const Dev& d, cudaStream_t st);
+
+// Feature gradient through the global sort: emission (list phase only), scan, scatter, gather.
+template <typename T>
+static int backward_feats_sort_t(const Plan& pl, const Dev& d, cudaStream_t st) {
+  int rc;
+  switch (pl.V) {
+    case 1: rc = launch(bwd_feats_kernel<T, 1, true>, pl, d, st); break;
+    case 2: rc = launch(bwd_feats_kernel<T, 2, true>, pl, d, st); break;
+    default: rc = launch(bwd_feats_kernel<T, 4, true>, pl, d, st); break;
+  }
+  if (rc != FBEV_OK) return rc;
+  return sort_finish_t<T>(pl, d, st);
+}
+
+// Scan, scatter and gather of the sorted feature gradient, after a kernel that called emit_entries.
+template <typename T>
+static int sort_finish_t(const Plan& pl, const Dev& d, cudaStream_t st) {
+  const unsigned texels = (unsigned)((size_t)d.B * d.N * d.H * d.W);
+  tex_scan_kernel<<<1, 1024, 0, st>>>(d.tex_count, texels);
+  const int sms = sm_count();
+  ent_scatter_kernel<<<sms * 8, 256, 0, st>>>(d.ent, d.ent_sorted, d.tex_count, d.ent_count, d.ent_cap, texels);
+  const int gb = sms * 4;
+  if (d.out_f32) {
+    switch (pl.V) {
+      case 1: feats_gather_kernel<T, 1, true><<<gb, 256, 0, st>>>(d, texels); break;
+      case 2: feats_gather_kernel<T, 2, true><<<gb, 256, 0, st>>>(d, texels); break;
+      default: feats_gather_kernel<T, 4, true><<<gb, 256, 0, st>>>(d, texels); break;
+    }
+  } else {
+    switch (pl.V) {
+      case 1: feats_gather_kernel<T, 1, false><<<gb, 256, 0, st>>>(d, texels); break;
+      case 2: feats_gather_kernel<T, 2, false><<<gb, 256, 0, st>>>(d, texels); break;
+      default: feats_gather_kernel<T, 4, false><<<gb, 256, 0, st>>>(d, texels); break;
+    }
+  }
+  return cudaGetLastError() == cudaSuccess ? FBEV_OK : FBEV_ERR_LAUNCH;
+}
+
+template <typename T>
 static int backward_feats_t(const Plan& pl, const Dev& d, cudaStream_t st) {
+  if (d.ent != nullptr) return backward_feats_sort_t<T>(pl, d, st);
   // measured: ahead of the direct kernel on small feature maps with many cells per texel, behind it otherwise
   if (g_tuning.minb != 1 && (g_tuning.minb == 6 || ((long long)d.H * d.W <= 1024 && (long long)d.X * (d.y1 - d.y0) >= 30000)) &&
       (long long)d.H * d.W < (1 << 21)) {
@@ -1863,9 +2120,9 @@ static int backward_feats_t(const Plan& pl, const Dev& d, cudaStream_t st) {
     }
   }
   switch (pl.V) {
-    case 1: return launch(bwd_feats_kernel<T, 1>, pl, d, st);
-    case 2: return launch(bwd_feats_kernel<T, 2>, pl, d, st);
-    default: return launch(bwd_feats_kernel<T, 4>, pl, d, st);
+    case 1: return launch(bwd_feats_kernel<T, 1, false>, pl, d, st);
+    case 2: return launch(bwd_feats_kernel<T, 2, false>, pl, d, st);
+    default: return launch(bwd_feats_kernel<T, 4, false>, pl, d, st);
   }
 }
 
@@ -1874,26 +2131,38 @@ static int backward_feats_t(const Plan& pl, const Dev& d, cudaStream_t st) {
 template <typename T>
 static int backward_t(const Plan& pl, Dev d, const Plan& plf, const Dev& df, cudaStream_t st) {
   if (!pl.chunked) return launch(bwd_generic_kernel<T>, pl, d, st);
+  // the record-based depth kernel (categorical depth only: the parametric modes have two gradient slots per
+  // texel, and one lane per sample firing at them contends more than the per-group issue of bwd_kernel)
+  const bool depth_on_records = (d.flags & FBEV_BWD_DEPTH) && plf.chunked &&
+                                (d.mode == FBEV_DEPTH_CATEGORICAL || g_tuning.minb == 5) &&
+                                (unsigned long long)df.B * df.N * df.H * df.W * (unsigned long long)df.D < (1ull << 32);
+  Plan pld = plf;
+  Dev dd = df;
+  pld.smem = header_bytes(dd.N) + (size_t)pld.warps * depth_warp_bytes(pld.CPW, pld.cap);
   if ((d.flags & FBEV_BWD_FEATS) && plf.chunked) {
+    if (depth_on_records && df.ent != nullptr) {
+      // both gradients from one list phase: the depth kernel also emits the entries of the sorted feature gradient
+      dd.flags = d.flags;
+      int rc;
+      switch (pld.V) {
+        case 1: rc = launch(bwd_depth_kernel<T, 1, true>, pld, dd, st); break;
+        case 2: rc = launch(bwd_depth_kernel<T, 2, true>, pld, dd, st); break;
+        default: rc = launch(bwd_depth_kernel<T, 4, true>, pld, dd, st); break;
+      }
+      return rc != FBEV_OK ? rc : sort_finish_t<T>(pld, dd, st);
+    }
     const int rc = backward_feats_t<T>(plf, df, st);
     if (rc != FBEV_OK) return rc;
     d.flags &= ~FBEV_BWD_FEATS;
     if (!(d.flags & FBEV_BWD_DEPTH)) return FBEV_OK;
   }
-  // (categorical depth only: the parametric modes have two gradient slots per texel, and one lane per sample
-  // firing at them contends more than the per-group issue of the sample kernel below)
-  if (d.flags == (d.flags & (FBEV_BWD_DEPTH | FBEV_BWD_LEGACY_DEPTH)) && plf.chunked &&
-      (d.mode == FBEV_DEPTH_CATEGORICAL || g_tuning.minb == 5) &&
-      (unsigned long long)df.B * df.N * df.H * df.W * (unsigned long long)df.D < (1ull << 32)) {
+  if (depth_on_records) {
     // depth gradient alone: per-texel dot products on the forward's row records
-    Plan pld = plf;
-    Dev dd = df;
     dd.flags = d.flags;
-    pld.smem = header_bytes(dd.N) + (size_t)pld.warps * depth_warp_bytes(pld.CPW, pld.cap);
     switch (pld.V) {
-      case 1: return launch(bwd_depth_kernel<T, 1>, pld, dd, st);
-      case 2: return launch(bwd_depth_kernel<T, 2>, pld, dd, st);
-      default: return launch(bwd_depth_kernel<T, 4>, pld, dd, st);
+      case 1: return launch(bwd_depth_kernel<T, 1, false>, pld, dd, st);
+      case 2: return launch(bwd_depth_kernel<T, 2, false>, pld, dd, st);
+      default: return launch(bwd_depth_kernel<T, 4, false>, pld, dd, st);
     }
   }
   switch (pl.V) {
@@ -1942,7 +2211,7 @@ const char* fbev_strerror(int status) {
     case FBEV_ERR_MODE: return "unknown depth model or pooling, or depth_delta <= 0 in the categorical mode";
     case FBEV_ERR_ALIGN: return "a pointer is not aligned to its element size";
     case FBEV_ERR_RANGE: return "sizes exceed kernel indexing: B*N*H*W and B*Y*X must be below 2^31, N <= 1024, shared memory per block <= 200 KiB";
-    case FBEV_ERR_SCRATCH: return "scratch buffer missing, misaligned or smaller than fbev_backward_scratch_bytes()";
+    case FBEV_ERR_SCRATCH: return "scratch buffer missing, misaligned or smaller than fbev_backward_min_scratch_bytes()";
     case FBEV_ERR_LAUNCH: return "the CUDA runtime refused a launch or memset (cudaGetLastError)";
     case FBEV_ERR_NO_DEVICE: return "no usable sm_100 device";
     case FBEV_ERR_STATIC_LIMIT: return "the problem needs more float32 scratch than fbev_backward_static_scratch holds (FBEV_STATIC_SCRATCH_BYTES); use fbev_backward with caller scratch";
@@ -1958,13 +2227,38 @@ int fbev_forward(const FbevProblem* p, void* out, int32_t* valid_count, void* st
   return forward_impl(p, out, valid_count, stream, false);
 }
 
-size_t fbev_backward_scratch_bytes(const FbevProblem* p, int flags) {
-  if (p == nullptr || p->dtype == FBEV_F32) return 0;
+// float32 accumulation targets of the 16-bit types: what fbev_backward cannot do without
+static size_t scratch_min_bytes(const FbevProblem* p, int flags) {
+  if (p->dtype == FBEV_F32) return 0;
   size_t n = 0;
   const size_t tex = (size_t)p->B * p->N * p->H * p->W;
   if (flags & FBEV_BWD_FEATS) n += ((tex * p->C * 4 + 255) / 256) * 256;
   if (flags & FBEV_BWD_DEPTH) n += ((tex * p->D * 4 + 255) / 256) * 256;
   return n;
+}
+
+// Entry lists of the sorted feature gradient: capacity (entries) and bytes.  One entry per candidate is
+// about twice what the benchmark rigs emit; warps that find the list full add directly instead.
+static size_t sort_capacity(const FbevProblem* p) {
+  if (g_tuning.minb == 8) return 4096;  // tests: nearly every warp finds the list full
+  const size_t cand = (size_t)p->B * p->X * (size_t)(p->y_end - p->y_begin) * p->N * p->Z;
+  const size_t top = (size_t)1 << 26;
+  return cand < top ? (cand < 4096 ? 4096 : cand) : top;
+}
+static size_t sort_bytes(const FbevProblem* p, int flags) {
+  if (!(flags & FBEV_BWD_FEATS)) return 0;
+  const size_t tex = (size_t)p->B * p->N * p->H * p->W;
+  if (tex >= 0xfffffff0ull || (size_t)p->B * p->Y * p->X >= 0xfffffff0ull) return 0;
+  return (((tex + 1) * 4 + 255) / 256) * 256 + 256 + 2 * sort_capacity(p) * 16;
+}
+
+size_t fbev_backward_min_scratch_bytes(const FbevProblem* p, int flags) {
+  return p == nullptr ? 0 : scratch_min_bytes(p, flags);
+}
+
+size_t fbev_backward_scratch_bytes(const FbevProblem* p, int flags) {
+  if (p == nullptr) return 0;
+  return scratch_min_bytes(p, flags) + sort_bytes(p, flags);
 }
 
 int fbev_backward(const FbevProblem* p, const void* grad_out, void* grad_feats, void* grad_depth, void* scratch,
@@ -1990,7 +2284,7 @@ int fbev_backward(const FbevProblem* p, const void* grad_out, void* grad_feats, 
     d.gfeat = reinterpret_cast<float*>(grad_feats);
     d.gdepth = reinterpret_cast<float*>(grad_depth);
   } else {
-    const size_t need = fbev_backward_scratch_bytes(p, flags);
+    const size_t need = scratch_min_bytes(p, flags);
     if (scratch == nullptr || scratch_bytes < need || ((uintptr_t)scratch % 256)) return FBEV_ERR_SCRATCH;
     unsigned char* s = reinterpret_cast<unsigned char*>(scratch);
     if (flags & FBEV_BWD_FEATS) {
@@ -1998,6 +2292,25 @@ int fbev_backward(const FbevProblem* p, const void* grad_out, void* grad_feats, 
       s += ((nf * 4 + 255) / 256) * 256;
     }
     if (flags & FBEV_BWD_DEPTH) d.gdepth = reinterpret_cast<float*>(s);
+  }
+  // what lies beyond the accumulation targets holds the entry lists of the sorted feature gradient, when
+  // the caller gave that much (fbev_backward_scratch_bytes asks for it)
+  const size_t sortb = sort_bytes(p, flags), minb = scratch_min_bytes(p, flags);
+  // small problems keep the single-launch kernels: three more launches cost more than they save there
+  const bool want_sort = g_tuning.minb == 7 || g_tuning.minb == 8 ||
+                         (g_tuning.minb == 0 && (size_t)p->B * p->X * (size_t)(p->y_end - p->y_begin) * p->N * p->Z >= 200000);
+  if (want_sort && sortb != 0 && scratch != nullptr && ((uintptr_t)scratch % 256) == 0 && scratch_bytes >= minb + sortb) {
+    unsigned char* s = reinterpret_cast<unsigned char*>(scratch) + minb;
+    const size_t cnt_bytes = (((tex + 1) * 4 + 255) / 256) * 256;
+    d.tex_count = reinterpret_cast<unsigned*>(s);
+    d.ent_count = reinterpret_cast<unsigned*>(s + cnt_bytes);
+    d.ent_cap = (unsigned)sort_capacity(p);
+    d.ent = reinterpret_cast<uint4*>(s + cnt_bytes + 256);
+    d.ent_sorted = d.ent + d.ent_cap;
+    if (cudaMemsetAsync(s, 0, cnt_bytes + 256, st) != cudaSuccess) {
+      cudaGetLastError();
+      return FBEV_ERR_LAUNCH;
+    }
   }
   if ((flags & FBEV_BWD_FEATS) && cudaMemsetAsync(d.gfeat, 0, nf * 4, st) != cudaSuccess) {
     cudaGetLastError();
@@ -2147,7 +2460,7 @@ int fbev_backward_static_scratch(const FbevProblem* p, const void* grad_out, voi
                                  int flags, void* stream) {
   const int rc = validate(p);
   if (rc != FBEV_OK) return rc;
-  const size_t need = fbev_backward_scratch_bytes(p, flags);
+  const size_t need = scratch_min_bytes(p, flags);  // the entry lists of the sorted gradient are used when they fit too
   if (need > FBEV_STATIC_SCRATCH_LIMIT) return FBEV_ERR_STATIC_LIMIT;
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {

@@ -116,17 +116,25 @@ typedef struct FbevProblem {
  * int32 [B,Y,X]) receives the number of accepted samples per cell. */
 int fbev_forward(const FbevProblem* p, void* out, int32_t* valid_count, void* stream);
 
-/* Bytes of float32 scratch fbev_backward needs for this problem and flags:
- * 0 for float32 tensors (gradients accumulate in place), otherwise room for
- * float32 copies of the requested gradients. */
+/* Bytes of scratch fbev_backward works best with for this problem and flags: the float32 accumulation
+ * targets of the 16-bit types (fbev_backward_min_scratch_bytes) plus, when the feature gradient is asked
+ * for, the entry lists of its sort by texel: (B*N*H*W + 1) * 4 bytes of counters and 32 bytes per entry,
+ * one entry per candidate B*X*rows*N*Z (at most 2^26). */
 size_t fbev_backward_scratch_bytes(const FbevProblem* p, int flags);
+
+/* The least scratch fbev_backward accepts: 0 for float32 tensors (gradients accumulate in place),
+ * otherwise room for float32 copies of the requested gradients.  With less than
+ * fbev_backward_scratch_bytes() the feature gradient falls back to its single-launch kernels
+ * (direct float reductions), about 1.6 times slower on the benchmark shape. */
+size_t fbev_backward_min_scratch_bytes(const FbevProblem* p, int flags);
 
 /* Backward.  Replaces flash_bevpool_backward (flash_bevpool.cpp:168-241) ->
  * flash_bevpool_grad() (flash_bevpool_cuda.cu:867-938).  grad_out device
  * [B,Y,X,C]; grad_feats device [B,N,H,W,C]; grad_depth device [B,N,H,W,D]; all
  * of the problem's dtype.  The requested gradients are overwritten (the
  * library clears them itself).  scratch: device, 256-byte aligned, at least
- * fbev_backward_scratch_bytes(); may be NULL when that is 0. */
+ * fbev_backward_min_scratch_bytes() (may be NULL when that is 0), preferably
+ * fbev_backward_scratch_bytes(). */
 int fbev_backward(const FbevProblem* p, const void* grad_out, void* grad_feats, void* grad_depth,
                   void* scratch, size_t scratch_bytes, int flags, void* stream);
 
@@ -141,7 +149,7 @@ int fbev_backward(const FbevProblem* p, const void* grad_out, void* grad_feats, 
  * nothing: no cudaMalloc, no cudaFree, no library routine that allocates.
  *
  * Limits and rules:
- *  - the problem's fbev_backward_scratch_bytes() must not exceed FBEV_STATIC_SCRATCH_BYTES, else
+ *  - the problem's fbev_backward_min_scratch_bytes() must not exceed FBEV_STATIC_SCRATCH_BYTES, else
  *    FBEV_ERR_STATIC_LIMIT is returned and nothing is launched (float32 problems need none and
  *    always fit);
  *  - the array costs FBEV_STATIC_SCRATCH_BYTES of device memory on every GPU that loads the library,

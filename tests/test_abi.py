@@ -91,11 +91,16 @@ def test_validation_status_codes():
 def test_backward_scratch_size_and_checks():
     lib = _lib.load()
     p = _problem()
-    assert lib.fbev_backward_scratch_bytes(ctypes.byref(p), 3) == 0            # float32: in place
-    p.dtype = p.out_dtype = _lib.BF16
     tex = 1 * 2 * 4 * 4
-    assert lib.fbev_backward_scratch_bytes(ctypes.byref(p), 3) == tex * 8 * 4 + tex * 2 * 4
-    assert lib.fbev_backward_scratch_bytes(ctypes.byref(p), 1) == tex * 8 * 4
+    assert lib.fbev_backward_min_scratch_bytes(ctypes.byref(p), 3) == 0        # float32: in place
+    # the sorted feature gradient: counters, one word, two lists of 4096 16-byte entries (the least capacity)
+    lists = 256 + 256 + 2 * 4096 * 16
+    assert lib.fbev_backward_scratch_bytes(ctypes.byref(p), 3) == lists
+    assert lib.fbev_backward_scratch_bytes(ctypes.byref(p), 2) == 0            # depth gradient alone: no lists
+    p.dtype = p.out_dtype = _lib.BF16
+    assert lib.fbev_backward_min_scratch_bytes(ctypes.byref(p), 3) == tex * 8 * 4 + tex * 2 * 4
+    assert lib.fbev_backward_min_scratch_bytes(ctypes.byref(p), 1) == tex * 8 * 4
+    assert lib.fbev_backward_scratch_bytes(ctypes.byref(p), 1) == tex * 8 * 4 + lists
     # 16-bit gradients without scratch are refused before anything is launched
     assert lib.fbev_backward(ctypes.byref(p), 256, 256, 256, None, 0, 3, None) == 8   # FBEV_ERR_SCRATCH
     assert lib.fbev_backward(ctypes.byref(p), 256, 256, 256, None, 0, 0, None) == 0   # nothing requested

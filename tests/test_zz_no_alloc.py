@@ -50,7 +50,7 @@ def test_static_scratch_backward_matches_caller_scratch_backward(cuda_device, dt
     prob, keep = make_problem(inp["depth_params"], inp["image_feats"], inp["projection_matrices"],
                               inp["feature_size"], inp["image_size"], inp["roi_range"], inp["grid_size"], spec,
                               1e-6, 0.0)
-    need = lib.fbev_backward_scratch_bytes(ctypes.byref(prob), 3)
+    need = lib.fbev_backward_min_scratch_bytes(ctypes.byref(prob), 3)
     assert 0 < need <= _lib.STATIC_SCRATCH_BYTES
     for call in range(2):  # two calls in a row share the built-in array
         go = synth.upstream_grad(w, seed_offset=call).to(device=cuda_device, dtype=keep[0].dtype)
@@ -71,7 +71,7 @@ def test_static_scratch_backward_refuses_problems_beyond_its_limit(cuda_device):
     prob, keep = make_problem(inp["depth_params"], inp["image_feats"], inp["projection_matrices"],
                               inp["feature_size"], inp["image_size"], inp["roi_range"], inp["grid_size"],
                               DepthSpec(2, depth_bin_range=(w.d0, w.delta)), 1e-6, 0.0)
-    assert lib.fbev_backward_scratch_bytes(ctypes.byref(prob), 3) > _lib.STATIC_SCRATCH_BYTES
+    assert lib.fbev_backward_min_scratch_bytes(ctypes.byref(prob), 3) > _lib.STATIC_SCRATCH_BYTES
     go = torch.zeros(w.B, w.Y, w.X, w.C, dtype=torch.bfloat16, device=cuda_device)
     g_feats, g_depth = torch.empty_like(keep[0]), torch.empty_like(keep[1])
     rc = lib.fbev_backward_static_scratch(ctypes.byref(prob), go.data_ptr(), g_feats.data_ptr(), g_depth.data_ptr(),
