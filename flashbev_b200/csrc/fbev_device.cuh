@@ -49,6 +49,8 @@ struct Dev {
   unsigned* ent_count;   // [1] entries emitted so far
   uint4* ent;            // [ent_cap] {texel, cell, weight bits, 0} in emission order
   uint4* ent_sorted;     // [ent_cap] the same, grouped by texel
+  float2* ent_d;         // [ent_cap] parametric depth: d mean, d sigma of the entry's texel (else null)
+  float2* ent_d_sorted;  // [ent_cap]
   unsigned ent_cap;
 };
 

@@ -592,11 +592,12 @@ __device__ __forceinline__ void add_records_direct(const Dev& p, const uint4* re
 
 // Entry emission of the sorted feature gradient, for the whole warp: every row record of the warp's cells
 // leaves {texel, cell, weight * inv, position within the texel's segment} for each of its two texels in p.ent.
-// Slots come from p.ent_count (one atomic per call), positions from p.tex_count.  rec / n / cell / inv_cell
+// Slots come from p.ent_count (one atomic per call), positions from p.tex_count.  The weights are left out
+// when no feature gradient was asked for (the entries then only carry the parametric depth gradient).  rec / n / cell / inv_cell
 // describe this lane's cell (n = 0 for lanes without one), sLen the list lengths of all cells of the warp.
 // Returns false, having stored nothing, when the list is full.
 __device__ __forceinline__ bool emit_entries(const Dev& p, const uint4* rec, int n, int g, int lg, int lane, unsigned cell,
-                                             float inv_cell, const int* sLen, unsigned ucpt) {
+                                             float inv_cell, const int* sLen, unsigned ucpt, unsigned* first_slot = nullptr) {
   int before = 0, total = 0;  // records of the cells before mine in this warp, and of the whole warp
   for (int c = 0; c < p.CPW; ++c) {
     const int lc = sLen[c];
@@ -614,6 +615,7 @@ __device__ __forceinline__ bool emit_entries(const Dev& p, const uint4* rec, int
     return false;
   }
   uint4* dst = p.ent + base + 2u * (unsigned)before;
+  if (first_slot != nullptr) *first_slot = base + 2u * (unsigned)before;  // record i of my cell owns slots 2i, 2i+1 from here
   int nmax = n;
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) nmax = max(nmax, __shfl_xor_sync(kFull, nmax, off));
@@ -790,21 +792,25 @@ __global__ void __launch_bounds__(1024) tex_scan_kernel(unsigned* __restrict__ c
 
 // Every emitted entry moves to its place: start of its texel's segment + the position it drew there.
 __global__ void __launch_bounds__(256) ent_scatter_kernel(const uint4* __restrict__ ent, uint4* __restrict__ sorted,
+                                                          const float2* __restrict__ ent_d, float2* __restrict__ sorted_d,
                                                           const unsigned* __restrict__ start, const unsigned* __restrict__ ent_count,
                                                           unsigned cap, unsigned texels) {
   const unsigned n = min(*ent_count, cap);
   for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
     const uint4 e = ent[i];
     if (e.x >= texels) continue;  // void slot
-    sorted[__ldg(start + e.x) + e.w] = e;
+    const unsigned dst = __ldg(start + e.x) + e.w;
+    sorted[dst] = e;
+    if (ent_d != nullptr) sorted_d[dst] = ent_d[i];
   }
 }
 
-constexpr int kGatherRun = 32;  // entries one lane group walks between two visits of the scheduler
 
 // GF32: the upstream gradient is float32 although the features are 16-bit.
-template <typename T, int V, bool GF32>
-__global__ void __launch_bounds__(256, 2) feats_gather_kernel(const __grid_constant__ Dev p, unsigned texels) {
+// PDEPTH: the entries also carry the parametric depth gradient (p.ent_d_sorted).
+template <typename T, int V, bool GF32, bool PDEPTH>
+__global__ void __launch_bounds__(128, (PDEPTH || GF32) ? 4 : 5)
+    feats_gather_kernel(const __grid_constant__ Dev p, unsigned texels, unsigned run_len) {
   constexpr int E = Chunk<T>::E;
   constexpr int R = (GF32 && E == 8) ? 2 : 1;  // 16-byte loads per chunk of E channels
   constexpr int U = V == 4 ? 2 : 4;            // entries in flight per lane
@@ -815,13 +821,19 @@ __global__ void __launch_bounds__(256, 2) feats_gather_kernel(const __grid_const
   const unsigned cpt = (unsigned)(p.GL * V);
   const unsigned groups = gridDim.x * nwarps * p.CPW;
   const uint4* gl = reinterpret_cast<const uint4*>(p.gout) + (size_t)lg * R;
-  for (unsigned run = (blockIdx.x * nwarps + warp) * p.CPW + g; (unsigned long long)run * kGatherRun < n; run += groups) {
-    const unsigned i0 = run * kGatherRun, i1 = min(i0 + (unsigned)kGatherRun, n);
+  const bool feats = (p.flags & FBEV_BWD_FEATS) != 0;
+  for (unsigned run = (blockIdx.x * nwarps + warp) * p.CPW + g; (unsigned long long)run * run_len < n; run += groups) {
+    const unsigned i0 = run * run_len, i1 = min(i0 + run_len, n);
     float2 acc[V * E / 2];
 #pragma unroll
     for (int k = 0; k < V * E / 2; ++k) acc[k] = make_float2(0.0f, 0.0f);
-    unsigned cur = __ldg(&p.ent_sorted[i0].x);
+    float2 dacc = make_float2(0.0f, 0.0f);  // parametric depth: d mean, d sigma of the texel
     auto flush = [&](unsigned tex) {
+      if (PDEPTH && lg == 0) {
+        atomicAdd(p.gdepth + (size_t)tex * 2, dacc.x);
+        atomicAdd(p.gdepth + (size_t)tex * 2 + 1, dacc.y);
+      }
+      if (!feats) return;
 #pragma unroll
       for (int j = 0; j < V; ++j) {
         float* d = p.gfeat + ((size_t)tex * cpt + lg + j * p.GL) * E;
@@ -831,27 +843,57 @@ __global__ void __launch_bounds__(256, 2) feats_gather_kernel(const __grid_const
                    acc[(j * E + e4) / 2 + 1].y);
       }
     };
+    // {texel, cell, weight} of the entries one step ahead, so that their latency overlaps the gathers of this step
+    unsigned nt[U], nc[U], nw[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint4 e = __ldg(p.ent_sorted + min(i0 + u, i1 - 1));
+      nt[u] = e.x; nc[u] = e.y; nw[u] = e.z;
+    }
+    unsigned cur = nt[0];
     for (unsigned i = i0; i < i1; i += U) {
-      uint4 e[U];
+      unsigned et[U], ew[U];
       uint4 q[U][V][R];
+      float2 dv[U];
 #pragma unroll
-      for (int u = 0; u < U; ++u) e[u] = i + u < i1 ? __ldg(p.ent_sorted + i + u) : make_uint4(cur, 0u, 0u, 0u);
+      for (int u = 0; u < U; ++u) {
+        et[u] = nt[u]; ew[u] = nw[u];
+      }
+      if (feats) {
 #pragma unroll
-      for (int u = 0; u < U; ++u)
+        for (int u = 0; u < U; ++u)
 #pragma unroll
-        for (int j = 0; j < V; ++j)
+          for (int j = 0; j < V; ++j)
 #pragma unroll
-          for (int r = 0; r < R; ++r) q[u][j][r] = ldg16(gl + ((size_t)e[u].y * cpt + j * p.GL) * R + r);
+            for (int r = 0; r < R; ++r) q[u][j][r] = ldg16(gl + ((size_t)nc[u] * cpt + j * p.GL) * R + r);
+      }
+      if (PDEPTH) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) dv[u] = __ldg(p.ent_d_sorted + min(i + u, i1 - 1));
+      }
+      if (i + U < i1) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const uint4 e = __ldg(p.ent_sorted + min(i + U + u, i1 - 1));
+          nt[u] = e.x; nc[u] = e.y; nw[u] = e.z;
+        }
+      }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         if (i + u >= i1) break;
-        if (e[u].x != cur) {
+        if (et[u] != cur) {
           flush(cur);
 #pragma unroll
           for (int k = 0; k < V * E / 2; ++k) acc[k] = make_float2(0.0f, 0.0f);
-          cur = e[u].x;
+          dacc = make_float2(0.0f, 0.0f);
+          cur = et[u];
         }
-        const float w = __uint_as_float(e[u].z);
+        if (PDEPTH) {
+          dacc.x += dv[u].x;
+          dacc.y += dv[u].y;
+        }
+        if (!feats) continue;
+        const float w = __uint_as_float(ew[u]);
         const float2 w2 = make_float2(w, w);
 #pragma unroll
         for (int j = 0; j < V; ++j) {
@@ -1319,6 +1361,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_depth_kernel(const __gr
   const uint4* fl = reinterpret_cast<const uint4*>(p.feats) + lg;
   const bool legacy = (p.flags & FBEV_BWD_LEGACY_DEPTH) != 0;
   const bool mean_pool = p.pool == FBEV_POOL_MEAN;
+  const bool by_record = (p.flags & FBEV_BWD_DEPTH) != 0 && (!EMIT || p.ent_d != nullptr);
   int loaded_b = -1;
   TileLoop loop;
   loop.begin(p, s_tile);
@@ -1374,11 +1417,14 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_depth_kernel(const __gr
           inv_of_lane = cnt > 0 ? __fdiv_rn(1.0f, (float)cnt) : 0.0f;
         }
         const int n = cell_ok ? sLen[g] : 0;
+        bool emitted = false;       // warp-uniform: this pass's records have slots in the entry list
+        unsigned first_slot = 0;    // slots 2i, 2i+1 from here belong to record i of my cell
         if (EMIT) {
           const float inv_cell = __shfl_sync(kFull, inv_of_lane, g < p.CPW ? g : 0);
           const uint4* rec_e = recs + (size_t)g * rstride;
           const size_t cell = ((size_t)t.b * p.Y + y) * p.X + x;
-          if (!emit_entries(p, rec_e, n, g, lg, lane, (unsigned)cell, inv_cell, sLen, (unsigned)cpt)) {
+          emitted = emit_entries(p, rec_e, n, g, lg, lane, (unsigned)cell, inv_cell, sLen, (unsigned)cpt, &first_slot);
+          if (!emitted && (p.flags & FBEV_BWD_FEATS)) {
             float gs[V * E];
 #pragma unroll
             for (int k = 0; k < V * E; ++k) gs[k] = go[k] * inv_cell;
@@ -1415,6 +1461,71 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_depth_kernel(const __gr
           }
         }
         __syncwarp();
+        if (p.mode != FBEV_DEPTH_CATEGORICAL && by_record) {
+          // ---- parametric depth, per record: the samples of a run share their texels, so their (d mean,
+          // d sigma) contributions are summed per record texel in shared memory first; the sums leave as the
+          // depth part of the record's entries (summed per texel by feats_gather_kernel) or, without entry
+          // slots, as one atomic per record texel ----
+          for (int c = 0; c < p.CPW; ++c) {  // S * inv of every sample, kept in its record
+            const int ns = sSmp[c];
+            const float inv = mean_pool ? __shfl_sync(kFull, inv_of_lane, c) : 1.0f;
+            const uint4* rc = recs + (size_t)c * rstride;
+            for (int idx = lane; idx < ns; idx += 32) {
+              uint4* sr = samp + ((size_t)c * p.cap + idx) * 3;
+              const uint4 sw = sr[0];
+              const unsigned pos = sr[2].x;
+              const uint4 ra = rc[pos & 0xffffu], rb = rc[pos >> 16];
+              float S = __uint_as_float(sw.x) * __uint_as_float(ra.z);
+              S = fmaf(__uint_as_float(sw.z), __uint_as_float(ra.w), S);
+              S = fmaf(__uint_as_float(sw.y), __uint_as_float(rb.z), S);
+              S = fmaf(__uint_as_float(sw.w), __uint_as_float(rb.w), S);
+              sr[1].x = __float_as_uint(S * inv);
+            }
+          }
+          __syncwarp();
+          for (int which = 0; which < 2; ++which) {  // 0: d mean, 1: d sigma
+            for (int c = 0; c < p.CPW; ++c) {
+              uint4* rc = recs + (size_t)c * rstride;
+              const int nr = sLen[c];
+              for (int i = lane; i < nr; i += 32) rc[i].z = rc[i].w = 0u;
+            }
+            __syncwarp();
+            for (int c = 0; c < p.CPW; ++c) {
+              const int ns = sSmp[c];
+              uint4* rc = recs + (size_t)c * rstride;
+              for (int idx = lane; idx < ns; idx += 32) {
+                const uint4* sr = samp + ((size_t)c * p.cap + idx) * 3;
+                const uint4 sw = sr[0], sp = sr[2];
+                const float sd = __uint_as_float(sr[1].x);
+                const float coef = legacy ? __uint_as_float(sp.y) : __uint_as_float(which == 0 ? sp.z : sp.w);
+                const float v = sd * coef;
+                float* a = reinterpret_cast<float*>(rc + (sp.x & 0xffffu));
+                float* b = reinterpret_cast<float*>(rc + (sp.x >> 16));
+                atomicAdd(a + 2, v * __uint_as_float(sw.x));  // w00 -> (v0, u0)
+                atomicAdd(a + 3, v * __uint_as_float(sw.z));  // w10 -> (v0, u1)
+                atomicAdd(b + 2, v * __uint_as_float(sw.y));  // w01 -> (v1, u0)
+                atomicAdd(b + 3, v * __uint_as_float(sw.w));  // w11 -> (v1, u1)
+              }
+            }
+            __syncwarp();
+            for (int i = lg; i < n; i += p.GL) {
+              const uint4 r = rec[i];
+              const float v0 = __uint_as_float(r.z), v1 = __uint_as_float(r.w);
+              const bool two = r.y != 0u;
+              if (emitted) {
+                float* e = reinterpret_cast<float*>(p.ent_d + first_slot + 2u * (unsigned)i);
+                e[which] = two ? v0 : v0 + v1;
+                if (two) e[2 + which] = v1;
+              } else {
+                const unsigned tex = r.x / (unsigned)cpt;
+                atomicAdd(p.gdepth + (size_t)tex * 2 + which, v0);
+                atomicAdd(p.gdepth + (size_t)(tex + (two ? 1u : 0u)) * 2 + which, v1);
+              }
+            }
+            __syncwarp();
+          }
+          continue;
+        }
         // ---- one lane per sample: S from four T values, then the sample's atomics ----
         for (int c = 0; c < p.CPW; ++c) {
           const int ns = sSmp[c];
@@ -1986,8 +2097,9 @@ static Plan make_plan(const FbevProblem* p, Dev& d, bool bwd, const void* a, con
     tx = pl.CPW * (6 / pl.CPW > 1 ? 6 / pl.CPW : 1);
     ty = 4;
   }
-  d.TX = g_tuning.tx > 0 ? g_tuning.tx : tx;
-  d.TY = g_tuning.ty > 0 ? g_tuning.ty : ty;
+  const bool tile_tuned = g_tuning.minb != 9;  // 9: tile_x / tile_y steer the gather kernel instead
+  d.TX = tile_tuned && g_tuning.tx > 0 ? g_tuning.tx : tx;
+  d.TY = tile_tuned && g_tuning.ty > 0 ? g_tuning.ty : ty;
   d.tiles_x = (p->X + d.TX - 1) / d.TX;
   d.tiles_y = (p->y_end - p->y_begin + d.TY - 1) / d.TY;
   pl.blocks = d.tiles_x * d.tiles_y * p->B;
@@ -2061,7 +2173,10 @@ static int sort_finish_t(const Plan& pl, const Dev& d, cudaStream_t st);
 
 // Feature gradient through the global sort: emission (list phase only), scan, scatter, gather.
 template <typename T>
-static int backward_feats_sort_t(const Plan& pl, const Dev& d, cudaStream_t st) {
+static int backward_feats_sort_t(const Plan& pl, const Dev& d_in, cudaStream_t st) {
+  Dev d = d_in;
+  d.ent_d = d.ent_d_sorted = nullptr;  // this emitter writes no depth values
+  d.flags &= ~FBEV_BWD_DEPTH;
   int rc;
   switch (pl.V) {
     case 1: rc = launch(bwd_feats_kernel<T, 1, true>, pl, d, st); break;
@@ -2078,21 +2193,25 @@ static int sort_finish_t(const Plan& pl, const Dev& d, cudaStream_t st) {
   const unsigned texels = (unsigned)((size_t)d.B * d.N * d.H * d.W);
   tex_scan_kernel<<<1, 1024, 0, st>>>(d.tex_count, texels);
   const int sms = sm_count();
-  ent_scatter_kernel<<<sms * 8, 256, 0, st>>>(d.ent, d.ent_sorted, d.tex_count, d.ent_count, d.ent_cap, texels);
-  const int gb = sms * 4;
-  if (d.out_f32) {
-    switch (pl.V) {
-      case 1: feats_gather_kernel<T, 1, true><<<gb, 256, 0, st>>>(d, texels); break;
-      case 2: feats_gather_kernel<T, 2, true><<<gb, 256, 0, st>>>(d, texels); break;
-      default: feats_gather_kernel<T, 4, true><<<gb, 256, 0, st>>>(d, texels); break;
-    }
-  } else {
-    switch (pl.V) {
-      case 1: feats_gather_kernel<T, 1, false><<<gb, 256, 0, st>>>(d, texels); break;
-      case 2: feats_gather_kernel<T, 2, false><<<gb, 256, 0, st>>>(d, texels); break;
-      default: feats_gather_kernel<T, 4, false><<<gb, 256, 0, st>>>(d, texels); break;
-    }
+  ent_scatter_kernel<<<sms * 8, 256, 0, st>>>(d.ent, d.ent_sorted, d.ent_d, d.ent_d_sorted, d.tex_count, d.ent_count, d.ent_cap, texels);
+  // entries one lane group walks per run (experiments: fbev_set_tuning tile_y / tile_x with min_blocks 9)
+  const unsigned run_len = g_tuning.minb == 9 && g_tuning.ty > 0 ? (unsigned)g_tuning.ty : 32u;
+  const int gb = sms * (g_tuning.minb == 9 && g_tuning.tx > 0 ? g_tuning.tx : 10);
+  const bool pd = d.ent_d_sorted != nullptr;
+#define FBEV_GATHER(VV, GF, PD) feats_gather_kernel<T, VV, GF, PD><<<gb, 128, 0, st>>>(d, texels, run_len)
+#define FBEV_GATHER_V(GF, PD)                 \
+  switch (pl.V) {                             \
+    case 1: FBEV_GATHER(1, GF, PD); break;    \
+    case 2: FBEV_GATHER(2, GF, PD); break;    \
+    default: FBEV_GATHER(4, GF, PD); break;   \
   }
+  if (d.out_f32) {
+    if (pd) { FBEV_GATHER_V(true, true) } else { FBEV_GATHER_V(true, false) }
+  } else {
+    if (pd) { FBEV_GATHER_V(false, true) } else { FBEV_GATHER_V(false, false) }
+  }
+#undef FBEV_GATHER_V
+#undef FBEV_GATHER
   return cudaGetLastError() == cudaSuccess ? FBEV_OK : FBEV_ERR_LAUNCH;
 }
 
@@ -2134,10 +2253,13 @@ static int backward_t(const Plan& pl, Dev d, const Plan& plf, const Dev& df, cud
   // the record-based depth kernel (categorical depth only: the parametric modes have two gradient slots per
   // texel, and one lane per sample firing at them contends more than the per-group issue of bwd_kernel)
   const bool depth_on_records = (d.flags & FBEV_BWD_DEPTH) && plf.chunked &&
-                                (d.mode == FBEV_DEPTH_CATEGORICAL || g_tuning.minb == 5) &&
+                                (d.mode == FBEV_DEPTH_CATEGORICAL || g_tuning.minb == 5 || df.ent_d != nullptr) &&
                                 (unsigned long long)df.B * df.N * df.H * df.W * (unsigned long long)df.D < (1ull << 32);
   Plan pld = plf;
   Dev dd = df;
+  // 16 candidates per cell and pass: half the shared memory of the forward's 32, twice the resident warps, which
+  // this latency-bound kernel needs more than it minds a second pass on tiles that three cameras see
+  pld.cap = dd.cap = g_tuning.minb == 10 ? 32 : 16;
   pld.smem = header_bytes(dd.N) + (size_t)pld.warps * depth_warp_bytes(pld.CPW, pld.cap);
   if ((d.flags & FBEV_BWD_FEATS) && plf.chunked) {
     if (depth_on_records && df.ent != nullptr) {
@@ -2155,6 +2277,17 @@ static int backward_t(const Plan& pl, Dev d, const Plan& plf, const Dev& df, cud
     if (rc != FBEV_OK) return rc;
     d.flags &= ~FBEV_BWD_FEATS;
     if (!(d.flags & FBEV_BWD_DEPTH)) return FBEV_OK;
+  }
+  if (depth_on_records && df.ent_d != nullptr) {
+    // parametric depth gradient alone: its per-texel sums travel through the entry lists
+    dd.flags = d.flags;
+    int rc;
+    switch (pld.V) {
+      case 1: rc = launch(bwd_depth_kernel<T, 1, true>, pld, dd, st); break;
+      case 2: rc = launch(bwd_depth_kernel<T, 2, true>, pld, dd, st); break;
+      default: rc = launch(bwd_depth_kernel<T, 4, true>, pld, dd, st); break;
+    }
+    return rc != FBEV_OK ? rc : sort_finish_t<T>(pld, dd, st);
   }
   if (depth_on_records) {
     // depth gradient alone: per-texel dot products on the forward's row records
@@ -2245,11 +2378,15 @@ static size_t sort_capacity(const FbevProblem* p) {
   const size_t top = (size_t)1 << 26;
   return cand < top ? (cand < 4096 ? 4096 : cand) : top;
 }
+// the parametric depth gradient rides on the same entries (8 more bytes in each list)
+static bool sort_carries_depth(const FbevProblem* p, int flags) {
+  return (flags & FBEV_BWD_DEPTH) && p->mode != FBEV_DEPTH_CATEGORICAL;
+}
 static size_t sort_bytes(const FbevProblem* p, int flags) {
-  if (!(flags & FBEV_BWD_FEATS)) return 0;
+  if (!(flags & FBEV_BWD_FEATS) && !sort_carries_depth(p, flags)) return 0;
   const size_t tex = (size_t)p->B * p->N * p->H * p->W;
   if (tex >= 0xfffffff0ull || (size_t)p->B * p->Y * p->X >= 0xfffffff0ull) return 0;
-  return (((tex + 1) * 4 + 255) / 256) * 256 + 256 + 2 * sort_capacity(p) * 16;
+  return (((tex + 1) * 4 + 255) / 256) * 256 + 256 + 2 * sort_capacity(p) * (sort_carries_depth(p, flags) ? 24 : 16);
 }
 
 size_t fbev_backward_min_scratch_bytes(const FbevProblem* p, int flags) {
@@ -2297,7 +2434,7 @@ int fbev_backward(const FbevProblem* p, const void* grad_out, void* grad_feats, 
   // the caller gave that much (fbev_backward_scratch_bytes asks for it)
   const size_t sortb = sort_bytes(p, flags), minb = scratch_min_bytes(p, flags);
   // small problems keep the single-launch kernels: three more launches cost more than they save there
-  const bool want_sort = g_tuning.minb == 7 || g_tuning.minb == 8 ||
+  const bool want_sort = g_tuning.minb == 7 || g_tuning.minb == 8 || g_tuning.minb == 9 ||
                          (g_tuning.minb == 0 && (size_t)p->B * p->X * (size_t)(p->y_end - p->y_begin) * p->N * p->Z >= 200000);
   if (want_sort && sortb != 0 && scratch != nullptr && ((uintptr_t)scratch % 256) == 0 && scratch_bytes >= minb + sortb) {
     unsigned char* s = reinterpret_cast<unsigned char*>(scratch) + minb;
@@ -2307,6 +2444,10 @@ int fbev_backward(const FbevProblem* p, const void* grad_out, void* grad_feats, 
     d.ent_cap = (unsigned)sort_capacity(p);
     d.ent = reinterpret_cast<uint4*>(s + cnt_bytes + 256);
     d.ent_sorted = d.ent + d.ent_cap;
+    if (sort_carries_depth(p, flags)) {
+      d.ent_d = reinterpret_cast<float2*>(d.ent_sorted + d.ent_cap);
+      d.ent_d_sorted = d.ent_d + d.ent_cap;
+    }
     if (cudaMemsetAsync(s, 0, cnt_bytes + 256, st) != cudaSuccess) {
       cudaGetLastError();
       return FBEV_ERR_LAUNCH;
