@@ -44,13 +44,14 @@ struct Dev {
   int flags;  // FBEV_BWD_*
   int out_f32;        // output / upstream gradient are float32 although the features are 16-bit
   unsigned* sched;    // tile scheduler words {next tile, blocks done}, or null for one tile per block
-  // feature gradient through a global sort by texel (null / 0 when not in use)
-  unsigned* tex_count;   // [texels + 1] entries per texel, then (after the scan) the next free slot per texel
+  // gradients through a global sort by texel (null / 0 when not in use)
+  unsigned* tex_count;   // [texels + 1] entries per texel; after the scan: start of the texel's segment, total last
   unsigned* ent_count;   // [1] entries emitted so far
-  uint4* ent;            // [ent_cap] {texel, cell, weight bits, 0} in emission order
-  uint4* ent_sorted;     // [ent_cap] the same, grouped by texel
-  float2* ent_d;         // [ent_cap] parametric depth: d mean, d sigma of the entry's texel (else null)
-  float2* ent_d_sorted;  // [ent_cap]
+  uint4* ent;            // [ent_cap] {texel of (row, u0), cell, weight of u0, weight of u1} in emission order
+  unsigned* ent_pos;     // [ent_cap] position the entry drew inside its texel's segment
+  uint4* ent_sorted;     // [ent_cap] the entries grouped by texel
+  float4* ent_d;         // [ent_cap] parametric depth: d mean, d sigma of u0, then of u1 (else null)
+  float4* ent_d_sorted;  // [ent_cap]
   unsigned ent_cap;
 };
 

@@ -590,11 +590,11 @@ __device__ __forceinline__ void add_records_direct(const Dev& p, const uint4* re
   }
 }
 
-// Entry emission of the sorted feature gradient, for the whole warp: every row record of the warp's cells
-// leaves {texel, cell, weight * inv, position within the texel's segment} for each of its two texels in p.ent.
-// Slots come from p.ent_count (one atomic per call), positions from p.tex_count.  The weights are left out
-// when no feature gradient was asked for (the entries then only carry the parametric depth gradient).  rec / n / cell / inv_cell
-// describe this lane's cell (n = 0 for lanes without one), sLen the list lengths of all cells of the warp.
+// Entry emission of the sorted gradients, for the whole warp: every row record of the warp's cells leaves one
+// entry {texel of (row, u0), cell, weight of u0 * inv, weight of u1 * inv} in p.ent and, in p.ent_pos, the
+// position it drew inside its texel's segment.  Slots come from p.ent_count (one atomic per call), positions
+// from p.tex_count.  rec / n / cell / inv_cell describe this lane's cell (n = 0 for lanes without one), sLen the
+// list lengths of all cells of the warp.  first_slot: record i of the lane's cell owns slot first_slot + i.
 // Returns false, having stored nothing, when the list is full.
 __device__ __forceinline__ bool emit_entries(const Dev& p, const uint4* rec, int n, int g, int lg, int lane, unsigned cell,
                                              float inv_cell, const int* sLen, unsigned ucpt, unsigned* first_slot = nullptr) {
@@ -605,17 +605,17 @@ __device__ __forceinline__ bool emit_entries(const Dev& p, const uint4* rec, int
     total += lc;
   }
   unsigned base = 0;
-  if (lane == 0 && total > 0) base = atomicAdd(p.ent_count, 2u * (unsigned)total);
+  if (lane == 0 && total > 0) base = atomicAdd(p.ent_count, (unsigned)total);
   base = __shfl_sync(kFull, base, 0);
-  if ((unsigned long long)base + 2ull * (unsigned)total > (unsigned long long)p.ent_cap) {
+  if ((unsigned long long)base + (unsigned)total > (unsigned long long)p.ent_cap) {
     // the slots drawn stay unused: ent_scatter_kernel skips what lies beyond the capacity, and the part of
     // this reservation below it is marked void
     if (lane == 0 && base < p.ent_cap)
       for (unsigned k = base; k < p.ent_cap; ++k) p.ent[k] = make_uint4(0xffffffffu, 0u, 0u, 0u);
     return false;
   }
-  uint4* dst = p.ent + base + 2u * (unsigned)before;
-  if (first_slot != nullptr) *first_slot = base + 2u * (unsigned)before;  // record i of my cell owns slots 2i, 2i+1 from here
+  const unsigned slot0 = base + (unsigned)before;
+  if (first_slot != nullptr) *first_slot = slot0;
   int nmax = n;
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) nmax = max(nmax, __shfl_xor_sync(kFull, nmax, off));
@@ -628,29 +628,24 @@ __device__ __forceinline__ bool emit_entries(const Dev& p, const uint4* rec, int
     uint4 r = make_uint4(0u, 0u, 0u, 0u);
     if (valid) r = rec[i];
     const unsigned tex0 = r.x / ucpt;
-    const bool two = valid && r.y != 0u;
-    const unsigned key0 = valid ? tex0 : 0xffffffffu - (unsigned)lane;
-    const unsigned key1 = two ? tex0 + 1u : 0x7fffffffu - (unsigned)lane;
-    const unsigned peers0 = __match_any_sync(kFull, key0), peers1 = __match_any_sync(kFull, key1);
-    const int lead0 = __ffs((int)peers0) - 1, lead1 = __ffs((int)peers1) - 1;
-    unsigned old0 = 0, old1 = 0;
-    if (valid && lane == lead0) old0 = atomicAdd(p.tex_count + tex0, (unsigned)__popc(peers0));
-    if (two && lane == lead1) old1 = atomicAdd(p.tex_count + tex0 + 1u, (unsigned)__popc(peers1));
-    old0 = __shfl_sync(kFull, old0, lead0) + (unsigned)__popc(peers0 & lt_mask);
-    old1 = __shfl_sync(kFull, old1, lead1) + (unsigned)__popc(peers1 & lt_mask);
+    const unsigned key = valid ? tex0 : 0xffffffffu - (unsigned)lane;
+    const unsigned peers = __match_any_sync(kFull, key);
+    const int lead = __ffs((int)peers) - 1;
+    unsigned old = 0;
+    if (valid && lane == lead) old = atomicAdd(p.tex_count + tex0, (unsigned)__popc(peers));
+    old = __shfl_sync(kFull, old, lead) + (unsigned)__popc(peers & lt_mask);
     if (valid) {
       const float w0 = __uint_as_float(r.z) * inv_cell, w1 = __uint_as_float(r.w) * inv_cell;
-      // u1 == u0 (last column): one entry with both weights, one void slot
-      dst[2 * i] = make_uint4(tex0, cell, __float_as_uint(two ? w0 : w0 + w1), old0);
-      dst[2 * i + 1] = two ? make_uint4(tex0 + 1u, cell, __float_as_uint(w1), old1) : make_uint4(0xffffffffu, 0u, 0u, 0u);
+      const bool two = r.y != 0u;  // u1 == u0 (last column): both weights belong to u0
+      p.ent[slot0 + i] = make_uint4(tex0, cell, __float_as_uint(two ? w0 : w0 + w1), __float_as_uint(two ? w1 : 0.0f));
+      p.ent_pos[slot0 + i] = old;
     }
   }
   return true;
 }
 
-// EMIT: instead of adding to global memory, every record leaves two entries {texel, cell, weight * inv} in
-// p.ent (slots drawn from p.ent_count, one atomic per warp and pass) and counts them per texel in
-// p.tex_count; tex_scan_kernel, ent_scatter_kernel and feats_gather_kernel finish the job.  A warp whose
+// EMIT: instead of adding to global memory, every record leaves an entry in p.ent (emit_entries) and is counted
+// per texel in p.tex_count; tex_scan_kernel, ent_scatter_kernel and feats_gather_kernel finish the job.  A warp whose
 // entries do not fit the array any more adds its contributions directly, as without EMIT.
 template <typename T, int V, bool EMIT>
 __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_feats_kernel(const __grid_constant__ Dev p) {
@@ -756,14 +751,17 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_feats_kernel(const __gr
 }
 
 // ---------------------------------------------------------------------------
-// Feature gradient through a global sort by texel
+// Gradients through a global sort by texel
 // ---------------------------------------------------------------------------
-// d_feats = W^T * dO with W the sparse [cells x texels] matrix of record weights.  bwd_feats_kernel<EMIT>
-// writes W as a list of entries and counts them per texel; tex_scan_kernel turns the counts into start
-// offsets; ent_scatter_kernel moves every entry to its texel's segment; feats_gather_kernel walks the
-// grouped list, gathers the cells' upstream gradient rows from L2 into float32 registers and adds one
-// 16-byte reduction per chunk and texel change -- some 20 times fewer reductions than the scatter, whose
-// rate at the L2 is what bounds the direct kernel.
+// d_feats = W^T * dO with W the sparse [cells x texels] matrix of record weights.  A list-phase kernel
+// (bwd_feats_kernel<EMIT> or bwd_depth_kernel<EMIT>) writes W as one entry per row record and counts the
+// entries per texel (of u0); the counts become segment starts (inside ent_scatter_kernel for small feature
+// maps, else tex_scan_kernel); ent_scatter_kernel moves every entry to its texel's segment;
+// feats_gather_kernel walks the grouped list, gathers each entry's dO row from L2 once and accumulates it,
+// in float32 registers, for the entry's two neighbouring texels -- one 16-byte reduction per chunk when the
+// texel changes instead of one per record, which is some 20 times fewer reductions than the direct scatter,
+// whose rate at the L2 is what bounds bwd_feats_kernel.  The parametric depth gradient (two floats per
+// texel, hopelessly contended as atomics) travels with the entries and is summed the same way.
 
 // Exclusive prefix sum of count[0, n) in place; count[n] receives the total.  One block.
 __global__ void __launch_bounds__(1024) tex_scan_kernel(unsigned* __restrict__ count, unsigned n) {
@@ -790,48 +788,79 @@ __global__ void __launch_bounds__(1024) tex_scan_kernel(unsigned* __restrict__ c
   if (tid == nt - 1) count[n] = part[tid];
 }
 
+constexpr unsigned kScanInBlock = 8192;  // texels up to which every scatter block scans the counts itself
+
 // Every emitted entry moves to its place: start of its texel's segment + the position it drew there.
-__global__ void __launch_bounds__(256) ent_scatter_kernel(const uint4* __restrict__ ent, uint4* __restrict__ sorted,
-                                                          const float2* __restrict__ ent_d, float2* __restrict__ sorted_d,
-                                                          const unsigned* __restrict__ start, const unsigned* __restrict__ ent_count,
-                                                          unsigned cap, unsigned texels) {
-  const unsigned n = min(*ent_count, cap);
+// SCAN: tex_count still holds counts; every block derives the starts in shared memory (dynamic,
+// (texels + 1) * 4 bytes) and the total goes to total_out.  Otherwise tex_count holds the starts already.
+template <bool SCAN>
+__global__ void __launch_bounds__(256) ent_scatter_kernel(const Dev p, unsigned texels, unsigned* __restrict__ total_out) {
+  extern __shared__ unsigned s_start[];
+  const unsigned* start = p.tex_count;
+  if (SCAN) {
+    __shared__ unsigned part[256];
+    const unsigned tid = threadIdx.x;
+    const unsigned per = (texels + 255u) / 256u;
+    const unsigned lo = min(tid * per, texels), hi = min(lo + per, texels);
+    unsigned sum = 0;
+    for (unsigned i = lo; i < hi; ++i) sum += __ldg(p.tex_count + i);
+    part[tid] = sum;
+    __syncthreads();
+    for (unsigned d = 1; d < 256u; d <<= 1) {
+      const unsigned v = tid >= d ? part[tid - d] : 0u;
+      __syncthreads();
+      part[tid] += v;
+      __syncthreads();
+    }
+    unsigned run = part[tid] - sum;
+    for (unsigned i = lo; i < hi; ++i) {
+      s_start[i] = run;
+      run += __ldg(p.tex_count + i);
+    }
+    if (blockIdx.x == 0 && tid == 255u) *total_out = part[255];
+    __syncthreads();
+    start = s_start;
+  }
+  const unsigned n = min(*p.ent_count, p.ent_cap);
   for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
-    const uint4 e = ent[i];
+    const uint4 e = p.ent[i];
     if (e.x >= texels) continue;  // void slot
-    const unsigned dst = __ldg(start + e.x) + e.w;
-    sorted[dst] = e;
-    if (ent_d != nullptr) sorted_d[dst] = ent_d[i];
+    const unsigned dst = start[e.x] + p.ent_pos[i];
+    p.ent_sorted[dst] = e;
+    if (p.ent_d != nullptr) p.ent_d_sorted[dst] = p.ent_d[i];
   }
 }
 
-
 // GF32: the upstream gradient is float32 although the features are 16-bit.
 // PDEPTH: the entries also carry the parametric depth gradient (p.ent_d_sorted).
+// n_entries: device word holding the number of grouped entries.
 template <typename T, int V, bool GF32, bool PDEPTH>
-__global__ void __launch_bounds__(128, (PDEPTH || GF32) ? 4 : 5)
-    feats_gather_kernel(const __grid_constant__ Dev p, unsigned texels, unsigned run_len) {
+__global__ void __launch_bounds__(128, (PDEPTH || GF32) ? 3 : 4)
+    feats_gather_kernel(const __grid_constant__ Dev p, const unsigned* __restrict__ n_entries, unsigned run_len) {
   constexpr int E = Chunk<T>::E;
   constexpr int R = (GF32 && E == 8) ? 2 : 1;  // 16-byte loads per chunk of E channels
   constexpr int U = V == 4 ? 2 : 4;            // entries in flight per lane
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const int g = lane / p.GL, lg = lane - g * p.GL;
   if (g >= p.CPW) return;
-  const unsigned n = p.tex_count[texels];  // all entries that were counted
+  const unsigned n = *n_entries;
   const unsigned cpt = (unsigned)(p.GL * V);
   const unsigned groups = gridDim.x * nwarps * p.CPW;
   const uint4* gl = reinterpret_cast<const uint4*>(p.gout) + (size_t)lg * R;
   const bool feats = (p.flags & FBEV_BWD_FEATS) != 0;
   for (unsigned run = (blockIdx.x * nwarps + warp) * p.CPW + g; (unsigned long long)run * run_len < n; run += groups) {
     const unsigned i0 = run * run_len, i1 = min(i0 + run_len, n);
-    float2 acc[V * E / 2];
+    // sums for texel `cur` (acc0) and its right neighbour (acc1); when the next texel is that neighbour,
+    // acc1 slides into acc0
+    float2 acc0[V * E / 2], acc1[V * E / 2];
+    float2 d0 = make_float2(0.0f, 0.0f), d1 = make_float2(0.0f, 0.0f);  // parametric depth: d mean, d sigma
+    bool any1 = false;  // acc1 / d1 received something (a texel without right neighbour never does)
 #pragma unroll
-    for (int k = 0; k < V * E / 2; ++k) acc[k] = make_float2(0.0f, 0.0f);
-    float2 dacc = make_float2(0.0f, 0.0f);  // parametric depth: d mean, d sigma of the texel
-    auto flush = [&](unsigned tex) {
+    for (int k = 0; k < V * E / 2; ++k) acc0[k] = acc1[k] = make_float2(0.0f, 0.0f);
+    auto flush = [&](unsigned tex, const float2* acc, float2 dd) {
       if (PDEPTH && lg == 0) {
-        atomicAdd(p.gdepth + (size_t)tex * 2, dacc.x);
-        atomicAdd(p.gdepth + (size_t)tex * 2 + 1, dacc.y);
+        atomicAdd(p.gdepth + (size_t)tex * 2, dd.x);
+        atomicAdd(p.gdepth + (size_t)tex * 2 + 1, dd.y);
       }
       if (!feats) return;
 #pragma unroll
@@ -843,29 +872,24 @@ __global__ void __launch_bounds__(128, (PDEPTH || GF32) ? 4 : 5)
                    acc[(j * E + e4) / 2 + 1].y);
       }
     };
-    // {texel, cell, weight} of the entries one step ahead, so that their latency overlaps the gathers of this step
-    unsigned nt[U], nc[U], nw[U];
+    // entries one step ahead, so that their latency overlaps the gathers of this step
+    uint4 nx[U];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const uint4 e = __ldg(p.ent_sorted + min(i0 + u, i1 - 1));
-      nt[u] = e.x; nc[u] = e.y; nw[u] = e.z;
-    }
-    unsigned cur = nt[0];
+    for (int u = 0; u < U; ++u) nx[u] = __ldg(p.ent_sorted + min(i0 + u, i1 - 1));
+    unsigned cur = nx[0].x;
     for (unsigned i = i0; i < i1; i += U) {
-      unsigned et[U], ew[U];
+      uint4 e[U];
       uint4 q[U][V][R];
-      float2 dv[U];
+      float4 dv[U];
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        et[u] = nt[u]; ew[u] = nw[u];
-      }
+      for (int u = 0; u < U; ++u) e[u] = nx[u];
       if (feats) {
 #pragma unroll
         for (int u = 0; u < U; ++u)
 #pragma unroll
           for (int j = 0; j < V; ++j)
 #pragma unroll
-            for (int r = 0; r < R; ++r) q[u][j][r] = ldg16(gl + ((size_t)nc[u] * cpt + j * p.GL) * R + r);
+            for (int r = 0; r < R; ++r) q[u][j][r] = ldg16(gl + ((size_t)e[u].y * cpt + j * p.GL) * R + r);
       }
       if (PDEPTH) {
 #pragma unroll
@@ -873,28 +897,41 @@ __global__ void __launch_bounds__(128, (PDEPTH || GF32) ? 4 : 5)
       }
       if (i + U < i1) {
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const uint4 e = __ldg(p.ent_sorted + min(i + U + u, i1 - 1));
-          nt[u] = e.x; nc[u] = e.y; nw[u] = e.z;
-        }
+        for (int u = 0; u < U; ++u) nx[u] = __ldg(p.ent_sorted + min(i + U + u, i1 - 1));
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         if (i + u >= i1) break;
-        if (et[u] != cur) {
-          flush(cur);
+        const unsigned t = e[u].x;
+        if (t != cur) {
+          flush(cur, acc0, d0);
+          if (t == cur + 1u) {
 #pragma unroll
-          for (int k = 0; k < V * E / 2; ++k) acc[k] = make_float2(0.0f, 0.0f);
-          dacc = make_float2(0.0f, 0.0f);
-          cur = et[u];
+            for (int k = 0; k < V * E / 2; ++k) acc0[k] = acc1[k];
+            d0 = d1;
+          } else {
+            if (any1) flush(cur + 1u, acc1, d1);
+#pragma unroll
+            for (int k = 0; k < V * E / 2; ++k) acc0[k] = make_float2(0.0f, 0.0f);
+            d0 = make_float2(0.0f, 0.0f);
+          }
+#pragma unroll
+          for (int k = 0; k < V * E / 2; ++k) acc1[k] = make_float2(0.0f, 0.0f);
+          d1 = make_float2(0.0f, 0.0f);
+          any1 = false;
+          cur = t;
         }
+        const float w0 = __uint_as_float(e[u].z), w1 = __uint_as_float(e[u].w);
+        any1 = any1 || w1 != 0.0f;
         if (PDEPTH) {
-          dacc.x += dv[u].x;
-          dacc.y += dv[u].y;
+          d0.x += dv[u].x;
+          d0.y += dv[u].y;
+          d1.x += dv[u].z;
+          d1.y += dv[u].w;
+          any1 = any1 || dv[u].z != 0.0f || dv[u].w != 0.0f;
         }
         if (!feats) continue;
-        const float w = __uint_as_float(ew[u]);
-        const float2 w2 = make_float2(w, w);
+        const float2 w0v = make_float2(w0, w0), w1v = make_float2(w1, w1);
 #pragma unroll
         for (int j = 0; j < V; ++j) {
           float f[E];
@@ -905,12 +942,16 @@ __global__ void __launch_bounds__(128, (PDEPTH || GF32) ? 4 : 5)
             Chunk<T>::unpack(q[u][j][0], f);
           }
 #pragma unroll
-          for (int k = 0; k < E / 2; ++k)
-            acc[j * E / 2 + k] = __ffma2_rn(w2, make_float2(f[2 * k], f[2 * k + 1]), acc[j * E / 2 + k]);
+          for (int k = 0; k < E / 2; ++k) {
+            const float2 fv = make_float2(f[2 * k], f[2 * k + 1]);
+            acc0[j * E / 2 + k] = __ffma2_rn(w0v, fv, acc0[j * E / 2 + k]);
+            acc1[j * E / 2 + k] = __ffma2_rn(w1v, fv, acc1[j * E / 2 + k]);
+          }
         }
       }
     }
-    flush(cur);
+    flush(cur, acc0, d0);
+    if (any1) flush(cur + 1u, acc1, d1);
   }
 }
 
@@ -1513,9 +1554,9 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_depth_kernel(const __gr
               const float v0 = __uint_as_float(r.z), v1 = __uint_as_float(r.w);
               const bool two = r.y != 0u;
               if (emitted) {
-                float* e = reinterpret_cast<float*>(p.ent_d + first_slot + 2u * (unsigned)i);
+                float* e = reinterpret_cast<float*>(p.ent_d + first_slot + (unsigned)i);
                 e[which] = two ? v0 : v0 + v1;
-                if (two) e[2 + which] = v1;
+                e[2 + which] = two ? v1 : 0.0f;
               } else {
                 const unsigned tex = r.x / (unsigned)cpt;
                 atomicAdd(p.gdepth + (size_t)tex * 2 + which, v0);
@@ -1859,11 +1900,26 @@ __global__ void __launch_bounds__(kMaxWarps * 32) bwd_generic_kernel(const __gri
   loop.end(p);
 }
 
-// float32 accumulation buffer -> gradient tensor of a 16-bit type
+// float32 accumulation buffers -> gradient tensors of a 16-bit type; two arrays (either may be empty) in one
+// launch, four elements per step
 template <typename T>
-__global__ void convert_kernel(const float* __restrict__ src, T* __restrict__ dst, size_t n) {
+__global__ void convert2_kernel(const float* __restrict__ sa, T* __restrict__ da, size_t na, const float* __restrict__ sb,
+                                T* __restrict__ db, size_t nb) {
+  const size_t ua = (na + 3) / 4, ub = (nb + 3) / 4;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) dst[i] = from_float<T>(src[i]);
+  for (size_t u = (size_t)blockIdx.x * blockDim.x + threadIdx.x; u < ua + ub; u += stride) {
+    const bool first = u < ua;
+    const float* src = first ? sa : sb;
+    T* dst = first ? da : db;
+    const size_t n = first ? na : nb, i = (first ? u : u - ua) * 4;
+    if (i + 4 <= n && ((uintptr_t)(dst + i) % 8) == 0) {
+      const float4 v = *reinterpret_cast<const float4*>(src + i);
+      T o[4] = {from_float<T>(v.x), from_float<T>(v.y), from_float<T>(v.z), from_float<T>(v.w)};
+      *reinterpret_cast<uint2*>(dst + i) = *reinterpret_cast<const uint2*>(o);
+    } else {
+      for (size_t k = i; k < n && k < i + 4; ++k) dst[k] = from_float<T>(src[k]);
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -2187,18 +2243,24 @@ static int backward_feats_sort_t(const Plan& pl, const Dev& d_in, cudaStream_t s
   return sort_finish_t<T>(pl, d, st);
 }
 
-// Scan, scatter and gather of the sorted feature gradient, after a kernel that called emit_entries.
+// Scan, scatter and gather of the sorted gradients, after a kernel that called emit_entries.
 template <typename T>
 static int sort_finish_t(const Plan& pl, const Dev& d, cudaStream_t st) {
   const unsigned texels = (unsigned)((size_t)d.B * d.N * d.H * d.W);
-  tex_scan_kernel<<<1, 1024, 0, st>>>(d.tex_count, texels);
   const int sms = sm_count();
-  ent_scatter_kernel<<<sms * 8, 256, 0, st>>>(d.ent, d.ent_sorted, d.ent_d, d.ent_d_sorted, d.tex_count, d.ent_count, d.ent_cap, texels);
-  // entries one lane group walks per run (experiments: fbev_set_tuning tile_y / tile_x with min_blocks 9)
+  unsigned* total = d.ent_count + 1;  // second word of the counter block
+  if (texels <= kScanInBlock) {
+    ent_scatter_kernel<true><<<sms * 8, 256, (size_t)(texels + 1) * 4, st>>>(d, texels, total);
+  } else {
+    tex_scan_kernel<<<1, 1024, 0, st>>>(d.tex_count, texels);
+    ent_scatter_kernel<false><<<sms * 8, 256, 0, st>>>(d, texels, nullptr);
+    total = d.tex_count + texels;
+  }
+  // entries one lane group walks per run, blocks per SM (experiments: fbev_set_tuning tile_y / tile_x with min_blocks 9)
   const unsigned run_len = g_tuning.minb == 9 && g_tuning.ty > 0 ? (unsigned)g_tuning.ty : 32u;
-  const int gb = sms * (g_tuning.minb == 9 && g_tuning.tx > 0 ? g_tuning.tx : 10);
+  const int gb = sms * (g_tuning.minb == 9 && g_tuning.tx > 0 ? g_tuning.tx : 8);
   const bool pd = d.ent_d_sorted != nullptr;
-#define FBEV_GATHER(VV, GF, PD) feats_gather_kernel<T, VV, GF, PD><<<gb, 128, 0, st>>>(d, texels, run_len)
+#define FBEV_GATHER(VV, GF, PD) feats_gather_kernel<T, VV, GF, PD><<<gb, 128, 0, st>>>(d, total, run_len)
 #define FBEV_GATHER_V(GF, PD)                 \
   switch (pl.V) {                             \
     case 1: FBEV_GATHER(1, GF, PD); break;    \
@@ -2370,23 +2432,28 @@ static size_t scratch_min_bytes(const FbevProblem* p, int flags) {
   return n;
 }
 
-// Entry lists of the sorted feature gradient: capacity (entries) and bytes.  One entry per candidate is
-// about twice what the benchmark rigs emit; warps that find the list full add directly instead.
+// Entry lists of the sorted gradients: capacity (entries) and bytes.  One entry per two candidates is a
+// little over twice what the benchmark rigs emit (one per row record); warps that find the list full add
+// directly instead.
 static size_t sort_capacity(const FbevProblem* p) {
   if (g_tuning.minb == 8) return 4096;  // tests: nearly every warp finds the list full
-  const size_t cand = (size_t)p->B * p->X * (size_t)(p->y_end - p->y_begin) * p->N * p->Z;
+  const size_t cand = (size_t)p->B * p->X * (size_t)(p->y_end - p->y_begin) * p->N * p->Z / 2;
   const size_t top = (size_t)1 << 26;
   return cand < top ? (cand < 4096 ? 4096 : cand) : top;
 }
-// the parametric depth gradient rides on the same entries (8 more bytes in each list)
+// the parametric depth gradient rides on the same entries (16 more bytes in each list)
 static bool sort_carries_depth(const FbevProblem* p, int flags) {
   return (flags & FBEV_BWD_DEPTH) && p->mode != FBEV_DEPTH_CATEGORICAL;
+}
+static size_t sort_entry_bytes(const FbevProblem* p, int flags) {
+  // entry and its grouped copy, position, and for the parametric depth gradient four floats in either list
+  return 16 + 16 + 4 + (sort_carries_depth(p, flags) ? 32 : 0);
 }
 static size_t sort_bytes(const FbevProblem* p, int flags) {
   if (!(flags & FBEV_BWD_FEATS) && !sort_carries_depth(p, flags)) return 0;
   const size_t tex = (size_t)p->B * p->N * p->H * p->W;
   if (tex >= 0xfffffff0ull || (size_t)p->B * p->Y * p->X >= 0xfffffff0ull) return 0;
-  return (((tex + 1) * 4 + 255) / 256) * 256 + 256 + 2 * sort_capacity(p) * (sort_carries_depth(p, flags) ? 24 : 16);
+  return (((tex + 1) * 4 + 255) / 256) * 256 + 256 + sort_capacity(p) * sort_entry_bytes(p, flags);
 }
 
 size_t fbev_backward_min_scratch_bytes(const FbevProblem* p, int flags) {
@@ -2434,6 +2501,7 @@ int fbev_backward(const FbevProblem* p, const void* grad_out, void* grad_feats, 
   // the caller gave that much (fbev_backward_scratch_bytes asks for it)
   const size_t sortb = sort_bytes(p, flags), minb = scratch_min_bytes(p, flags);
   // small problems keep the single-launch kernels: three more launches cost more than they save there
+  size_t sort_clear = 0;  // bytes of counters to clear at d.tex_count
   const bool want_sort = g_tuning.minb == 7 || g_tuning.minb == 8 || g_tuning.minb == 9 ||
                          (g_tuning.minb == 0 && (size_t)p->B * p->X * (size_t)(p->y_end - p->y_begin) * p->N * p->Z >= 200000);
   if (want_sort && sortb != 0 && scratch != nullptr && ((uintptr_t)scratch % 256) == 0 && scratch_bytes >= minb + sortb) {
@@ -2444,22 +2512,34 @@ int fbev_backward(const FbevProblem* p, const void* grad_out, void* grad_feats, 
     d.ent_cap = (unsigned)sort_capacity(p);
     d.ent = reinterpret_cast<uint4*>(s + cnt_bytes + 256);
     d.ent_sorted = d.ent + d.ent_cap;
+    unsigned char* after = reinterpret_cast<unsigned char*>(d.ent_sorted + d.ent_cap);
     if (sort_carries_depth(p, flags)) {
-      d.ent_d = reinterpret_cast<float2*>(d.ent_sorted + d.ent_cap);
+      d.ent_d = reinterpret_cast<float4*>(after);
       d.ent_d_sorted = d.ent_d + d.ent_cap;
+      after = reinterpret_cast<unsigned char*>(d.ent_d_sorted + d.ent_cap);
     }
-    if (cudaMemsetAsync(s, 0, cnt_bytes + 256, st) != cudaSuccess) {
+    d.ent_pos = reinterpret_cast<unsigned*>(after);
+    sort_clear = cnt_bytes + 256;
+  }
+  // clears: the accumulation targets and the sort's counters; one memset when they are neighbours in the scratch
+  if (!f32 && sort_clear != 0) {
+    if (cudaMemsetAsync(scratch, 0, minb + sort_clear, st) != cudaSuccess) {
       cudaGetLastError();
       return FBEV_ERR_LAUNCH;
     }
-  }
-  if ((flags & FBEV_BWD_FEATS) && cudaMemsetAsync(d.gfeat, 0, nf * 4, st) != cudaSuccess) {
-    cudaGetLastError();
-    return FBEV_ERR_LAUNCH;
-  }
-  if ((flags & FBEV_BWD_DEPTH) && cudaMemsetAsync(d.gdepth, 0, nd * 4, st) != cudaSuccess) {
-    cudaGetLastError();
-    return FBEV_ERR_LAUNCH;
+  } else {
+    if (sort_clear != 0 && cudaMemsetAsync(d.tex_count, 0, sort_clear, st) != cudaSuccess) {
+      cudaGetLastError();
+      return FBEV_ERR_LAUNCH;
+    }
+    if ((flags & FBEV_BWD_FEATS) && cudaMemsetAsync(d.gfeat, 0, nf * 4, st) != cudaSuccess) {
+      cudaGetLastError();
+      return FBEV_ERR_LAUNCH;
+    }
+    if ((flags & FBEV_BWD_DEPTH) && cudaMemsetAsync(d.gdepth, 0, nd * 4, st) != cudaSuccess) {
+      cudaGetLastError();
+      return FBEV_ERR_LAUNCH;
+    }
   }
   // the feature gradient has a kernel of its own, laid out like the forward
   Dev df = d;
@@ -2472,21 +2552,19 @@ int fbev_backward(const FbevProblem* p, const void* grad_out, void* grad_feats, 
   }
   if (lrc != FBEV_OK) return lrc;
   if (!f32) {
+    // float32 accumulation targets -> gradient tensors, both in one launch
+    const float* sa = (flags & FBEV_BWD_FEATS) ? d.gfeat : nullptr;
+    const float* sb = (flags & FBEV_BWD_DEPTH) ? d.gdepth : nullptr;
+    const size_t na = sa ? nf : 0, nb = sb ? nd : 0;
+    const size_t units = (na + 3) / 4 + (nb + 3) / 4;
     const int threads = 256;
-    if (flags & FBEV_BWD_FEATS) {
-      const int blocks = (int)((nf + threads - 1) / threads < 148 * 16 ? (nf + threads - 1) / threads : 148 * 16);
-      if (p->dtype == FBEV_BF16)
-        convert_kernel<__nv_bfloat16><<<blocks, threads, 0, st>>>(d.gfeat, reinterpret_cast<__nv_bfloat16*>(grad_feats), nf);
-      else
-        convert_kernel<__half><<<blocks, threads, 0, st>>>(d.gfeat, reinterpret_cast<__half*>(grad_feats), nf);
-    }
-    if (flags & FBEV_BWD_DEPTH) {
-      const int blocks = (int)((nd + threads - 1) / threads < 148 * 16 ? (nd + threads - 1) / threads : 148 * 16);
-      if (p->dtype == FBEV_BF16)
-        convert_kernel<__nv_bfloat16><<<blocks, threads, 0, st>>>(d.gdepth, reinterpret_cast<__nv_bfloat16*>(grad_depth), nd);
-      else
-        convert_kernel<__half><<<blocks, threads, 0, st>>>(d.gdepth, reinterpret_cast<__half*>(grad_depth), nd);
-    }
+    const int blocks = (int)((units + threads - 1) / threads < 148 * 16 ? (units + threads - 1) / threads : 148 * 16);
+    if (p->dtype == FBEV_BF16)
+      convert2_kernel<__nv_bfloat16><<<blocks, threads, 0, st>>>(sa, reinterpret_cast<__nv_bfloat16*>(grad_feats), na, sb,
+                                                                 reinterpret_cast<__nv_bfloat16*>(grad_depth), nb);
+    else
+      convert2_kernel<__half><<<blocks, threads, 0, st>>>(sa, reinterpret_cast<__half*>(grad_feats), na, sb,
+                                                          reinterpret_cast<__half*>(grad_depth), nb);
     if (cudaGetLastError() != cudaSuccess) return FBEV_ERR_LAUNCH;
   }
   return FBEV_OK;

@@ -118,8 +118,9 @@ int fbev_forward(const FbevProblem* p, void* out, int32_t* valid_count, void* st
 
 /* Bytes of scratch fbev_backward works best with for this problem and flags: the float32 accumulation
  * targets of the 16-bit types (fbev_backward_min_scratch_bytes) plus, when the feature gradient is asked
- * for, the entry lists of its sort by texel: (B*N*H*W + 1) * 4 bytes of counters and 32 bytes per entry,
- * one entry per candidate B*X*rows*N*Z (at most 2^26). */
+ * for (or the depth gradient of a parametric mode), the entry lists of the sort by texel: (B*N*H*W + 1) * 4
+ * bytes of counters and 36 bytes per entry (68 with a parametric depth gradient), one entry per two
+ * candidates B*X*rows*N*Z (at least 4096, at most 2^26 entries). */
 size_t fbev_backward_scratch_bytes(const FbevProblem* p, int flags);
 
 /* The least scratch fbev_backward accepts: 0 for float32 tensors (gradients accumulate in place),

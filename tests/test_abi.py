@@ -93,15 +93,15 @@ def test_backward_scratch_size_and_checks():
     p = _problem()
     tex = 1 * 2 * 4 * 4
     assert lib.fbev_backward_min_scratch_bytes(ctypes.byref(p), 3) == 0        # float32: in place
-    # the gradients' sort by texel: counters, one word, two lists of 4096 entries (the least capacity); an entry
-    # is 16 bytes, 24 when it also carries the parametric depth gradient
-    assert lib.fbev_backward_scratch_bytes(ctypes.byref(p), 1) == 256 + 256 + 2 * 4096 * 16
-    assert lib.fbev_backward_scratch_bytes(ctypes.byref(p), 3) == 256 + 256 + 2 * 4096 * 24
-    assert lib.fbev_backward_scratch_bytes(ctypes.byref(p), 2) == 256 + 256 + 2 * 4096 * 24
+    # the gradients' sort by texel: counters, a counter block, 4096 entries (the least capacity) of 36 bytes
+    # (entry, grouped copy, position), 68 when they also carry the parametric depth gradient
+    assert lib.fbev_backward_scratch_bytes(ctypes.byref(p), 1) == 256 + 256 + 4096 * 36
+    assert lib.fbev_backward_scratch_bytes(ctypes.byref(p), 3) == 256 + 256 + 4096 * 68
+    assert lib.fbev_backward_scratch_bytes(ctypes.byref(p), 2) == 256 + 256 + 4096 * 68
     p.dtype = p.out_dtype = _lib.BF16
     assert lib.fbev_backward_min_scratch_bytes(ctypes.byref(p), 3) == tex * 8 * 4 + tex * 2 * 4
     assert lib.fbev_backward_min_scratch_bytes(ctypes.byref(p), 1) == tex * 8 * 4
-    assert lib.fbev_backward_scratch_bytes(ctypes.byref(p), 1) == tex * 8 * 4 + 256 + 256 + 2 * 4096 * 16
+    assert lib.fbev_backward_scratch_bytes(ctypes.byref(p), 1) == tex * 8 * 4 + 256 + 256 + 4096 * 36
     # 16-bit gradients without scratch are refused before anything is launched
     assert lib.fbev_backward(ctypes.byref(p), 256, 256, 256, None, 0, 3, None) == 8   # FBEV_ERR_SCRATCH
     assert lib.fbev_backward(ctypes.byref(p), 256, 256, 256, None, 0, 0, None) == 0   # nothing requested
