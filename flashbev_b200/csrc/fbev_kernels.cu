@@ -1351,8 +1351,8 @@ __device__ __forceinline__ void red_add4(float* addr, float a, float b, float c,
 
 // Sum over the GL lanes of a group; the result is valid in the group's first lane.
 __device__ __forceinline__ float group_sum(float v, int lg, int GL) {
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) {
+  // first step: the largest power of two below GL (larger offsets would add nothing)
+  for (int off = GL > 16 ? 16 : GL > 8 ? 8 : GL > 4 ? 4 : GL > 2 ? 2 : 1; off > 0; off >>= 1) {
     const float o = __shfl_down_sync(kFull, v, off);
     if (lg + off < GL) v += o;
   }
@@ -1567,14 +1567,35 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_depth_kernel(const __gr
           }
           continue;
         }
-        // ---- one lane per sample: S from four T values, then the sample's atomics ----
-        for (int c = 0; c < p.CPW; ++c) {
-          const int ns = sSmp[c];
+        // ---- one lane per sample: S from four T values, then the sample's atomics.  The samples of all cells of
+        // the warp are walked as one list.  Categorical: neighbouring samples are the height bins of one camera
+        // column, which mostly share the texel AND the depth bin (depth barely changes with height), so equal
+        // (texel, bin) neighbours are summed with a segmented scan first and one lane adds for the run ----
+        int ns_total = 0;
+        for (int c = 0; c < p.CPW; ++c) ns_total += sSmp[c];
+        const unsigned lt_mask = (1u << lane) - 1u;
+        for (int base = 0; base < ns_total; base += 32) {
+          int off = base + lane, c = 0;
+          bool active = false;
+          for (int cc = 0; cc < p.CPW; ++cc) {
+            const int nsc = sSmp[cc];
+            if (!active) {
+              if (off < nsc) {
+                c = cc;
+                active = true;
+              } else {
+                off -= nsc;
+              }
+            }
+          }
           const float inv = mean_pool ? __shfl_sync(kFull, inv_of_lane, c) : 1.0f;
-          const uint4* rc = recs + (size_t)c * rstride;
-          for (int idx = lane; idx < ns; idx += 32) {
-            const uint4* sr = samp + ((size_t)c * p.cap + idx) * 3;
-            const uint4 sw = sr[0], sa = sr[1], sp = sr[2];
+          float v00 = 0.0f, v01 = 0.0f, v10 = 0.0f, v11 = 0.0f, cm = 0.0f, cs = 0.0f;
+          uint4 sa = make_uint4(0u, 0u, 0u, 0u);
+          if (active) {
+            const uint4* rc = recs + (size_t)c * rstride;
+            const uint4* sr = samp + ((size_t)c * p.cap + off) * 3;
+            const uint4 sw = sr[0], sp = sr[2];
+            sa = sr[1];
             const float w00 = __uint_as_float(sw.x), w01 = __uint_as_float(sw.y), w10 = __uint_as_float(sw.z),
                         w11 = __uint_as_float(sw.w);
             const uint4 ra = rc[sp.x & 0xffffu], rb = rc[sp.x >> 16];
@@ -1583,29 +1604,45 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_depth_kernel(const __gr
             S = fmaf(w01, __uint_as_float(rb.z), S);
             S = fmaf(w11, __uint_as_float(rb.w), S);
             const float sd = S * inv;
-            float* d00 = p.gdepth + sa.x;
-            float* d10 = d00 + sa.y;
-            float* d01 = d00 + sa.z;
-            float* d11 = d01 + sa.y;
-            if (p.mode == FBEV_DEPTH_CATEGORICAL) {
-              const int k = (int)sa.w;
-              atomicAdd(d00 + k, sd * w00);
-              atomicAdd(d01 + k, sd * w01);
-              atomicAdd(d10 + k, sd * w10);
-              atomicAdd(d11 + k, sd * w11);
-            } else {
-              const float wgt = __uint_as_float(sp.y);
-              const float cm = legacy ? wgt : __uint_as_float(sp.z);
-              const float cs = legacy ? wgt : __uint_as_float(sp.w);
-              atomicAdd(d00 + 0, sd * cm * w00);
-              atomicAdd(d00 + 1, sd * cs * w00);
-              atomicAdd(d01 + 0, sd * cm * w01);
-              atomicAdd(d01 + 1, sd * cs * w01);
-              atomicAdd(d10 + 0, sd * cm * w10);
-              atomicAdd(d10 + 1, sd * cs * w10);
-              atomicAdd(d11 + 0, sd * cm * w11);
-              atomicAdd(d11 + 1, sd * cs * w11);
+            v00 = sd * w00; v01 = sd * w01; v10 = sd * w10; v11 = sd * w11;
+            const float wgt = __uint_as_float(sp.y);
+            cm = legacy ? wgt : __uint_as_float(sp.z);
+            cs = legacy ? wgt : __uint_as_float(sp.w);
+          }
+          float* d00 = p.gdepth + sa.x;
+          float* d10 = d00 + sa.y;
+          float* d01 = d00 + sa.z;
+          float* d11 = d01 + sa.y;
+          if (p.mode == FBEV_DEPTH_CATEGORICAL) {
+            const unsigned key = active ? sa.x + sa.w : 0xffffffffu - (unsigned)lane;  // element index of (texel, bin)
+            const unsigned pkey = __shfl_up_sync(kFull, key, 1);
+            const unsigned headm = __ballot_sync(kFull, active && (lane == 0 || pkey != key));
+            const int rs = 31 - __clz((int)(headm & (lt_mask | (1u << lane))));
+            for (int d = 1; d < 32 && d < p.Z; d <<= 1) {
+              const float a = __shfl_up_sync(kFull, v00, d), b = __shfl_up_sync(kFull, v01, d);
+              const float e = __shfl_up_sync(kFull, v10, d), f = __shfl_up_sync(kFull, v11, d);
+              if (active && lane - d >= rs) {
+                v00 += a; v01 += b; v10 += e; v11 += f;
+              }
             }
+            const unsigned actm = __ballot_sync(kFull, active);
+            const bool tail = active && (lane == 31 || ((headm >> (lane + 1)) & 1u) || !((actm >> (lane + 1)) & 1u));
+            if (tail) {
+              const int k = (int)sa.w;
+              atomicAdd(d00 + k, v00);
+              atomicAdd(d01 + k, v01);
+              atomicAdd(d10 + k, v10);
+              atomicAdd(d11 + k, v11);
+            }
+          } else if (active) {
+            atomicAdd(d00 + 0, cm * v00);
+            atomicAdd(d00 + 1, cs * v00);
+            atomicAdd(d01 + 0, cm * v01);
+            atomicAdd(d01 + 1, cs * v01);
+            atomicAdd(d10 + 0, cm * v10);
+            atomicAdd(d10 + 1, cs * v10);
+            atomicAdd(d11 + 0, cm * v11);
+            atomicAdd(d11 + 1, cs * v11);
           }
         }
         __syncwarp();
@@ -2321,7 +2358,6 @@ static int backward_t(const Plan& pl, Dev d, const Plan& plf, const Dev& df, cud
   Dev dd = df;
   // 16 candidates per cell and pass: half the shared memory of the forward's 32, twice the resident warps, which
   // this latency-bound kernel needs more than it minds a second pass on tiles that three cameras see
-  pld.cap = dd.cap = g_tuning.minb == 10 ? 32 : 16;
   pld.smem = header_bytes(dd.N) + (size_t)pld.warps * depth_warp_bytes(pld.CPW, pld.cap);
   if ((d.flags & FBEV_BWD_FEATS) && plf.chunked) {
     if (depth_on_records && df.ent != nullptr) {
