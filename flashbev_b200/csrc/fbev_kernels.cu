@@ -2358,6 +2358,7 @@ static int backward_t(const Plan& pl, Dev d, const Plan& plf, const Dev& df, cud
   Dev dd = df;
   // 16 candidates per cell and pass: half the shared memory of the forward's 32, twice the resident warps, which
   // this latency-bound kernel needs more than it minds a second pass on tiles that three cameras see
+  pld.cap = dd.cap = 16;
   pld.smem = header_bytes(dd.N) + (size_t)pld.warps * depth_warp_bytes(pld.CPW, pld.cap);
   if ((d.flags & FBEV_BWD_FEATS) && plf.chunked) {
     if (depth_on_records && df.ent != nullptr) {
