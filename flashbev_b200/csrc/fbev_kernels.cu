@@ -330,6 +330,10 @@ __device__ __forceinline__ void row_list_phase(const Dev& p, const Tile& t, cons
   const int rstride = row_stride(p.cap);
   const float inv_per = 1.0f / (float)per, inv_z = 1.0f / (float)p.Z, inv_tx = 1.0f / (float)p.TX;
   const unsigned lt = (1u << lane) - 1u;
+  // camera of the ci-th set bit of vis, as a byte table in the unused part of sLen (cells use entries 0..7)
+  unsigned char* visl = reinterpret_cast<unsigned char*>(sLen + kMaxCellsPerWarp);
+  if ((vis >> lane) & 1u) visl[__popc(vis & lt)] = (unsigned char)lane;
+  __syncwarp();
   for (int base = 0; base < total; base += 32) {
     const int q = base + lane;
     bool ok = false;
@@ -347,7 +351,7 @@ __device__ __forceinline__ void row_list_phase(const Dev& p, const Tile& t, cons
       const int ly = fast_div(tc, inv_tx), lx = tc - ly * p.TX;
       const int x = t.x0 + lx, y = t.y0 + ly;
       if (tc < tile_cells && x < t.x1 && y < t.y1) {
-        const int n = (int)__fns(vis, 0u, ci + 1);  // ci-th visible camera
+        const int n = visl[ci];  // ci-th visible camera
         const int fh = h.fs[n * 2];
         fw = h.fs[n * 2 + 1];
         const float vx = centre(x, vs[0], vmin[0]), vy = centre(y, vs[1], vmin[1]), vz = centre(z, vs[2], vmin[2]);
