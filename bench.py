@@ -365,6 +365,21 @@ def main():
             extra["fwd_bwd_us"] = ms_fb * 1e3
             extra["fwd_bwd_note"] = "forward + backward (gradients for features and depth), device time, L2 flushed"
 
+            # the same seven launches replayed from a CUDA graph (what a training loop with static shapes does)
+            side = torch.cuda.Stream(device=device)
+            with torch.cuda.stream(side):
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    cs = torch.cuda.current_stream().cuda_stream
+                    rc = lib.fbev_forward(ctypes.byref(prob), out.data_ptr(), None, cs)
+                    rc = rc or lib.fbev_backward(ctypes.byref(prob), go.data_ptr(), g_feats.data_ptr(), g_depth.data_ptr(),
+                                                 scratch.data_ptr() if nbytes else None, nbytes, flags, cs)
+                if rc:
+                    raise RuntimeError(_lib.strerror(rc))
+            torch.cuda.synchronize()
+            ms_g, _ = timed(graph.replay, nb, 5)
+            extra["fwd_bwd_us_cuda_graph"] = ms_g * 1e3
+
             # the reference's own mode on the same shapes (float32, parametric laplace depth, mean pooling), for
             # comparison with the reference CUDA kernel that `--impl reference` times on the same box
             wp = synth.workload(args.workload, dtype="fp32")

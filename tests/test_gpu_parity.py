@@ -300,6 +300,44 @@ def test_backward_only_requested_gradients(cuda_device, mode, name):
         assert rel_err(inp[which].grad.float().cpu().numpy(), both[which].grad.float().cpu().numpy()) < 5 * tol
 
 
+def test_forward_and_backward_replay_from_a_cuda_graph(cuda_device):
+    """Every launch of the library is stream-ordered and allocation-free, so a captured forward + backward
+    replays with new inputs in the same buffers."""
+    lib = _lib.load()
+    w = CFG2
+    inp = to_device(inputs_for(w, "categorical"), cuda_device)
+    from flashbev_b200.flash_bevpool import DepthSpec, make_problem
+    prob, keep = make_problem(inp["depth_params"], inp["image_feats"], inp["projection_matrices"], inp["feature_size"],
+                              inp["image_size"], inp["roi_range"], inp["grid_size"],
+                              DepthSpec(2, depth_bin_range=(w.d0, w.delta)), 1e-6, 0.0)
+    out = torch.empty(w.B, w.Y, w.X, w.C, dtype=keep[0].dtype, device=cuda_device)
+    go = synth.upstream_grad(w).to(device=cuda_device, dtype=keep[0].dtype)
+    gf, gd = torch.empty_like(keep[0]), torch.empty_like(keep[1])
+    nbytes = lib.fbev_backward_scratch_bytes(ctypes.byref(prob), 3)
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=cuda_device)
+
+    def run(stream):
+        assert lib.fbev_forward(ctypes.byref(prob), out.data_ptr(), None, stream) == 0
+        assert lib.fbev_backward(ctypes.byref(prob), go.data_ptr(), gf.data_ptr(), gd.data_ptr(), scratch.data_ptr(),
+                                 nbytes, 3, stream) == 0
+
+    side = torch.cuda.Stream(device=cuda_device)
+    with torch.cuda.stream(side):
+        run(side.cuda_stream)  # warm-up outside the capture: function attributes, module load
+        side.synchronize()
+        ref = [t.clone() for t in (out, gf, gd)]
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            run(torch.cuda.current_stream().cuda_stream)
+        keep[0].mul_(0.5)   # new features in the same buffer: output and feature... gradients change
+        graph.replay()
+        side.synchronize()
+    assert rel_err(out.float().cpu().numpy(), 0.5 * ref[0].float().cpu().numpy()) < TOL_LOWP
+    # gradients: float32 sums in a different atomic order, then rounded to bfloat16 -- one ulp (2^-8) apart at most
+    assert rel_err(gf.float().cpu().numpy(), ref[1].float().cpu().numpy()) < 2 * TOL_LOWP  # linear in dO only
+    assert rel_err(gd.float().cpu().numpy(), 0.5 * ref[2].float().cpu().numpy()) < 2 * TOL_LOWP
+
+
 def test_result_buffer_given_by_the_caller(cuda_device):
     """out= on the device and in page-locked host memory (written by the kernel) equal the default result."""
     w = SMALL
