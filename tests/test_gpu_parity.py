@@ -190,17 +190,18 @@ def test_kernel_matches_reference_dense_path_fixtures(cuda_device, path):
     assert (diff ** 2).mean() < 1e-6 and np.abs(diff).mean() < 1e-6     # tools/profile_differences.py:75-77
 
 
-def backward_case(w, mode, device, pool=None, dtype=None, legacy=False, threshold=0.0):
+def backward_case(w, mode, device, pool=None, dtype=None, legacy=False, threshold=0.0, out_f32=False):
     inp = synth.make_inputs(w, "categorical" if mode == "categorical" else "parametric", dtype=dtype)
     go = synth.upstream_grad(w)
-    if (dtype or w.dtype) != "fp32":
+    if (dtype or w.dtype) != "fp32" and not out_f32:
         go = go.to(inp["image_feats"].dtype)
     p = oracle_problem(inp, w, mode, pool=pool, threshold=threshold)
     rf, rd = O.backward(p, go.float().numpy(), dtype=np.float64, legacy_depth_grad=legacy)
     dev = to_device(inp, device)
     dev["image_feats"].requires_grad_(True)
     dev["depth_params"].requires_grad_(True)
-    out = flash_bevpool(**dev, **op_kwargs(w, mode, threshold, pool), legacy_depth_grad=legacy)
+    out = flash_bevpool(**dev, **op_kwargs(w, mode, threshold, pool), legacy_depth_grad=legacy,
+                        out_dtype=torch.float32 if out_f32 else None)
     out.backward(go.to(device))
     torch.cuda.synchronize()
     name = dtype or w.dtype
@@ -268,6 +269,11 @@ def test_backward_kernel_variants_agree_with_the_oracle(cuda_device, variant):
         backward_case(CFG3S, "categorical", cuda_device)
         backward_case(tall, "categorical", cuda_device, pool="mean")   # several passes per cell
         backward_case(tall, "laplace", cuda_device)
+        # float32 output / upstream gradient of a 16-bit operator, the reference's depth gradient, a threshold
+        backward_case(SMALL, "categorical", cuda_device, dtype="bf16", out_f32=True)
+        backward_case(SMALL, "laplace", cuda_device, dtype="fp16", out_f32=True, pool="mean")
+        backward_case(SMALL, "laplace", cuda_device, legacy=True)
+        backward_case(SMALL, "gaussian", cuda_device, legacy=True, threshold=1e-3, dtype="bf16")
     finally:
         lib.fbev_set_tuning(0, 0, 0, 0, 0)
 
