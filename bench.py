@@ -461,6 +461,26 @@ def main():
             e2e_ms_max = min(ms_copy, ms_direct)
             extra["e2e_path"] = "out=pinned host tensor" if ms_direct <= ms_copy else "device result + copy"
 
+            if world > 1:
+                # one large sample (cfg5) with its BEV rows split over the ranks: all-gather of the output
+                # against the kernel storing its rows into every rank's buffer; one GPU alone beside them
+                from flashbev_b200 import sharding
+                w5 = synth.workload("cfg5")
+                in5 = {k: v.to(device) for k, v in synth.make_inputs(w5, "categorical", batch_slice=(0, 1)).items()}
+                kw5 = dict(depth_distribution=2, depth_bin_range=(w5.d0, w5.delta), depth_weight_threshold=0.0)
+                variants = {
+                    "rows_split_allgather_us": lambda: sharding.flash_bevpool_rows(**in5, **kw5),
+                    "rows_split_peer_stores_us": lambda: sharding.flash_bevpool_rows_p2p(**in5, **kw5),
+                    "rows_split_one_gpu_us": lambda: flash_bevpool(**in5, **kw5),
+                }
+                with torch.no_grad():
+                    for name, fn in variants.items():
+                        ms_v, _ = timed(fn, 20, 5)
+                        tv = torch.tensor([ms_v], dtype=torch.float64, device=device)
+                        dist.all_reduce(tv, op=dist.ReduceOp.MAX)
+                        extra[name] = float(tv[0]) * 1e3
+                extra["rows_split_workload"] = "cfg5, one sample: 512x512x16 grid, 6 cams, C=256"
+
             # L2-resident read bandwidth: 32 MiB buffer read 50 times
             buf = torch.empty(32 << 20, dtype=torch.uint8, device=device)
             sink = torch.zeros(1, dtype=torch.int32, device=device)

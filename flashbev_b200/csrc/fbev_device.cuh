@@ -29,6 +29,8 @@ struct Dev {
   const int* isize;
   const float* roi;
   void* out;
+  void* out_peers[7];  // further copies of the output to store to (other GPUs' buffers), n_peers of them
+  int n_peers;
   int* count;
   int* status;
   const void* gout;  // backward: upstream gradient

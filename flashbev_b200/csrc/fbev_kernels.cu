@@ -551,6 +551,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32, MINB) fwd_kernel(const __grid_
         const size_t cell = ((size_t)t.b * p.Y + y) * p.X + x;
 #pragma unroll
         for (int j = 0; j < V; ++j) store_chunk<T>(p.out, p.out_f32, cell * cpt + lg + j * p.GL, acc + j * E);
+        for (int k = 0; k < p.n_peers; ++k) {  // the same rows into the other ranks' buffers (plain peer stores)
+#pragma unroll
+          for (int j = 0; j < V; ++j) store_chunk<T>(p.out_peers[k], p.out_f32, cell * cpt + lg + j * p.GL, acc + j * E);
+        }
         if (p.count != nullptr && lg == 0) p.count[cell] = cnt;
       }
       __syncwarp();
@@ -1332,10 +1336,13 @@ __global__ void __launch_bounds__(kMaxWarps * 32) fwd_generic_kernel(const __gri
         if (c < p.C) {
           float v = acc[k];
           if (p.pool == FBEV_POOL_MEAN) v = cnt > 0 ? __fdiv_rn(v, (float)cnt) : 0.0f;
-          if (p.out_f32)
+          if (p.out_f32) {
             obase32[cell * p.C + c] = v;
-          else
+            for (int q = 0; q < p.n_peers; ++q) reinterpret_cast<float*>(p.out_peers[q])[cell * p.C + c] = v;
+          } else {
             obase[cell * p.C + c] = from_float<T>(v);
+            for (int q = 0; q < p.n_peers; ++q) reinterpret_cast<T*>(p.out_peers[q])[cell * p.C + c] = from_float<T>(v);
+          }
         }
       }
     }
@@ -2414,15 +2421,23 @@ using namespace fbev;
 
 // unknown_hw: the caller could not tell the tensor's H and W (reference launcher signature); the
 // kernels then trust feature_size, as the reference does.
-static int forward_impl(const FbevProblem* p, void* out, int32_t* valid_count, void* stream, bool unknown_hw) {
+static int forward_impl(const FbevProblem* p, void* out, int32_t* valid_count, void* stream, bool unknown_hw,
+                        void* const* peers = nullptr, int n_peers = 0) {
   const int rc = validate(p);
   if (rc != FBEV_OK) return rc;
   if (out == nullptr) return FBEV_ERR_NULL;
   if (((uintptr_t)out % elem_size(p->out_dtype)) || ((uintptr_t)valid_count % 4)) return FBEV_ERR_ALIGN;
+  if (n_peers < 0 || n_peers > 7 || (n_peers > 0 && peers == nullptr)) return FBEV_ERR_SHAPE;
   Dev d;
   fill_dev(p, d);
   d.out = out;
   d.count = valid_count;
+  d.n_peers = n_peers;
+  for (int k = 0; k < n_peers; ++k) {
+    if (peers[k] == nullptr) return FBEV_ERR_NULL;
+    if ((uintptr_t)peers[k] % 16 != (uintptr_t)out % 16) return FBEV_ERR_ALIGN;  // same kernel, same store width
+    d.out_peers[k] = peers[k];
+  }
   if (unknown_hw) d.H = d.W = 46340;  // feature_size entries up to 2^31 texels pass the in-kernel bound
   const Plan pl = make_plan(p, d, false, p->image_feats, out, nullptr);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
@@ -2495,6 +2510,11 @@ static size_t sort_bytes(const FbevProblem* p, int flags) {
   const size_t tex = (size_t)p->B * p->N * p->H * p->W;
   if (tex >= 0xfffffff0ull || (size_t)p->B * p->Y * p->X >= 0xfffffff0ull) return 0;
   return (((tex + 1) * 4 + 255) / 256) * 256 + 256 + sort_capacity(p) * sort_entry_bytes(p, flags);
+}
+
+int fbev_forward_peers(const FbevProblem* p, void* out, void* const* peer_outs, int n_peers, int32_t* valid_count,
+                       void* stream) {
+  return forward_impl(p, out, valid_count, stream, false, peer_outs, n_peers);
 }
 
 size_t fbev_backward_min_scratch_bytes(const FbevProblem* p, int flags) {

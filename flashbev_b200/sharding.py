@@ -13,6 +13,9 @@ The reference has no distributed code.  The operator shards in two ways:
   which are summed with one all-reduce each.
 
 Collectives are NCCL's (NVLink / NVSwitch); tensors are in local HBM before any kernel reads them.
+``flash_bevpool_rows_p2p`` is the inference form of the row split without a collective: the forward kernel
+stores its rows into every rank's output buffer itself (peer stores over NVLink, symmetric memory from
+``torch.distributed._symmetric_memory``), and one cross-rank barrier replaces the all-gather.
 """
 from __future__ import annotations
 
@@ -21,7 +24,10 @@ from typing import Callable, Optional, Tuple
 import torch
 import torch.distributed as dist
 
-from .flash_bevpool import _host_values, flash_bevpool
+import ctypes
+
+from . import _lib
+from .flash_bevpool import DepthSpec, _host_values, flash_bevpool, make_problem
 
 
 def even_slice(n: int, world: int, rank: int) -> Tuple[int, int]:
@@ -159,3 +165,65 @@ def flash_bevpool_batch(image_feats, depth_params, projection_matrices, feature_
     if batch is None:
         raise ValueError("gather=True needs the size of the whole batch")
     return gather_batch(out.detach(), batch, group)
+
+
+# symmetric output buffers per (group, shape, dtype, device): allocation and rendezvous are collective and cost
+# milliseconds, the steady state reuses them.  Two buffers alternate, see flash_bevpool_rows_p2p.
+_p2p_buffers = {}
+
+
+def _p2p_buffer(shape, dtype, device, group):
+    import torch.distributed._symmetric_memory as symm_mem
+    pg = dist.group.WORLD if group is None else group
+    key = (pg.group_name, tuple(shape), dtype, str(device))
+    hit = _p2p_buffers.get(key)
+    if hit is None:
+        bufs = [symm_mem.empty(*shape, dtype=dtype, device=device) for _ in range(2)]
+        hdls = [symm_mem.rendezvous(b, pg) for b in bufs]
+        hit = {"bufs": bufs, "hdls": hdls, "calls": 0, "flag": torch.zeros(1, dtype=torch.int32, device=device)}
+        _p2p_buffers[key] = hit
+    return hit
+
+
+def flash_bevpool_rows_p2p(image_feats, depth_params, projection_matrices, feature_size, image_size, roi_range,
+                           grid_size, depth_distribution=0, epsilon=1e-6, depth_weight_threshold=1e-6, group=None,
+                           **spec_kwargs) -> torch.Tensor:
+    """Row-split forward whose kernel writes every rank's copy of the output (inference; no autograd).
+
+    Rank r computes rows ``row_slice(Y, world, r)`` and stores them into its own and all peers' output buffers
+    (``fbev_forward_peers``: plain peer stores over NVLink, the kernel waits on nothing).  One tiny NCCL
+    all-reduce after the launch is the barrier: when it completes on a rank, every rank's kernel has finished
+    and all rows are in this rank's buffer.  It replaces the all-gather of the whole output.
+
+    Two symmetric buffers alternate between calls.  A rank passes the barrier of call k+1 only after every
+    rank's stream has finished everything queued before it, the consumers of result k included, so call k+2
+    may overwrite the buffer of call k without a second barrier.  The returned tensor is therefore valid until
+    the call after the next one with the same shape on this group; consumers must be queued on the calling
+    stream (or copy the result).
+    """
+    world, rank = _world(group)
+    if world == 1:
+        return flash_bevpool(image_feats, depth_params, projection_matrices, feature_size, image_size, roi_range,
+                             grid_size, depth_distribution, epsilon=epsilon,
+                             depth_weight_threshold=depth_weight_threshold, **spec_kwargs)
+    if world > 8:
+        raise ValueError("flash_bevpool_rows_p2p supports up to 8 ranks (one NVLink domain)")
+    rows = int(_host_values(grid_size)[1])
+    spec = DepthSpec(depth_distribution, y_range=row_slice(rows, world, rank), **spec_kwargs)
+    with torch.no_grad():
+        p, keep = make_problem(depth_params, image_feats, projection_matrices, feature_size, image_size, roi_range,
+                               grid_size, spec, epsilon, depth_weight_threshold)
+        feats = keep[0]
+        dtype = torch.float32 if spec.out_dtype == torch.float32 else feats.dtype
+        state = _p2p_buffer((p.B, p.Y, p.X, p.C), dtype, feats.device, group)
+        which = state["calls"] & 1
+        state["calls"] += 1
+        out, hdl = state["bufs"][which], state["hdls"][which]
+        peers = [ptr for r, ptr in enumerate(hdl.buffer_ptrs) if r != rank]
+        arr = (ctypes.c_void_p * len(peers))(*peers)
+        with torch.cuda.device(feats.device):
+            stream = torch.cuda.current_stream().cuda_stream
+            rc = _lib.load().fbev_forward_peers(ctypes.byref(p), out.data_ptr(), arr, len(peers), None, stream)
+            _lib.check(rc, "fbev_forward_peers")
+            dist.all_reduce(state["flag"], group=group)  # barrier in stream order
+    return out

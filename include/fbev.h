@@ -116,6 +116,17 @@ typedef struct FbevProblem {
  * int32 [B,Y,X]) receives the number of accepted samples per cell. */
 int fbev_forward(const FbevProblem* p, void* out, int32_t* valid_count, void* stream);
 
+/* Forward whose result rows also go to other GPUs.  (No counterpart in the reference, which has no
+ * distributed code.)  Same as fbev_forward, and every 16-byte piece of out[:, y_begin:y_end] is stored to
+ * peer_outs[0 .. n_peers) as well: device pointers of [B,Y,X,C] buffers in other GPUs' memory that this
+ * device may write (peer access enabled, or a symmetric-memory mapping), n_peers <= 7, same alignment
+ * modulo 16 as out.  With BEV rows split over ranks through y_begin / y_end this replaces the all-gather of
+ * the output: every rank ends up with all rows once all ranks' kernels have finished, which the caller
+ * establishes with its own cross-rank barrier after the launch.  Plain st.global stores; the kernel waits
+ * on nothing. */
+int fbev_forward_peers(const FbevProblem* p, void* out, void* const* peer_outs, int n_peers, int32_t* valid_count,
+                       void* stream);
+
 /* Bytes of scratch fbev_backward works best with for this problem and flags: the float32 accumulation
  * targets of the 16-bit types (fbev_backward_min_scratch_bytes) plus, when the feature gradient is asked
  * for (or the depth gradient of a parametric mode), the entry lists of the sort by texel: (B*N*H*W + 1) * 4

@@ -43,6 +43,34 @@ def _worker(rank, world, port, results):
                                            inp["roi_range"], inp["grid_size"], **kw)
         rows.backward(go)
         ok_rows = bool(torch.equal(rows, alone))
+        # rows over the ranks without a collective: the kernel stores into every rank's buffer
+        args = [inp[k] for k in ("projection_matrices", "feature_size", "image_size", "roi_range", "grid_size")]
+        ok_p2p = True
+        for call in range(3):  # the two symmetric buffers alternate; the third call reuses the first
+            scale_in = 1.0 + call
+            p2p = sharding.flash_bevpool_rows_p2p(inp["image_feats"] * scale_in, inp["depth_params"], *args, **kw)
+            want = flash_bevpool(inp["image_feats"] * scale_in, inp["depth_params"], *args, **kw)
+            ok_p2p = ok_p2p and bool(torch.equal(p2p, want))
+        # device time of the two row-split forwards (informative)
+        def timed(fn, n=20):
+            for _ in range(3):
+                fn()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            dist.barrier()
+            s.record()
+            for _ in range(n):
+                fn()
+            e.record()
+            torch.cuda.synchronize()
+            return s.elapsed_time(e) / n * 1e3
+        with torch.no_grad():
+            t_nccl = timed(lambda: sharding.flash_bevpool_rows(inp["image_feats"], inp["depth_params"], *args, **kw))
+            t_p2p = timed(lambda: sharding.flash_bevpool_rows_p2p(inp["image_feats"], inp["depth_params"], *args, **kw))
+            t_one = timed(lambda: flash_bevpool(inp["image_feats"], inp["depth_params"], *args, **kw))
+        if rank == 0:
+            print(f"row split on {world} GPUs: all-gather {t_nccl:.1f} us, peer stores {t_p2p:.1f} us, one GPU {t_one:.1f} us",
+                  flush=True)
         scale = float(f0.grad.abs().max())
         ok_gf = float((f1.grad - f0.grad).abs().max()) < 1e-5 * scale
         ok_gd = float((d1.grad - d0.grad).abs().max()) < 1e-5 * float(d0.grad.abs().max())
@@ -57,7 +85,7 @@ def _worker(rank, world, port, results):
                                                 part["grid_size"], batch=wb.B, gather=True, **kw)
         ok_batch = bool(torch.equal(gathered, full))
         torch.cuda.synchronize()
-        results.put((rank, ok_rows, ok_gf, ok_gd, ok_batch))
+        results.put((rank, ok_rows and ok_p2p, ok_gf, ok_gd, ok_batch))
     finally:
         dist.destroy_process_group()
 
