@@ -475,6 +475,16 @@ def main():
                 }
                 with torch.no_grad():
                     for name, fn in variants.items():
+                        # an extra must not cost the run its headline line: a failure is recorded, on all ranks alike
+                        try:
+                            fn()
+                            failed = 0
+                        except Exception as exc:  # noqa: BLE001
+                            failed, extra[name + "_error"] = 1, str(exc)[:200]
+                        tf = torch.tensor([failed], dtype=torch.int32, device=device)
+                        dist.all_reduce(tf, op=dist.ReduceOp.MAX)
+                        if int(tf[0]):
+                            continue
                         ms_v, _ = timed(fn, 20, 5)
                         tv = torch.tensor([ms_v], dtype=torch.float64, device=device)
                         dist.all_reduce(tv, op=dist.ReduceOp.MAX)
