@@ -42,6 +42,8 @@ from flashbev_b200 import synth  # noqa: E402
 # dram__bytes_read.sum + dram__bytes_write.sum of one fwd_kernel launch on the default workload, from the ncu
 # capture summarised in profiles/fwd_kernel_cfg2_z8.md (the output stays in L2 until it is evicted later)
 NCU_DRAM_BYTES_PER_LAUNCH = {"cfg2": 1425408}
+# smsp__inst_executed.sum of fwd_kernel from the same ncu capture (profiles/fwd_kernel_cfg2_z8.md)
+NCU_WARP_INSTRUCTIONS_PER_LAUNCH = {"cfg2": 19693446}
 METRIC = "bev_pool_forward_cells_per_s"
 UNIT = "BEV cells/s"
 
@@ -539,6 +541,14 @@ def main():
                             "peak_kind": "L2-resident 16-byte loads of a 32 MiB buffer, measured in this run"},
         "clocks": clk, "gpu_launches": args.steps, "extra": extra,
     }
+    wi = NCU_WARP_INSTRUCTIONS_PER_LAUNCH.get(args.workload) if Bl == 1 and args.mode == "categorical" else None
+    if wi and clk.get("sm_mhz"):
+        # what actually bounds the kernel: one warp instruction per scheduler and cycle, 4 schedulers on each SM
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+        floor_us = wi / (sms * 4) / clk["sm_mhz"]
+        line["roofline_issue"] = {"bound": "instruction issue", "warp_instructions_per_launch": wi,
+                                  "floor_us": floor_us, "achieved_us": ms_fwd * 1e3, "frac": floor_us / (ms_fwd * 1e3),
+                                  "note": "instructions from the ncu capture, SM clock sampled in this run"}
     if not args.no_extras:
         line["e2e"] = {"value": cells_total / (ms_e2e_max * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
                        "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e_max}

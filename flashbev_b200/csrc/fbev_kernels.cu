@@ -239,7 +239,7 @@ __device__ __forceinline__ void list_phase(const Dev& p, const Tile& t, const Bl
       }
     }
     const unsigned vm = __ballot_sync(kFull, ok);
-    // lanes [lo, hi) of this round hold candidates of cell cl
+    // lanes [lo, hi) of this sweep hold candidates of cell cl
     const int lo = min(max(cl * per - base, 0), 31);
     const int hi = min(max((cl + 1) * per - base, 0), 32);
     const unsigned seg = (hi >= 32 ? kFull : ((1u << hi) - 1u)) & ~((1u << lo) - 1u);
@@ -312,7 +312,7 @@ __host__ __device__ inline size_t fwd_warp_bytes(int CPW, int cap) { return 256 
 // Every run then emits at most two records {texel of (row, u0), u1-u0, weight of u0, weight of u1},
 // already multiplied by the depth weight.  The channel phase reads two texels per record instead of
 // four per sample, which is some 2.5 to 5 times fewer gathers for the benchmark shapes.  Runs do not
-// extend across the 32 candidates of one round; that only costs merges, never correctness.
+// extend across the 32 candidates of one sweep; that only costs merges, never correctness.
 // SAMPLES (depth-gradient kernel): every accepted sample is also kept, per cell, as three uint4
 //   [0] bilinear weights w00 w01 w10 w11
 //   [1] element index of depth[(v0,u0)][0], element distance to u1, to v1, depth bin (or -1)
@@ -411,7 +411,7 @@ __device__ __forceinline__ void row_list_phase(const Dev& p, const Tile& t, cons
     const bool emit_a = tail && !given_to_next;
     const bool emit_b = tail && has_b;
     const unsigned m1 = __ballot_sync(kFull, emit_a || emit_b), m2 = __ballot_sync(kFull, emit_a && emit_b);
-    // lanes [lo, hi) of this round hold candidates of cell cl
+    // lanes [lo, hi) of this sweep hold candidates of cell cl
     const int lo = min(max(cl * per - base, 0), 31);
     const int hi = min(max((cl + 1) * per - base, 0), 32);
     const unsigned seg = (hi >= 32 ? kFull : ((1u << hi) - 1u)) & ~((1u << lo) - 1u);
@@ -2189,7 +2189,7 @@ static Plan make_plan(const FbevProblem* p, Dev& d, bool bwd, const void* a, con
   d.GL = pl.GL;
   d.CPW = pl.CPW;
   d.cap = pl.cap;
-  // backward: tile = 16 groups of CPW cells, two rounds for eight warps.  forward: small tiles of about 24
+  // backward: tile = 16 groups of CPW cells, two passes for eight warps.  forward: small tiles of about 24
   // cells for four warps: a single sample has only some 10^4 cells, and the tail of the last tiles is what
   // a launch waits for.
   int tx = 4 * pl.CPW, ty = 4;

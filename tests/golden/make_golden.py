@@ -1,6 +1,6 @@
 """Generates tests/golden/*.npz from the reference's own dense PyTorch path.
 
-Run in a container that has the reference checkout (default /root/reference); the
+Run in a container that has the reference checkout (see --reference); the
 fixtures it writes are committed, this script is how they were made:
 
     python tests/golden/make_golden.py [--reference /path/to/FlashBEV]
