@@ -83,6 +83,15 @@ def test_validation_status_codes():
     assert fwd(p) == 1
     p = _problem()
     assert lib.fbev_forward(ctypes.byref(p), None, None, None) == 1
+    # peer copies of the output: at most seven, none of them NULL, aligned like the output (checked before any launch)
+    one = (ctypes.c_void_p * 1)(512)
+    assert lib.fbev_forward_peers(ctypes.byref(p), 256, None, 1, None, None) == 3
+    assert lib.fbev_forward_peers(ctypes.byref(p), 256, one, 8, None, None) == 3
+    assert lib.fbev_forward_peers(ctypes.byref(p), 256, (ctypes.c_void_p * 1)(None), 1, None, None) == 1
+    assert lib.fbev_forward_peers(ctypes.byref(p), 256, (ctypes.c_void_p * 1)(516), 1, None, None) == 6
+    # the projection builder refuses missing arrays and empty batches
+    assert lib.fbev_projection_matrices(None, 256, 256, 256, 256, 1, None) == 1
+    assert lib.fbev_projection_matrices(256, 256, 256, 256, 256, 0, None) == 3
     assert _lib.strerror(99) == "unknown status"
     for code in range(0, 12):
         assert _lib.strerror(code) != "unknown status"
