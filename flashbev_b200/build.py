@@ -17,7 +17,8 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 INCLUDE = os.path.join(os.path.dirname(PKG_DIR), "include")
 LIB_PATH = os.path.join(PKG_DIR, "libfbev.so")
 SOURCES = ["fbev_kernels.cu"]
-HEADERS = [os.path.join(CSRC, "fbev_device.cuh"), os.path.join(INCLUDE, "fbev.h")]
+HEADERS = [os.path.join(CSRC, h) for h in ("fbev_device.cuh", "fbev_lists.cuh", "fbev_forward.cuh", "fbev_backward.cuh",
+                                            "fbev_sort.cuh", "fbev_misc.cuh")] + [os.path.join(INCLUDE, "fbev.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -19,6 +19,10 @@
 //                registers.  The result leaves with one 16-byte store per chunk.
 //
 // No frustum, voxel or sample tensor is ever written to global memory.
+//
+// Files: fbev_device.cuh (arithmetic of one candidate), fbev_lists.cuh (block state, list phases),
+// fbev_forward.cuh, fbev_backward.cuh, fbev_sort.cuh, fbev_misc.cuh (kernels), this file (plans, launches and
+// the C ABI).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -26,2053 +30,13 @@
 
 #include "fbev.h"
 #include "fbev_device.cuh"
+#include "fbev_lists.cuh"
+#include "fbev_forward.cuh"
+#include "fbev_backward.cuh"
+#include "fbev_sort.cuh"
+#include "fbev_misc.cuh"
 
 namespace fbev {
-
-constexpr int kMaxWarps = 8;
-// narrow channel vectors would put up to 32 cells on a warp; the record lists of that many cells
-// do not fit the shared-memory budget, so the rest of the lanes idle in the channel phase
-constexpr int kMaxCellsPerWarp = 8;
-
-// Shared-memory header of a block: matrices, feature sizes, visible-camera list.
-struct BlockHeader {
-  float* P;    // [N][12]
-  int* fs;     // [N][2]
-  int* vis;    // [N]
-  int* nvis;   // [1]
-  unsigned char* warp_area;
-};
-
-__host__ __device__ inline size_t header_bytes(int N) {
-  size_t words = (size_t)N * 12 + (size_t)N * 2 + (size_t)N + 4;
-  return (words * 4 + 15) & ~(size_t)15;
-}
-
-__device__ __forceinline__ BlockHeader carve(unsigned char* smem, int N) {
-  BlockHeader h;
-  h.P = reinterpret_cast<float*>(smem);
-  h.fs = reinterpret_cast<int*>(h.P + (size_t)N * 12);
-  h.vis = h.fs + (size_t)N * 2;
-  h.nvis = h.vis + N;
-  h.warp_area = smem + header_bytes(N);
-  return h;
-}
-
-// Per-warp shared area: list lengths of this pass, running totals, then the records.
-template <int REC_U4>
-__host__ __device__ inline size_t warp_bytes(int CPW, int cap) {
-  return 256 + (size_t)CPW * cap * REC_U4 * 16;
-}
-
-struct Tile {
-  int b, x0, y0, x1, y1;
-};
-
-__device__ __forceinline__ Tile tile_of(const Dev& p, int tile) {
-  Tile t;
-  const int per = p.tiles_x * p.tiles_y;
-  t.b = tile / per;
-  const int r = tile - t.b * per;
-  const int ty = r / p.tiles_x, tx = r - ty * p.tiles_x;
-  t.x0 = tx * p.TX;
-  t.y0 = p.y0 + ty * p.TY;
-  t.x1 = min(t.x0 + p.TX, p.X);
-  t.y1 = min(t.y0 + p.TY, p.y1);
-  return t;
-}
-
-// Tile scheduling.  With a scheduler word (FbevProblem.workspace) the grid is one resident wave of
-// blocks and every block draws tiles from an atomic counter, fetching the next index while it works
-// on the current one; the last block to leave puts both words back to zero for the next launch.
-// Without it, block i owns tile i.
-struct TileLoop {
-  int it;
-  int ntiles;
-  int* slot;  // shared int[2]
-
-  __device__ __forceinline__ void begin(const Dev& p, int* shared_slot) {
-    it = 0;
-    ntiles = p.tiles_x * p.tiles_y * p.B;
-    slot = shared_slot;
-    if (p.sched != nullptr) {
-      if (threadIdx.x == 0) slot[0] = (int)atomicAdd(p.sched, 1u);
-      __syncthreads();
-    }
-  }
-  // index of the tile of this iteration, or -1 when the block is done
-  __device__ __forceinline__ int current(const Dev& p) {
-    const int cur = p.sched != nullptr ? slot[it & 1] : (it == 0 ? (int)blockIdx.x : ntiles);
-    if (cur >= ntiles) return -1;
-    if (p.sched != nullptr && threadIdx.x == 0) slot[(it + 1) & 1] = (int)atomicAdd(p.sched, 1u);
-    return cur;
-  }
-  __device__ __forceinline__ void advance() {
-    __syncthreads();  // everyone is done with this tile's shared state; also publishes the prefetched index
-    ++it;
-  }
-  __device__ __forceinline__ void end(const Dev& p) {
-    if (p.sched != nullptr && threadIdx.x == 0) {
-      __threadfence();  // this block's draws are performed before it reports itself done
-      const unsigned done = atomicAdd(p.sched + 1, 1u);
-      if (done == gridDim.x - 1) {
-        p.sched[0] = 0u;
-        p.sched[1] = 0u;
-      }
-    }
-  }
-};
-
-// Loads matrices and feature sizes of the tile's sample (when it differs from the one already in
-// shared memory) and builds the list of cameras that may see the tile.  Ends with a block barrier.
-__device__ __forceinline__ void block_prologue(const Dev& p, const Tile& t, const BlockHeader& h, const float vs[3],
-                                               const float vmin[3], int image_h, int image_w, int& loaded_b) {
-  const int tid = threadIdx.x, nt = blockDim.x;
-  if (loaded_b != t.b) {
-    for (int i = tid; i < p.N * 12; i += nt) {
-      const int n = i / 12, k = i - n * 12;
-      h.P[i] = __ldg(p.proj + ((size_t)t.b * p.N + n) * p.pstride + k);
-    }
-    for (int i = tid; i < p.N * 2; i += nt) h.fs[i] = __ldg(p.fsize + (size_t)t.b * p.N * 2 + i);
-    loaded_b = t.b;
-  }
-  __syncthreads();
-  if (tid < 32) {
-    const float bx0 = centre(t.x0, vs[0], vmin[0]), bx1 = centre(t.x1 - 1, vs[0], vmin[0]);
-    const float by0 = centre(t.y0, vs[1], vmin[1]), by1 = centre(t.y1 - 1, vs[1], vmin[1]);
-    const float bz0 = centre(0, vs[2], vmin[2]), bz1 = centre(p.Z - 1, vs[2], vmin[2]);
-    int base = 0;
-    for (int n0 = 0; n0 < p.N; n0 += 32) {
-      const int n = n0 + tid;
-      bool see = false;
-      if (n < p.N) {
-        const int fh = h.fs[n * 2], fw = h.fs[n * 2 + 1];
-        const bool ok = fh > 0 && fw > 0 && (long long)fh * fw <= (long long)p.H * p.W;
-        if (!ok) {
-          if (p.status != nullptr) atomicOr(p.status, (int)FBEV_DEV_BAD_FEATURE_SIZE);
-        } else {
-          see = camera_may_see(p, h.P + n * 12, bx0, bx1, by0, by1, bz0, bz1, image_h, image_w);
-        }
-      }
-      const unsigned m = __ballot_sync(kFull, see);
-      if (see) h.vis[base + __popc(m & ((1u << tid) - 1u))] = n;
-      base += __popc(m);
-    }
-    if (tid == 0) *h.nvis = base;
-  }
-  __syncthreads();
-}
-
-// Forward-kernel prologue for up to 32 cameras.  The matrices are (re)loaded only when the tile
-// belongs to another sample than the one in shared memory (block barriers then); the camera cull is
-// evaluated by every warp for itself and returned as a bit mask, so the steady state has no barrier.
-__device__ __forceinline__ unsigned tile_visibility(const Dev& p, const Tile& t, const BlockHeader& h,
-                                                    const float vs[3], const float vmin[3], int image_h, int image_w,
-                                                    int& loaded_b) {
-  if (loaded_b != t.b) {  // uniform over the block
-    __syncthreads();      // nobody still reads the matrices of the sample before
-    for (int i = threadIdx.x; i < p.N * 12; i += blockDim.x) {
-      const int n = i / 12, k = i - n * 12;
-      h.P[i] = __ldg(p.proj + ((size_t)t.b * p.N + n) * p.pstride + k);
-    }
-    for (int i = threadIdx.x; i < p.N * 2; i += blockDim.x) h.fs[i] = __ldg(p.fsize + (size_t)t.b * p.N * 2 + i);
-    loaded_b = t.b;
-    __syncthreads();
-  }
-  const int lane = threadIdx.x & 31;
-  bool see = false;
-  if (lane < p.N) {
-    const int fh = h.fs[lane * 2], fw = h.fs[lane * 2 + 1];
-    if (fh > 0 && fw > 0 && (long long)fh * fw <= (long long)p.H * p.W) {
-      const float bx0 = centre(t.x0, vs[0], vmin[0]), bx1 = centre(t.x1 - 1, vs[0], vmin[0]);
-      const float by0 = centre(t.y0, vs[1], vmin[1]), by1 = centre(t.y1 - 1, vs[1], vmin[1]);
-      const float bz0 = centre(0, vs[2], vmin[2]), bz1 = centre(p.Z - 1, vs[2], vmin[2]);
-      see = camera_may_see(p, h.P + lane * 12, bx0, bx1, by0, by1, bz0, bz1, image_h, image_w);
-    } else if (p.status != nullptr && threadIdx.x < 32) {
-      atomicOr(p.status, (int)FBEV_DEV_BAD_FEATURE_SIZE);
-    }
-  }
-  return __ballot_sync(kFull, see);
-}
-
-// List phase for one group of cells and one pass over candidates [r0, r1) of
-// every cell (candidate r = visible-camera index * Z + z).
-//   t0      first tile-linear cell of the group; cell = t0 + c, c < CPW
-//   sLen    [CPW] list lengths produced by this pass
-//   recs    [CPW][cap] records of REC_U4 uint4 each:
-//             [0] bilinear weights w00 w01 w10 w11 (forward: already times the depth weight)
-//             [1] texel index of (v0,u0) within the whole feature tensor, u1-u0, (v1-v0)*fw, depth bin
-//             [2] backward only: depth weight, d/dmean, d/dsigma, texel-local depth row (unused)
-template <typename T, bool BWD, bool COUNT_ONLY>
-__device__ __forceinline__ void list_phase(const Dev& p, const Tile& t, const BlockHeader& h, int nvis, int t0,
-                                           int r0, int r1, const float vs[3], const float vmin[3], int image_h,
-                                           int image_w, int* sLen, uint4* recs, int lane) {
-  constexpr int REC_U4 = BWD ? 3 : 2;
-  const int per = r1 - r0;
-  const int total = p.CPW * per;
-  const int tile_cells = p.TX * p.TY;
-  if (lane < p.CPW) sLen[lane] = 0;
-  __syncwarp();
-  for (int base = 0; base < total; base += 32) {
-    const int q = base + lane;
-    bool ok = false;
-    int cl = 0;
-    Sample s;
-    size_t tex00 = 0;
-    int fw = 0;
-    if (q < total) {
-      cl = q / per;
-      const int r = r0 + (q - cl * per);
-      const int ci = r / p.Z, z = r - ci * p.Z;
-      const int tc = t0 + cl;
-      const int ly = tc / p.TX, lx = tc - ly * p.TX;
-      const int x = t.x0 + lx, y = t.y0 + ly;
-      if (tc < tile_cells && x < t.x1 && y < t.y1 && ci < nvis) {
-        const int n = h.vis[ci];
-        const int fh = h.fs[n * 2];
-        fw = h.fs[n * 2 + 1];
-        const float vx = centre(x, vs[0], vmin[0]), vy = centre(y, vs[1], vmin[1]), vz = centre(z, vs[2], vmin[2]);
-        if (geometry(h.P + n * 12, vx, vy, vz, image_h, image_w, fh, fw, p.eps, s)) {
-          const size_t texbase = ((size_t)t.b * p.N + n) * (size_t)fh * fw;
-          ok = depth_weight<T, BWD>(p, reinterpret_cast<const T*>(p.depth) + texbase * p.D, fw, s);
-          tex00 = texbase + (size_t)s.v0 * fw + s.u0;
-        }
-      }
-    }
-    const unsigned vm = __ballot_sync(kFull, ok);
-    // lanes [lo, hi) of this sweep hold candidates of cell cl
-    const int lo = min(max(cl * per - base, 0), 31);
-    const int hi = min(max((cl + 1) * per - base, 0), 32);
-    const unsigned seg = (hi >= 32 ? kFull : ((1u << hi) - 1u)) & ~((1u << lo) - 1u);
-    const int before = sLen[cl];
-    __syncwarp();
-    if (!COUNT_ONLY && ok) {
-      const int pos = before + __popc(vm & seg & ((1u << lane) - 1u));
-      uint4* rec = recs + ((size_t)cl * p.cap + pos) * REC_U4;
-      if (BWD) {
-        rec[0] = make_uint4(__float_as_uint(s.w00), __float_as_uint(s.w01), __float_as_uint(s.w10),
-                            __float_as_uint(s.w11));
-        rec[2] = make_uint4(__float_as_uint(s.wgt), __float_as_uint(s.dmean), __float_as_uint(s.dsigma), 0u);
-      } else {
-        rec[0] = make_uint4(__float_as_uint(s.w00 * s.wgt), __float_as_uint(s.w01 * s.wgt),
-                            __float_as_uint(s.w10 * s.wgt), __float_as_uint(s.w11 * s.wgt));
-      }
-      rec[1] = make_uint4((uint32_t)tex00, (uint32_t)(s.u1 - s.u0), (uint32_t)((s.v1 - s.v0) * fw), (uint32_t)s.k);
-    }
-    if (q < total && lane == lo) sLen[cl] = before + __popc(vm & seg);
-    __syncwarp();
-  }
-}
-
-// One 16-byte chunk of channels of the output (or of the upstream gradient): element type T, or
-// float32 when a 16-bit operator was asked for a float32 output.  `chunk` counts T-sized chunks.
-template <typename T>
-__device__ __forceinline__ void store_chunk(void* base, int as_f32, size_t chunk, const float* v) {
-  constexpr int E = Chunk<T>::E;
-  if (E == 8 && as_f32) {
-    float4* o = reinterpret_cast<float4*>(base) + chunk * 2;
-    o[0] = make_float4(v[0], v[1], v[2], v[3]);
-    o[1] = make_float4(v[4], v[5], v[6], v[7]);
-  } else {
-    reinterpret_cast<uint4*>(base)[chunk] = Chunk<T>::pack(v);
-  }
-}
-template <typename T>
-__device__ __forceinline__ void load_chunk(const void* base, int as_f32, size_t chunk, float* v) {
-  constexpr int E = Chunk<T>::E;
-  if (E == 8 && as_f32) {
-    const float4* g = reinterpret_cast<const float4*>(base) + chunk * 2;
-    const float4 a = __ldg(g), b = __ldg(g + 1);
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-  } else {
-    Chunk<T>::unpack(ldg16(reinterpret_cast<const uint4*>(base) + chunk), v);
-  }
-}
-
-// ---------------------------------------------------------------------------
-// Forward
-// ---------------------------------------------------------------------------
-
-// exact q / d for 0 <= q < 2^21, given inv = 1.0f / d
-__device__ __forceinline__ int fast_div(int q, float inv) { return __float2int_rz((__int2float_rn(q) + 0.5f) * inv); }
-
-// Per-warp shared area of the forward kernel: record-list lengths and sample counts, then per cell
-// a list of row records (one padding slot per cell keeps the cells' lists on different banks).
-__host__ __device__ inline int row_stride(int cap) { return 2 * cap + 1; }
-__host__ __device__ inline size_t fwd_warp_bytes(int CPW, int cap) { return 256 + (size_t)CPW * row_stride(cap) * 16; }
-
-// List phase of the forward kernel.  As list_phase() it evaluates one candidate per lane, but it
-// emits ROW records instead of samples.  A sample touches two feature rows (v0 and v1) at the
-// columns (u0, u1); the z samples of one (cell, camera) are neighbouring lanes and mostly fall on
-// the same or on adjacent rows, so
-//   * neighbouring accepted lanes with the same (cell, camera, texel (v0,u0), u1-u0) form a run whose
-//     weights are summed with a segmented warp scan, and
-//   * the v1 part of a run is merged with the v0 part of the run before it when that one sits
-//     exactly one row further down (the usual order: v decreases as z grows).
-// Every run then emits at most two records {texel of (row, u0), u1-u0, weight of u0, weight of u1},
-// already multiplied by the depth weight.  The channel phase reads two texels per record instead of
-// four per sample, which is some 2.5 to 5 times fewer gathers for the benchmark shapes.  Runs do not
-// extend across the 32 candidates of one sweep; that only costs merges, never correctness.
-// SAMPLES (depth-gradient kernel): every accepted sample is also kept, per cell, as three uint4
-//   [0] bilinear weights w00 w01 w10 w11
-//   [1] element index of depth[(v0,u0)][0], element distance to u1, to v1, depth bin (or -1)
-//   [2] positions of the row records holding its v0 and its v1 texels (low / high 16 bits), depth
-//       weight, d weight / d mean, d weight / d sigma
-// in `samp` ([CPW][cap] records), counted in sSmp.
-template <typename T, bool WRITE = true, bool SAMPLES = false>
-__device__ __forceinline__ void row_list_phase(const Dev& p, const Tile& t, const BlockHeader& h, unsigned vis, unsigned cpt, int t0, int r0,
-                                               int r1, const float vs[3], const float vmin[3], int image_h,
-                                               int image_w, int* sLen, int* sCnt, uint4* recs, int lane,
-                                               uint4* samp = nullptr, int* sSmp = nullptr) {
-  const int per = r1 - r0;
-  const int total = p.CPW * per;
-  const int tile_cells = p.TX * p.TY;
-  const int rstride = row_stride(p.cap);
-  const float inv_per = 1.0f / (float)per, inv_z = 1.0f / (float)p.Z, inv_tx = 1.0f / (float)p.TX;
-  const unsigned lt = (1u << lane) - 1u;
-  // camera of the ci-th set bit of vis, as a byte table in the unused part of sLen (cells use entries 0..7)
-  unsigned char* visl = reinterpret_cast<unsigned char*>(sLen + kMaxCellsPerWarp);
-  if ((vis >> lane) & 1u) visl[__popc(vis & lt)] = (unsigned char)lane;
-  __syncwarp();
-  for (int base = 0; base < total; base += 32) {
-    const int q = base + lane;
-    bool ok = false;
-    int cl = 0;
-    unsigned tex = 0, kk = 0;
-    int fw = 0;
-    float A0 = 0.0f, A1 = 0.0f, B0 = 0.0f, B1 = 0.0f;
-    Sample s;
-    unsigned dep00 = 0;
-    if (q < total) {
-      cl = fast_div(q, inv_per);
-      const int r = r0 + (q - cl * per);
-      const int ci = fast_div(r, inv_z), z = r - ci * p.Z;
-      const int tc = t0 + cl;
-      const int ly = fast_div(tc, inv_tx), lx = tc - ly * p.TX;
-      const int x = t.x0 + lx, y = t.y0 + ly;
-      if (tc < tile_cells && x < t.x1 && y < t.y1) {
-        const int n = visl[ci];  // ci-th visible camera
-        const int fh = h.fs[n * 2];
-        fw = h.fs[n * 2 + 1];
-        const float vx = centre(x, vs[0], vmin[0]), vy = centre(y, vs[1], vmin[1]), vz = centre(z, vs[2], vmin[2]);
-        if (geometry(h.P + n * 12, vx, vy, vz, image_h, image_w, fh, fw, p.eps, s)) {
-          const size_t texbase = ((size_t)t.b * p.N + n) * (size_t)fh * fw;
-          ok = depth_weight<T, SAMPLES>(p, reinterpret_cast<const T*>(p.depth) + texbase * p.D, fw, s);
-          if (ok) {
-            tex = (unsigned)(texbase + (size_t)s.v0 * fw + s.u0);
-            dep00 = tex * (unsigned)p.D;
-            const unsigned du = (unsigned)(s.u1 - s.u0), dvf = (unsigned)(s.v1 - s.v0);
-            kk = (unsigned)cl | ((unsigned)ci << 4) | (du << 28) | (dvf << 29) | (1u << 31);
-            A0 = s.w00 * s.wgt;
-            A1 = s.w10 * s.wgt;
-            B0 = s.w01 * s.wgt;
-            B1 = s.w11 * s.wgt;
-            if (!dvf) {  // last feature row: v1 == v0, both parts land on the same texels
-              A0 += B0;
-              A1 += B1;
-              B0 = B1 = 0.0f;
-            }
-          }
-        }
-      }
-    }
-    const unsigned okm = __ballot_sync(kFull, ok);
-    // same run as the lane before?
-    const unsigned ptex1 = __shfl_up_sync(kFull, tex, 1), pkk1 = __shfl_up_sync(kFull, kk, 1);
-    const bool sap = ok && lane > 0 && pkk1 == kk && ptex1 == tex;
-    const unsigned sapm = __ballot_sync(kFull, sap);
-    const unsigned headm = okm & ~sapm;
-    const int rs = 31 - __clz((int)(headm & (lt | (1u << lane))));  // first lane of my run (ok lanes only)
-    // segmented inclusive sums over the run
-    for (int d = 1; d < 32 && d < p.Z; d <<= 1) {
-      const float a0 = __shfl_up_sync(kFull, A0, d), a1 = __shfl_up_sync(kFull, A1, d);
-      const float b0 = __shfl_up_sync(kFull, B0, d), b1 = __shfl_up_sync(kFull, B1, d);
-      if (ok && lane - d >= rs) {
-        A0 += a0;
-        A1 += a1;
-        B0 += b0;
-        B1 += b1;
-      }
-    }
-    const bool tail = ok && (lane == 31 || !((sapm >> (lane + 1)) & 1u));
-    // the run before mine ends at lane rs - 1; its tail lane holds its totals
-    const int pl = (rs - 1) & 31;
-    const unsigned ptex = __shfl_sync(kFull, tex, pl), pkk = __shfl_sync(kFull, kk, pl);
-    const float pA0 = __shfl_sync(kFull, A0, pl), pA1 = __shfl_sync(kFull, A1, pl);
-    const unsigned ntex = __shfl_down_sync(kFull, tex, 1), nkk = __shfl_down_sync(kFull, kk, 1);
-    const unsigned colmask = 0x1fffffffu;  // cell, camera and u1-u0 must agree; not the v1-v0 bit
-    const bool has_b = (kk >> 29) & 1u;
-    // my v1 part meets the v0 part of the run before me, one row further down
-    const bool absorb_prev = tail && has_b && rs > 0 && ((okm >> pl) & 1u) && ((pkk ^ kk) & colmask) == 0 &&
-                             ptex == tex + (unsigned)fw;
-    // my v0 part is taken by the run after me under the same rule
-    const bool given_to_next = tail && lane < 31 && ((okm >> ((lane + 1) & 31)) & 1u) && ((nkk ^ kk) & colmask) == 0 &&
-                               ((nkk >> 29) & 1u) && tex == ntex + (unsigned)fw;
-    const bool emit_a = tail && !given_to_next;
-    const bool emit_b = tail && has_b;
-    const unsigned m1 = __ballot_sync(kFull, emit_a || emit_b), m2 = __ballot_sync(kFull, emit_a && emit_b);
-    // lanes [lo, hi) of this sweep hold candidates of cell cl
-    const int lo = min(max(cl * per - base, 0), 31);
-    const int hi = min(max((cl + 1) * per - base, 0), 32);
-    const unsigned seg = (hi >= 32 ? kFull : ((1u << hi) - 1u)) & ~((1u << lo) - 1u);
-    const int before = sLen[cl];
-    __syncwarp();
-    const int pos0 = before + __popc(m1 & seg & lt) + __popc(m2 & seg & lt);
-    const int pos_a = emit_a ? pos0 : -1;                    // tail lanes: where the run's records go
-    const int pos_b = emit_b ? pos0 + (emit_a ? 1 : 0) : -1;
-    if (WRITE && tail) {
-      uint4* rec = recs + (size_t)cl * rstride;
-      const unsigned du = (kk >> 28) & 1u;
-      // chunk index of texel (row, u0), chunk distance to (row, u1), weights
-      if (emit_a) rec[pos_a] = make_uint4(tex * cpt, du * cpt, __float_as_uint(A0), __float_as_uint(A1));
-      if (emit_b)
-        rec[pos_b] = make_uint4((tex + (unsigned)fw) * cpt, du * cpt, __float_as_uint(B0 + (absorb_prev ? pA0 : 0.0f)),
-                                __float_as_uint(B1 + (absorb_prev ? pA1 : 0.0f)));
-    }
-    if (SAMPLES) {
-      // every sample learns which records hold its texels: its run's tail lane knows
-      const unsigned tailm = __ballot_sync(kFull, tail);
-      const unsigned ahead = tailm >> lane;                  // bit 0: me
-      const int tl = ahead ? lane + __ffs((int)ahead) - 1 : lane;
-      const int run_a = __shfl_sync(kFull, pos_a, tl), run_b = __shfl_sync(kFull, pos_b, tl);
-      // a run whose v0 part was taken over by the next run finds it in that run's v1 record
-      const unsigned after = tl < 31 ? tailm >> (tl + 1) : 0u;
-      const int ntl = after ? tl + 1 + __ffs((int)after) - 1 : tl;
-      const int next_b = __shfl_sync(kFull, pos_b, ntl);
-      if (ok) {
-        const int my_a = run_a >= 0 ? run_a : next_b;
-        const int my_b = has_b ? run_b : my_a;               // v1 == v0: both parts sit in the v0 record
-        const int spos = sSmp[cl] + __popc(okm & seg & lt);
-        uint4* sr = samp + ((size_t)cl * p.cap + spos) * 3;
-        const unsigned du = (kk >> 28) & 1u;
-        sr[0] = make_uint4(__float_as_uint(s.w00), __float_as_uint(s.w01), __float_as_uint(s.w10), __float_as_uint(s.w11));
-        sr[1] = make_uint4(dep00, du * (unsigned)p.D, has_b ? (unsigned)(fw * p.D) : 0u, (unsigned)s.k);
-        sr[2] = make_uint4((unsigned)my_a | ((unsigned)my_b << 16), __float_as_uint(s.wgt), __float_as_uint(s.dmean),
-                           __float_as_uint(s.dsigma));
-      }
-      __syncwarp();
-      if (q < total && lane == lo) sSmp[cl] += __popc(okm & seg);
-    }
-    if (q < total && lane == lo) {
-      sLen[cl] = before + __popc(m1 & seg) + __popc(m2 & seg);
-      sCnt[cl] += __popc(okm & seg);
-    }
-    __syncwarp();
-  }
-}
-
-template <typename T, int V, int MINB>
-__global__ void __launch_bounds__(kMaxWarps * 32, MINB) fwd_kernel(const __grid_constant__ Dev p) {
-  constexpr int E = Chunk<T>::E;
-  extern __shared__ __align__(16) unsigned char smem[];
-  const BlockHeader h = carve(smem, p.N);
-  __shared__ int s_tile[2];
-  float vs[3], vmin[3];
-  voxel_frame(p, vs, vmin);
-  const int image_h = __ldg(p.isize), image_w = __ldg(p.isize + 1);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  unsigned char* wa = h.warp_area + (size_t)warp * fwd_warp_bytes(p.CPW, p.cap);
-  int* sLen = reinterpret_cast<int*>(wa);  // [32] records in the list of each cell
-  int* sCnt = sLen + 32;                    // [32] accepted samples of each cell
-  uint4* recs = reinterpret_cast<uint4*>(wa + 256);
-  const int rstride = row_stride(p.cap);
-
-  const int g = lane / p.GL, lg = lane - g * p.GL;
-  const bool lane_used = g < p.CPW;
-  const int cpt = p.GL * V;  // 16-byte chunks per texel
-  const int tile_cells = p.TX * p.TY;
-  const int ngroups = (tile_cells + p.CPW - 1) / p.CPW;
-  const uint4* fl = reinterpret_cast<const uint4*>(p.feats) + lg;  // this lane's chunk of texel 0
-  int loaded_b = -1;
-  TileLoop loop;
-  loop.begin(p, s_tile);
-  for (int tile; (tile = loop.current(p)) >= 0; loop.advance()) {
-    const Tile t = tile_of(p, tile);
-    const unsigned vis = tile_visibility(p, t, h, vs, vmin, image_h, image_w, loaded_b);
-    const int nvis = __popc(vis);
-    const int ncand = nvis * p.Z;
-
-    for (int grp = warp; grp < ngroups; grp += nwarps) {
-      const int t0 = grp * p.CPW;
-      const int tc = t0 + g;
-      const int ly = tc / p.TX, lx = tc - ly * p.TX;
-      const int x = t.x0 + lx, y = t.y0 + ly;
-      const bool cell_ok = lane_used && tc < tile_cells && x < t.x1 && y < t.y1;
-
-      // accumulators as pairs: one packed FFMA2 (two independent IEEE fp32 fmas) per pair of channels
-      float2 acc2[V * E / 2];
-#pragma unroll
-      for (int i = 0; i < V * E / 2; ++i) acc2[i] = make_float2(0.0f, 0.0f);
-      if (lane < p.CPW) sCnt[lane] = 0;
-
-      for (int r0 = 0; r0 < ncand; r0 += p.cap) {
-        if (lane < p.CPW) sLen[lane] = 0;
-        __syncwarp();
-        row_list_phase<T>(p, t, h, vis, (unsigned)cpt, t0, r0, min(r0 + p.cap, ncand), vs, vmin, image_h, image_w, sLen, sCnt, recs,
-                          lane);
-        const int n = cell_ok ? sLen[g] : 0;
-        const uint4* rec = recs + (size_t)g * rstride;
-#pragma unroll 2
-        for (int i = 0; i < n; ++i) {
-          const uint4 r = rec[i];
-          const float2 wa0 = make_float2(__uint_as_float(r.z), __uint_as_float(r.z));
-          const float2 wa1 = make_float2(__uint_as_float(r.w), __uint_as_float(r.w));
-#pragma unroll
-          for (int j = 0; j < V; ++j) {
-            const uint4 q0 = ldg16(fl + (r.x + j * p.GL));
-            const uint4 q1 = ldg16(fl + (r.x + r.y + j * p.GL));
-            float f0[E], f1[E];
-            Chunk<T>::unpack(q0, f0);
-            Chunk<T>::unpack(q1, f1);
-#pragma unroll
-            for (int e = 0; e < E / 2; ++e)
-              acc2[j * E / 2 + e] = __ffma2_rn(wa1, make_float2(f1[2 * e], f1[2 * e + 1]),
-                                               __ffma2_rn(wa0, make_float2(f0[2 * e], f0[2 * e + 1]), acc2[j * E / 2 + e]));
-          }
-        }
-        __syncwarp();
-      }
-      __syncwarp();
-
-      float acc[V * E];
-#pragma unroll
-      for (int i = 0; i < V * E / 2; ++i) {
-        acc[2 * i] = acc2[i].x;
-        acc[2 * i + 1] = acc2[i].y;
-      }
-      if (cell_ok) {
-        const int cnt = sCnt[g];
-        if (p.pool == FBEV_POOL_MEAN) {
-          const float c = (float)cnt;
-#pragma unroll
-          for (int i = 0; i < V * E; ++i) acc[i] = cnt > 0 ? __fdiv_rn(acc[i], c) : 0.0f;
-        }
-        const size_t cell = ((size_t)t.b * p.Y + y) * p.X + x;
-#pragma unroll
-        for (int j = 0; j < V; ++j) store_chunk<T>(p.out, p.out_f32, cell * cpt + lg + j * p.GL, acc + j * E);
-        for (int k = 0; k < p.n_peers; ++k) {  // the same rows into the other ranks' buffers (plain peer stores)
-#pragma unroll
-          for (int j = 0; j < V; ++j) store_chunk<T>(p.out_peers[k], p.out_f32, cell * cpt + lg + j * p.GL, acc + j * E);
-        }
-        if (p.count != nullptr && lg == 0) p.count[cell] = cnt;
-      }
-      __syncwarp();
-    }
-  }  // tiles
-  loop.end(p);
-}
-
-// Feature-gradient kernel: the forward kernel run backwards.  It builds the same merged row records
-// (texel pair, summed weights with the depth weight folded in) and, instead of gathering, adds
-//   d_feats[texel, c] += g_c * inv * weight          (flash_bevpool_cuda.cu:665,676-679)
-// with one 16-byte float32 reduction per chunk and texel.  Merging the height bins that share a feature
-// row cuts the number of reductions, which is what bounds this kernel, by the same factor as the
-// forward's gathers; no feature is read at all.  inv = 1/count for mean pooling, 1 for sum.
-
-__device__ __forceinline__ void red_add4(float* addr, float a, float b, float c, float d);
-
-// Adds the contributions of one cell's row records to the float32 feature gradient; go holds this lane's
-// chunks of the cell's upstream gradient, already times 1/count.
-template <typename T, int V>
-__device__ __forceinline__ void add_records_direct(const Dev& p, const uint4* rec, int n, const float* go, float* gl) {
-  constexpr int E = Chunk<T>::E;
-  for (int i = 0; i < n; ++i) {
-    const uint4 r = rec[i];
-    const float w0 = __uint_as_float(r.z), w1 = __uint_as_float(r.w);
-#pragma unroll
-    for (int j = 0; j < V; ++j) {
-      float* d0 = gl + (size_t)(r.x + j * p.GL) * E;
-      float* d1 = gl + (size_t)(r.x + r.y + j * p.GL) * E;
-#pragma unroll
-      for (int e4 = 0; e4 < E; e4 += 4) {
-        const float g0 = go[j * E + e4], g1 = go[j * E + e4 + 1], g2 = go[j * E + e4 + 2], g3 = go[j * E + e4 + 3];
-        red_add4(d0 + e4, g0 * w0, g1 * w0, g2 * w0, g3 * w0);
-        if (r.y != 0u) {
-          red_add4(d1 + e4, g0 * w1, g1 * w1, g2 * w1, g3 * w1);
-        } else {  // u1 == u0 (last column): both weights belong to the same texel
-          red_add4(d0 + e4, g0 * w1, g1 * w1, g2 * w1, g3 * w1);
-        }
-      }
-    }
-  }
-}
-
-// Entry emission of the sorted gradients, for the whole warp: every row record of the warp's cells leaves one
-// entry {texel of (row, u0), cell, weight of u0 * inv, weight of u1 * inv} in p.ent and, in p.ent_pos, the
-// position it drew inside its texel's segment.  Slots come from p.ent_count (one atomic per call), positions
-// from p.tex_count.  rec / n / cell / inv_cell describe this lane's cell (n = 0 for lanes without one), sLen the
-// list lengths of all cells of the warp.  first_slot: record i of the lane's cell owns slot first_slot + i.
-// Returns false, having stored nothing, when the list is full.
-__device__ __forceinline__ bool emit_entries(const Dev& p, const uint4* rec, int n, int g, int lg, int lane, unsigned cell,
-                                             float inv_cell, const int* sLen, unsigned ucpt, unsigned* first_slot = nullptr) {
-  int before = 0, total = 0;  // records of the cells before mine in this warp, and of the whole warp
-  for (int c = 0; c < p.CPW; ++c) {
-    const int lc = sLen[c];
-    before += c < g ? lc : 0;
-    total += lc;
-  }
-  unsigned base = 0;
-  if (lane == 0 && total > 0) base = atomicAdd(p.ent_count, (unsigned)total);
-  base = __shfl_sync(kFull, base, 0);
-  if ((unsigned long long)base + (unsigned)total > (unsigned long long)p.ent_cap) {
-    // the slots drawn stay unused: ent_scatter_kernel skips what lies beyond the capacity, and the part of
-    // this reservation below it is marked void
-    if (lane == 0 && base < p.ent_cap)
-      for (unsigned k = base; k < p.ent_cap; ++k) p.ent[k] = make_uint4(0xffffffffu, 0u, 0u, 0u);
-    return false;
-  }
-  const unsigned slot0 = base + (unsigned)before;
-  if (first_slot != nullptr) *first_slot = slot0;
-  int nmax = n;
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) nmax = max(nmax, __shfl_xor_sync(kFull, nmax, off));
-  const unsigned lt_mask = (1u << lane) - 1u;
-  // lanes with the same group-local index hold the same record of neighbouring cells, which mostly lies on the
-  // same texel: lanes with equal texels draw their positions with one atomic between them
-  for (int i0 = 0; i0 < nmax; i0 += p.GL) {
-    const int i = i0 + lg;
-    const bool valid = i < n;
-    uint4 r = make_uint4(0u, 0u, 0u, 0u);
-    if (valid) r = rec[i];
-    const unsigned tex0 = r.x / ucpt;
-    const unsigned key = valid ? tex0 : 0xffffffffu - (unsigned)lane;
-    const unsigned peers = __match_any_sync(kFull, key);
-    const int lead = __ffs((int)peers) - 1;
-    unsigned old = 0;
-    if (valid && lane == lead) old = atomicAdd(p.tex_count + tex0, (unsigned)__popc(peers));
-    old = __shfl_sync(kFull, old, lead) + (unsigned)__popc(peers & lt_mask);
-    if (valid) {
-      const float w0 = __uint_as_float(r.z) * inv_cell, w1 = __uint_as_float(r.w) * inv_cell;
-      const bool two = r.y != 0u;  // u1 == u0 (last column): both weights belong to u0
-      p.ent[slot0 + i] = make_uint4(tex0, cell, __float_as_uint(two ? w0 : w0 + w1), __float_as_uint(two ? w1 : 0.0f));
-      p.ent_pos[slot0 + i] = old;
-    }
-  }
-  return true;
-}
-
-// EMIT: instead of adding to global memory, every record leaves an entry in p.ent (emit_entries) and is counted
-// per texel in p.tex_count; tex_scan_kernel, ent_scatter_kernel and feats_gather_kernel finish the job.  A warp whose
-// entries do not fit the array any more adds its contributions directly, as without EMIT.
-template <typename T, int V, bool EMIT>
-__global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_feats_kernel(const __grid_constant__ Dev p) {
-  constexpr int E = Chunk<T>::E;
-  extern __shared__ __align__(16) unsigned char smem[];
-  const BlockHeader h = carve(smem, p.N);
-  __shared__ int s_tile[2];
-  float vs[3], vmin[3];
-  voxel_frame(p, vs, vmin);
-  const int image_h = __ldg(p.isize), image_w = __ldg(p.isize + 1);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  unsigned char* wa = h.warp_area + (size_t)warp * fwd_warp_bytes(p.CPW, p.cap);
-  int* sLen = reinterpret_cast<int*>(wa);
-  int* sCnt = sLen + 32;
-  uint4* recs = reinterpret_cast<uint4*>(wa + 256);
-  const int rstride = row_stride(p.cap);
-
-  const int g = lane / p.GL, lg = lane - g * p.GL;
-  const bool lane_used = g < p.CPW;
-  const int cpt = p.GL * V;
-  const int tile_cells = p.TX * p.TY;
-  const int ngroups = (tile_cells + p.CPW - 1) / p.CPW;
-  float* gl = p.gfeat + (size_t)lg * E;  // this lane's chunk of texel 0 in the float32 gradient
-  const bool mean_pool = p.pool == FBEV_POOL_MEAN;
-  int loaded_b = -1;
-  TileLoop loop;
-  loop.begin(p, s_tile);
-  for (int tile; (tile = loop.current(p)) >= 0; loop.advance()) {
-    const Tile t = tile_of(p, tile);
-    const unsigned vis = tile_visibility(p, t, h, vs, vmin, image_h, image_w, loaded_b);
-    const int nvis = __popc(vis);
-    const int ncand = nvis * p.Z;
-    const bool single_pass = ncand <= p.cap;
-
-    for (int grp = warp; grp < ngroups; grp += nwarps) {
-      const int t0 = grp * p.CPW;
-      const int tc = t0 + g;
-      const int ly = tc / p.TX, lx = tc - ly * p.TX;
-      const int x = t.x0 + lx, y = t.y0 + ly;
-      const bool cell_ok = lane_used && tc < tile_cells && x < t.x1 && y < t.y1;
-
-      float go[V * E];
-#pragma unroll
-      for (int i = 0; i < V * E; ++i) go[i] = 0.0f;
-      const size_t cell = ((size_t)t.b * p.Y + y) * p.X + x;
-      if (!EMIT && cell_ok) {
-#pragma unroll
-        for (int j = 0; j < V; ++j) load_chunk<T>(p.gout, p.out_f32, cell * cpt + lg + j * p.GL, go + j * E);
-      }
-      float inv_cell = 1.0f;  // EMIT: 1 / count of this lane's cell (mean pooling)
-      if (lane < p.CPW) sCnt[lane] = 0;
-      __syncwarp();
-      if (mean_pool && !single_pass) {
-        // the count of all passes is needed before the first contribution leaves
-        for (int r0 = 0; r0 < ncand; r0 += p.cap) {
-          if (lane < p.CPW) sLen[lane] = 0;
-          __syncwarp();
-          row_list_phase<T, false>(p, t, h, vis, (unsigned)cpt, t0, r0, min(r0 + p.cap, ncand), vs, vmin, image_h,
-                                   image_w, sLen, sCnt, recs, lane);
-        }
-        const int cnt = lane_used ? sCnt[g] : 0;
-        const float inv = cnt > 0 ? __fdiv_rn(1.0f, (float)cnt) : 0.0f;
-        inv_cell = inv;
-#pragma unroll
-        for (int i = 0; i < V * E; ++i) go[i] *= inv;
-        __syncwarp();
-      }
-
-      for (int r0 = 0; r0 < ncand; r0 += p.cap) {
-        if (lane < p.CPW) sLen[lane] = 0;
-        __syncwarp();
-        row_list_phase<T, true>(p, t, h, vis, (unsigned)cpt, t0, r0, min(r0 + p.cap, ncand), vs, vmin, image_h,
-                                image_w, sLen, sCnt, recs, lane);
-        if (mean_pool && single_pass) {
-          const int cnt = lane_used ? sCnt[g] : 0;
-          const float inv = cnt > 0 ? __fdiv_rn(1.0f, (float)cnt) : 0.0f;
-          inv_cell = inv;
-#pragma unroll
-          for (int i = 0; i < V * E; ++i) go[i] *= inv;
-        }
-        const int n = cell_ok ? sLen[g] : 0;
-        const uint4* rec = recs + (size_t)g * rstride;
-        if (EMIT) {
-          if (emit_entries(p, rec, n, g, lg, lane, (unsigned)cell, inv_cell, sLen, (unsigned)cpt)) {
-            __syncwarp();
-            continue;
-          }
-          if (cell_ok) {  // no room left in the entry list: add directly; the upstream gradient was not needed so far
-#pragma unroll
-            for (int j = 0; j < V; ++j) load_chunk<T>(p.gout, p.out_f32, cell * cpt + lg + j * p.GL, go + j * E);
-#pragma unroll
-            for (int k = 0; k < V * E; ++k) go[k] *= inv_cell;
-          }
-        }
-        add_records_direct<T, V>(p, rec, n, go, gl);
-        __syncwarp();
-      }
-      __syncwarp();
-    }
-  }  // tiles
-  loop.end(p);
-}
-
-// ---------------------------------------------------------------------------
-// Gradients through a global sort by texel
-// ---------------------------------------------------------------------------
-// d_feats = W^T * dO with W the sparse [cells x texels] matrix of record weights.  A list-phase kernel
-// (bwd_feats_kernel<EMIT> or bwd_depth_kernel<EMIT>) writes W as one entry per row record and counts the
-// entries per texel (of u0); the counts become segment starts (inside ent_scatter_kernel for small feature
-// maps, else tex_scan_kernel); ent_scatter_kernel moves every entry to its texel's segment;
-// feats_gather_kernel walks the grouped list, gathers each entry's dO row from L2 once and accumulates it,
-// in float32 registers, for the entry's two neighbouring texels -- one 16-byte reduction per chunk when the
-// texel changes instead of one per record, which is some 20 times fewer reductions than the direct scatter,
-// whose rate at the L2 is what bounds bwd_feats_kernel.  The parametric depth gradient (two floats per
-// texel, hopelessly contended as atomics) travels with the entries and is summed the same way.
-
-// Exclusive prefix sum of count[0, n) in place; count[n] receives the total.  One block.
-__global__ void __launch_bounds__(1024) tex_scan_kernel(unsigned* __restrict__ count, unsigned n) {
-  __shared__ unsigned part[1024];
-  const unsigned tid = threadIdx.x, nt = blockDim.x;
-  const unsigned per = (n + nt - 1) / nt;
-  const unsigned lo = min(tid * per, n), hi = min(lo + per, n);
-  unsigned sum = 0;
-  for (unsigned i = lo; i < hi; ++i) sum += count[i];
-  part[tid] = sum;
-  __syncthreads();
-  for (unsigned d = 1; d < nt; d <<= 1) {
-    const unsigned v = tid >= d ? part[tid - d] : 0u;
-    __syncthreads();
-    part[tid] += v;
-    __syncthreads();
-  }
-  unsigned run = part[tid] - sum;
-  for (unsigned i = lo; i < hi; ++i) {
-    const unsigned c = count[i];
-    count[i] = run;
-    run += c;
-  }
-  if (tid == nt - 1) count[n] = part[tid];
-}
-
-constexpr unsigned kScanInBlock = 8192;  // texels up to which every scatter block scans the counts itself
-
-// Every emitted entry moves to its place: start of its texel's segment + the position it drew there.
-// SCAN: tex_count still holds counts; every block derives the starts in shared memory (dynamic,
-// (texels + 1) * 4 bytes) and the total goes to total_out.  Otherwise tex_count holds the starts already.
-template <bool SCAN>
-__global__ void __launch_bounds__(256) ent_scatter_kernel(const Dev p, unsigned texels, unsigned* __restrict__ total_out) {
-  extern __shared__ unsigned s_start[];
-  const unsigned* start = p.tex_count;
-  if (SCAN) {
-    __shared__ unsigned part[256];
-    const unsigned tid = threadIdx.x;
-    const unsigned per = (texels + 255u) / 256u;
-    const unsigned lo = min(tid * per, texels), hi = min(lo + per, texels);
-    unsigned sum = 0;
-    for (unsigned i = lo; i < hi; ++i) sum += __ldg(p.tex_count + i);
-    part[tid] = sum;
-    __syncthreads();
-    for (unsigned d = 1; d < 256u; d <<= 1) {
-      const unsigned v = tid >= d ? part[tid - d] : 0u;
-      __syncthreads();
-      part[tid] += v;
-      __syncthreads();
-    }
-    unsigned run = part[tid] - sum;
-    for (unsigned i = lo; i < hi; ++i) {
-      s_start[i] = run;
-      run += __ldg(p.tex_count + i);
-    }
-    if (blockIdx.x == 0 && tid == 255u) *total_out = part[255];
-    __syncthreads();
-    start = s_start;
-  }
-  const unsigned n = min(*p.ent_count, p.ent_cap);
-  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
-    const uint4 e = p.ent[i];
-    if (e.x >= texels) continue;  // void slot
-    const unsigned dst = start[e.x] + p.ent_pos[i];
-    p.ent_sorted[dst] = e;
-    if (p.ent_d != nullptr) p.ent_d_sorted[dst] = p.ent_d[i];
-  }
-}
-
-// GF32: the upstream gradient is float32 although the features are 16-bit.
-// PDEPTH: the entries also carry the parametric depth gradient (p.ent_d_sorted).
-// n_entries: device word holding the number of grouped entries.
-template <typename T, int V, bool GF32, bool PDEPTH>
-__global__ void __launch_bounds__(128, (PDEPTH || GF32) ? 3 : 4)
-    feats_gather_kernel(const __grid_constant__ Dev p, const unsigned* __restrict__ n_entries, unsigned run_len) {
-  constexpr int E = Chunk<T>::E;
-  constexpr int R = (GF32 && E == 8) ? 2 : 1;  // 16-byte loads per chunk of E channels
-  constexpr int U = V == 4 ? 2 : 4;            // entries in flight per lane
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  const int g = lane / p.GL, lg = lane - g * p.GL;
-  if (g >= p.CPW) return;
-  const unsigned n = *n_entries;
-  const unsigned cpt = (unsigned)(p.GL * V);
-  const unsigned groups = gridDim.x * nwarps * p.CPW;
-  const uint4* gl = reinterpret_cast<const uint4*>(p.gout) + (size_t)lg * R;
-  const bool feats = (p.flags & FBEV_BWD_FEATS) != 0;
-  for (unsigned run = (blockIdx.x * nwarps + warp) * p.CPW + g; (unsigned long long)run * run_len < n; run += groups) {
-    const unsigned i0 = run * run_len, i1 = min(i0 + run_len, n);
-    // sums for texel `cur` (acc0) and its right neighbour (acc1); when the next texel is that neighbour,
-    // acc1 slides into acc0
-    float2 acc0[V * E / 2], acc1[V * E / 2];
-    float2 d0 = make_float2(0.0f, 0.0f), d1 = make_float2(0.0f, 0.0f);  // parametric depth: d mean, d sigma
-    bool any1 = false;  // acc1 / d1 received something (a texel without right neighbour never does)
-#pragma unroll
-    for (int k = 0; k < V * E / 2; ++k) acc0[k] = acc1[k] = make_float2(0.0f, 0.0f);
-    auto flush = [&](unsigned tex, const float2* acc, float2 dd) {
-      if (PDEPTH && lg == 0) {
-        atomicAdd(p.gdepth + (size_t)tex * 2, dd.x);
-        atomicAdd(p.gdepth + (size_t)tex * 2 + 1, dd.y);
-      }
-      if (!feats) return;
-#pragma unroll
-      for (int j = 0; j < V; ++j) {
-        float* d = p.gfeat + ((size_t)tex * cpt + lg + j * p.GL) * E;
-#pragma unroll
-        for (int e4 = 0; e4 < E; e4 += 4)
-          red_add4(d + e4, acc[(j * E + e4) / 2].x, acc[(j * E + e4) / 2].y, acc[(j * E + e4) / 2 + 1].x,
-                   acc[(j * E + e4) / 2 + 1].y);
-      }
-    };
-    // entries one step ahead, so that their latency overlaps the gathers of this step
-    uint4 nx[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) nx[u] = __ldg(p.ent_sorted + min(i0 + u, i1 - 1));
-    unsigned cur = nx[0].x;
-    for (unsigned i = i0; i < i1; i += U) {
-      uint4 e[U];
-      uint4 q[U][V][R];
-      float4 dv[U];
-#pragma unroll
-      for (int u = 0; u < U; ++u) e[u] = nx[u];
-      if (feats) {
-#pragma unroll
-        for (int u = 0; u < U; ++u)
-#pragma unroll
-          for (int j = 0; j < V; ++j)
-#pragma unroll
-            for (int r = 0; r < R; ++r) q[u][j][r] = ldg16(gl + ((size_t)e[u].y * cpt + j * p.GL) * R + r);
-      }
-      if (PDEPTH) {
-#pragma unroll
-        for (int u = 0; u < U; ++u) dv[u] = __ldg(p.ent_d_sorted + min(i + u, i1 - 1));
-      }
-      if (i + U < i1) {
-#pragma unroll
-        for (int u = 0; u < U; ++u) nx[u] = __ldg(p.ent_sorted + min(i + U + u, i1 - 1));
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (i + u >= i1) break;
-        const unsigned t = e[u].x;
-        if (t != cur) {
-          flush(cur, acc0, d0);
-          if (t == cur + 1u) {
-#pragma unroll
-            for (int k = 0; k < V * E / 2; ++k) acc0[k] = acc1[k];
-            d0 = d1;
-          } else {
-            if (any1) flush(cur + 1u, acc1, d1);
-#pragma unroll
-            for (int k = 0; k < V * E / 2; ++k) acc0[k] = make_float2(0.0f, 0.0f);
-            d0 = make_float2(0.0f, 0.0f);
-          }
-#pragma unroll
-          for (int k = 0; k < V * E / 2; ++k) acc1[k] = make_float2(0.0f, 0.0f);
-          d1 = make_float2(0.0f, 0.0f);
-          any1 = false;
-          cur = t;
-        }
-        const float w0 = __uint_as_float(e[u].z), w1 = __uint_as_float(e[u].w);
-        any1 = any1 || w1 != 0.0f;
-        if (PDEPTH) {
-          d0.x += dv[u].x;
-          d0.y += dv[u].y;
-          d1.x += dv[u].z;
-          d1.y += dv[u].w;
-          any1 = any1 || dv[u].z != 0.0f || dv[u].w != 0.0f;
-        }
-        if (!feats) continue;
-        const float2 w0v = make_float2(w0, w0), w1v = make_float2(w1, w1);
-#pragma unroll
-        for (int j = 0; j < V; ++j) {
-          float f[E];
-          if (R == 2) {
-            Chunk<float>::unpack(q[u][j][0], f);
-            Chunk<float>::unpack(q[u][j][R - 1], f + 4);
-          } else {
-            Chunk<T>::unpack(q[u][j][0], f);
-          }
-#pragma unroll
-          for (int k = 0; k < E / 2; ++k) {
-            const float2 fv = make_float2(f[2 * k], f[2 * k + 1]);
-            acc0[j * E / 2 + k] = __ffma2_rn(w0v, fv, acc0[j * E / 2 + k]);
-            acc1[j * E / 2 + k] = __ffma2_rn(w1v, fv, acc1[j * E / 2 + k]);
-          }
-        }
-      }
-    }
-    flush(cur, acc0, d0);
-    if (any1) flush(cur + 1u, acc1, d1);
-  }
-}
-
-// ---------------------------------------------------------------------------
-// Feature gradient, texel-stationary
-// ---------------------------------------------------------------------------
-// d_feats[texel, c] = sum over the cells that sampled the texel of  g_cell[c] * inv_cell * weight.
-// A scatter with float atomics is bound by the atomic rate of the L2: neighbouring cells hit the same
-// few texels (a 12 x 8 tile of cfg2 makes some 2000 texel updates on fewer than 100 distinct texels
-// per camera).  This kernel therefore turns the scatter of a tile into a gather:
-//   1. list phase as in the forward (merged row records), every record becomes two entries
-//      {texel key, cell of the tile, weight} in a block-wide array;
-//   2. the entries are counting-sorted by texel key (shared-memory integer atomics);
-//   3. one lane group per texel walks that texel's entries, gathers the cells' upstream gradient
-//      chunks (L1-resident: the tile's rows of dO) into float32 registers, and issues ONE 16-byte
-//      reduction per chunk for the whole tile.
-// Keys index the rectangles camera_rect() predicts per visible camera.  An entry outside its
-// rectangle, a camera whose rectangle does not fit the key space, or an entry beyond the array's
-// capacity is added to global memory directly by the lane that found it (slow, rare: only tiles right
-// next to the rig have footprints that large).
-constexpr int kFeatKeys = 3072;     // texel keys per tile (all visible cameras together)
-constexpr int kFeatEntries = 4096;  // entries per tile
-
-__host__ __device__ inline size_t feats_block_bytes() {
-  return (size_t)kFeatEntries * 8 + (size_t)kFeatEntries * 2 + (size_t)(kFeatKeys + 1) * 4 + 64;
-}
-
-// Rectangle of feature texels the cells of a tile can touch in one camera, from the tile's eight box
-// corners: u and v are ratios of affine functions of the voxel centre, so over a box on which the
-// depth stays positive their extremes sit at the corners.  A hint only: every entry is checked.
-__device__ __forceinline__ bool camera_rect(const float* P, int fh, int fw, float bx0, float bx1, float by0, float by1,
-                                            float bz0, float bz1, int image_h, int image_w, int& r0, int& r1,
-                                            int& c0, int& c1) {
-  const float inf = __int_as_float(0x7f800000);
-  float umin = inf, umax = -inf, vmin = inf, vmax = -inf;
-#pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    const float x = (c & 1) ? bx1 : bx0, y = (c & 2) ? by1 : by0, z = (c & 4) ? bz1 : bz0;
-    const float ld = fmaf(P[10], z, fmaf(P[9], y, P[8] * x)) + P[11];
-    if (!(ld > 1e-2f)) return false;
-    const float u = (fmaf(P[2], z, fmaf(P[1], y, P[0] * x)) + P[3]) / ld / (float)image_w * (float)fw;
-    const float v = (fmaf(P[6], z, fmaf(P[5], y, P[4] * x)) + P[7]) / ld / (float)image_h * (float)fh;
-    umin = fminf(umin, u);
-    umax = fmaxf(umax, u);
-    vmin = fminf(vmin, v);
-    vmax = fmaxf(vmax, v);
-  }
-  if (!(umax >= -2.0f && umin <= (float)fw + 2.0f && vmax >= -2.0f && vmin <= (float)fh + 2.0f)) return false;
-  c0 = max(0, (int)floorf(fmaxf(umin, 0.0f)) - 1);
-  c1 = min(fw - 1, (int)floorf(fminf(umax, (float)fw)) + 2);
-  r0 = max(0, (int)floorf(fmaxf(vmin, 0.0f)) - 1);
-  r1 = min(fh - 1, (int)floorf(fminf(vmax, (float)fh)) + 2);
-  return c0 <= c1 && r0 <= r1;
-}
-
-template <typename T, int V>
-__global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_feats_sorted_kernel(const __grid_constant__ Dev p) {
-  constexpr int E = Chunk<T>::E;
-  extern __shared__ __align__(16) unsigned char smem[];
-  const BlockHeader h = carve(smem, p.N);
-  __shared__ int s_tile[2];
-  __shared__ int4 s_rect[32];        // per camera: first row, first column, columns, first key (-1: no keys)
-  __shared__ int s_rows[32];         // per camera: rows of the rectangle
-  __shared__ unsigned s_texbase[32]; // per camera: texel index of (0, 0)
-  __shared__ int s_nent, s_nkeys;
-  __shared__ int s_wsum[kMaxWarps];
-  float vs[3], vmin[3];
-  voxel_frame(p, vs, vmin);
-  const int image_h = __ldg(p.isize), image_w = __ldg(p.isize + 1);
-
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
-  unsigned char* wa = h.warp_area + (size_t)warp * fwd_warp_bytes(p.CPW, p.cap);
-  int* sLen = reinterpret_cast<int*>(wa);
-  int* sCnt = sLen + 32;
-  uint4* recs = reinterpret_cast<uint4*>(wa + 256);
-  const int rstride = row_stride(p.cap);
-  unsigned char* blk = h.warp_area + (size_t)nwarps * fwd_warp_bytes(p.CPW, p.cap);
-  uint2* ent = reinterpret_cast<uint2*>(blk);                                     // {key | cell << 16, weight}
-  unsigned short* order = reinterpret_cast<unsigned short*>(ent + kFeatEntries);  // entries sorted by key
-  int* hist = reinterpret_cast<int*>(order + kFeatEntries);                       // counts, then offsets / ends
-
-  const int g = lane / p.GL, lg = lane - g * p.GL;
-  const bool lane_used = g < p.CPW;
-  const int cpt = p.GL * V;  // 16-byte chunks per texel
-  const int tile_cells = p.TX * p.TY;
-  const int ngroups = (tile_cells + p.CPW - 1) / p.CPW;
-  const float inv_tx = 1.0f / (float)p.TX;
-  const bool mean_pool = p.pool == FBEV_POOL_MEAN;
-  int loaded_b = -1;
-  TileLoop loop;
-  loop.begin(p, s_tile);
-  for (int tile; (tile = loop.current(p)) >= 0; loop.advance()) {
-    const Tile t = tile_of(p, tile);
-    const unsigned vis = tile_visibility(p, t, h, vs, vmin, image_h, image_w, loaded_b);
-    const int ncand = __popc(vis) * p.Z;
-    const bool single_pass = ncand <= p.cap;
-
-    // ---- key space: one rectangle per visible camera (warp 0); clear the counts ----
-    if (warp == 0) {
-      int r0 = 0, r1 = -1, c0 = 0, c1 = -1;
-      bool have = false;
-      if (lane < p.N && ((vis >> lane) & 1u)) {
-        const float bx0 = centre(t.x0, vs[0], vmin[0]), bx1 = centre(t.x1 - 1, vs[0], vmin[0]);
-        const float by0 = centre(t.y0, vs[1], vmin[1]), by1 = centre(t.y1 - 1, vs[1], vmin[1]);
-        const float bz0 = centre(0, vs[2], vmin[2]), bz1 = centre(p.Z - 1, vs[2], vmin[2]);
-        have = camera_rect(h.P + lane * 12, h.fs[lane * 2], h.fs[lane * 2 + 1], bx0, bx1, by0, by1, bz0, bz1, image_h,
-                           image_w, r0, r1, c0, c1);
-      }
-      const int need = have ? (r1 - r0 + 1) * (c1 - c0 + 1) : 0;
-      int base = 0, mine = -1;
-      for (int n = 0; n < p.N; ++n) {  // cameras take their keys in index order; one that does not fit gets none
-        const int sz = __shfl_sync(kFull, need, n);
-        const bool fits = sz > 0 && base + sz <= kFeatKeys;
-        if (n == lane && fits) mine = base;
-        if (fits) base += sz;
-      }
-      if (lane < p.N) {
-        s_rect[lane] = make_int4(r0, c0, c1 - c0 + 1, mine);
-        s_rows[lane] = r1 - r0 + 1;
-        s_texbase[lane] = (unsigned)(((size_t)t.b * p.N + lane) * (size_t)h.fs[lane * 2] * h.fs[lane * 2 + 1]);
-      }
-      if (lane == 0) {
-        s_nkeys = base;
-        s_nent = 0;
-      }
-    }
-    for (int i = tid; i <= kFeatKeys; i += blockDim.x) hist[i] = 0;
-    __syncthreads();
-
-    // ---- list phase per group, records -> entries ----
-    for (int grp = warp; grp < ngroups; grp += nwarps) {
-      const int t0 = grp * p.CPW;
-      if (lane < p.CPW) sCnt[lane] = 0;
-      __syncwarp();
-      float inv_of_lane = 1.0f;  // lane c keeps 1 / count of cell c of the group (mean pooling)
-      if (mean_pool && !single_pass) {
-        for (int r0 = 0; r0 < ncand; r0 += p.cap) {
-          if (lane < p.CPW) sLen[lane] = 0;
-          __syncwarp();
-          row_list_phase<T, false>(p, t, h, vis, 1u, t0, r0, min(r0 + p.cap, ncand), vs, vmin, image_h, image_w, sLen,
-                                   sCnt, recs, lane);
-        }
-        if (lane < p.CPW) inv_of_lane = sCnt[lane] > 0 ? __fdiv_rn(1.0f, (float)sCnt[lane]) : 0.0f;
-      }
-      for (int r0 = 0; r0 < ncand; r0 += p.cap) {
-        if (lane < p.CPW) {
-          sLen[lane] = 0;
-          if (single_pass) sCnt[lane] = 0;
-        }
-        __syncwarp();
-        // cpt = 1: the records hold the texel index and u1 - u0 themselves
-        row_list_phase<T, true>(p, t, h, vis, 1u, t0, r0, min(r0 + p.cap, ncand), vs, vmin, image_h, image_w, sLen,
-                                sCnt, recs, lane);
-        if (mean_pool && single_pass && lane < p.CPW)
-          inv_of_lane = sCnt[lane] > 0 ? __fdiv_rn(1.0f, (float)sCnt[lane]) : 0.0f;
-        for (int c = 0; c < p.CPW; ++c) {
-          const int n = sLen[c];
-          const float inv = mean_pool ? __shfl_sync(kFull, inv_of_lane, c) : 1.0f;
-          const int tc = t0 + c;  // cell of the tile
-          for (int i = lane; i < n; i += 32) {
-            const uint4 r = recs[(size_t)c * rstride + i];
-            const unsigned tex = r.x, du = r.y;
-            float w0 = __uint_as_float(r.z) * inv, w1 = __uint_as_float(r.w) * inv;
-            if (du == 0u) {  // u1 == u0: one texel takes both weights
-              w0 += w1;
-              w1 = 0.0f;
-            }
-            // camera of the texel, its row and column
-            int cam = -1;
-            for (unsigned m = vis; m; m &= m - 1u) {
-              const int n2 = __ffs((int)m) - 1;
-              const unsigned tb = s_texbase[n2];
-              if (tex >= tb && tex - tb < (unsigned)(h.fs[n2 * 2] * h.fs[n2 * 2 + 1])) cam = n2;
-            }
-            int key = -1;
-            if (cam >= 0) {
-              const int fw = h.fs[cam * 2 + 1];
-              const int rel = (int)(tex - s_texbase[cam]);
-              const int row = fast_div(rel, 1.0f / (float)fw), col = rel - row * fw;
-              const int4 rc = s_rect[cam];
-              const int lr = row - rc.x, lc = col - rc.y;
-              if (rc.w >= 0 && lr >= 0 && lr < s_rows[cam] && lc >= 0 && lc + (int)du < rc.z) key = rc.w + lr * rc.z + lc;
-            }
-            const int want = 1 + (int)du;
-            int slot = -1;
-            if (key >= 0) {
-              slot = atomicAdd(&s_nent, want);
-              if (slot + want > kFeatEntries) {
-                // array full: this record goes the direct way; a slot it reserved below the capacity is
-                // marked void so that the sort never reads an unwritten entry
-                if (slot < kFeatEntries) ent[slot] = make_uint2(0xffffu, 0u);
-                slot = -1;
-              }
-            }
-            if (slot >= 0) {
-              ent[slot] = make_uint2((unsigned)key | ((unsigned)tc << 16), __float_as_uint(w0));
-              atomicAdd(&hist[key], 1);
-              if (du) {
-                ent[slot + 1] = make_uint2((unsigned)(key + 1) | ((unsigned)tc << 16), __float_as_uint(w1));
-                atomicAdd(&hist[key + 1], 1);
-              }
-            } else {
-              // direct: this lane alone adds g * w to the record's texel(s), chunk by chunk
-              const int ly = fast_div(tc, inv_tx), lx = tc - ly * p.TX;
-              const size_t cell = ((size_t)t.b * p.Y + t.y0 + ly) * p.X + t.x0 + lx;
-              for (int ch = 0; ch < cpt; ++ch) {
-                float gv[E];
-                load_chunk<T>(p.gout, p.out_f32, cell * cpt + ch, gv);
-                float* d0 = p.gfeat + ((size_t)tex * cpt + ch) * E;
-#pragma unroll
-                for (int e4 = 0; e4 < E; e4 += 4) {
-                  red_add4(d0 + e4, gv[e4] * w0, gv[e4 + 1] * w0, gv[e4 + 2] * w0, gv[e4 + 3] * w0);
-                  if (du)
-                    red_add4(d0 + (size_t)cpt * E + e4, gv[e4] * w1, gv[e4 + 1] * w1, gv[e4 + 2] * w1, gv[e4 + 3] * w1);
-                }
-              }
-            }
-          }
-        }
-        __syncwarp();
-      }
-    }
-    __syncthreads();
-
-    // ---- counting sort of the entries by key ----
-    const int nkeys = s_nkeys;
-    const int nent = min(s_nent, kFeatEntries);
-    {
-      const int chunk = (nkeys + (int)blockDim.x - 1) / (int)blockDim.x;
-      const int k0 = min(tid * chunk, nkeys), k1 = min(k0 + chunk, nkeys);
-      int local = 0;
-      for (int k = k0; k < k1; ++k) local += hist[k];
-      int incl = local;
-#pragma unroll
-      for (int off = 1; off < 32; off <<= 1) {
-        const int o = __shfl_up_sync(kFull, incl, off);
-        if (lane >= off) incl += o;
-      }
-      if (lane == 31) s_wsum[warp] = incl;
-      __syncthreads();
-      int run = incl - local;
-      for (int w2 = 0; w2 < warp; ++w2) run += s_wsum[w2];
-      for (int k = k0; k < k1; ++k) {  // counts -> first position of each key
-        const int c = hist[k];
-        hist[k] = run;
-        run += c;
-      }
-    }
-    __syncthreads();
-    for (int e = tid; e < nent; e += blockDim.x) {
-      const int key = (int)(ent[e].x & 0xffffu);
-      if (key < nkeys) order[atomicAdd(&hist[key], 1)] = (unsigned short)e;  // afterwards hist[key] = end of the key's entries
-    }
-    __syncthreads();
-
-    // ---- one lane group per texel: gather the cells' gradients, one reduction per chunk ----
-    const int G = nwarps * p.CPW;
-    for (int k = warp * p.CPW + g; k < nkeys + G; k += G) {  // same trip count for every lane of a warp
-      if (!(lane_used && k < nkeys)) continue;
-      const int start = k > 0 ? hist[k - 1] : 0, end = hist[k];
-      if (end <= start) continue;
-      float acc[V * E];
-#pragma unroll
-      for (int i = 0; i < V * E; ++i) acc[i] = 0.0f;
-      for (int e = start; e < end; ++e) {
-        const uint2 en = ent[order[e]];
-        const int tc = (int)(en.x >> 16);
-        const float w = __uint_as_float(en.y);
-        const int ly = fast_div(tc, inv_tx), lx = tc - ly * p.TX;
-        const size_t cell = ((size_t)t.b * p.Y + t.y0 + ly) * p.X + t.x0 + lx;
-#pragma unroll
-        for (int j = 0; j < V; ++j) {
-          float gv[E];
-          load_chunk<T>(p.gout, p.out_f32, cell * cpt + lg + j * p.GL, gv);
-#pragma unroll
-          for (int e2 = 0; e2 < E; ++e2) acc[j * E + e2] = fmaf(w, gv[e2], acc[j * E + e2]);
-        }
-      }
-      // texel of the key
-      unsigned tex = 0;
-      for (unsigned m = vis; m; m &= m - 1u) {
-        const int n2 = __ffs((int)m) - 1;
-        const int4 rc = s_rect[n2];
-        if (rc.w >= 0 && k >= rc.w && k < rc.w + s_rows[n2] * rc.z) {
-          const int rel = k - rc.w;
-          const int lr = fast_div(rel, 1.0f / (float)rc.z), lc = rel - lr * rc.z;
-          tex = s_texbase[n2] + (unsigned)((rc.x + lr) * h.fs[n2 * 2 + 1] + rc.y + lc);
-        }
-      }
-#pragma unroll
-      for (int j = 0; j < V; ++j) {
-        float* d0 = p.gfeat + ((size_t)tex * cpt + lg + j * p.GL) * E;
-#pragma unroll
-        for (int e4 = 0; e4 < E; e4 += 4)
-          red_add4(d0 + e4, acc[j * E + e4], acc[j * E + e4 + 1], acc[j * E + e4 + 2], acc[j * E + e4 + 3]);
-      }
-    }
-  }  // tiles
-  loop.end(p);
-}
-
-// Any channel count and alignment: one cell per warp, lanes stride over channels
-// with scalar loads.  Slow path for shapes the chunked kernel cannot take.
-template <typename T>
-__global__ void __launch_bounds__(kMaxWarps * 32) fwd_generic_kernel(const __grid_constant__ Dev p) {
-  extern __shared__ __align__(16) unsigned char smem[];
-  const BlockHeader h = carve(smem, p.N);
-  __shared__ int s_tile[2];
-  float vs[3], vmin[3];
-  voxel_frame(p, vs, vmin);
-  const int image_h = __ldg(p.isize), image_w = __ldg(p.isize + 1);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  unsigned char* wa = h.warp_area + (size_t)warp * warp_bytes<2>(1, p.cap);
-  int* sLen = reinterpret_cast<int*>(wa);
-  uint4* recs = reinterpret_cast<uint4*>(wa + 256);
-  const int tile_cells = p.TX * p.TY;
-  const T* fbase = reinterpret_cast<const T*>(p.feats);
-  T* obase = reinterpret_cast<T*>(p.out);
-  float* obase32 = reinterpret_cast<float*>(p.out);
-  constexpr int KC = 4;  // channels per lane per block of 128
-  int loaded_b = -1;
-  TileLoop loop;
-  loop.begin(p, s_tile);
-  for (int tile; (tile = loop.current(p)) >= 0; loop.advance()) {
-  const Tile t = tile_of(p, tile);
-  block_prologue(p, t, h, vs, vmin, image_h, image_w, loaded_b);
-  const int nvis = *h.nvis;
-  const int ncand = nvis * p.Z;
-
-  for (int tc = warp; tc < tile_cells; tc += nwarps) {
-    const int ly = tc / p.TX, lx = tc - ly * p.TX;
-    const int x = t.x0 + lx, y = t.y0 + ly;
-    if (!(x < t.x1 && y < t.y1)) continue;  // uniform per warp
-    const size_t cell = ((size_t)t.b * p.Y + y) * p.X + x;
-    int cnt = 0;
-    for (int r0 = 0; r0 < ncand; r0 += p.cap) {  // count first (mean pooling divides every block)
-      list_phase<T, false, true>(p, t, h, nvis, tc, r0, min(r0 + p.cap, ncand), vs, vmin, image_h, image_w, sLen,
-                                 recs, lane);
-      cnt += sLen[0];
-      __syncwarp();
-    }
-    for (int c0 = 0; c0 < p.C; c0 += 32 * KC) {
-      float acc[KC];
-#pragma unroll
-      for (int k = 0; k < KC; ++k) acc[k] = 0.0f;
-      for (int r0 = 0; r0 < ncand; r0 += p.cap) {
-        list_phase<T, false, false>(p, t, h, nvis, tc, r0, min(r0 + p.cap, ncand), vs, vmin, image_h, image_w,
-                                    sLen, recs, lane);
-        const int n = sLen[0];
-        for (int i = 0; i < n; ++i) {
-          const uint4 rw = recs[i * 2], ri = recs[i * 2 + 1];
-          const float w00 = __uint_as_float(rw.x), w01 = __uint_as_float(rw.y), w10 = __uint_as_float(rw.z),
-                      w11 = __uint_as_float(rw.w);
-          const T* c00 = fbase + (size_t)ri.x * p.C;
-          const size_t du = (size_t)ri.y * p.C, dv = (size_t)ri.z * p.C;
-#pragma unroll
-          for (int k = 0; k < KC; ++k) {
-            const int c = c0 + k * 32 + lane;
-            if (c < p.C) {
-              float a = acc[k];
-              a = fmaf(w00, to_float(__ldg(c00 + c)), a);
-              a = fmaf(w01, to_float(__ldg(c00 + dv + c)), a);
-              a = fmaf(w10, to_float(__ldg(c00 + du + c)), a);
-              a = fmaf(w11, to_float(__ldg(c00 + du + dv + c)), a);
-              acc[k] = a;
-            }
-          }
-        }
-        __syncwarp();
-      }
-#pragma unroll
-      for (int k = 0; k < KC; ++k) {
-        const int c = c0 + k * 32 + lane;
-        if (c < p.C) {
-          float v = acc[k];
-          if (p.pool == FBEV_POOL_MEAN) v = cnt > 0 ? __fdiv_rn(v, (float)cnt) : 0.0f;
-          if (p.out_f32) {
-            obase32[cell * p.C + c] = v;
-            for (int q = 0; q < p.n_peers; ++q) reinterpret_cast<float*>(p.out_peers[q])[cell * p.C + c] = v;
-          } else {
-            obase[cell * p.C + c] = from_float<T>(v);
-            for (int q = 0; q < p.n_peers; ++q) reinterpret_cast<T*>(p.out_peers[q])[cell * p.C + c] = from_float<T>(v);
-          }
-        }
-      }
-    }
-    if (p.count != nullptr && lane == 0) p.count[cell] = cnt;
-  }
-  }  // tiles
-  loop.end(p);
-}
-
-// ---------------------------------------------------------------------------
-// Backward
-// ---------------------------------------------------------------------------
-__device__ __forceinline__ void red_add4(float* addr, float a, float b, float c, float d) {
-  // one 16-byte reduction instead of four scalar ones (sm_90+)
-  atomicAdd(reinterpret_cast<float4*>(addr), make_float4(a, b, c, d));
-}
-
-// Sum over the GL lanes of a group; the result is valid in the group's first lane.
-__device__ __forceinline__ float group_sum(float v, int lg, int GL) {
-  // first step: the largest power of two below GL (larger offsets would add nothing)
-  for (int off = GL > 16 ? 16 : GL > 8 ? 8 : GL > 4 ? 4 : GL > 2 ? 2 : 1; off > 0; off >>= 1) {
-    const float o = __shfl_down_sync(kFull, v, off);
-    if (lg + off < GL) v += o;
-  }
-  return v;
-}
-
-// Depth-gradient kernel.  For every accepted sample
-//   parametric, analytic:  d_mean_ij  += inv * S * dwgt/dmean  * w_ij,  d_sigma_ij += inv * S * dwgt/dsigma * w_ij
-//   parametric, legacy:    both slots += inv * S * wgt * w_ij                          (flash_bevpool_cuda.cu:667-674)
-//   categorical:           d_prob[corner_ij, k] += inv * S * w_ij
-// with S = sum_c g_c f_c, f the bilinearly interpolated feature.  S is linear in the four corner
-// texels, S = sum_ij w_ij T_ij with T = <g, feature of the texel>, and the samples of a cell share
-// their texels exactly as in the forward.  So the kernel builds the forward's row records, computes T
-// once per record texel (two gathers, a dot product, a shuffle reduction over the group's lanes) and
-// then lets one lane per SAMPLE combine four T values and issue that sample's atomics.  Compared with
-// evaluating S per sample this reads 2.7 times fewer texels and spreads the atomics over all lanes.
-__host__ __device__ inline size_t depth_warp_bytes(int CPW, int cap) {
-  return 512 + (size_t)CPW * row_stride(cap) * 16 + (size_t)CPW * cap * 48;
-}
-
-// EMIT: the kernel also leaves the entries of the sorted feature gradient (emit_entries) from the same row
-// records, so that one list phase serves both gradients.
-template <typename T, int V, bool EMIT>
-__global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_depth_kernel(const __grid_constant__ Dev p) {
-  constexpr int E = Chunk<T>::E;
-  extern __shared__ __align__(16) unsigned char smem[];
-  const BlockHeader h = carve(smem, p.N);
-  __shared__ int s_tile[2];
-  float vs[3], vmin[3];
-  voxel_frame(p, vs, vmin);
-  const int image_h = __ldg(p.isize), image_w = __ldg(p.isize + 1);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  unsigned char* wa = h.warp_area + (size_t)warp * depth_warp_bytes(p.CPW, p.cap);
-  int* sLen = reinterpret_cast<int*>(wa);  // [32] row records per cell
-  int* sCnt = sLen + 32;                    // [32] accepted samples per cell, all passes
-  int* sSmp = sCnt + 32;                    // [32] sample records per cell, this pass
-  const int rstride = row_stride(p.cap);
-  uint4* recs = reinterpret_cast<uint4*>(wa + 512);
-  uint4* samp = recs + (size_t)p.CPW * rstride;
-
-  const int g = lane / p.GL, lg = lane - g * p.GL;
-  const bool lane_used = g < p.CPW;
-  const int cpt = p.GL * V;
-  const int tile_cells = p.TX * p.TY;
-  const int ngroups = (tile_cells + p.CPW - 1) / p.CPW;
-  const uint4* fl = reinterpret_cast<const uint4*>(p.feats) + lg;
-  const bool legacy = (p.flags & FBEV_BWD_LEGACY_DEPTH) != 0;
-  const bool mean_pool = p.pool == FBEV_POOL_MEAN;
-  const bool by_record = (p.flags & FBEV_BWD_DEPTH) != 0 && (!EMIT || p.ent_d != nullptr);
-  int loaded_b = -1;
-  TileLoop loop;
-  loop.begin(p, s_tile);
-  for (int tile; (tile = loop.current(p)) >= 0; loop.advance()) {
-    const Tile t = tile_of(p, tile);
-    const unsigned vis = tile_visibility(p, t, h, vs, vmin, image_h, image_w, loaded_b);
-    const int ncand = __popc(vis) * p.Z;
-    const bool single_pass = ncand <= p.cap;
-
-    for (int grp = warp; grp < ngroups; grp += nwarps) {
-      const int t0 = grp * p.CPW;
-      const int tc = t0 + g;
-      const int ly = tc / p.TX, lx = tc - ly * p.TX;
-      const int x = t.x0 + lx, y = t.y0 + ly;
-      const bool cell_ok = lane_used && tc < tile_cells && x < t.x1 && y < t.y1;
-
-      float go[V * E];
-#pragma unroll
-      for (int i = 0; i < V * E; ++i) go[i] = 0.0f;
-      if (cell_ok) {
-        const size_t cell = ((size_t)t.b * p.Y + y) * p.X + x;
-#pragma unroll
-        for (int j = 0; j < V; ++j) load_chunk<T>(p.gout, p.out_f32, cell * cpt + lg + j * p.GL, go + j * E);
-      }
-      if (lane < p.CPW) sCnt[lane] = 0;
-      __syncwarp();
-      if (mean_pool && !single_pass) {  // the count of all passes is needed before the first contribution
-        for (int r0 = 0; r0 < ncand; r0 += p.cap) {
-          if (lane < p.CPW) sLen[lane] = 0;
-          __syncwarp();
-          row_list_phase<T, false>(p, t, h, vis, (unsigned)cpt, t0, r0, min(r0 + p.cap, ncand), vs, vmin, image_h,
-                                   image_w, sLen, sCnt, recs, lane);
-        }
-      }
-      // inverse count per cell of the group, kept by lane c for cell c
-      float inv_of_lane = 1.0f;
-      if (mean_pool && !single_pass && lane < p.CPW) {
-        const int cnt = sCnt[lane];
-        inv_of_lane = cnt > 0 ? __fdiv_rn(1.0f, (float)cnt) : 0.0f;
-      }
-
-      for (int r0 = 0; r0 < ncand; r0 += p.cap) {
-        if (lane < p.CPW) {
-          sLen[lane] = 0;
-          sSmp[lane] = 0;
-          if (single_pass) sCnt[lane] = 0;
-        }
-        __syncwarp();
-        row_list_phase<T, true, true>(p, t, h, vis, (unsigned)cpt, t0, r0, min(r0 + p.cap, ncand), vs, vmin, image_h,
-                                      image_w, sLen, sCnt, recs, lane, samp, sSmp);
-        if (mean_pool && single_pass && lane < p.CPW) {
-          const int cnt = sCnt[lane];
-          inv_of_lane = cnt > 0 ? __fdiv_rn(1.0f, (float)cnt) : 0.0f;
-        }
-        const int n = cell_ok ? sLen[g] : 0;
-        bool emitted = false;       // warp-uniform: this pass's records have slots in the entry list
-        unsigned first_slot = 0;    // slots 2i, 2i+1 from here belong to record i of my cell
-        if (EMIT) {
-          const float inv_cell = __shfl_sync(kFull, inv_of_lane, g < p.CPW ? g : 0);
-          const uint4* rec_e = recs + (size_t)g * rstride;
-          const size_t cell = ((size_t)t.b * p.Y + y) * p.X + x;
-          emitted = emit_entries(p, rec_e, n, g, lg, lane, (unsigned)cell, inv_cell, sLen, (unsigned)cpt, &first_slot);
-          if (!emitted && (p.flags & FBEV_BWD_FEATS)) {
-            float gs[V * E];
-#pragma unroll
-            for (int k = 0; k < V * E; ++k) gs[k] = go[k] * inv_cell;
-            add_records_direct<T, V>(p, rec_e, n, gs, p.gfeat + (size_t)lg * E);
-          }
-          __syncwarp();
-        }
-        // ---- T = <g, texel> for the two texels of every row record; stored over the record's weights ----
-        int nmax = n;
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) nmax = max(nmax, __shfl_xor_sync(kFull, nmax, off));
-        uint4* rec = recs + (size_t)g * rstride;
-        for (int i = 0; i < nmax; ++i) {
-          float d0 = 0.0f, d1 = 0.0f;
-          if (i < n) {
-            const uint4 r = rec[i];
-#pragma unroll
-            for (int j = 0; j < V; ++j) {
-              float f0[E], f1[E];
-              Chunk<T>::unpack(ldg16(fl + (r.x + j * p.GL)), f0);
-              Chunk<T>::unpack(ldg16(fl + (r.x + r.y + j * p.GL)), f1);
-#pragma unroll
-              for (int e = 0; e < E; ++e) {
-                d0 = fmaf(go[j * E + e], f0[e], d0);
-                d1 = fmaf(go[j * E + e], f1[e], d1);
-              }
-            }
-          }
-          d0 = group_sum(d0, lg, p.GL);
-          d1 = group_sum(d1, lg, p.GL);
-          if (i < n && lg == 0) {
-            rec[i].z = __float_as_uint(d0);
-            rec[i].w = __float_as_uint(d1);
-          }
-        }
-        __syncwarp();
-        if (p.mode != FBEV_DEPTH_CATEGORICAL && by_record) {
-          // ---- parametric depth, per record: the samples of a run share their texels, so their (d mean,
-          // d sigma) contributions are summed per record texel in shared memory first; the sums leave as the
-          // depth part of the record's entries (summed per texel by feats_gather_kernel) or, without entry
-          // slots, as one atomic per record texel ----
-          for (int c = 0; c < p.CPW; ++c) {  // S * inv of every sample, kept in its record
-            const int ns = sSmp[c];
-            const float inv = mean_pool ? __shfl_sync(kFull, inv_of_lane, c) : 1.0f;
-            const uint4* rc = recs + (size_t)c * rstride;
-            for (int idx = lane; idx < ns; idx += 32) {
-              uint4* sr = samp + ((size_t)c * p.cap + idx) * 3;
-              const uint4 sw = sr[0];
-              const unsigned pos = sr[2].x;
-              const uint4 ra = rc[pos & 0xffffu], rb = rc[pos >> 16];
-              float S = __uint_as_float(sw.x) * __uint_as_float(ra.z);
-              S = fmaf(__uint_as_float(sw.z), __uint_as_float(ra.w), S);
-              S = fmaf(__uint_as_float(sw.y), __uint_as_float(rb.z), S);
-              S = fmaf(__uint_as_float(sw.w), __uint_as_float(rb.w), S);
-              sr[1].x = __float_as_uint(S * inv);
-            }
-          }
-          __syncwarp();
-          for (int which = 0; which < 2; ++which) {  // 0: d mean, 1: d sigma
-            for (int c = 0; c < p.CPW; ++c) {
-              uint4* rc = recs + (size_t)c * rstride;
-              const int nr = sLen[c];
-              for (int i = lane; i < nr; i += 32) rc[i].z = rc[i].w = 0u;
-            }
-            __syncwarp();
-            for (int c = 0; c < p.CPW; ++c) {
-              const int ns = sSmp[c];
-              uint4* rc = recs + (size_t)c * rstride;
-              for (int idx = lane; idx < ns; idx += 32) {
-                const uint4* sr = samp + ((size_t)c * p.cap + idx) * 3;
-                const uint4 sw = sr[0], sp = sr[2];
-                const float sd = __uint_as_float(sr[1].x);
-                const float coef = legacy ? __uint_as_float(sp.y) : __uint_as_float(which == 0 ? sp.z : sp.w);
-                const float v = sd * coef;
-                float* a = reinterpret_cast<float*>(rc + (sp.x & 0xffffu));
-                float* b = reinterpret_cast<float*>(rc + (sp.x >> 16));
-                atomicAdd(a + 2, v * __uint_as_float(sw.x));  // w00 -> (v0, u0)
-                atomicAdd(a + 3, v * __uint_as_float(sw.z));  // w10 -> (v0, u1)
-                atomicAdd(b + 2, v * __uint_as_float(sw.y));  // w01 -> (v1, u0)
-                atomicAdd(b + 3, v * __uint_as_float(sw.w));  // w11 -> (v1, u1)
-              }
-            }
-            __syncwarp();
-            for (int i = lg; i < n; i += p.GL) {
-              const uint4 r = rec[i];
-              const float v0 = __uint_as_float(r.z), v1 = __uint_as_float(r.w);
-              const bool two = r.y != 0u;
-              if (emitted) {
-                float* e = reinterpret_cast<float*>(p.ent_d + first_slot + (unsigned)i);
-                e[which] = two ? v0 : v0 + v1;
-                e[2 + which] = two ? v1 : 0.0f;
-              } else {
-                const unsigned tex = r.x / (unsigned)cpt;
-                atomicAdd(p.gdepth + (size_t)tex * 2 + which, v0);
-                atomicAdd(p.gdepth + (size_t)(tex + (two ? 1u : 0u)) * 2 + which, v1);
-              }
-            }
-            __syncwarp();
-          }
-          continue;
-        }
-        // ---- one lane per sample: S from four T values, then the sample's atomics.  The samples of all cells of
-        // the warp are walked as one list.  Categorical: neighbouring samples are the height bins of one camera
-        // column, which mostly share the texel AND the depth bin (depth barely changes with height), so equal
-        // (texel, bin) neighbours are summed with a segmented scan first and one lane adds for the run ----
-        int ns_total = 0;
-        for (int c = 0; c < p.CPW; ++c) ns_total += sSmp[c];
-        const unsigned lt_mask = (1u << lane) - 1u;
-        for (int base = 0; base < ns_total; base += 32) {
-          int off = base + lane, c = 0;
-          bool active = false;
-          for (int cc = 0; cc < p.CPW; ++cc) {
-            const int nsc = sSmp[cc];
-            if (!active) {
-              if (off < nsc) {
-                c = cc;
-                active = true;
-              } else {
-                off -= nsc;
-              }
-            }
-          }
-          const float inv = mean_pool ? __shfl_sync(kFull, inv_of_lane, c) : 1.0f;
-          float v00 = 0.0f, v01 = 0.0f, v10 = 0.0f, v11 = 0.0f, cm = 0.0f, cs = 0.0f;
-          uint4 sa = make_uint4(0u, 0u, 0u, 0u);
-          if (active) {
-            const uint4* rc = recs + (size_t)c * rstride;
-            const uint4* sr = samp + ((size_t)c * p.cap + off) * 3;
-            const uint4 sw = sr[0], sp = sr[2];
-            sa = sr[1];
-            const float w00 = __uint_as_float(sw.x), w01 = __uint_as_float(sw.y), w10 = __uint_as_float(sw.z),
-                        w11 = __uint_as_float(sw.w);
-            const uint4 ra = rc[sp.x & 0xffffu], rb = rc[sp.x >> 16];
-            float S = w00 * __uint_as_float(ra.z);
-            S = fmaf(w10, __uint_as_float(ra.w), S);
-            S = fmaf(w01, __uint_as_float(rb.z), S);
-            S = fmaf(w11, __uint_as_float(rb.w), S);
-            const float sd = S * inv;
-            v00 = sd * w00; v01 = sd * w01; v10 = sd * w10; v11 = sd * w11;
-            const float wgt = __uint_as_float(sp.y);
-            cm = legacy ? wgt : __uint_as_float(sp.z);
-            cs = legacy ? wgt : __uint_as_float(sp.w);
-          }
-          float* d00 = p.gdepth + sa.x;
-          float* d10 = d00 + sa.y;
-          float* d01 = d00 + sa.z;
-          float* d11 = d01 + sa.y;
-          if (p.mode == FBEV_DEPTH_CATEGORICAL) {
-            const unsigned key = active ? sa.x + sa.w : 0xffffffffu - (unsigned)lane;  // element index of (texel, bin)
-            const unsigned pkey = __shfl_up_sync(kFull, key, 1);
-            const unsigned headm = __ballot_sync(kFull, active && (lane == 0 || pkey != key));
-            const int rs = 31 - __clz((int)(headm & (lt_mask | (1u << lane))));
-            for (int d = 1; d < 32 && d < p.Z; d <<= 1) {
-              const float a = __shfl_up_sync(kFull, v00, d), b = __shfl_up_sync(kFull, v01, d);
-              const float e = __shfl_up_sync(kFull, v10, d), f = __shfl_up_sync(kFull, v11, d);
-              if (active && lane - d >= rs) {
-                v00 += a; v01 += b; v10 += e; v11 += f;
-              }
-            }
-            const unsigned actm = __ballot_sync(kFull, active);
-            const bool tail = active && (lane == 31 || ((headm >> (lane + 1)) & 1u) || !((actm >> (lane + 1)) & 1u));
-            if (tail) {
-              const int k = (int)sa.w;
-              atomicAdd(d00 + k, v00);
-              atomicAdd(d01 + k, v01);
-              atomicAdd(d10 + k, v10);
-              atomicAdd(d11 + k, v11);
-            }
-          } else if (active) {
-            atomicAdd(d00 + 0, cm * v00);
-            atomicAdd(d00 + 1, cs * v00);
-            atomicAdd(d01 + 0, cm * v01);
-            atomicAdd(d01 + 1, cs * v01);
-            atomicAdd(d10 + 0, cm * v10);
-            atomicAdd(d10 + 1, cs * v10);
-            atomicAdd(d11 + 0, cm * v11);
-            atomicAdd(d11 + 1, cs * v11);
-          }
-        }
-        __syncwarp();
-      }
-      __syncwarp();
-    }
-  }  // tiles
-  loop.end(p);
-}
-
-// Gradient kernel.  Same decomposition as the forward.  For every accepted sample
-//   d_feats[corner_ij, c] += g_c * wgt * inv * w_ij          (flash_bevpool_cuda.cu:665,676-679)
-//   parametric, analytic:  d_mean_ij  += inv * (sum_c g_c f_c) * dwgt/dmean  * w_ij
-//                          d_sigma_ij += inv * (sum_c g_c f_c) * dwgt/dsigma * w_ij
-//   parametric, legacy:    both slots += inv * wgt * (sum_c g_c f_c) * w_ij  (:667-674)
-//   categorical:           d_prob[corner_ij, k] += inv * (sum_c g_c f_c) * w_ij
-// with f_c the bilinearly interpolated feature and inv = 1/count (mean) or 1 (sum).
-// Feature gradients leave as 16-byte float32 reductions, depth gradients as scalar
-// atomics from the first lane of each group after a shuffle reduction over channels.
-template <typename T, int V>
-__global__ void __launch_bounds__(kMaxWarps * 32) bwd_kernel(const __grid_constant__ Dev p) {
-  constexpr int E = Chunk<T>::E;
-  extern __shared__ __align__(16) unsigned char smem[];
-  const BlockHeader h = carve(smem, p.N);
-  __shared__ int s_tile[2];
-  float vs[3], vmin[3];
-  voxel_frame(p, vs, vmin);
-  const int image_h = __ldg(p.isize), image_w = __ldg(p.isize + 1);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  unsigned char* wa = h.warp_area + (size_t)warp * warp_bytes<3>(p.CPW, p.cap);
-  int* sLen = reinterpret_cast<int*>(wa);
-  int* sTot = sLen + 32;
-  uint4* recs = reinterpret_cast<uint4*>(wa + 256);
-
-  const int g = lane / p.GL, lg = lane - g * p.GL;
-  const bool lane_used = g < p.CPW;
-  const int cpt = p.GL * V;
-  const int tile_cells = p.TX * p.TY;
-  const int ngroups = (tile_cells + p.CPW - 1) / p.CPW;
-  const uint4* fbase = reinterpret_cast<const uint4*>(p.feats);
-  const bool want_feats = (p.flags & FBEV_BWD_FEATS) != 0;
-  const bool want_depth = (p.flags & FBEV_BWD_DEPTH) != 0;
-  const bool legacy = (p.flags & FBEV_BWD_LEGACY_DEPTH) != 0;
-  const bool mean_pool = p.pool == FBEV_POOL_MEAN;
-  int loaded_b = -1;
-  TileLoop loop;
-  loop.begin(p, s_tile);
-  for (int tile; (tile = loop.current(p)) >= 0; loop.advance()) {
-  const Tile t = tile_of(p, tile);
-  block_prologue(p, t, h, vs, vmin, image_h, image_w, loaded_b);
-  const int nvis = *h.nvis;
-  const int ncand = nvis * p.Z;
-
-  for (int grp = warp; grp < ngroups; grp += nwarps) {
-    const int t0 = grp * p.CPW;
-    const int tc = t0 + g;
-    const int ly = tc / p.TX, lx = tc - ly * p.TX;
-    const int x = t.x0 + lx, y = t.y0 + ly;
-    const bool cell_ok = lane_used && tc < tile_cells && x < t.x1 && y < t.y1;
-
-    // mean pooling needs the cell's total count before the first contribution
-    const bool single_pass = ncand <= p.cap;
-    if (mean_pool && !single_pass) {
-      if (lane < p.CPW) sTot[lane] = 0;
-      for (int r0 = 0; r0 < ncand; r0 += p.cap) {
-        list_phase<T, true, true>(p, t, h, nvis, t0, r0, min(r0 + p.cap, ncand), vs, vmin, image_h, image_w, sLen,
-                                  recs, lane);
-        if (lane < p.CPW) sTot[lane] += sLen[lane];
-        __syncwarp();
-      }
-    }
-
-    float go[V * E];
-#pragma unroll
-    for (int i = 0; i < V * E; ++i) go[i] = 0.0f;
-    if (cell_ok) {
-      const size_t cell = ((size_t)t.b * p.Y + y) * p.X + x;
-#pragma unroll
-      for (int j = 0; j < V; ++j) load_chunk<T>(p.gout, p.out_f32, cell * cpt + lg + j * p.GL, go + j * E);
-    }
-
-    for (int r0 = 0; r0 < ncand; r0 += p.cap) {
-      list_phase<T, true, false>(p, t, h, nvis, t0, r0, min(r0 + p.cap, ncand), vs, vmin, image_h, image_w, sLen,
-                                 recs, lane);
-      const int n = cell_ok ? sLen[g] : 0;
-      float inv = 1.0f;
-      if (mean_pool) {
-        const int cnt = lane_used ? (single_pass ? sLen[g] : sTot[g]) : 0;
-        inv = cnt > 0 ? __fdiv_rn(1.0f, (float)cnt) : 0.0f;
-      }
-      // all lanes of the warp run the same trip count so that the shuffles below are converged
-      int nmax = n;
-#pragma unroll
-      for (int off = 16; off > 0; off >>= 1) nmax = max(nmax, __shfl_xor_sync(kFull, nmax, off));
-      const uint4* rec = recs + (size_t)g * p.cap * 3;
-      for (int i = 0; i < nmax; ++i) {
-        const bool live = i < n;
-        uint4 rw = make_uint4(0, 0, 0, 0), ri = rw, rd = rw;
-        if (live) {
-          rw = rec[i * 3];
-          ri = rec[i * 3 + 1];
-          rd = rec[i * 3 + 2];
-        }
-        const float w00 = __uint_as_float(rw.x), w01 = __uint_as_float(rw.y), w10 = __uint_as_float(rw.z),
-                    w11 = __uint_as_float(rw.w);
-        const float wgt = __uint_as_float(rd.x);
-        const size_t du = (size_t)ri.y * cpt, dv = (size_t)ri.z * cpt;
-        const size_t c00 = (size_t)ri.x * cpt + lg;
-        float dot = 0.0f;
-        if (live) {
-          const float s = wgt * inv;
-          const float a00 = s * w00, a01 = s * w01, a10 = s * w10, a11 = s * w11;
-#pragma unroll
-          for (int j = 0; j < V; ++j) {
-            if (want_depth) {
-              float f00[E], f01[E], f10[E], f11[E];
-              Chunk<T>::unpack(ldg16(fbase + c00 + j * p.GL), f00);
-              Chunk<T>::unpack(ldg16(fbase + c00 + dv + j * p.GL), f01);
-              Chunk<T>::unpack(ldg16(fbase + c00 + du + j * p.GL), f10);
-              Chunk<T>::unpack(ldg16(fbase + c00 + du + dv + j * p.GL), f11);
-#pragma unroll
-              for (int e = 0; e < E; ++e) {
-                float f = w00 * f00[e];
-                f = fmaf(w01, f01[e], f);
-                f = fmaf(w10, f10[e], f);
-                f = fmaf(w11, f11[e], f);
-                dot = fmaf(go[j * E + e], f, dot);
-              }
-            }
-            if (want_feats) {
-              // element offset of this lane's chunk inside the float32 gradient tensor
-              const size_t e00 = ((size_t)ri.x * cpt + lg + (size_t)j * p.GL) * E;
-              const size_t edu = du * E, edv = dv * E;
-#pragma unroll
-              for (int e4 = 0; e4 < E; e4 += 4) {
-                const float g0 = go[j * E + e4], g1 = go[j * E + e4 + 1], g2 = go[j * E + e4 + 2],
-                            g3 = go[j * E + e4 + 3];
-                red_add4(p.gfeat + e00 + e4, g0 * a00, g1 * a00, g2 * a00, g3 * a00);
-                red_add4(p.gfeat + e00 + edv + e4, g0 * a01, g1 * a01, g2 * a01, g3 * a01);
-                red_add4(p.gfeat + e00 + edu + e4, g0 * a10, g1 * a10, g2 * a10, g3 * a10);
-                red_add4(p.gfeat + e00 + edu + edv + e4, g0 * a11, g1 * a11, g2 * a11, g3 * a11);
-              }
-            }
-          }
-        }
-        if (want_depth) {
-          dot = group_sum(dot, lg, p.GL);
-          if (live && lg == 0) {
-            const float sd = dot * inv;
-            const size_t D = (size_t)p.D;
-            float* d00 = p.gdepth + (size_t)ri.x * D;
-            float* d01 = d00 + (size_t)ri.z * D;
-            float* d10 = d00 + (size_t)ri.y * D;
-            float* d11 = d01 + (size_t)ri.y * D;
-            if (p.mode == FBEV_DEPTH_CATEGORICAL) {
-              const int k = (int)ri.w;
-              atomicAdd(d00 + k, sd * w00);
-              atomicAdd(d01 + k, sd * w01);
-              atomicAdd(d10 + k, sd * w10);
-              atomicAdd(d11 + k, sd * w11);
-            } else {
-              const float cm = legacy ? wgt : __uint_as_float(rd.y);
-              const float cs = legacy ? wgt : __uint_as_float(rd.z);
-              atomicAdd(d00 + 0, sd * cm * w00);
-              atomicAdd(d00 + 1, sd * cs * w00);
-              atomicAdd(d01 + 0, sd * cm * w01);
-              atomicAdd(d01 + 1, sd * cs * w01);
-              atomicAdd(d10 + 0, sd * cm * w10);
-              atomicAdd(d10 + 1, sd * cs * w10);
-              atomicAdd(d11 + 0, sd * cm * w11);
-              atomicAdd(d11 + 1, sd * cs * w11);
-            }
-          }
-        }
-      }
-      __syncwarp();
-    }
-  }
-  }  // tiles
-  loop.end(p);
-}
-
-// Gradient kernel for any channel count and alignment: one cell per warp, lanes stride over the
-// channels with scalar loads and scalar float32 atomics.  Slow path, same arithmetic as bwd_kernel.
-template <typename T>
-__global__ void __launch_bounds__(kMaxWarps * 32) bwd_generic_kernel(const __grid_constant__ Dev p) {
-  extern __shared__ __align__(16) unsigned char smem[];
-  const BlockHeader h = carve(smem, p.N);
-  __shared__ int s_tile[2];
-  float vs[3], vmin[3];
-  voxel_frame(p, vs, vmin);
-  const int image_h = __ldg(p.isize), image_w = __ldg(p.isize + 1);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  unsigned char* wa = h.warp_area + (size_t)warp * warp_bytes<3>(1, p.cap);
-  int* sLen = reinterpret_cast<int*>(wa);
-  uint4* recs = reinterpret_cast<uint4*>(wa + 256);
-  const int tile_cells = p.TX * p.TY;
-  const T* fbase = reinterpret_cast<const T*>(p.feats);
-  const bool want_feats = (p.flags & FBEV_BWD_FEATS) != 0;
-  const bool want_depth = (p.flags & FBEV_BWD_DEPTH) != 0;
-  const bool legacy = (p.flags & FBEV_BWD_LEGACY_DEPTH) != 0;
-  int loaded_b = -1;
-  TileLoop loop;
-  loop.begin(p, s_tile);
-  for (int tile; (tile = loop.current(p)) >= 0; loop.advance()) {
-    const Tile t = tile_of(p, tile);
-    block_prologue(p, t, h, vs, vmin, image_h, image_w, loaded_b);
-    const int nvis = *h.nvis;
-    const int ncand = nvis * p.Z;
-    for (int tc = warp; tc < tile_cells; tc += nwarps) {
-      const int ly = tc / p.TX, lx = tc - ly * p.TX;
-      const int x = t.x0 + lx, y = t.y0 + ly;
-      if (!(x < t.x1 && y < t.y1)) continue;  // uniform per warp
-      const size_t cell = ((size_t)t.b * p.Y + y) * p.X + x;
-      float inv = 1.0f;
-      if (p.pool == FBEV_POOL_MEAN) {
-        int cnt = 0;
-        for (int r0 = 0; r0 < ncand; r0 += p.cap) {
-          list_phase<T, true, true>(p, t, h, nvis, tc, r0, min(r0 + p.cap, ncand), vs, vmin, image_h, image_w,
-                                    sLen, recs, lane);
-          cnt += sLen[0];
-          __syncwarp();
-        }
-        inv = cnt > 0 ? __fdiv_rn(1.0f, (float)cnt) : 0.0f;
-      }
-      for (int r0 = 0; r0 < ncand; r0 += p.cap) {
-        list_phase<T, true, false>(p, t, h, nvis, tc, r0, min(r0 + p.cap, ncand), vs, vmin, image_h, image_w,
-                                   sLen, recs, lane);
-        const int n = sLen[0];
-        for (int i = 0; i < n; ++i) {
-          const uint4 rw = recs[i * 3], ri = recs[i * 3 + 1], rd = recs[i * 3 + 2];
-          const float w00 = __uint_as_float(rw.x), w01 = __uint_as_float(rw.y), w10 = __uint_as_float(rw.z),
-                      w11 = __uint_as_float(rw.w);
-          const float wgt = __uint_as_float(rd.x);
-          const float sc = wgt * inv;
-          const size_t t00 = (size_t)ri.x, t01 = t00 + ri.z, t10 = t00 + ri.y, t11 = t01 + ri.y;
-          float dot = 0.0f;
-          for (int c = lane; c < p.C; c += 32) {
-            const float gc = p.out_f32 ? __ldg(reinterpret_cast<const float*>(p.gout) + cell * p.C + c)
-                                       : to_float(__ldg(reinterpret_cast<const T*>(p.gout) + cell * p.C + c));
-            if (want_depth) {
-              float f = w00 * to_float(__ldg(fbase + t00 * p.C + c));
-              f = fmaf(w01, to_float(__ldg(fbase + t01 * p.C + c)), f);
-              f = fmaf(w10, to_float(__ldg(fbase + t10 * p.C + c)), f);
-              f = fmaf(w11, to_float(__ldg(fbase + t11 * p.C + c)), f);
-              dot = fmaf(gc, f, dot);
-            }
-            if (want_feats) {
-              const float a = gc * sc;
-              atomicAdd(p.gfeat + t00 * p.C + c, a * w00);
-              atomicAdd(p.gfeat + t01 * p.C + c, a * w01);
-              atomicAdd(p.gfeat + t10 * p.C + c, a * w10);
-              atomicAdd(p.gfeat + t11 * p.C + c, a * w11);
-            }
-          }
-          if (want_depth) {
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(kFull, dot, off);
-            if (lane == 0) {
-              const float sd = dot * inv;
-              const size_t D = (size_t)p.D;
-              float* d00 = p.gdepth + t00 * D;
-              float* d01 = p.gdepth + t01 * D;
-              float* d10 = p.gdepth + t10 * D;
-              float* d11 = p.gdepth + t11 * D;
-              if (p.mode == FBEV_DEPTH_CATEGORICAL) {
-                const int k = (int)ri.w;
-                atomicAdd(d00 + k, sd * w00);
-                atomicAdd(d01 + k, sd * w01);
-                atomicAdd(d10 + k, sd * w10);
-                atomicAdd(d11 + k, sd * w11);
-              } else {
-                const float cm = legacy ? wgt : __uint_as_float(rd.y);
-                const float cs = legacy ? wgt : __uint_as_float(rd.z);
-                atomicAdd(d00 + 0, sd * cm * w00);
-                atomicAdd(d00 + 1, sd * cs * w00);
-                atomicAdd(d01 + 0, sd * cm * w01);
-                atomicAdd(d01 + 1, sd * cs * w01);
-                atomicAdd(d10 + 0, sd * cm * w10);
-                atomicAdd(d10 + 1, sd * cs * w10);
-                atomicAdd(d11 + 0, sd * cm * w11);
-                atomicAdd(d11 + 1, sd * cs * w11);
-              }
-            }
-          }
-        }
-        __syncwarp();
-      }
-    }
-  }  // tiles
-  loop.end(p);
-}
-
-// float32 accumulation buffers -> gradient tensors of a 16-bit type; two arrays (either may be empty) in one
-// launch, four elements per step
-template <typename T>
-__global__ void convert2_kernel(const float* __restrict__ sa, T* __restrict__ da, size_t na, const float* __restrict__ sb,
-                                T* __restrict__ db, size_t nb) {
-  const size_t ua = (na + 3) / 4, ub = (nb + 3) / 4;
-  const size_t stride = (size_t)gridDim.x * blockDim.x;
-  for (size_t u = (size_t)blockIdx.x * blockDim.x + threadIdx.x; u < ua + ub; u += stride) {
-    const bool first = u < ua;
-    const float* src = first ? sa : sb;
-    T* dst = first ? da : db;
-    const size_t n = first ? na : nb, i = (first ? u : u - ua) * 4;
-    if (i + 4 <= n && ((uintptr_t)(dst + i) % 8) == 0) {
-      const float4 v = *reinterpret_cast<const float4*>(src + i);
-      T o[4] = {from_float<T>(v.x), from_float<T>(v.y), from_float<T>(v.z), from_float<T>(v.w)};
-      *reinterpret_cast<uint2*>(dst + i) = *reinterpret_cast<const uint2*>(o);
-    } else {
-      for (size_t k = i; k < n && k < i + 4; ++k) dst[k] = from_float<T>(src[k]);
-    }
-  }
-}
-
-// ---------------------------------------------------------------------------
-// Integer decisions of every candidate (one thread per BEV cell)
-// ---------------------------------------------------------------------------
-template <typename T>
-__global__ void indices_kernel(const __grid_constant__ Dev p, int* u0, int* v0, int* kbin, unsigned char* valid) {
-  const size_t cells = (size_t)p.B * p.Y * p.X;
-  const size_t cell = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (cell >= cells) return;
-  const int x = (int)(cell % p.X);
-  const int y = (int)((cell / p.X) % p.Y);
-  const int b = (int)(cell / ((size_t)p.X * p.Y));
-  float vs[3], vmin[3];
-  voxel_frame(p, vs, vmin);
-  const int image_h = __ldg(p.isize), image_w = __ldg(p.isize + 1);
-  const float vx = centre(x, vs[0], vmin[0]), vy = centre(y, vs[1], vmin[1]);
-  int cnt = 0;
-  for (int n = 0; n < p.N; ++n) {
-    float P[12];
-    for (int k = 0; k < 12; ++k) P[k] = __ldg(p.proj + ((size_t)b * p.N + n) * p.pstride + k);
-    const int fh = __ldg(p.fsize + ((size_t)b * p.N + n) * 2), fw = __ldg(p.fsize + ((size_t)b * p.N + n) * 2 + 1);
-    const bool fs_ok = fh > 0 && fw > 0 && (long long)fh * fw <= (long long)p.H * p.W;
-    const size_t texbase = ((size_t)b * p.N + n) * (size_t)fh * fw;
-    for (int z = 0; z < p.Z; ++z) {
-      const size_t q = ((((size_t)b * p.N + n) * p.Y + y) * p.X + x) * p.Z + z;
-      int ou = -1, ov = -1, ok = -1;
-      unsigned char oval = 0;
-      Sample s;
-      if (fs_ok && geometry(P, vx, vy, centre(z, vs[2], vmin[2]), image_h, image_w, fh, fw, p.eps, s) &&
-          depth_weight<T, false>(p, reinterpret_cast<const T*>(p.depth) + texbase * p.D, fw, s)) {
-        ou = s.u0;
-        ov = s.v0;
-        ok = s.k;
-        oval = 1;
-        ++cnt;
-      }
-      u0[q] = ou;
-      v0[q] = ov;
-      kbin[q] = ok;
-      valid[q] = oval;
-    }
-  }
-  p.count[cell] = cnt;
-}
-
-// One thread per camera: P = K4 * inverse(sensor2ego), rows 0-2 (sampling_vt.py:21-33).
-__global__ void projection_kernel(const float* __restrict__ s2e, const float* __restrict__ k33,
-                                  const float* __restrict__ rot, const float* __restrict__ trans,
-                                  float* __restrict__ out, int count) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= count) return;
-  double m[16], inv[16];
-  for (int k = 0; k < 16; ++k) m[k] = (double)s2e[(size_t)i * 16 + k];
-  // adjugate / determinant
-  inv[0] = m[5] * m[10] * m[15] - m[5] * m[11] * m[14] - m[9] * m[6] * m[15] + m[9] * m[7] * m[14] + m[13] * m[6] * m[11] - m[13] * m[7] * m[10];
-  inv[4] = -m[4] * m[10] * m[15] + m[4] * m[11] * m[14] + m[8] * m[6] * m[15] - m[8] * m[7] * m[14] - m[12] * m[6] * m[11] + m[12] * m[7] * m[10];
-  inv[8] = m[4] * m[9] * m[15] - m[4] * m[11] * m[13] - m[8] * m[5] * m[15] + m[8] * m[7] * m[13] + m[12] * m[5] * m[11] - m[12] * m[7] * m[9];
-  inv[12] = -m[4] * m[9] * m[14] + m[4] * m[10] * m[13] + m[8] * m[5] * m[14] - m[8] * m[6] * m[13] - m[12] * m[5] * m[10] + m[12] * m[6] * m[9];
-  inv[1] = -m[1] * m[10] * m[15] + m[1] * m[11] * m[14] + m[9] * m[2] * m[15] - m[9] * m[3] * m[14] - m[13] * m[2] * m[11] + m[13] * m[3] * m[10];
-  inv[5] = m[0] * m[10] * m[15] - m[0] * m[11] * m[14] - m[8] * m[2] * m[15] + m[8] * m[3] * m[14] + m[12] * m[2] * m[11] - m[12] * m[3] * m[10];
-  inv[9] = -m[0] * m[9] * m[15] + m[0] * m[11] * m[13] + m[8] * m[1] * m[15] - m[8] * m[3] * m[13] - m[12] * m[1] * m[11] + m[12] * m[3] * m[9];
-  inv[13] = m[0] * m[9] * m[14] - m[0] * m[10] * m[13] - m[8] * m[1] * m[14] + m[8] * m[2] * m[13] + m[12] * m[1] * m[10] - m[12] * m[2] * m[9];
-  inv[2] = m[1] * m[6] * m[15] - m[1] * m[7] * m[14] - m[5] * m[2] * m[15] + m[5] * m[3] * m[14] + m[13] * m[2] * m[7] - m[13] * m[3] * m[6];
-  inv[6] = -m[0] * m[6] * m[15] + m[0] * m[7] * m[14] + m[4] * m[2] * m[15] - m[4] * m[3] * m[14] - m[12] * m[2] * m[7] + m[12] * m[3] * m[6];
-  inv[10] = m[0] * m[5] * m[15] - m[0] * m[7] * m[13] - m[4] * m[1] * m[15] + m[4] * m[3] * m[13] + m[12] * m[1] * m[7] - m[12] * m[3] * m[5];
-  inv[14] = -m[0] * m[5] * m[14] + m[0] * m[6] * m[13] + m[4] * m[1] * m[14] - m[4] * m[2] * m[13] - m[12] * m[1] * m[6] + m[12] * m[2] * m[5];
-  inv[3] = -m[1] * m[6] * m[11] + m[1] * m[7] * m[10] + m[5] * m[2] * m[11] - m[5] * m[3] * m[10] - m[9] * m[2] * m[7] + m[9] * m[3] * m[6];
-  inv[7] = m[0] * m[6] * m[11] - m[0] * m[7] * m[10] - m[4] * m[2] * m[11] + m[4] * m[3] * m[10] + m[8] * m[2] * m[7] - m[8] * m[3] * m[6];
-  inv[11] = -m[0] * m[5] * m[11] + m[0] * m[7] * m[9] + m[4] * m[1] * m[11] - m[4] * m[3] * m[9] - m[8] * m[1] * m[7] + m[8] * m[3] * m[5];
-  inv[15] = m[0] * m[5] * m[10] - m[0] * m[6] * m[9] - m[4] * m[1] * m[10] + m[4] * m[2] * m[9] + m[8] * m[1] * m[6] - m[8] * m[2] * m[5];
-  const double det = m[0] * inv[0] + m[1] * inv[4] + m[2] * inv[8] + m[3] * inv[12];
-  const double rdet = 1.0 / det;  // a singular pose gives inf / nan, as torch.inverse would complain about
-  for (int k = 0; k < 16; ++k) inv[k] *= rdet;
-  // K4 rows 0-2: (post_rots * camera2imgs) with post_trans added to column 2, fourth column 0
-  double K[12];
-  for (int r = 0; r < 3; ++r) {
-    for (int c = 0; c < 3; ++c) {
-      double a = 0.0;
-      for (int k = 0; k < 3; ++k) a += (double)rot[(size_t)i * 9 + r * 3 + k] * (double)k33[(size_t)i * 9 + k * 3 + c];
-      K[r * 4 + c] = a;
-    }
-    K[r * 4 + 2] += (double)trans[(size_t)i * 3 + r];
-    K[r * 4 + 3] = 0.0;
-  }
-  for (int r = 0; r < 3; ++r)
-    for (int c = 0; c < 4; ++c) {
-      double a = 0.0;
-      for (int k = 0; k < 4; ++k) a += K[r * 4 + k] * inv[k * 4 + c];
-      out[(size_t)i * 12 + r * 4 + c] = (float)a;
-    }
-}
-
-__global__ void probe_read_kernel(const uint4* __restrict__ buf, size_t n16, int repeats, unsigned* sink) {
-  unsigned acc = 0;
-  const size_t stride = (size_t)gridDim.x * blockDim.x;
-  for (int r = 0; r < repeats; ++r)
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += stride) {
-      uint4 v;
-      // volatile: every repeat re-reads memory instead of reusing registers; .cg: served by L2, not by L1
-      asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(buf + i));
-      acc ^= v.x ^ v.y ^ v.z ^ v.w;
-    }
-  if (acc == 0x9e3779b9u) *sink = acc;  // practically never true; keeps the loads alive
-}
 
 // ---------------------------------------------------------------------------
 // Host side
