@@ -21,7 +21,7 @@ ERR_STATIC_LIMIT = 11
 
 # every symbol include/fbev.h declares
 EXPORTS = (
-    "fbev_forward", "fbev_forward_peers", "fbev_backward", "fbev_backward_scratch_bytes", "fbev_backward_min_scratch_bytes", "fbev_backward_static_scratch",
+    "fbev_forward", "fbev_forward_to_host", "fbev_forward_peers", "fbev_backward", "fbev_backward_scratch_bytes", "fbev_backward_min_scratch_bytes", "fbev_backward_static_scratch",
     "fbev_debug_indices",
     "fbev_flash_bevpool", "fbev_flash_bevpool_grad", "fbev_projection_matrices", "fbev_set_tuning", "fbev_probe_read",
     "fbev_strerror", "fbev_version",
@@ -81,6 +81,8 @@ def load(build_if_missing: bool = True) -> ctypes.CDLL:
     vp, i32, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
     lib.fbev_forward.argtypes = [ctypes.POINTER(FbevProblem), vp, vp, vp]
     lib.fbev_forward.restype = i32
+    lib.fbev_forward_to_host.argtypes = [ctypes.POINTER(FbevProblem), vp, vp, i32, vp]
+    lib.fbev_forward_to_host.restype = i32
     lib.fbev_forward_peers.argtypes = [ctypes.POINTER(FbevProblem), vp, ctypes.POINTER(vp), i32, vp, vp]
     lib.fbev_forward_peers.restype = i32
     lib.fbev_backward_scratch_bytes.argtypes = [ctypes.POINTER(FbevProblem), i32]

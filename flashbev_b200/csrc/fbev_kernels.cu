@@ -442,6 +442,75 @@ int fbev_forward(const FbevProblem* p, void* out, int32_t* valid_count, void* st
   return forward_impl(p, out, valid_count, stream, false);
 }
 
+// Side stream and events of fbev_forward_to_host, one set per device, created on first use.
+struct HostPipe {
+  cudaStream_t side = nullptr;
+  cudaEvent_t ready[16] = {};
+  cudaEvent_t done = nullptr;
+  bool ok = false;
+};
+static HostPipe g_host_pipe[64];
+
+int fbev_forward_to_host(const FbevProblem* p, void* out_dev, void* out_host, int row_chunks, void* stream) {
+  const int rc = validate(p);
+  if (rc != FBEV_OK) return rc;
+  if (out_dev == nullptr || out_host == nullptr) return FBEV_ERR_NULL;
+  if (row_chunks < 1 || row_chunks > 16) return FBEV_ERR_SHAPE;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    cudaGetLastError();
+    return FBEV_ERR_NO_DEVICE;
+  }
+  HostPipe& hp = g_host_pipe[dev];
+  if (!hp.ok) {
+    bool good = cudaStreamCreateWithFlags(&hp.side, cudaStreamNonBlocking) == cudaSuccess;
+    for (int k = 0; k < 16 && good; ++k) good = cudaEventCreateWithFlags(&hp.ready[k], cudaEventDisableTiming) == cudaSuccess;
+    good = good && cudaEventCreateWithFlags(&hp.done, cudaEventDisableTiming) == cudaSuccess;
+    if (!good) {
+      cudaGetLastError();
+      return FBEV_ERR_LAUNCH;
+    }
+    hp.ok = true;
+  }
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int y0 = p->y_begin, rows = p->y_end - p->y_begin;
+  const size_t row_bytes = (size_t)p->X * p->C * elem_size(p->out_dtype);
+  const size_t pitch = (size_t)p->Y * row_bytes;  // one batch sample
+  // bands are whole rows of tiles: the launches then work on exactly the tiles of one launch over all rows, and
+  // the result is bit-identical to it (which candidates share a sweep, and so which weights are summed before
+  // they meet the features, depends on the tiling)
+  Dev probe;
+  fill_dev(p, probe);
+  (void)make_plan(p, probe, false, p->image_feats, out_dev, nullptr);
+  const int ty = probe.TY > 0 ? probe.TY : 1;
+  const int tile_rows = (rows + ty - 1) / ty;
+  for (int k = 0; k < row_chunks; ++k) {
+    FbevProblem q = *p;
+    q.y_begin = y0 + (int)((long long)tile_rows * k / row_chunks) * ty;
+    q.y_end = y0 + (int)((long long)tile_rows * (k + 1) / row_chunks) * ty;
+    if (q.y_end > p->y_end) q.y_end = p->y_end;
+    if (q.y_end <= q.y_begin) continue;
+    const int frc = forward_impl(&q, out_dev, nullptr, stream, false);
+    if (frc != FBEV_OK) return frc;
+    // the copy engine takes the rows of this launch while the next launch computes
+    const size_t off = (size_t)q.y_begin * row_bytes;
+    if (cudaEventRecord(hp.ready[k], st) != cudaSuccess || cudaStreamWaitEvent(hp.side, hp.ready[k], 0) != cudaSuccess ||
+        cudaMemcpy2DAsync(reinterpret_cast<unsigned char*>(out_host) + off, pitch,
+                          reinterpret_cast<const unsigned char*>(out_dev) + off, pitch,
+                          (size_t)(q.y_end - q.y_begin) * row_bytes, (size_t)p->B, cudaMemcpyDeviceToHost,
+                          hp.side) != cudaSuccess) {
+      cudaGetLastError();
+      return FBEV_ERR_LAUNCH;
+    }
+  }
+  // the caller's stream continues when the last rows have landed
+  if (cudaEventRecord(hp.done, hp.side) != cudaSuccess || cudaStreamWaitEvent(st, hp.done, 0) != cudaSuccess) {
+    cudaGetLastError();
+    return FBEV_ERR_LAUNCH;
+  }
+  return FBEV_OK;
+}
+
 // float32 accumulation targets of the 16-bit types: what fbev_backward cannot do without
 static size_t scratch_min_bytes(const FbevProblem* p, int flags) {
   if (p->dtype == FBEV_F32) return 0;

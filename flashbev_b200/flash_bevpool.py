@@ -47,7 +47,7 @@ class DepthSpec(int):
 
     def __new__(cls, mode: int, pool: Optional[str] = None, depth_bin_range: Optional[Tuple[float, float]] = None,
                 legacy_depth_grad: bool = False, y_range: Optional[Tuple[int, int]] = None,
-                out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None):
+                out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None, host_row_chunks: int = 0):
         mode = int(mode)
         if mode not in (0, 1, 2):
             raise ValueError(f"depth_distribution must be 0 (gaussian), 1 (laplace) or 2 (categorical), got {mode}")
@@ -72,6 +72,9 @@ class DepthSpec(int):
             raise ValueError("out_dtype must be None (the feature dtype) or torch.float32")
         self.out_dtype = out_dtype
         self.out = out
+        self.host_row_chunks = int(host_row_chunks)
+        if not 0 <= self.host_row_chunks <= 16:
+            raise ValueError("host_row_chunks must be 0 (the kernel stores to the host buffer) or 1..16 row bands")
         return self
 
 
@@ -219,8 +222,15 @@ class FlashBEVPool(torch.autograd.Function):
             out = (torch.zeros if partial else torch.empty)(shape, dtype=_out_dtype(spec, feats), device=feats.device)
         with torch.cuda.device(feats.device):
             stream = torch.cuda.current_stream().cuda_stream
-            rc = _lib.load().fbev_forward(ctypes.byref(p), out.data_ptr(), None, stream)
-        _lib.check(rc, "fbev_forward")
+            if spec.out is not None and not out.is_cuda and spec.host_row_chunks > 0:
+                # bands of rows: the copy engine moves one band to the host while the next is computed
+                staging = torch.empty(shape, dtype=out.dtype, device=feats.device)
+                rc = _lib.load().fbev_forward_to_host(ctypes.byref(p), staging.data_ptr(), out.data_ptr(),
+                                                      spec.host_row_chunks, stream)
+                _lib.check(rc, "fbev_forward_to_host")
+            else:
+                rc = _lib.load().fbev_forward(ctypes.byref(p), out.data_ptr(), None, stream)
+                _lib.check(rc, "fbev_forward")
         ctx.save_for_backward(*keep)
         ctx.spec = spec
         ctx.grid = (p.X, p.Y, p.Z)
@@ -273,7 +283,8 @@ class FlashBEVPool(torch.autograd.Function):
 def flash_bevpool(image_feats, depth_params, projection_matrices, feature_size, image_size, roi_range, grid_size,
                   depth_distribution=0, use_shared_memory=True, optimize_z_precompute=True, use_warp_kernel=False,
                   use_vectorized_load=False, epsilon=1e-6, depth_weight_threshold=1e-6, *, pool=None,
-                  depth_bin_range=None, legacy_depth_grad=False, y_range=None, out_dtype=None, out=None):
+                  depth_bin_range=None, legacy_depth_grad=False, y_range=None, out_dtype=None, out=None,
+                  host_row_chunks=0):
     """Fused BEV pooling; same arguments as the reference wrapper (flash_bevpool.py:139-178).
 
     Args:
@@ -293,11 +304,14 @@ def flash_bevpool(image_feats, depth_params, projection_matrices, feature_size, 
         out: result buffer to fill and return instead of a new tensor: on the device, or page-locked host
             memory, which the kernel then writes directly (inference only; the caller synchronises the stream
             before reading it).
+        host_row_chunks: with a host ``out``: 0 lets the kernel store to it over the bus; 1..16 computes that
+            many bands of rows into a device buffer and copies each band while the next is computed.
     Returns:
         BEV features [B,Y,X,C] in the dtype of ``image_feats`` (or float32, see ``out_dtype``).
     """
     spec = DepthSpec(depth_distribution, pool=pool, depth_bin_range=depth_bin_range,
-                     legacy_depth_grad=legacy_depth_grad, y_range=y_range, out_dtype=out_dtype, out=out)
+                     legacy_depth_grad=legacy_depth_grad, y_range=y_range, out_dtype=out_dtype, out=out,
+                     host_row_chunks=host_row_chunks)
     return FlashBEVPool.apply(depth_params, image_feats, projection_matrices, feature_size, image_size, roi_range,
                               grid_size, spec, use_shared_memory, optimize_z_precompute, use_warp_kernel,
                               use_vectorized_load, epsilon, depth_weight_threshold)

@@ -43,8 +43,15 @@ def batch_slice(batch: int, world: int, rank: int) -> Tuple[int, int]:
     return even_slice(batch, world, rank)
 
 
+ROW_ALIGN = 4  # rows of one tile of the forward kernel
+
+
 def row_slice(rows: int, world: int, rank: int) -> Tuple[int, int]:
-    return even_slice(rows, world, rank)
+    """Rows of ``rank``: an even share of the rows of tiles, so that every rank works on whole tiles of the
+    single-GPU launch and the assembled result is bit-identical to it (the kernel's summation grouping depends on
+    the tiling)."""
+    t0, t1 = even_slice(-(-rows // ROW_ALIGN), world, rank)
+    return min(t0 * ROW_ALIGN, rows), min(t1 * ROW_ALIGN, rows)
 
 
 def _world(group) -> Tuple[int, int]:
@@ -79,8 +86,9 @@ def gather_rows(local_rows: torch.Tensor, rows: int, group=None) -> torch.Tensor
     if world == 1:
         return local_rows
     B = local_rows.shape[0]
-    per = -(-rows // world)
-    if B == 1 and rows % world == 0:
+    sizes = [y1 - y0 for y0, y1 in (row_slice(rows, world, r) for r in range(world))]
+    per = max(sizes)
+    if B == 1 and min(sizes) == per:
         full = local_rows.new_empty((1, rows) + tuple(local_rows.shape[2:]))
         dist.all_gather_into_tensor(full.view((rows,) + tuple(local_rows.shape[2:])),
                                     local_rows.reshape((per,) + tuple(local_rows.shape[2:])).contiguous(), group=group)

@@ -116,6 +116,16 @@ typedef struct FbevProblem {
  * int32 [B,Y,X]) receives the number of accepted samples per cell. */
 int fbev_forward(const FbevProblem* p, void* out, int32_t* valid_count, void* stream);
 
+/* Forward whose result ends in page-locked host memory, computed in row_chunks launches (1..16) over
+ * consecutive bands of rows [y_begin, y_end) so that the device-to-host copy of one band (copy engine, a side
+ * stream owned by the library) runs while the next band is computed.  (No counterpart in the reference, whose
+ * callers copy the whole result after the kernel.)  out_dev: device [B,Y,X,C] staging buffer; out_host:
+ * page-locked host [B,Y,X,C]; both receive the rows.  The caller's stream waits for the last copy, so work
+ * queued on it afterwards, or a synchronisation of it, sees the host buffer complete.  The first call on a
+ * device creates the side stream and its events; make it outside any stream capture.  Calls on the same
+ * device must not overlap each other in time (they share the side stream's events). */
+int fbev_forward_to_host(const FbevProblem* p, void* out_dev, void* out_host, int row_chunks, void* stream);
+
 /* Forward whose result rows also go to other GPUs.  (No counterpart in the reference, which has no
  * distributed code.)  Same as fbev_forward, and every 16-byte piece of out[:, y_begin:y_end] is stored to
  * peer_outs[0 .. n_peers) as well: device pointers of [B,Y,X,C] buffers in other GPUs' memory that this

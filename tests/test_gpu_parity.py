@@ -49,6 +49,31 @@ def run_case(w, mode, device, threshold=0.0, pool=None, tol=None, dtype=None, y_
     return err
 
 
+@pytest.mark.parametrize("seed", range(16))
+def test_random_shapes_forward_and_backward(cuda_device, seed):
+    """Seeded random problems: camera count, channel width (chunked and scalar kernels), map and grid sizes,
+    height bins (one and several passes per cell), depth model, pooling, element type, threshold; odd seeds
+    force the gradients' global sort, which problems of this size would not get by default."""
+    rng = np.random.default_rng(1000 + seed)
+    mode = ["categorical", "laplace", "gaussian"][seed % 3]
+    dtype = ["fp32", "bf16", "fp16"][int(rng.integers(0, 3))]
+    w = synth.Workload(f"rand{seed}", B=int(rng.integers(1, 3)), N=int(rng.integers(1, 8)),
+                       C=int(rng.choice([4, 6, 8, 16, 24, 40, 64, 80])), H=int(rng.integers(3, 12)),
+                       W=int(rng.integers(5, 30)), D=int(rng.integers(4, 40)), X=int(rng.integers(3, 50)),
+                       Y=int(rng.integers(3, 50)), Z=int(rng.choice([1, 2, 5, 8, 20, 40])),
+                       xy_extent=float(rng.uniform(10.0, 50.0)), d0=1.0, delta=float(rng.uniform(0.5, 3.0)),
+                       dtype=dtype, seed=200 + seed, jitter=bool(seed & 2))
+    pool = ["mean", "sum"][int(rng.integers(0, 2))]
+    threshold = [0.0, 1e-3][int(rng.integers(0, 2))]
+    lib = _lib.load()
+    try:
+        lib.fbev_set_tuning(0, 0, 0, 0, 7 if seed & 1 else 0)
+        run_case(w, mode, cuda_device, threshold=threshold, pool=pool)
+        backward_case(w, mode, cuda_device, pool=pool, threshold=threshold)
+    finally:
+        lib.fbev_set_tuning(0, 0, 0, 0, 0)
+
+
 @pytest.mark.parametrize("mode", ["gaussian", "laplace", "categorical"])
 @pytest.mark.parametrize("threshold", [0.0, 1e-3])
 def test_forward_small_fp32(cuda_device, mode, threshold):
@@ -356,7 +381,13 @@ def test_result_buffer_given_by_the_caller(cuda_device):
         host_out = torch.full(ref.shape, float("nan"), dtype=ref.dtype).pin_memory()
         flash_bevpool(**inp, **kw, out=host_out)
         torch.cuda.synchronize()
-    assert torch.equal(dev_out, ref) and torch.equal(host_out, ref.cpu())
+        assert torch.equal(host_out, ref.cpu())
+        for chunks in (1, 3, 16):  # row bands through a device buffer, copies overlapping the next band
+            host_out.fill_(float("nan"))
+            flash_bevpool(**inp, **kw, out=host_out, host_row_chunks=chunks)
+            torch.cuda.current_stream().synchronize()
+            assert torch.equal(host_out, ref.cpu()), chunks
+    assert torch.equal(dev_out, ref)
     with pytest.raises(ValueError):
         flash_bevpool(**inp, **kw, out=torch.empty(ref.shape, dtype=ref.dtype))  # pageable host memory
     with pytest.raises(ValueError):
