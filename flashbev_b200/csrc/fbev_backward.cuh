@@ -19,8 +19,8 @@ __device__ __forceinline__ void red_add4(float* addr, float a, float b, float c,
 
 // Sum over the GL lanes of a group; the result is valid in the group's first lane.
 __device__ __forceinline__ float group_sum(float v, int lg, int GL) {
-  // first step: the largest power of two below GL (larger offsets would add nothing)
-  for (int off = GL > 16 ? 16 : GL > 8 ? 8 : GL > 4 ? 4 : GL > 2 ? 2 : 1; off > 0; off >>= 1) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
     const float o = __shfl_down_sync(kFull, v, off);
     if (lg + off < GL) v += o;
   }
@@ -562,6 +562,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_depth_kernel(const __gr
   const bool legacy = (p.flags & FBEV_BWD_LEGACY_DEPTH) != 0;
   const bool mean_pool = p.pool == FBEV_POOL_MEAN;
   const bool by_record = (p.flags & FBEV_BWD_DEPTH) != 0 && (!EMIT || p.ent_d != nullptr);
+  // categorical: sum equal (texel, bin) neighbours before the atomics.  Pays with six cells per warp (the scan's
+  // fixed cost is shared by many samples and the depth tensor is small enough for its atomics to contend);
+  // measured a loss with two or three cells per warp on large feature maps
+  const bool merge_bins = p.CPW >= 4;
   int loaded_b = -1;
   TileLoop loop;
   loop.begin(p, s_tile);
@@ -772,7 +776,15 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_depth_kernel(const __gr
           float* d10 = d00 + sa.y;
           float* d01 = d00 + sa.z;
           float* d11 = d01 + sa.y;
-          if (p.mode == FBEV_DEPTH_CATEGORICAL) {
+          if (p.mode == FBEV_DEPTH_CATEGORICAL && !merge_bins) {
+            if (active) {
+              const int k = (int)sa.w;
+              atomicAdd(d00 + k, v00);
+              atomicAdd(d01 + k, v01);
+              atomicAdd(d10 + k, v10);
+              atomicAdd(d11 + k, v11);
+            }
+          } else if (p.mode == FBEV_DEPTH_CATEGORICAL) {
             const unsigned key = active ? sa.x + sa.w : 0xffffffffu - (unsigned)lane;  // element index of (texel, bin)
             const unsigned pkey = __shfl_up_sync(kFull, key, 1);
             const unsigned headm = __ballot_sync(kFull, active && (lane == 0 || pkey != key));

@@ -108,7 +108,10 @@ struct Plan {
 
 // Chooses the lane layout.  chunks = 16-byte chunks per texel.  A lane owns V of
 // them; GL = chunks / V lanes share a cell; CPW = 32 / GL cells per warp.
-static Plan make_plan(const FbevProblem* p, Dev& d, bool bwd, const void* a, const void* b2, const void* c) {
+// wide_ok: four chunks per lane may be chosen for float32 (measured: better everywhere but in the categorical
+// depth-gradient kernel, whose registers it exhausts).
+static Plan make_plan(const FbevProblem* p, Dev& d, bool bwd, const void* a, const void* b2, const void* c,
+                      bool wide_ok = true) {
   Plan pl{};
   const size_t es = elem_size(p->dtype);
   const size_t row = (size_t)p->C * es;
@@ -130,7 +133,9 @@ static Plan make_plan(const FbevProblem* p, Dev& d, bool bwd, const void* a, con
       const int CPW = 32 / GL < kMaxCellsPerWarp ? 32 / GL : kMaxCellsPerWarp;
       // lane utilisation first
       double score = (double)(CPW * GL) / 32.0;
-      if (V == 2) score += 0.02;  // two chunks per lane amortise the record handling; four cost registers
+      // at equal utilisation: as many chunks per lane as sixteen float32 accumulators hold (two of a 16-bit
+      // type, four of float32) -- more cells per warp share one list phase; beyond that registers run out
+      if (V * (es == 4 ? 4 : 8) <= 16 && (V < 4 || wide_ok)) score += 0.01 * V;
       if (score > best) {
         best = score;
         bestV = V;
@@ -637,7 +642,8 @@ int fbev_backward(const FbevProblem* p, const void* grad_out, void* grad_feats, 
   }
   // the feature gradient has a kernel of its own, laid out like the forward
   Dev df = d;
-  const Plan plf = make_plan(p, df, false, p->image_feats, grad_out, d.gfeat);
+  const bool wide_ok = !((flags & FBEV_BWD_DEPTH) && p->mode == FBEV_DEPTH_CATEGORICAL);
+  const Plan plf = make_plan(p, df, false, p->image_feats, grad_out, d.gfeat, wide_ok);
   int lrc;
   switch (p->dtype) {
     case FBEV_F32: lrc = backward_t<float>(pl, d, plf, df, st); break;
