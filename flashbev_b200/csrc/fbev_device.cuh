@@ -46,6 +46,7 @@ struct Dev {
   int flags;  // FBEV_BWD_*
   int out_f32;        // output / upstream gradient are float32 although the features are 16-bit
   unsigned* sched;    // tile scheduler words {next tile, blocks done}, or null for one tile per block
+  int static_units;   // forward, one sample: warps stride over (tile, group) units, no barrier, no atomic
   // gradients through a global sort by texel (null / 0 when not in use)
   unsigned* tex_count;   // [texels + 1] entries per texel; after the scan: start of the texel's segment, total last
   unsigned* ent_count;   // [1] entries emitted so far

@@ -204,8 +204,10 @@ static int sm_count() {
   return cached[dev];
 }
 
+// One resident wave when the blocks can draw tiles from the scheduler word or stride over the work themselves
+// (static_units), else one block per tile.  static_units is decided here, where the wave is known.
 template <typename K>
-static int launch(K kernel, const Plan& pl, const Dev& d, cudaStream_t st) {
+static int launch(K kernel, const Plan& pl, Dev d, cudaStream_t st, int groups_per_tile = 0) {
   if (pl.blocks <= 0) return FBEV_OK;
   if (pl.smem > 200 * 1024) return FBEV_ERR_RANGE;
   if (pl.smem > 48 * 1024) {
@@ -215,8 +217,8 @@ static int launch(K kernel, const Plan& pl, const Dev& d, cudaStream_t st) {
     }
   }
   int blocks = pl.blocks;
-  if (d.sched != nullptr) {
-    // one resident wave; the blocks draw their tiles from the scheduler word
+  if (d.sched != nullptr || groups_per_tile > 0) {
+    // one resident wave
     int per_sm = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, pl.warps * 32, pl.smem) != cudaSuccess ||
         per_sm <= 0) {
@@ -224,7 +226,16 @@ static int launch(K kernel, const Plan& pl, const Dev& d, cudaStream_t st) {
       per_sm = 1;
     }
     const long long wave = (long long)per_sm * sm_count();
-    if (wave < blocks) blocks = (int)wave;
+    // forward: a single sample with at most three units of work per resident warp takes the barrier-free
+    // static order (measured ahead there, behind the counter on larger problems)
+    const long long units = (long long)pl.blocks * groups_per_tile;
+    const bool few = groups_per_tile > 0 && d.B == 1 && units <= 3 * wave * pl.warps && g_tuning.minb != 14;
+    if (few || (groups_per_tile > 0 && g_tuning.minb == 15)) d.static_units = d.B == 1 ? 1 : 0;
+    if (d.sched == nullptr && !d.static_units) {
+      // no scheduler word and too much work for the static order: one block per tile
+    } else if (wave < blocks) {
+      blocks = (int)wave;
+    }
   }
   kernel<<<blocks, pl.warps * 32, pl.smem, st>>>(d);
   return cudaGetLastError() == cudaSuccess ? FBEV_OK : FBEV_ERR_LAUNCH;
@@ -234,10 +245,11 @@ template <typename T>
 static int forward_t(const Plan& pl, const Dev& d, cudaStream_t st) {
   if (!pl.chunked) return launch(fwd_generic_kernel<T>, pl, d, st);
   const bool two = g_tuning.minb == 2;  // compiled for two resident blocks per SM (128 registers) instead of three (80)
+  const int gpt = (d.TX * d.TY + pl.CPW - 1) / pl.CPW;  // groups of CPW cells per tile
   switch (pl.V) {
-    case 1: return two ? launch(fwd_kernel<T, 1, 2>, pl, d, st) : launch(fwd_kernel<T, 1, 3>, pl, d, st);
-    case 2: return two ? launch(fwd_kernel<T, 2, 2>, pl, d, st) : launch(fwd_kernel<T, 2, 3>, pl, d, st);
-    default: return launch(fwd_kernel<T, 4, 2>, pl, d, st);
+    case 1: return two ? launch(fwd_kernel<T, 1, 2>, pl, d, st, gpt) : launch(fwd_kernel<T, 1, 3>, pl, d, st, gpt);
+    case 2: return two ? launch(fwd_kernel<T, 2, 2>, pl, d, st, gpt) : launch(fwd_kernel<T, 2, 3>, pl, d, st, gpt);
+    default: return launch(fwd_kernel<T, 4, 2>, pl, d, st, gpt);
   }
 }
 
