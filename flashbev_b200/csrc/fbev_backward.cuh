@@ -142,16 +142,21 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_feats_kernel(const __gr
   float* gl = p.gfeat + (size_t)lg * E;  // this lane's chunk of texel 0 in the float32 gradient
   const bool mean_pool = p.pool == FBEV_POOL_MEAN;
   int loaded_b = -1;
-  TileLoop loop;
-  loop.begin(p, s_tile);
-  for (int tile; (tile = loop.current(p)) >= 0; loop.advance()) {
+  UnitLoop sched;
+  sched.begin(p, s_tile, ngroups, warp, nwarps);
+  if (sched.stat) {  // the sample's matrices, once, by the whole block
+    const Tile tt = tile_of(p, 0);
+    (void)tile_visibility(p, tt, h, vs, vmin, image_h, image_w, loaded_b);
+  }
+  int g_first = 0, g_step = 1;
+  for (int tile; (tile = sched.current(p, g_first, g_step)) >= 0; sched.advance()) {
     const Tile t = tile_of(p, tile);
     const unsigned vis = tile_visibility(p, t, h, vs, vmin, image_h, image_w, loaded_b);
     const int nvis = __popc(vis);
     const int ncand = nvis * p.Z;
     const bool single_pass = ncand <= p.cap;
 
-    for (int grp = warp; grp < ngroups; grp += nwarps) {
+    for (int grp = g_first; grp < ngroups; grp += g_step) {
       const int t0 = grp * p.CPW;
       const int tc = t0 + g;
       const int ly = tc / p.TX, lx = tc - ly * p.TX;
@@ -217,7 +222,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_feats_kernel(const __gr
       __syncwarp();
     }
   }  // tiles
-  loop.end(p);
+  sched.end(p);
 }
 
 // ---------------------------------------------------------------------------
@@ -567,15 +572,20 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_depth_kernel(const __gr
   // measured a loss with two or three cells per warp on large feature maps
   const bool merge_bins = p.CPW >= 4;
   int loaded_b = -1;
-  TileLoop loop;
-  loop.begin(p, s_tile);
-  for (int tile; (tile = loop.current(p)) >= 0; loop.advance()) {
+  UnitLoop sched;
+  sched.begin(p, s_tile, ngroups, warp, nwarps);
+  if (sched.stat) {  // the sample's matrices, once, by the whole block
+    const Tile tt = tile_of(p, 0);
+    (void)tile_visibility(p, tt, h, vs, vmin, image_h, image_w, loaded_b);
+  }
+  int g_first = 0, g_step = 1;
+  for (int tile; (tile = sched.current(p, g_first, g_step)) >= 0; sched.advance()) {
     const Tile t = tile_of(p, tile);
     const unsigned vis = tile_visibility(p, t, h, vs, vmin, image_h, image_w, loaded_b);
     const int ncand = __popc(vis) * p.Z;
     const bool single_pass = ncand <= p.cap;
 
-    for (int grp = warp; grp < ngroups; grp += nwarps) {
+    for (int grp = g_first; grp < ngroups; grp += g_step) {
       const int t0 = grp * p.CPW;
       const int tc = t0 + g;
       const int ly = tc / p.TX, lx = tc - ly * p.TX;
@@ -821,7 +831,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_depth_kernel(const __gr
       __syncwarp();
     }
   }  // tiles
-  loop.end(p);
+  sched.end(p);
 }
 
 // Gradient kernel.  Same decomposition as the forward.  For every accepted sample

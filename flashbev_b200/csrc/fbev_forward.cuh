@@ -35,38 +35,18 @@ __global__ void __launch_bounds__(kMaxWarps * 32, MINB) fwd_kernel(const __grid_
   const int ngroups = (tile_cells + p.CPW - 1) / p.CPW;
   const uint4* fl = reinterpret_cast<const uint4*>(p.feats) + lg;  // this lane's chunk of texel 0
   int loaded_b = -1;
-  // Two schedules.  Default: the block draws whole tiles from an atomic counter and its warps share out the
-  // tile's groups, with a barrier per tile; it balances large problems.  static_units (one sample, at most
-  // a few units per warp): the unit of work is one group of one tile and warp w of the grid takes units
-  // w, w + W, w + 2W, ...; the warps of a block still work on the groups of one tile at about the same
-  // time (their texels stay in the SM's L1), but none waits for another: no barrier, no atomic.  On the
-  // benchmark shape, where a block sees about two tiles, that is 35.0 against 37.6 us; warps drawing units
-  // one by one from a counter gave 37.0 us (the groups of a tile then land on different SMs); on shapes with
-  // many tiles per block the static order loses 10-17 % to the counter.
-  const bool stat = p.static_units != 0;
-  const int units = p.tiles_x * p.tiles_y * p.B * ngroups;
-  const int W = gridDim.x * nwarps;
-  int unit = blockIdx.x * nwarps + warp;
-  if (stat) {  // the sample's matrices, once, by the whole block (the loop below has no barrier)
+  UnitLoop sched;  // counter of tiles with a barrier per tile, or the barrier-free static order of units
+  sched.begin(p, s_tile, ngroups, warp, nwarps);
+  if (sched.stat) {  // the sample's matrices, once, by the whole block
     const Tile tt = tile_of(p, 0);
     (void)tile_visibility(p, tt, h, vs, vmin, image_h, image_w, loaded_b);
   }
-  TileLoop loop;
-  if (!stat) loop.begin(p, s_tile);
-  for (int tile;;) {
-    if (stat) {
-      if (unit >= units) break;
-      tile = unit / ngroups;
-    } else {
-      tile = loop.current(p);
-      if (tile < 0) break;
-    }
+  int g_first = 0, g_step = 1;
+  for (int tile; (tile = sched.current(p, g_first, g_step)) >= 0; sched.advance()) {
     const Tile t = tile_of(p, tile);
     const unsigned vis = tile_visibility(p, t, h, vs, vmin, image_h, image_w, loaded_b);
     const int nvis = __popc(vis);
     const int ncand = nvis * p.Z;
-    const int g_first = stat ? unit - tile * ngroups : warp;
-    const int g_step = stat ? ngroups : nwarps;
 
     for (int grp = g_first; grp < ngroups; grp += g_step) {
       const int t0 = grp * p.CPW;
@@ -134,13 +114,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, MINB) fwd_kernel(const __grid_
       }
       __syncwarp();
     }
-    if (stat) {
-      unit += W;
-    } else {
-      loop.advance();
-    }
   }  // tiles
-  if (!stat) loop.end(p);
+  sched.end(p);
 }
 
 // Any channel count and alignment: one cell per warp, lanes stride over channels

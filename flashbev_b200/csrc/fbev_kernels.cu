@@ -264,9 +264,9 @@ static int backward_feats_sort_t(const Plan& pl, const Dev& d_in, cudaStream_t s
   d.flags &= ~FBEV_BWD_DEPTH;
   int rc;
   switch (pl.V) {
-    case 1: rc = launch(bwd_feats_kernel<T, 1, true>, pl, d, st); break;
-    case 2: rc = launch(bwd_feats_kernel<T, 2, true>, pl, d, st); break;
-    default: rc = launch(bwd_feats_kernel<T, 4, true>, pl, d, st); break;
+    case 1: rc = launch(bwd_feats_kernel<T, 1, true>, pl, d, st, (d.TX * d.TY + pl.CPW - 1) / pl.CPW); break;
+    case 2: rc = launch(bwd_feats_kernel<T, 2, true>, pl, d, st, (d.TX * d.TY + pl.CPW - 1) / pl.CPW); break;
+    default: rc = launch(bwd_feats_kernel<T, 4, true>, pl, d, st, (d.TX * d.TY + pl.CPW - 1) / pl.CPW); break;
   }
   if (rc != FBEV_OK) return rc;
   return sort_finish_t<T>(pl, d, st);
@@ -330,9 +330,9 @@ static int backward_feats_t(const Plan& pl, const Dev& d, cudaStream_t st) {
     }
   }
   switch (pl.V) {
-    case 1: return launch(bwd_feats_kernel<T, 1, false>, pl, d, st);
-    case 2: return launch(bwd_feats_kernel<T, 2, false>, pl, d, st);
-    default: return launch(bwd_feats_kernel<T, 4, false>, pl, d, st);
+    case 1: return launch(bwd_feats_kernel<T, 1, false>, pl, d, st, (d.TX * d.TY + pl.CPW - 1) / pl.CPW);
+    case 2: return launch(bwd_feats_kernel<T, 2, false>, pl, d, st, (d.TX * d.TY + pl.CPW - 1) / pl.CPW);
+    default: return launch(bwd_feats_kernel<T, 4, false>, pl, d, st, (d.TX * d.TY + pl.CPW - 1) / pl.CPW);
   }
 }
 
@@ -358,9 +358,9 @@ static int backward_t(const Plan& pl, Dev d, const Plan& plf, const Dev& df, cud
       dd.flags = d.flags;
       int rc;
       switch (pld.V) {
-        case 1: rc = launch(bwd_depth_kernel<T, 1, true>, pld, dd, st); break;
-        case 2: rc = launch(bwd_depth_kernel<T, 2, true>, pld, dd, st); break;
-        default: rc = launch(bwd_depth_kernel<T, 4, true>, pld, dd, st); break;
+        case 1: rc = launch(bwd_depth_kernel<T, 1, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW); break;
+        case 2: rc = launch(bwd_depth_kernel<T, 2, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW); break;
+        default: rc = launch(bwd_depth_kernel<T, 4, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW); break;
       }
       return rc != FBEV_OK ? rc : sort_finish_t<T>(pld, dd, st);
     }
@@ -374,9 +374,9 @@ static int backward_t(const Plan& pl, Dev d, const Plan& plf, const Dev& df, cud
     dd.flags = d.flags;
     int rc;
     switch (pld.V) {
-      case 1: rc = launch(bwd_depth_kernel<T, 1, true>, pld, dd, st); break;
-      case 2: rc = launch(bwd_depth_kernel<T, 2, true>, pld, dd, st); break;
-      default: rc = launch(bwd_depth_kernel<T, 4, true>, pld, dd, st); break;
+      case 1: rc = launch(bwd_depth_kernel<T, 1, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW); break;
+      case 2: rc = launch(bwd_depth_kernel<T, 2, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW); break;
+      default: rc = launch(bwd_depth_kernel<T, 4, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW); break;
     }
     return rc != FBEV_OK ? rc : sort_finish_t<T>(pld, dd, st);
   }
@@ -384,9 +384,9 @@ static int backward_t(const Plan& pl, Dev d, const Plan& plf, const Dev& df, cud
     // depth gradient alone: per-texel dot products on the forward's row records
     dd.flags = d.flags;
     switch (pld.V) {
-      case 1: return launch(bwd_depth_kernel<T, 1, false>, pld, dd, st);
-      case 2: return launch(bwd_depth_kernel<T, 2, false>, pld, dd, st);
-      default: return launch(bwd_depth_kernel<T, 4, false>, pld, dd, st);
+      case 1: return launch(bwd_depth_kernel<T, 1, false>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW);
+      case 2: return launch(bwd_depth_kernel<T, 2, false>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW);
+      default: return launch(bwd_depth_kernel<T, 4, false>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW);
     }
   }
   switch (pl.V) {

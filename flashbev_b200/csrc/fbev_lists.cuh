@@ -105,6 +105,58 @@ struct TileLoop {
   }
 };
 
+// The two schedules of the kernels whose warps work on groups of CPW cells independently of each other
+// (forward, feature-gradient and depth-gradient kernels).
+//   counter (default): the block draws whole tiles from the atomic counter (TileLoop) and its warps share out
+//     the tile's groups, with a barrier per tile; it balances large problems.
+//   static (Dev.static_units: one sample, at most a few units per warp): the unit of work is one group of one
+//     tile and warp w of the grid takes units w, w + W, w + 2W, ...  The warps of a block still work on the
+//     groups of one tile at about the same time (their texels stay in the SM's L1), but none waits for
+//     another: no barrier, no atomic.  Forward on the benchmark shape, where a block sees about two tiles:
+//     35.0 against 37.6 us; warps drawing units one by one from a counter gave 37.0 us (the groups of a tile
+//     then land on different SMs); with many tiles per block the static order loses 10-17 % to the counter.
+// Use: begin(); while ((tile = current(p, g_first, g_step)) >= 0) { groups g_first, g_first + g_step, ... ;
+// advance(); } end().  In the static schedule the caller loads the sample's matrices once before the loop
+// (tile_visibility on tile 0, by the whole block): the loop itself must not meet a block barrier.
+struct UnitLoop {
+  TileLoop loop;
+  bool stat;
+  int unit, units, W, ngroups, nwarps, warp;
+
+  __device__ __forceinline__ void begin(const Dev& p, int* shared_slot, int ngroups_, int warp_, int nwarps_) {
+    stat = p.static_units != 0;
+    ngroups = ngroups_;
+    warp = warp_;
+    nwarps = nwarps_;
+    units = p.tiles_x * p.tiles_y * p.B * ngroups;
+    W = gridDim.x * nwarps;
+    unit = blockIdx.x * nwarps + warp;
+    if (!stat) loop.begin(p, shared_slot);
+  }
+  __device__ __forceinline__ int current(const Dev& p, int& g_first, int& g_step) {
+    if (stat) {
+      if (unit >= units) return -1;
+      const int tile = unit / ngroups;
+      g_first = unit - tile * ngroups;
+      g_step = ngroups;  // one group per visit
+      return tile;
+    }
+    g_first = warp;
+    g_step = nwarps;
+    return loop.current(p);
+  }
+  __device__ __forceinline__ void advance() {
+    if (stat) {
+      unit += W;
+    } else {
+      loop.advance();
+    }
+  }
+  __device__ __forceinline__ void end(const Dev& p) {
+    if (!stat) loop.end(p);
+  }
+};
+
 // Loads matrices and feature sizes of the tile's sample (when it differs from the one already in
 // shared memory) and builds the list of cameras that may see the tile.  Ends with a block barrier.
 __device__ __forceinline__ void block_prologue(const Dev& p, const Tile& t, const BlockHeader& h, const float vs[3],
