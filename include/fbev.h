@@ -230,9 +230,15 @@ int fbev_flash_bevpool_grad(int total_threads, int num_channels, int num_cameras
 int fbev_projection_matrices(const float* sensor2ego, const float* camera2imgs, const float* post_rots,
                              const float* post_trans, float* out, int count, void* stream);
 
-/* Process-wide launch tuning for experiments: cells per tile in x and y,
- * 16-byte chunks per lane, warps per block, resident blocks per SM the forward
- * kernel is compiled for (2 or 3); 0 = choose automatically. */
+/* Process-wide launch tuning for experiments and tests: cells per tile in x and y, 16-byte chunks per
+ * lane, warps per block, and a selector (last argument); 0 = choose automatically.  Selector values:
+ *   2  forward compiled for two resident blocks per SM (128 registers) instead of three
+ *   1  feature gradient by direct reductions      6  feature gradient with the per-tile sort
+ *   5  record-based depth-gradient kernel also for the parametric modes without entry lists
+ *   7  gradients through the global sort whatever the problem size      8  the same with a 4096-entry list
+ *   9  global sort with tile_x = gather blocks per SM and tile_y = entries per gather run
+ *   14 forward / list kernels always on the tile counter      15 always in the static unit order (one sample)
+ * Any non-zero selector other than 7, 8, 9 also turns the global sort off. */
 void fbev_set_tuning(int tile_x, int tile_y, int chunks_per_lane, int warps, int min_blocks);
 
 /* Reads `bytes` of device memory `repeats` times with 16-byte loads (a bandwidth
