@@ -120,6 +120,7 @@ __device__ __forceinline__ bool emit_entries(const Dev& p, const uint4* rec, int
 template <typename T, int V, bool EMIT>
 __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_feats_kernel(const __grid_constant__ Dev p) {
   constexpr int E = Chunk<T>::E;
+  grid_dependency_trigger();  // the kernel after this one may bring its blocks in as ours leave
   extern __shared__ __align__(16) unsigned char smem[];
   const BlockHeader h = carve(smem, p.N);
   __shared__ int s_tile[2];
@@ -542,6 +543,7 @@ __host__ __device__ inline size_t depth_warp_bytes(int CPW, int cap) {
 template <typename T, int V, bool EMIT>
 __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_depth_kernel(const __grid_constant__ Dev p) {
   constexpr int E = Chunk<T>::E;
+  grid_dependency_trigger();  // the kernel after this one may bring its blocks in as ours leave
   extern __shared__ __align__(16) unsigned char smem[];
   const BlockHeader h = carve(smem, p.N);
   __shared__ int s_tile[2];
@@ -1123,6 +1125,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32) bwd_generic_kernel(const __gri
 template <typename T>
 __global__ void convert2_kernel(const float* __restrict__ sa, T* __restrict__ da, size_t na, const float* __restrict__ sb,
                                 T* __restrict__ db, size_t nb) {
+  grid_dependency_wait();
   const size_t ua = (na + 3) / 4, ub = (nb + 3) / 4;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (size_t u = (size_t)blockIdx.x * blockDim.x + threadIdx.x; u < ua + ub; u += stride) {

@@ -58,6 +58,13 @@ struct Dev {
   unsigned ent_cap;
 };
 
+// Programmatic dependent launch (sm_90+).  A kernel launched with the programmatic-serialization attribute may
+// start while the kernel before it in the stream is still draining; grid_dependency_wait() returns once that
+// kernel has completed and its writes are visible (a no-op for an ordinary launch).  grid_dependency_trigger()
+// tells the scheduler that the next kernel's blocks may be brought in as resources free up.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_trigger() { asm volatile("griddepcontrol.launch_dependents;"); }
+
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 __device__ __forceinline__ float to_float(__half v) { return __half2float(v); }

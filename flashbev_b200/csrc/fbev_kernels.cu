@@ -241,6 +241,24 @@ static int launch(K kernel, const Plan& pl, Dev d, cudaStream_t st, int groups_p
   return cudaGetLastError() == cudaSuccess ? FBEV_OK : FBEV_ERR_LAUNCH;
 }
 
+// Launch that may overlap the tail of the kernel before it in the stream (programmatic dependent launch); the
+// kernel calls grid_dependency_wait() before it touches anything that kernel wrote.
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_after(void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t st,
+                                Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 template <typename T>
 static int forward_t(const Plan& pl, const Dev& d, cudaStream_t st) {
   if (!pl.chunked) return launch(fwd_generic_kernel<T>, pl, d, st);
@@ -279,17 +297,17 @@ static int sort_finish_t(const Plan& pl, const Dev& d, cudaStream_t st) {
   const int sms = sm_count();
   unsigned* total = d.ent_count + 1;  // second word of the counter block
   if (texels <= kScanInBlock) {
-    ent_scatter_kernel<true><<<sms * 8, 256, (size_t)(texels + 1) * 4, st>>>(d, texels, total);
+    launch_after(ent_scatter_kernel<true>, sms * 8, 256, (size_t)(texels + 1) * 4, st, d, texels, total);
   } else {
-    tex_scan_kernel<<<1, 1024, 0, st>>>(d.tex_count, texels);
-    ent_scatter_kernel<false><<<sms * 8, 256, 0, st>>>(d, texels, nullptr);
+    launch_after(tex_scan_kernel, 1, 1024, 0, st, d.tex_count, texels);
+    launch_after(ent_scatter_kernel<false>, sms * 8, 256, 0, st, d, texels, (unsigned*)nullptr);
     total = d.tex_count + texels;
   }
   // entries one lane group walks per run, blocks per SM (experiments: fbev_set_tuning tile_y / tile_x with min_blocks 9)
   const unsigned run_len = g_tuning.minb == 9 && g_tuning.ty > 0 ? (unsigned)g_tuning.ty : 32u;
   const int gb = sms * (g_tuning.minb == 9 && g_tuning.tx > 0 ? g_tuning.tx : 8);
   const bool pd = d.ent_d_sorted != nullptr;
-#define FBEV_GATHER(VV, GF, PD) feats_gather_kernel<T, VV, GF, PD><<<gb, 128, 0, st>>>(d, total, run_len)
+#define FBEV_GATHER(VV, GF, PD) launch_after(feats_gather_kernel<T, VV, GF, PD>, gb, 128, 0, st, d, (const unsigned*)total, run_len)
 #define FBEV_GATHER_V(GF, PD)                 \
   switch (pl.V) {                             \
     case 1: FBEV_GATHER(1, GF, PD); break;    \
@@ -672,11 +690,11 @@ int fbev_backward(const FbevProblem* p, const void* grad_out, void* grad_feats, 
     const int threads = 256;
     const int blocks = (int)((units + threads - 1) / threads < 148 * 16 ? (units + threads - 1) / threads : 148 * 16);
     if (p->dtype == FBEV_BF16)
-      convert2_kernel<__nv_bfloat16><<<blocks, threads, 0, st>>>(sa, reinterpret_cast<__nv_bfloat16*>(grad_feats), na, sb,
-                                                                 reinterpret_cast<__nv_bfloat16*>(grad_depth), nb);
+      launch_after(convert2_kernel<__nv_bfloat16>, blocks, threads, 0, st, sa, reinterpret_cast<__nv_bfloat16*>(grad_feats), na,
+                   sb, reinterpret_cast<__nv_bfloat16*>(grad_depth), nb);
     else
-      convert2_kernel<__half><<<blocks, threads, 0, st>>>(sa, reinterpret_cast<__half*>(grad_feats), na, sb,
-                                                          reinterpret_cast<__half*>(grad_depth), nb);
+      launch_after(convert2_kernel<__half>, blocks, threads, 0, st, sa, reinterpret_cast<__half*>(grad_feats), na, sb,
+                   reinterpret_cast<__half*>(grad_depth), nb);
     if (cudaGetLastError() != cudaSuccess) return FBEV_ERR_LAUNCH;
   }
   return FBEV_OK;

@@ -26,6 +26,8 @@ namespace fbev {
 
 // Exclusive prefix sum of count[0, n) in place; count[n] receives the total.  One block.
 __global__ void __launch_bounds__(1024) tex_scan_kernel(unsigned* __restrict__ count, unsigned n) {
+  grid_dependency_wait();
+  grid_dependency_trigger();
   __shared__ unsigned part[1024];
   const unsigned tid = threadIdx.x, nt = blockDim.x;
   const unsigned per = (n + nt - 1) / nt;
@@ -57,6 +59,8 @@ constexpr unsigned kScanInBlock = 8192;  // texels up to which every scatter blo
 template <bool SCAN>
 __global__ void __launch_bounds__(256) ent_scatter_kernel(const Dev p, unsigned texels, unsigned* __restrict__ total_out) {
   extern __shared__ unsigned s_start[];
+  grid_dependency_wait();     // the emitting kernel (or the scan) has finished
+  grid_dependency_trigger();  // the gather kernel's blocks may move in as this kernel's leave
   const unsigned* start = p.tex_count;
   if (SCAN) {
     __shared__ unsigned part[256];
@@ -103,6 +107,8 @@ __global__ void __launch_bounds__(128, (PDEPTH || GF32) ? 3 : 4)
   constexpr int U = V == 4 ? 2 : 4;            // entries in flight per lane
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const int g = lane / p.GL, lg = lane - g * p.GL;
+  grid_dependency_wait();
+  grid_dependency_trigger();
   if (g >= p.CPW) return;
   const unsigned n = *n_entries;
   const unsigned cpt = (unsigned)(p.GL * V);
