@@ -28,6 +28,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "fbev.h"
 #include "fbev_device.cuh"
 #include "fbev_lists.cuh"
@@ -204,6 +206,36 @@ static int sm_count() {
   return cached[dev];
 }
 
+// Resident blocks per SM of a kernel at a block size and dynamic shared memory size; the runtime's answer is
+// remembered (per device: the library is sm_100a only, but the query needs a current device), because asking costs
+// about as much as a launch and every launch asks.
+static int resident_blocks(const void* kernel, int threads, size_t smem) {
+  struct Entry {
+    const void* kernel;
+    int threads, dev, per_sm;
+    size_t smem;
+  };
+  static Entry cache[64];
+  static int used = 0;
+  static std::mutex lock;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  {
+    std::lock_guard<std::mutex> g(lock);
+    for (int i = 0; i < used; ++i)
+      if (cache[i].kernel == kernel && cache[i].threads == threads && cache[i].smem == smem && cache[i].dev == dev)
+        return cache[i].per_sm;
+  }
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem) != cudaSuccess || per_sm <= 0) {
+    cudaGetLastError();
+    per_sm = 1;
+  }
+  std::lock_guard<std::mutex> g(lock);
+  if (used < 64) cache[used++] = Entry{kernel, threads, dev, per_sm, smem};
+  return per_sm;
+}
+
 // One resident wave when the blocks can draw tiles from the scheduler word or stride over the work themselves
 // (static_units), else one block per tile.  static_units is decided here, where the wave is known.
 template <typename K>
@@ -219,12 +251,7 @@ static int launch(K kernel, const Plan& pl, Dev d, cudaStream_t st, int groups_p
   int blocks = pl.blocks;
   if (d.sched != nullptr || groups_per_tile > 0) {
     // one resident wave
-    int per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, pl.warps * 32, pl.smem) != cudaSuccess ||
-        per_sm <= 0) {
-      cudaGetLastError();
-      per_sm = 1;
-    }
+    const int per_sm = resident_blocks(reinterpret_cast<const void*>(kernel), pl.warps * 32, pl.smem);
     const long long wave = (long long)per_sm * sm_count();
     // forward: a single sample with at most three units of work per resident warp takes the barrier-free
     // static order (measured ahead there, behind the counter on larger problems)

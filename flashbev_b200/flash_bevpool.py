@@ -127,7 +127,26 @@ def workspace(device: torch.device, stream_ptr: int) -> torch.Tensor:
 def _on(t: torch.Tensor, device: torch.device, dtype: torch.dtype) -> torch.Tensor:
     if t.device != device or t.dtype != dtype:
         t = t.to(device=device, dtype=dtype)
-    return t.contiguous()
+    return t if t.is_contiguous() else t.contiguous()
+
+
+class _on_device:
+    """Device guard that costs nothing when ``device`` is already current (the usual case; the library
+    launches on the current device, so a call for another device must switch)."""
+
+    __slots__ = ("guard",)
+
+    def __init__(self, device: torch.device):
+        idx = device.index
+        self.guard = None if idx is None or idx == torch.cuda.current_device() else torch.cuda.device(device)
+
+    def __enter__(self):
+        if self.guard is not None:
+            self.guard.__enter__()
+
+    def __exit__(self, *exc):
+        if self.guard is not None:
+            self.guard.__exit__(*exc)
 
 
 def make_problem(depth_params, image_feats, projection_matrices, feature_size, image_size, roi_range, grid_size,
@@ -172,8 +191,7 @@ def make_problem(depth_params, image_feats, projection_matrices, feature_size, i
     p.image_feats, p.depth, p.projection = feats.data_ptr(), depth.data_ptr(), proj.data_ptr()
     p.feature_size, p.image_size, p.roi_range = fsize.data_ptr(), isize.data_ptr(), roi.data_ptr()
     p.status = status_word(dev).data_ptr()
-    with torch.cuda.device(dev):
-        p.workspace = workspace(dev, torch.cuda.current_stream().cuda_stream).data_ptr()
+    p.workspace = workspace(dev, torch.cuda.current_stream(dev).cuda_stream).data_ptr()
     return p, (feats, depth, proj, fsize, isize, roi)
 
 
@@ -201,6 +219,35 @@ def _check_out(out, shape, dtype, device, partial, needs_grad):
     return out
 
 
+def _forward(depth_params, image_feats, projection_matrices, feature_size, image_size, roi_range, grid_size, spec,
+             epsilon, depth_weight_threshold, needs_grad):
+    """One forward launch; returns (out, problem, kept tensors)."""
+    p, keep = make_problem(depth_params, image_feats, projection_matrices, feature_size, image_size,
+                           roi_range, grid_size, spec, epsilon, depth_weight_threshold)
+    feats = keep[0]
+    dev = feats.device
+    shape = (p.B, p.Y, p.X, p.C)
+    partial = (p.y_begin, p.y_end) != (0, p.Y)
+    if spec.out is not None:
+        out = _check_out(spec.out, shape, _out_dtype(spec, feats), dev, partial, needs_grad)
+    else:
+        out = (torch.zeros if partial else torch.empty)(shape, dtype=_out_dtype(spec, feats), device=dev)
+    lib = _lib.load()
+    with _on_device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        if spec.out is not None and not out.is_cuda and spec.host_row_chunks > 0:
+            # bands of rows: the copy engine moves one band to the host while the next is computed
+            staging = torch.empty(shape, dtype=out.dtype, device=dev)
+            rc = lib.fbev_forward_to_host(ctypes.byref(p), staging.data_ptr(), out.data_ptr(), spec.host_row_chunks,
+                                          stream)
+            _lib.check(rc, "fbev_forward_to_host")
+        else:
+            rc = lib.fbev_forward(ctypes.byref(p), out.data_ptr(), None, stream)
+            if rc:
+                _lib.check(rc, "fbev_forward")
+    return out, p, keep
+
+
 class FlashBEVPool(torch.autograd.Function):
     """Fused BEV pooling: projection, depth weight, bilinear sampling and the reduction over
     cameras and height bins in one kernel; see the module docstring for the contract."""
@@ -210,29 +257,12 @@ class FlashBEVPool(torch.autograd.Function):
                 grid_size, depth_distribution=0, use_shared_memory=True, optimize_z_precompute=True,
                 use_warp_kernel=False, use_vectorized_load=False, epsilon=1e-6, depth_weight_threshold=1e-6):
         spec = depth_distribution if isinstance(depth_distribution, DepthSpec) else DepthSpec(depth_distribution)
-        p, keep = make_problem(depth_params, image_feats, projection_matrices, feature_size, image_size,
-                               roi_range, grid_size, spec, epsilon, depth_weight_threshold)
-        feats = keep[0]
-        shape = (p.B, p.Y, p.X, p.C)
-        partial = (p.y_begin, p.y_end) != (0, p.Y)
-        if spec.out is not None:
-            out = _check_out(spec.out, shape, _out_dtype(spec, feats), feats.device, partial,
-                             any(t.requires_grad for t in (depth_params, image_feats)))
-        else:
-            out = (torch.zeros if partial else torch.empty)(shape, dtype=_out_dtype(spec, feats), device=feats.device)
-        with torch.cuda.device(feats.device):
-            stream = torch.cuda.current_stream().cuda_stream
-            if spec.out is not None and not out.is_cuda and spec.host_row_chunks > 0:
-                # bands of rows: the copy engine moves one band to the host while the next is computed
-                staging = torch.empty(shape, dtype=out.dtype, device=feats.device)
-                rc = _lib.load().fbev_forward_to_host(ctypes.byref(p), staging.data_ptr(), out.data_ptr(),
-                                                      spec.host_row_chunks, stream)
-                _lib.check(rc, "fbev_forward_to_host")
-            else:
-                rc = _lib.load().fbev_forward(ctypes.byref(p), out.data_ptr(), None, stream)
-                _lib.check(rc, "fbev_forward")
+        out, p, keep = _forward(depth_params, image_feats, projection_matrices, feature_size, image_size, roi_range,
+                                grid_size, spec, epsilon, depth_weight_threshold,
+                                depth_params.requires_grad or image_feats.requires_grad)
         ctx.save_for_backward(*keep)
         ctx.spec = spec
+        ctx.problem = p  # the backward launches on the same tensors: same struct, as long as their addresses hold
         ctx.grid = (p.X, p.Y, p.Z)
         ctx.epsilon = float(epsilon)
         ctx.depth_weight_threshold = float(depth_weight_threshold)
@@ -243,9 +273,14 @@ class FlashBEVPool(torch.autograd.Function):
     def backward(ctx, out_grad):
         feats, depth, proj, fsize, isize, roi = ctx.saved_tensors
         spec = ctx.spec
-        grid = torch.tensor(ctx.grid, dtype=torch.int32)  # host tensor: no synchronisation
-        p, keep = make_problem(depth, feats, proj, fsize, isize, roi, grid, spec, ctx.epsilon,
-                               ctx.depth_weight_threshold)
+        p = ctx.problem
+        if (p.image_feats, p.depth, p.projection) != (feats.data_ptr(), depth.data_ptr(), proj.data_ptr()):
+            # the saved tensors came back at other addresses (a saved-tensor hook moved them): describe them anew
+            grid = torch.tensor(ctx.grid, dtype=torch.int32)  # host tensor: no synchronisation
+            p, _ = make_problem(depth, feats, proj, fsize, isize, roi, grid, spec, ctx.epsilon,
+                                ctx.depth_weight_threshold)
+        else:
+            p.workspace = workspace(feats.device, torch.cuda.current_stream(feats.device).cuda_stream).data_ptr()
         flags = 0
         if ctx.needs_input_grad[1]:
             flags |= _lib.BWD_FEATS
@@ -263,16 +298,14 @@ class FlashBEVPool(torch.autograd.Function):
                 grad_depth = torch.empty_like(depth)
             nbytes = lib.fbev_backward_scratch_bytes(ctypes.byref(p), flags)
             scratch = torch.empty(nbytes, dtype=torch.uint8, device=feats.device) if nbytes else None
-            with torch.cuda.device(feats.device):
-                stream = torch.cuda.current_stream().cuda_stream
+            with _on_device(feats.device):
+                stream = torch.cuda.current_stream(feats.device).cuda_stream
                 rc = lib.fbev_backward(
                     ctypes.byref(p), go.data_ptr(),
                     grad_feats.data_ptr() if grad_feats is not None else None,
                     grad_depth.data_ptr() if grad_depth is not None else None,
                     scratch.data_ptr() if scratch is not None else None, nbytes, flags, stream)
             _lib.check(rc, "fbev_backward")
-            if scratch is not None:
-                scratch.record_stream(torch.cuda.current_stream(feats.device))
             if grad_depth is not None and grad_depth.dtype != ctx.in_dtypes[0]:
                 grad_depth = grad_depth.to(ctx.in_dtypes[0])
             if grad_feats is not None and grad_feats.dtype != ctx.in_dtypes[1]:
@@ -312,6 +345,9 @@ def flash_bevpool(image_feats, depth_params, projection_matrices, feature_size, 
     spec = DepthSpec(depth_distribution, pool=pool, depth_bin_range=depth_bin_range,
                      legacy_depth_grad=legacy_depth_grad, y_range=y_range, out_dtype=out_dtype, out=out,
                      host_row_chunks=host_row_chunks)
+    if not (torch.is_grad_enabled() and (image_feats.requires_grad or depth_params.requires_grad)):
+        return _forward(depth_params, image_feats, projection_matrices, feature_size, image_size, roi_range, grid_size,
+                        spec, epsilon, depth_weight_threshold, False)[0]
     return FlashBEVPool.apply(depth_params, image_feats, projection_matrices, feature_size, image_size, roi_range,
                               grid_size, spec, use_shared_memory, optimize_z_precompute, use_warp_kernel,
                               use_vectorized_load, epsilon, depth_weight_threshold)
