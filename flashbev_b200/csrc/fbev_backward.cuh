@@ -120,7 +120,6 @@ __device__ __forceinline__ bool emit_entries(const Dev& p, const uint4* rec, int
 template <typename T, int V, bool EMIT>
 __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_feats_kernel(const __grid_constant__ Dev p) {
   constexpr int E = Chunk<T>::E;
-  grid_dependency_trigger();  // the kernel after this one may bring its blocks in as ours leave
   extern __shared__ __align__(16) unsigned char smem[];
   const BlockHeader h = carve(smem, p.N);
   __shared__ int s_tile[2];
@@ -144,13 +143,13 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_feats_kernel(const __gr
   const bool mean_pool = p.pool == FBEV_POOL_MEAN;
   int loaded_b = -1;
   UnitLoop sched;
-  sched.begin(p, s_tile, ngroups, warp, nwarps);
+  sched.begin(p, s_tile, warp, nwarps);
   if (sched.stat) {  // the sample's matrices, once, by the whole block
     const Tile tt = tile_of(p, 0);
     (void)tile_visibility(p, tt, h, vs, vmin, image_h, image_w, loaded_b);
   }
   int g_first = 0, g_step = 1;
-  for (int tile; (tile = sched.current(p, g_first, g_step)) >= 0; sched.advance()) {
+  for (int tile; (tile = sched.current(p, ngroups, warp, nwarps, g_first, g_step)) >= 0; sched.advance(nwarps)) {
     const Tile t = tile_of(p, tile);
     const unsigned vis = tile_visibility(p, t, h, vs, vmin, image_h, image_w, loaded_b);
     const int nvis = __popc(vis);
@@ -224,6 +223,9 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_feats_kernel(const __gr
     }
   }  // tiles
   sched.end(p);
+  // from here on the next kernel's blocks may move in (they wait for this whole grid before touching its output);
+  // triggering at the start instead lets them sit on the SMs for the whole run, which cost 25 % on large maps
+  grid_dependency_trigger();
 }
 
 // ---------------------------------------------------------------------------
@@ -543,7 +545,6 @@ __host__ __device__ inline size_t depth_warp_bytes(int CPW, int cap) {
 template <typename T, int V, bool EMIT>
 __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_depth_kernel(const __grid_constant__ Dev p) {
   constexpr int E = Chunk<T>::E;
-  grid_dependency_trigger();  // the kernel after this one may bring its blocks in as ours leave
   extern __shared__ __align__(16) unsigned char smem[];
   const BlockHeader h = carve(smem, p.N);
   __shared__ int s_tile[2];
@@ -575,13 +576,13 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_depth_kernel(const __gr
   const bool merge_bins = p.CPW >= 4;
   int loaded_b = -1;
   UnitLoop sched;
-  sched.begin(p, s_tile, ngroups, warp, nwarps);
+  sched.begin(p, s_tile, warp, nwarps);
   if (sched.stat) {  // the sample's matrices, once, by the whole block
     const Tile tt = tile_of(p, 0);
     (void)tile_visibility(p, tt, h, vs, vmin, image_h, image_w, loaded_b);
   }
   int g_first = 0, g_step = 1;
-  for (int tile; (tile = sched.current(p, g_first, g_step)) >= 0; sched.advance()) {
+  for (int tile; (tile = sched.current(p, ngroups, warp, nwarps, g_first, g_step)) >= 0; sched.advance(nwarps)) {
     const Tile t = tile_of(p, tile);
     const unsigned vis = tile_visibility(p, t, h, vs, vmin, image_h, image_w, loaded_b);
     const int ncand = __popc(vis) * p.Z;
@@ -834,6 +835,9 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_depth_kernel(const __gr
     }
   }  // tiles
   sched.end(p);
+  // from here on the next kernel's blocks may move in (they wait for this whole grid before touching its output);
+  // triggering at the start instead lets them sit on the SMs for the whole run, which cost 25 % on large maps
+  grid_dependency_trigger();
 }
 
 // Gradient kernel.  Same decomposition as the forward.  For every accepted sample

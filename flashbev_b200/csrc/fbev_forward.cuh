@@ -36,13 +36,13 @@ __global__ void __launch_bounds__(kMaxWarps * 32, MINB) fwd_kernel(const __grid_
   const uint4* fl = reinterpret_cast<const uint4*>(p.feats) + lg;  // this lane's chunk of texel 0
   int loaded_b = -1;
   UnitLoop sched;  // counter of tiles with a barrier per tile, or the barrier-free static order of units
-  sched.begin(p, s_tile, ngroups, warp, nwarps);
+  sched.begin(p, s_tile, warp, nwarps);
   if (sched.stat) {  // the sample's matrices, once, by the whole block
     const Tile tt = tile_of(p, 0);
     (void)tile_visibility(p, tt, h, vs, vmin, image_h, image_w, loaded_b);
   }
   int g_first = 0, g_step = 1;
-  for (int tile; (tile = sched.current(p, g_first, g_step)) >= 0; sched.advance()) {
+  for (int tile; (tile = sched.current(p, ngroups, warp, nwarps, g_first, g_step)) >= 0; sched.advance(nwarps)) {
     const Tile t = tile_of(p, tile);
     const unsigned vis = tile_visibility(p, t, h, vs, vmin, image_h, image_w, loaded_b);
     const int nvis = __popc(vis);

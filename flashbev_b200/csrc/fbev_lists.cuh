@@ -121,21 +121,17 @@ struct TileLoop {
 struct UnitLoop {
   TileLoop loop;
   bool stat;
-  int unit, units, W, ngroups, nwarps, warp;
+  int unit;  // static order: this warp's current unit
 
-  __device__ __forceinline__ void begin(const Dev& p, int* shared_slot, int ngroups_, int warp_, int nwarps_) {
+  __device__ __forceinline__ void begin(const Dev& p, int* shared_slot, int warp, int nwarps) {
     stat = p.static_units != 0;
-    ngroups = ngroups_;
-    warp = warp_;
-    nwarps = nwarps_;
-    units = p.tiles_x * p.tiles_y * p.B * ngroups;
-    W = gridDim.x * nwarps;
     unit = blockIdx.x * nwarps + warp;
     if (!stat) loop.begin(p, shared_slot);
   }
-  __device__ __forceinline__ int current(const Dev& p, int& g_first, int& g_step) {
+  // tile of this visit, or -1 when done; the caller handles groups g_first, g_first + g_step, ... of it
+  __device__ __forceinline__ int current(const Dev& p, int ngroups, int warp, int nwarps, int& g_first, int& g_step) {
     if (stat) {
-      if (unit >= units) return -1;
+      if (unit >= p.tiles_x * p.tiles_y * p.B * ngroups) return -1;
       const int tile = unit / ngroups;
       g_first = unit - tile * ngroups;
       g_step = ngroups;  // one group per visit
@@ -145,9 +141,9 @@ struct UnitLoop {
     g_step = nwarps;
     return loop.current(p);
   }
-  __device__ __forceinline__ void advance() {
+  __device__ __forceinline__ void advance(int nwarps) {
     if (stat) {
-      unit += W;
+      unit += gridDim.x * nwarps;
     } else {
       loop.advance();
     }

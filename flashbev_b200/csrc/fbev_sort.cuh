@@ -27,7 +27,6 @@ namespace fbev {
 // Exclusive prefix sum of count[0, n) in place; count[n] receives the total.  One block.
 __global__ void __launch_bounds__(1024) tex_scan_kernel(unsigned* __restrict__ count, unsigned n) {
   grid_dependency_wait();
-  grid_dependency_trigger();
   __shared__ unsigned part[1024];
   const unsigned tid = threadIdx.x, nt = blockDim.x;
   const unsigned per = (n + nt - 1) / nt;
@@ -49,6 +48,7 @@ __global__ void __launch_bounds__(1024) tex_scan_kernel(unsigned* __restrict__ c
     run += c;
   }
   if (tid == nt - 1) count[n] = part[tid];
+  grid_dependency_trigger();
 }
 
 constexpr unsigned kScanInBlock = 8192;  // texels up to which every scatter block scans the counts itself
@@ -59,8 +59,7 @@ constexpr unsigned kScanInBlock = 8192;  // texels up to which every scatter blo
 template <bool SCAN>
 __global__ void __launch_bounds__(256) ent_scatter_kernel(const Dev p, unsigned texels, unsigned* __restrict__ total_out) {
   extern __shared__ unsigned s_start[];
-  grid_dependency_wait();     // the emitting kernel (or the scan) has finished
-  grid_dependency_trigger();  // the gather kernel's blocks may move in as this kernel's leave
+  grid_dependency_wait();  // the emitting kernel (or the scan) has finished
   const unsigned* start = p.tex_count;
   if (SCAN) {
     __shared__ unsigned part[256];
@@ -94,6 +93,7 @@ __global__ void __launch_bounds__(256) ent_scatter_kernel(const Dev p, unsigned 
     p.ent_sorted[dst] = e;
     if (p.ent_d != nullptr) p.ent_d_sorted[dst] = p.ent_d[i];
   }
+  grid_dependency_trigger();  // the gather kernel's blocks may move in as this kernel's leave
 }
 
 // GF32: the upstream gradient is float32 although the features are 16-bit.
@@ -108,8 +108,10 @@ __global__ void __launch_bounds__(128, (PDEPTH || GF32) ? 3 : 4)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const int g = lane / p.GL, lg = lane - g * p.GL;
   grid_dependency_wait();
-  grid_dependency_trigger();
-  if (g >= p.CPW) return;
+  if (g >= p.CPW) {
+    grid_dependency_trigger();
+    return;
+  }
   const unsigned n = *n_entries;
   const unsigned cpt = (unsigned)(p.GL * V);
   const unsigned groups = gridDim.x * nwarps * p.CPW;
@@ -220,6 +222,7 @@ __global__ void __launch_bounds__(128, (PDEPTH || GF32) ? 3 : 4)
     flush(cur, acc0, d0);
     if (any1) flush(cur + 1u, acc1, d1);
   }
+  grid_dependency_trigger();
 }
 
 }  // namespace fbev
