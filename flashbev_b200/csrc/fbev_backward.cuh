@@ -542,8 +542,9 @@ __host__ __device__ inline size_t depth_warp_bytes(int CPW, int cap) {
 
 // EMIT: the kernel also leaves the entries of the sorted feature gradient (emit_entries) from the same row
 // records, so that one list phase serves both gradients.
-template <typename T, int V, bool EMIT>
-__global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_depth_kernel(const __grid_constant__ Dev p) {
+// CAT: categorical depth (compile-time so that each of the two kernels below carries only its own sample pass).
+template <typename T, int V, bool EMIT, bool CAT>
+__device__ __forceinline__ void bwd_depth_body(const Dev& p) {
   constexpr int E = Chunk<T>::E;
   extern __shared__ __align__(16) unsigned char smem[];
   const BlockHeader h = carve(smem, p.N);
@@ -678,7 +679,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_depth_kernel(const __gr
           }
         }
         __syncwarp();
-        if (p.mode != FBEV_DEPTH_CATEGORICAL && by_record) {
+        if (!CAT && by_record) {
           // ---- parametric depth, per record: the samples of a run share their texels, so their (d mean,
           // d sigma) contributions are summed per record texel in shared memory first; the sums leave as the
           // depth part of the record's entries (summed per texel by feats_gather_kernel) or, without entry
@@ -789,7 +790,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_depth_kernel(const __gr
           float* d10 = d00 + sa.y;
           float* d01 = d00 + sa.z;
           float* d11 = d01 + sa.y;
-          if (p.mode == FBEV_DEPTH_CATEGORICAL && !merge_bins) {
+          if (CAT && !merge_bins) {
             if (active) {
               const int k = (int)sa.w;
               atomicAdd(d00 + k, v00);
@@ -797,7 +798,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_depth_kernel(const __gr
               atomicAdd(d10 + k, v10);
               atomicAdd(d11 + k, v11);
             }
-          } else if (p.mode == FBEV_DEPTH_CATEGORICAL) {
+          } else if (CAT) {
             const unsigned key = active ? sa.x + sa.w : 0xffffffffu - (unsigned)lane;  // element index of (texel, bin)
             const unsigned pkey = __shfl_up_sync(kFull, key, 1);
             const unsigned headm = __ballot_sync(kFull, active && (lane == 0 || pkey != key));
@@ -838,6 +839,18 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_depth_kernel(const __gr
   // from here on the next kernel's blocks may move in (they wait for this whole grid before touching its output);
   // triggering at the start instead lets them sit on the SMs for the whole run, which cost 25 % on large maps
   grid_dependency_trigger();
+}
+
+// The two depth-gradient kernels.  Categorical: 96 registers, five resident blocks per SM (no spills; measured 4 %
+// ahead of 80 registers / six blocks on the benchmark shape, 9 % on cfg4).  Parametric: 80 registers / six blocks,
+// which its shared-memory sample pass prefers (96 registers cost it 8 % on the benchmark shape).
+template <typename T, int V, bool EMIT>
+__global__ void __maxnreg__(96) bwd_depth_kernel(const __grid_constant__ Dev p) {
+  bwd_depth_body<T, V, EMIT, true>(p);
+}
+template <typename T, int V, bool EMIT>
+__global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_depth_param_kernel(const __grid_constant__ Dev p) {
+  bwd_depth_body<T, V, EMIT, false>(p);
 }
 
 // Gradient kernel.  Same decomposition as the forward.  For every accepted sample

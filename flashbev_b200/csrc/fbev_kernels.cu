@@ -403,9 +403,9 @@ static int backward_t(const Plan& pl, Dev d, const Plan& plf, const Dev& df, cud
       dd.flags = d.flags;
       int rc;
       switch (pld.V) {
-        case 1: rc = launch(bwd_depth_kernel<T, 1, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW); break;
-        case 2: rc = launch(bwd_depth_kernel<T, 2, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW); break;
-        default: rc = launch(bwd_depth_kernel<T, 4, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW); break;
+        case 1: rc = (dd.mode == FBEV_DEPTH_CATEGORICAL ? launch(bwd_depth_kernel<T, 1, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW) : launch(bwd_depth_param_kernel<T, 1, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW)); break;
+        case 2: rc = (dd.mode == FBEV_DEPTH_CATEGORICAL ? launch(bwd_depth_kernel<T, 2, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW) : launch(bwd_depth_param_kernel<T, 2, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW)); break;
+        default: rc = (dd.mode == FBEV_DEPTH_CATEGORICAL ? launch(bwd_depth_kernel<T, 4, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW) : launch(bwd_depth_param_kernel<T, 4, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW)); break;
       }
       return rc != FBEV_OK ? rc : sort_finish_t<T>(pld, dd, st);
     }
@@ -419,9 +419,9 @@ static int backward_t(const Plan& pl, Dev d, const Plan& plf, const Dev& df, cud
     dd.flags = d.flags;
     int rc;
     switch (pld.V) {
-      case 1: rc = launch(bwd_depth_kernel<T, 1, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW); break;
-      case 2: rc = launch(bwd_depth_kernel<T, 2, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW); break;
-      default: rc = launch(bwd_depth_kernel<T, 4, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW); break;
+      case 1: rc = (dd.mode == FBEV_DEPTH_CATEGORICAL ? launch(bwd_depth_kernel<T, 1, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW) : launch(bwd_depth_param_kernel<T, 1, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW)); break;
+      case 2: rc = (dd.mode == FBEV_DEPTH_CATEGORICAL ? launch(bwd_depth_kernel<T, 2, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW) : launch(bwd_depth_param_kernel<T, 2, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW)); break;
+      default: rc = (dd.mode == FBEV_DEPTH_CATEGORICAL ? launch(bwd_depth_kernel<T, 4, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW) : launch(bwd_depth_param_kernel<T, 4, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW)); break;
     }
     return rc != FBEV_OK ? rc : sort_finish_t<T>(pld, dd, st);
   }
@@ -429,9 +429,9 @@ static int backward_t(const Plan& pl, Dev d, const Plan& plf, const Dev& df, cud
     // depth gradient alone: per-texel dot products on the forward's row records
     dd.flags = d.flags;
     switch (pld.V) {
-      case 1: return launch(bwd_depth_kernel<T, 1, false>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW);
-      case 2: return launch(bwd_depth_kernel<T, 2, false>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW);
-      default: return launch(bwd_depth_kernel<T, 4, false>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW);
+      case 1: return (dd.mode == FBEV_DEPTH_CATEGORICAL ? launch(bwd_depth_kernel<T, 1, false>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW) : launch(bwd_depth_param_kernel<T, 1, false>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW));
+      case 2: return (dd.mode == FBEV_DEPTH_CATEGORICAL ? launch(bwd_depth_kernel<T, 2, false>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW) : launch(bwd_depth_param_kernel<T, 2, false>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW));
+      default: return (dd.mode == FBEV_DEPTH_CATEGORICAL ? launch(bwd_depth_kernel<T, 4, false>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW) : launch(bwd_depth_param_kernel<T, 4, false>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW));
     }
   }
   switch (pl.V) {
