@@ -62,26 +62,35 @@ __global__ void __launch_bounds__(256) ent_scatter_kernel(const Dev p, unsigned 
   grid_dependency_wait();  // the emitting kernel (or the scan) has finished
   const unsigned* start = p.tex_count;
   if (SCAN) {
-    __shared__ unsigned part[256];
-    const unsigned tid = threadIdx.x;
+    // block-wide exclusive scan: a contiguous slice per thread, shuffles inside a warp, the eight warp totals
+    // through shared memory (two barriers)
+    __shared__ unsigned warp_total[8];
+    const unsigned tid = threadIdx.x, lane = tid & 31u, wid = tid >> 5;
     const unsigned per = (texels + 255u) / 256u;
     const unsigned lo = min(tid * per, texels), hi = min(lo + per, texels);
     unsigned sum = 0;
     for (unsigned i = lo; i < hi; ++i) sum += __ldg(p.tex_count + i);
-    part[tid] = sum;
-    __syncthreads();
-    for (unsigned d = 1; d < 256u; d <<= 1) {
-      const unsigned v = tid >= d ? part[tid - d] : 0u;
-      __syncthreads();
-      part[tid] += v;
-      __syncthreads();
+    unsigned incl = sum;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const unsigned v = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= (unsigned)d) incl += v;
     }
-    unsigned run = part[tid] - sum;
+    if (lane == 31u) warp_total[wid] = incl;
+    __syncthreads();
+    unsigned before = 0, all = 0;
+#pragma unroll
+    for (unsigned k = 0; k < 8u; ++k) {
+      const unsigned wt = warp_total[k];
+      before += k < wid ? wt : 0u;
+      all += wt;
+    }
+    unsigned run = before + incl - sum;
     for (unsigned i = lo; i < hi; ++i) {
       s_start[i] = run;
       run += __ldg(p.tex_count + i);
     }
-    if (blockIdx.x == 0 && tid == 255u) *total_out = part[255];
+    if (blockIdx.x == 0 && tid == 0u) *total_out = all;
     __syncthreads();
     start = s_start;
   }
