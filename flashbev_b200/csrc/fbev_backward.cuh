@@ -701,7 +701,54 @@ __device__ __forceinline__ void bwd_depth_body(const Dev& p) {
             }
           }
           __syncwarp();
-          for (int which = 0; which < 2; ++which) {  // 0: d mean, 1: d sigma
+          if (emitted) {
+            // the records' texel fields went into the entries already, so all four words of a record can hold
+            // sums: d mean / d sigma of u0, d mean / d sigma of u1 -- one walk over the samples instead of two.
+            // Which of my records have a second texel is remembered in a register first.
+            unsigned two_bits = 0;
+            for (int i = lg, k = 0; i < n; i += p.GL, ++k) two_bits |= (rec[i].y != 0u ? 1u : 0u) << k;
+            __syncwarp();
+            for (int c = 0; c < p.CPW; ++c) {
+              uint4* rc = recs + (size_t)c * rstride;
+              const int nr = sLen[c];
+              for (int i = lane; i < nr; i += 32) rc[i] = make_uint4(0u, 0u, 0u, 0u);
+            }
+            __syncwarp();
+            for (int c = 0; c < p.CPW; ++c) {
+              const int ns = sSmp[c];
+              uint4* rc = recs + (size_t)c * rstride;
+              for (int idx = lane; idx < ns; idx += 32) {
+                const uint4* sr = samp + ((size_t)c * p.cap + idx) * 3;
+                const uint4 sw = sr[0], sp = sr[2];
+                const float sd = __uint_as_float(sr[1].x);
+                const float vm = sd * (legacy ? __uint_as_float(sp.y) : __uint_as_float(sp.z));
+                const float vs2 = sd * (legacy ? __uint_as_float(sp.y) : __uint_as_float(sp.w));
+                float* a = reinterpret_cast<float*>(rc + (sp.x & 0xffffu));
+                float* b = reinterpret_cast<float*>(rc + (sp.x >> 16));
+                const float w00 = __uint_as_float(sw.x), w01 = __uint_as_float(sw.y), w10 = __uint_as_float(sw.z),
+                            w11 = __uint_as_float(sw.w);
+                atomicAdd(a + 0, vm * w00);   // (v0, u0)
+                atomicAdd(a + 1, vs2 * w00);
+                atomicAdd(a + 2, vm * w10);   // (v0, u1)
+                atomicAdd(a + 3, vs2 * w10);
+                atomicAdd(b + 0, vm * w01);   // (v1, u0)
+                atomicAdd(b + 1, vs2 * w01);
+                atomicAdd(b + 2, vm * w11);   // (v1, u1)
+                atomicAdd(b + 3, vs2 * w11);
+              }
+            }
+            __syncwarp();
+            for (int i = lg, k = 0; i < n; i += p.GL, ++k) {
+              const uint4 r = rec[i];
+              const float m0 = __uint_as_float(r.x), s0 = __uint_as_float(r.y), m1 = __uint_as_float(r.z),
+                          s1 = __uint_as_float(r.w);
+              const bool two = (two_bits >> k) & 1u;
+              p.ent_d[first_slot + (unsigned)i] = two ? make_float4(m0, s0, m1, s1) : make_float4(m0 + m1, s0 + s1, 0.0f, 0.0f);
+            }
+            __syncwarp();
+            continue;
+          }
+          for (int which = 0; which < 2; ++which) {  // 0: d mean, 1: d sigma (no entry slots: one atomic per record texel)
             for (int c = 0; c < p.CPW; ++c) {
               uint4* rc = recs + (size_t)c * rstride;
               const int nr = sLen[c];
