@@ -17,15 +17,19 @@ BWD_FEATS, BWD_DEPTH, BWD_LEGACY_DEPTH = 1, 2, 4
 DEV_BAD_FEATURE_SIZE = 1
 WORKSPACE_BYTES = 16
 STATIC_SCRATCH_BYTES = 16 << 20
+SORT_BUDGET_BYTES = 256 << 20
 ERR_STATIC_LIMIT = 11
 
-# every symbol include/fbev.h declares
+# every symbol include/fbev.h declares (the operator) ...
 EXPORTS = (
     "fbev_forward", "fbev_forward_to_host", "fbev_forward_peers", "fbev_backward", "fbev_backward_scratch_bytes", "fbev_backward_min_scratch_bytes", "fbev_backward_static_scratch",
     "fbev_debug_indices",
-    "fbev_flash_bevpool", "fbev_flash_bevpool_grad", "fbev_projection_matrices", "fbev_set_tuning", "fbev_probe_read",
-    "fbev_strerror", "fbev_version",
+    "fbev_flash_bevpool", "fbev_flash_bevpool_grad", "fbev_projection_matrices",
+    "fbev_strerror", "fbev_version", "fbev_source_hash",
 )
+# ... and include/fbev_debug.h (experiment and test helpers)
+DEBUG_EXPORTS = ("fbev_set_tuning", "fbev_set_experiment", "fbev_probe_read")
+EXP_PREFETCH, EXP_GROUP_CULL, EXP_DRAW = 1, 2, 4
 
 
 class FbevProblem(ctypes.Structure):
@@ -68,16 +72,23 @@ _lib = None
 
 
 def load(build_if_missing: bool = True) -> ctypes.CDLL:
-    """Loads libfbev.so, compiling it first when it is missing and nvcc is available."""
+    """Loads libfbev.so, compiling it first when it is missing or was built from other sources than the ones
+    beside it (compared by content hash) and nvcc is available.  A library whose embedded hash does not match
+    the sources is refused: kernels of another version never run silently."""
     global _lib
     if _lib is not None:
         return _lib
     path = _build.LIB_PATH
-    if not os.path.exists(path):
+    if _build.is_stale():
         if not build_if_missing:
-            raise ImportError(f"{path} is missing; build it with `python -m flashbev_b200.build`")
+            raise ImportError(f"{path} is missing or stale; build it with `python -m flashbev_b200.build`")
         _build.build()
     lib = ctypes.CDLL(path)
+    lib.fbev_source_hash.restype = ctypes.c_char_p
+    built_from = lib.fbev_source_hash().decode()
+    if built_from != _build.source_hash():
+        raise ImportError(f"{path} was built from other sources (hash {built_from[:12]}...) than the ones in "
+                          f"{_build.CSRC}; rebuild it with `python -m flashbev_b200.build --force`")
     vp, i32, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
     lib.fbev_forward.argtypes = [ctypes.POINTER(FbevProblem), vp, vp, vp]
     lib.fbev_forward.restype = i32
@@ -103,6 +114,8 @@ def load(build_if_missing: bool = True) -> ctypes.CDLL:
     lib.fbev_projection_matrices.restype = i32
     lib.fbev_set_tuning.argtypes = [i32] * 5
     lib.fbev_set_tuning.restype = None
+    lib.fbev_set_experiment.argtypes = [i32]
+    lib.fbev_set_experiment.restype = None
     lib.fbev_probe_read.argtypes = [vp, ctypes.c_size_t, i32, vp, vp]
     lib.fbev_probe_read.restype = i32
     lib.fbev_strerror.argtypes = [i32]

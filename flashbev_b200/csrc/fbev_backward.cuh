@@ -149,7 +149,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_feats_kernel(const __gr
     (void)tile_visibility(p, tt, h, vs, vmin, image_h, image_w, loaded_b);
   }
   int g_first = 0, g_step = 1;
-  for (int tile; (tile = sched.current(p, ngroups, warp, nwarps, g_first, g_step)) >= 0; sched.advance(nwarps)) {
+  for (int tile; (tile = sched.current(p, ngroups, warp, nwarps, g_first, g_step)) >= 0; sched.advance(p, nwarps)) {
     const Tile t = tile_of(p, tile);
     const unsigned vis = tile_visibility(p, t, h, vs, vmin, image_h, image_w, loaded_b);
     const int nvis = __popc(vis);
@@ -222,7 +222,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_feats_kernel(const __gr
       __syncwarp();
     }
   }  // tiles
-  sched.end(p);
+  sched.end(p, nwarps);
   // from here on the next kernel's blocks may move in (they wait for this whole grid before touching its output);
   // triggering at the start instead lets them sit on the SMs for the whole run, which cost 25 % on large maps
   grid_dependency_trigger();
@@ -583,7 +583,7 @@ __device__ __forceinline__ void bwd_depth_body(const Dev& p) {
     (void)tile_visibility(p, tt, h, vs, vmin, image_h, image_w, loaded_b);
   }
   int g_first = 0, g_step = 1;
-  for (int tile; (tile = sched.current(p, ngroups, warp, nwarps, g_first, g_step)) >= 0; sched.advance(nwarps)) {
+  for (int tile; (tile = sched.current(p, ngroups, warp, nwarps, g_first, g_step)) >= 0; sched.advance(p, nwarps)) {
     const Tile t = tile_of(p, tile);
     const unsigned vis = tile_visibility(p, t, h, vs, vmin, image_h, image_w, loaded_b);
     const int ncand = __popc(vis) * p.Z;
@@ -882,7 +882,7 @@ __device__ __forceinline__ void bwd_depth_body(const Dev& p) {
       __syncwarp();
     }
   }  // tiles
-  sched.end(p);
+  sched.end(p, nwarps);
   // from here on the next kernel's blocks may move in (they wait for this whole grid before touching its output);
   // triggering at the start instead lets them sit on the SMs for the whole run, which cost 25 % on large maps
   grid_dependency_trigger();

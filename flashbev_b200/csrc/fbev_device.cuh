@@ -15,6 +15,7 @@
 #include <stdint.h>
 
 #include "fbev.h"
+#include "fbev_debug.h"
 
 namespace fbev {
 
@@ -41,12 +42,14 @@ struct Dev {
   float vs[3], vmin[3];
   int TX, TY, tiles_x, tiles_y;
   int GL;     // lanes that share one cell (each owns V 16-byte channel chunks)
+  int cpt;    // 16-byte chunks per texel (GL * V) in the chunked kernels, 0 in the scalar ones
   int CPW;    // cells a warp works on at once = 32 / GL
   int cap;    // sample records per cell per pass
   int flags;  // FBEV_BWD_*
   int out_f32;        // output / upstream gradient are float32 although the features are 16-bit
   unsigned* sched;    // tile scheduler words {next tile, blocks done}, or null for one tile per block
   int static_units;   // forward, one sample: warps stride over (tile, group) units, no barrier, no atomic
+  int exp;            // experiment bits (fbev_debug.h: fbev_set_experiment); 0 in normal use
   // gradients through a global sort by texel (null / 0 when not in use)
   unsigned* tex_count;   // [texels + 1] entries per texel; after the scan: start of the texel's segment, total last
   unsigned* ent_count;   // [1] entries emitted so far

@@ -11,7 +11,9 @@
 
 namespace fbev {
 
-template <typename T, int V, int MINB>
+// EXPERIMENTS: the instantiation that honours the switches of fbev_set_experiment (Dev.exp); the ordinary one
+// carries none of their code.
+template <typename T, int V, int MINB, bool EXPERIMENTS = false>
 __global__ void __launch_bounds__(kMaxWarps * 32, MINB) fwd_kernel(const __grid_constant__ Dev p) {
   constexpr int E = Chunk<T>::E;
   extern __shared__ __align__(16) unsigned char smem[];
@@ -35,6 +37,17 @@ __global__ void __launch_bounds__(kMaxWarps * 32, MINB) fwd_kernel(const __grid_
   const int ngroups = (tile_cells + p.CPW - 1) / p.CPW;
   const uint4* fl = reinterpret_cast<const uint4*>(p.feats) + lg;  // this lane's chunk of texel 0
   int loaded_b = -1;
+  if (EXPERIMENTS && (p.exp & FBEV_EXP_PREFETCH)) {
+    // one 128-byte line per thread of the feature and depth tensors, the whole grid covering both once
+    const size_t tex = (size_t)p.B * p.N * p.H * p.W;
+    const size_t lf = (tex * p.C * sizeof(T) + 127) / 128, ld = (tex * p.D * sizeof(T) + 127) / 128;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < lf + ld; i += stride) {
+      const unsigned char* a = i < lf ? reinterpret_cast<const unsigned char*>(p.feats) + i * 128
+                                      : reinterpret_cast<const unsigned char*>(p.depth) + (i - lf) * 128;
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
+    }
+  }
   UnitLoop sched;  // counter of tiles with a barrier per tile, or the barrier-free static order of units
   sched.begin(p, s_tile, warp, nwarps);
   if (sched.stat) {  // the sample's matrices, once, by the whole block
@@ -42,11 +55,9 @@ __global__ void __launch_bounds__(kMaxWarps * 32, MINB) fwd_kernel(const __grid_
     (void)tile_visibility(p, tt, h, vs, vmin, image_h, image_w, loaded_b);
   }
   int g_first = 0, g_step = 1;
-  for (int tile; (tile = sched.current(p, ngroups, warp, nwarps, g_first, g_step)) >= 0; sched.advance(nwarps)) {
+  for (int tile; (tile = sched.current(p, ngroups, warp, nwarps, g_first, g_step)) >= 0; sched.advance(p, nwarps)) {
     const Tile t = tile_of(p, tile);
-    const unsigned vis = tile_visibility(p, t, h, vs, vmin, image_h, image_w, loaded_b);
-    const int nvis = __popc(vis);
-    const int ncand = nvis * p.Z;
+    const unsigned vis_tile = tile_visibility(p, t, h, vs, vmin, image_h, image_w, loaded_b);
 
     for (int grp = g_first; grp < ngroups; grp += g_step) {
       const int t0 = grp * p.CPW;
@@ -54,6 +65,22 @@ __global__ void __launch_bounds__(kMaxWarps * 32, MINB) fwd_kernel(const __grid_
       const int ly = tc / p.TX, lx = tc - ly * p.TX;
       const int x = t.x0 + lx, y = t.y0 + ly;
       const bool cell_ok = lane_used && tc < tile_cells && x < t.x1 && y < t.y1;
+      unsigned vis = vis_tile;
+      if (EXPERIMENTS && (p.exp & FBEV_EXP_GROUP_CULL)) {
+        // the cull again for the box of this group's cells alone (rows ly0..ly1 of the tile; one row: its columns)
+        const int last = min(t0 + p.CPW, tile_cells) - 1;
+        const int ly0 = t0 / p.TX, ly1 = last / p.TX;
+        Tile tg = t;
+        tg.y0 = t.y0 + ly0;
+        tg.y1 = min(t.y0 + ly1 + 1, t.y1);
+        if (ly0 == ly1) {
+          tg.x0 = t.x0 + (t0 - ly0 * p.TX);
+          tg.x1 = min(t.x0 + (last - ly0 * p.TX) + 1, t.x1);
+        }
+        vis = (tg.x0 < tg.x1 && tg.y0 < tg.y1) ? (vis_tile & box_visibility(p, tg, h, vs, vmin, image_h, image_w)) : 0u;
+      }
+      const int nvis = __popc(vis);
+      const int ncand = nvis * p.Z;
 
       // accumulators as pairs: one packed FFMA2 (two independent IEEE fp32 fmas) per pair of channels
       float2 acc2[V * E / 2];
@@ -115,7 +142,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, MINB) fwd_kernel(const __grid_
       __syncwarp();
     }
   }  // tiles
-  sched.end(p);
+  sched.end(p, nwarps);
 }
 
 // Any channel count and alignment: one cell per warp, lanes stride over channels

@@ -31,6 +31,7 @@
 #include <mutex>
 
 #include "fbev.h"
+#include "fbev_debug.h"
 #include "fbev_device.cuh"
 #include "fbev_lists.cuh"
 #include "fbev_forward.cuh"
@@ -43,10 +44,13 @@ namespace fbev {
 // ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
+// Launch tuning of experiments and tests (fbev_debug.h).  Per host thread: a launch reads the values its own
+// thread set, so one thread's experiments never change the kernels another thread launches.
 struct Tuning {
   int tx, ty, v, warps, minb;
 };
-static Tuning g_tuning = {0, 0, 0, 0, 0};
+static thread_local Tuning g_tuning = {0, 0, 0, 0, 0};
+static thread_local int g_experiment = 0;  // FBEV_EXP_* bits (fbev_debug.h)
 
 static size_t elem_size(int dtype) { return dtype == FBEV_F32 ? 4 : 2; }
 
@@ -88,6 +92,7 @@ static void fill_dev(const FbevProblem* p, Dev& d) {
   d.roi = p->roi_range;
   d.status = p->status;
   d.sched = reinterpret_cast<unsigned*>(p->workspace);
+  d.exp = g_experiment;
   d.out_f32 = (p->out_dtype == FBEV_F32 && p->dtype != FBEV_F32) ? 1 : 0;
   d.B = p->B; d.N = p->N; d.H = p->H; d.W = p->W; d.C = p->C; d.D = p->D;
   d.X = p->X; d.Y = p->Y; d.Z = p->Z;
@@ -159,6 +164,7 @@ static Plan make_plan(const FbevProblem* p, Dev& d, bool bwd, const void* a, con
   }
   d.GL = pl.GL;
   d.CPW = pl.CPW;
+  d.cpt = pl.chunked ? pl.GL * pl.V : 0;
   d.cap = pl.cap;
   // backward: tile = 16 groups of CPW cells, two passes for eight warps.  forward: small tiles of about 24
   // cells for four warps: a single sample has only some 10^4 cells, and the tail of the last tiles is what
@@ -187,6 +193,7 @@ static Plan make_plan(const FbevProblem* p, Dev& d, bool bwd, const void* a, con
     pl.V = 0;
     d.GL = pl.GL = 32;
     d.CPW = pl.CPW = 1;
+    d.cpt = 0;
   }
   const size_t wb = bwd ? warp_bytes<3>(pl.CPW, pl.cap)
                         : (pl.chunked ? fwd_warp_bytes(pl.CPW, pl.cap) : warp_bytes<2>(pl.CPW, pl.cap));
@@ -293,7 +300,9 @@ static int forward_t(const Plan& pl, const Dev& d, cudaStream_t st) {
   const int gpt = (d.TX * d.TY + pl.CPW - 1) / pl.CPW;  // groups of CPW cells per tile
   switch (pl.V) {
     case 1: return two ? launch(fwd_kernel<T, 1, 2>, pl, d, st, gpt) : launch(fwd_kernel<T, 1, 3>, pl, d, st, gpt);
-    case 2: return two ? launch(fwd_kernel<T, 2, 2>, pl, d, st, gpt) : launch(fwd_kernel<T, 2, 3>, pl, d, st, gpt);
+    case 2:
+      if (d.exp != 0 && !two) return launch(fwd_kernel<T, 2, 3, true>, pl, d, st, gpt);
+      return two ? launch(fwd_kernel<T, 2, 2>, pl, d, st, gpt) : launch(fwd_kernel<T, 2, 3>, pl, d, st, gpt);
     default: return launch(fwd_kernel<T, 4, 2>, pl, d, st, gpt);
   }
 }
@@ -478,6 +487,11 @@ extern "C" {
 
 int fbev_version(void) { return FBEV_ABI_VERSION; }
 
+#ifndef FBEV_SOURCE_HASH
+#define FBEV_SOURCE_HASH "unknown"
+#endif
+const char* fbev_source_hash(void) { return FBEV_SOURCE_HASH; }
+
 const char* fbev_strerror(int status) {
   switch (status) {
     case FBEV_OK: return "ok";
@@ -500,18 +514,45 @@ void fbev_set_tuning(int tile_x, int tile_y, int chunks_per_lane, int warps, int
   g_tuning = Tuning{tile_x, tile_y, chunks_per_lane, warps, min_blocks};
 }
 
+void fbev_set_experiment(int bits) { g_experiment = bits; }
+
 int fbev_forward(const FbevProblem* p, void* out, int32_t* valid_count, void* stream) {
   return forward_impl(p, out, valid_count, stream, false);
 }
 
-// Side stream and events of fbev_forward_to_host, one set per device, created on first use.
+// Side stream and events of fbev_forward_to_host: one set per (device, caller stream), created on first use
+// under a lock and kept for the life of the process.  Calls on different streams therefore share nothing;
+// calls on one stream are ordered by that stream.
 struct HostPipe {
+  int dev = -1;
+  cudaStream_t caller = nullptr;
   cudaStream_t side = nullptr;
   cudaEvent_t ready[16] = {};
   cudaEvent_t done = nullptr;
-  bool ok = false;
 };
-static HostPipe g_host_pipe[64];
+constexpr int kMaxHostPipes = 256;
+static HostPipe g_host_pipe[kMaxHostPipes];
+static int g_host_pipes = 0;
+static std::mutex g_host_pipe_lock;
+
+static HostPipe* host_pipe(int dev, cudaStream_t caller) {
+  std::lock_guard<std::mutex> g(g_host_pipe_lock);
+  for (int i = 0; i < g_host_pipes; ++i)
+    if (g_host_pipe[i].dev == dev && g_host_pipe[i].caller == caller) return &g_host_pipe[i];
+  if (g_host_pipes == kMaxHostPipes) return nullptr;
+  HostPipe hp;
+  hp.dev = dev;
+  hp.caller = caller;
+  bool good = cudaStreamCreateWithFlags(&hp.side, cudaStreamNonBlocking) == cudaSuccess;
+  for (int k = 0; k < 16 && good; ++k) good = cudaEventCreateWithFlags(&hp.ready[k], cudaEventDisableTiming) == cudaSuccess;
+  good = good && cudaEventCreateWithFlags(&hp.done, cudaEventDisableTiming) == cudaSuccess;
+  if (!good) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  g_host_pipe[g_host_pipes] = hp;
+  return &g_host_pipe[g_host_pipes++];
+}
 
 int fbev_forward_to_host(const FbevProblem* p, void* out_dev, void* out_host, int row_chunks, void* stream) {
   const int rc = validate(p);
@@ -519,21 +560,13 @@ int fbev_forward_to_host(const FbevProblem* p, void* out_dev, void* out_host, in
   if (out_dev == nullptr || out_host == nullptr) return FBEV_ERR_NULL;
   if (row_chunks < 1 || row_chunks > 16) return FBEV_ERR_SHAPE;
   int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) {
     cudaGetLastError();
     return FBEV_ERR_NO_DEVICE;
   }
-  HostPipe& hp = g_host_pipe[dev];
-  if (!hp.ok) {
-    bool good = cudaStreamCreateWithFlags(&hp.side, cudaStreamNonBlocking) == cudaSuccess;
-    for (int k = 0; k < 16 && good; ++k) good = cudaEventCreateWithFlags(&hp.ready[k], cudaEventDisableTiming) == cudaSuccess;
-    good = good && cudaEventCreateWithFlags(&hp.done, cudaEventDisableTiming) == cudaSuccess;
-    if (!good) {
-      cudaGetLastError();
-      return FBEV_ERR_LAUNCH;
-    }
-    hp.ok = true;
-  }
+  HostPipe* hpp = host_pipe(dev, reinterpret_cast<cudaStream_t>(stream));
+  if (hpp == nullptr) return FBEV_ERR_LAUNCH;
+  HostPipe& hp = *hpp;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int y0 = p->y_begin, rows = p->y_end - p->y_begin;
   const size_t row_bytes = (size_t)p->X * p->C * elem_size(p->out_dtype);
@@ -583,15 +616,12 @@ static size_t scratch_min_bytes(const FbevProblem* p, int flags) {
   return n;
 }
 
-// Entry lists of the sorted gradients: capacity (entries) and bytes.  One entry per two candidates is a
-// little over twice what the benchmark rigs emit (one per row record); warps that find the list full add
-// directly instead.
-static size_t sort_capacity(const FbevProblem* p) {
-  if (g_tuning.minb == 8) return 4096;  // tests: nearly every warp finds the list full
-  const size_t cand = (size_t)p->B * p->X * (size_t)(p->y_end - p->y_begin) * p->N * p->Z / 2;
-  const size_t top = (size_t)1 << 26;
-  return cand < top ? (cand < 4096 ? 4096 : cand) : top;
-}
+// Entry lists of the sorted gradients.  One entry per two candidates is a little over twice what the benchmark
+// rigs emit (one per row record); warps that find the list full add directly instead.  The lists are transient
+// scratch, so their size is bounded: at most kSortBudgetBytes, whatever the batch.  A batch whose lists would
+// not fit is processed in runs of as many samples as do (sort_batch_run); one sample that does not fit by itself
+// gets the capped list and its overflow takes the direct path.
+constexpr size_t kSortBudgetBytes = FBEV_SORT_BUDGET_BYTES;
 // the parametric depth gradient rides on the same entries (16 more bytes in each list)
 static bool sort_carries_depth(const FbevProblem* p, int flags) {
   return (flags & FBEV_BWD_DEPTH) && p->mode != FBEV_DEPTH_CATEGORICAL;
@@ -600,11 +630,28 @@ static size_t sort_entry_bytes(const FbevProblem* p, int flags) {
   // entry and its grouped copy, position, and for the parametric depth gradient four floats in either list
   return 16 + 16 + 4 + (sort_carries_depth(p, flags) ? 32 : 0);
 }
+static size_t sort_entries_per_sample(const FbevProblem* p) {
+  return (size_t)p->X * (size_t)(p->y_end - p->y_begin) * p->N * p->Z / 2;
+}
+// samples of the batch that share one set of entry lists
+static int sort_batch_run(const FbevProblem* p, int flags) {
+  const size_t per = sort_entries_per_sample(p) * sort_entry_bytes(p, flags);
+  if (per == 0 || per * (size_t)p->B <= kSortBudgetBytes) return p->B;
+  const size_t fit = kSortBudgetBytes / per;
+  return fit < 1 ? 1 : (int)fit;
+}
+static size_t sort_capacity(const FbevProblem* p, int flags) {
+  if (g_tuning.minb == 8) return 4096;  // tests: nearly every warp finds the list full
+  const size_t cand = sort_entries_per_sample(p) * (size_t)sort_batch_run(p, flags);
+  size_t top = kSortBudgetBytes / sort_entry_bytes(p, flags);
+  if (top > ((size_t)1 << 26)) top = (size_t)1 << 26;
+  return cand < top ? (cand < 4096 ? 4096 : cand) : top;
+}
 static size_t sort_bytes(const FbevProblem* p, int flags) {
   if (!(flags & FBEV_BWD_FEATS) && !sort_carries_depth(p, flags)) return 0;
-  const size_t tex = (size_t)p->B * p->N * p->H * p->W;
+  const size_t tex = (size_t)sort_batch_run(p, flags) * p->N * p->H * p->W;
   if (tex >= 0xfffffff0ull || (size_t)p->B * p->Y * p->X >= 0xfffffff0ull) return 0;
-  return (((tex + 1) * 4 + 255) / 256) * 256 + 256 + sort_capacity(p) * sort_entry_bytes(p, flags);
+  return (((tex + 1) * 4 + 255) / 256) * 256 + 256 + sort_capacity(p, flags) * sort_entry_bytes(p, flags);
 }
 
 int fbev_forward_peers(const FbevProblem* p, void* out, void* const* peer_outs, int n_peers, int32_t* valid_count,
@@ -629,89 +676,112 @@ int fbev_backward(const FbevProblem* p, const void* grad_out, void* grad_feats, 
   if (grad_out == nullptr) return FBEV_ERR_NULL;
   if ((flags & FBEV_BWD_FEATS) && grad_feats == nullptr) return FBEV_ERR_NULL;
   if ((flags & FBEV_BWD_DEPTH) && grad_depth == nullptr) return FBEV_ERR_NULL;
-  Dev d;
-  fill_dev(p, d);
-  d.gout = grad_out;
-  d.flags = flags;
-  const Plan pl = make_plan(p, d, true, p->image_feats, grad_out,
-                            p->dtype == FBEV_F32 ? grad_feats : (const void*)nullptr);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const size_t tex = (size_t)p->B * p->N * p->H * p->W;
-  const size_t nf = tex * p->C, nd = tex * p->D;
+  const size_t tex_all = (size_t)p->B * p->N * p->H * p->W;
+  const size_t nf = tex_all * p->C, nd = tex_all * p->D;
   const bool f32 = p->dtype == FBEV_F32;
+  // float32 accumulation targets of the whole batch: the gradient tensors themselves, or the head of the scratch
+  float* gfeat_all = nullptr;
+  float* gdepth_all = nullptr;
   if (f32) {
     if (((uintptr_t)grad_feats % 4) || ((uintptr_t)grad_depth % 4)) return FBEV_ERR_ALIGN;
-    d.gfeat = reinterpret_cast<float*>(grad_feats);
-    d.gdepth = reinterpret_cast<float*>(grad_depth);
+    gfeat_all = reinterpret_cast<float*>(grad_feats);
+    gdepth_all = reinterpret_cast<float*>(grad_depth);
   } else {
     const size_t need = scratch_min_bytes(p, flags);
     if (scratch == nullptr || scratch_bytes < need || ((uintptr_t)scratch % 256)) return FBEV_ERR_SCRATCH;
     unsigned char* s = reinterpret_cast<unsigned char*>(scratch);
     if (flags & FBEV_BWD_FEATS) {
-      d.gfeat = reinterpret_cast<float*>(s);
+      gfeat_all = reinterpret_cast<float*>(s);
       s += ((nf * 4 + 255) / 256) * 256;
     }
-    if (flags & FBEV_BWD_DEPTH) d.gdepth = reinterpret_cast<float*>(s);
+    if (flags & FBEV_BWD_DEPTH) gdepth_all = reinterpret_cast<float*>(s);
   }
-  // what lies beyond the accumulation targets holds the entry lists of the sorted feature gradient, when
-  // the caller gave that much (fbev_backward_scratch_bytes asks for it)
+  // what lies beyond the accumulation targets holds the entry lists of the sorted gradients, when the caller gave
+  // that much (fbev_backward_scratch_bytes asks for it); small problems keep the single-launch kernels: three more
+  // launches cost more than they save there
   const size_t sortb = sort_bytes(p, flags), minb = scratch_min_bytes(p, flags);
-  // small problems keep the single-launch kernels: three more launches cost more than they save there
-  size_t sort_clear = 0;  // bytes of counters to clear at d.tex_count
   const bool want_sort = g_tuning.minb == 7 || g_tuning.minb == 8 || g_tuning.minb == 9 ||
                          (g_tuning.minb == 0 && (size_t)p->B * p->X * (size_t)(p->y_end - p->y_begin) * p->N * p->Z >= 200000);
-  if (want_sort && sortb != 0 && scratch != nullptr && ((uintptr_t)scratch % 256) == 0 && scratch_bytes >= minb + sortb) {
-    unsigned char* s = reinterpret_cast<unsigned char*>(scratch) + minb;
-    const size_t cnt_bytes = (((tex + 1) * 4 + 255) / 256) * 256;
-    d.tex_count = reinterpret_cast<unsigned*>(s);
-    d.ent_count = reinterpret_cast<unsigned*>(s + cnt_bytes);
-    d.ent_cap = (unsigned)sort_capacity(p);
-    d.ent = reinterpret_cast<uint4*>(s + cnt_bytes + 256);
-    d.ent_sorted = d.ent + d.ent_cap;
-    unsigned char* after = reinterpret_cast<unsigned char*>(d.ent_sorted + d.ent_cap);
-    if (sort_carries_depth(p, flags)) {
-      d.ent_d = reinterpret_cast<float4*>(after);
-      d.ent_d_sorted = d.ent_d + d.ent_cap;
-      after = reinterpret_cast<unsigned char*>(d.ent_d_sorted + d.ent_cap);
-    }
-    d.ent_pos = reinterpret_cast<unsigned*>(after);
-    sort_clear = cnt_bytes + 256;
-  }
-  // clears: the accumulation targets and the sort's counters; one memset when they are neighbours in the scratch
-  if (!f32 && sort_clear != 0) {
-    if (cudaMemsetAsync(scratch, 0, minb + sort_clear, st) != cudaSuccess) {
+  const bool sorted = want_sort && sortb != 0 && scratch != nullptr && ((uintptr_t)scratch % 256) == 0 &&
+                      scratch_bytes >= minb + sortb;
+  const int run = sorted ? sort_batch_run(p, flags) : p->B;  // samples per pass over the entry lists
+  const size_t tex_run = (size_t)run * p->N * p->H * p->W;
+  const size_t cnt_bytes = (((tex_run + 1) * 4 + 255) / 256) * 256;
+  unsigned char* sort_base = sorted ? reinterpret_cast<unsigned char*>(scratch) + minb : nullptr;
+  // clears: the accumulation targets and, for the first run, the sort's counters; one memset when they are
+  // neighbours in the scratch
+  if (!f32 && sorted) {
+    if (cudaMemsetAsync(scratch, 0, minb + cnt_bytes + 256, st) != cudaSuccess) {
       cudaGetLastError();
       return FBEV_ERR_LAUNCH;
     }
   } else {
-    if (sort_clear != 0 && cudaMemsetAsync(d.tex_count, 0, sort_clear, st) != cudaSuccess) {
+    if (sorted && cudaMemsetAsync(sort_base, 0, cnt_bytes + 256, st) != cudaSuccess) {
       cudaGetLastError();
       return FBEV_ERR_LAUNCH;
     }
-    if ((flags & FBEV_BWD_FEATS) && cudaMemsetAsync(d.gfeat, 0, nf * 4, st) != cudaSuccess) {
+    if ((flags & FBEV_BWD_FEATS) && cudaMemsetAsync(gfeat_all, 0, nf * 4, st) != cudaSuccess) {
       cudaGetLastError();
       return FBEV_ERR_LAUNCH;
     }
-    if ((flags & FBEV_BWD_DEPTH) && cudaMemsetAsync(d.gdepth, 0, nd * 4, st) != cudaSuccess) {
+    if ((flags & FBEV_BWD_DEPTH) && cudaMemsetAsync(gdepth_all, 0, nd * 4, st) != cudaSuccess) {
       cudaGetLastError();
       return FBEV_ERR_LAUNCH;
     }
   }
-  // the feature gradient has a kernel of its own, laid out like the forward
-  Dev df = d;
-  const bool wide_ok = !((flags & FBEV_BWD_DEPTH) && p->mode == FBEV_DEPTH_CATEGORICAL);
-  const Plan plf = make_plan(p, df, false, p->image_feats, grad_out, d.gfeat, wide_ok);
-  int lrc;
-  switch (p->dtype) {
-    case FBEV_F32: lrc = backward_t<float>(pl, d, plf, df, st); break;
-    case FBEV_BF16: lrc = backward_t<__nv_bfloat16>(pl, d, plf, df, st); break;
-    default: lrc = backward_t<__half>(pl, d, plf, df, st); break;
+  const size_t es = elem_size(p->dtype), eso = elem_size(p->out_dtype);
+  const size_t tex_sample = (size_t)p->N * p->H * p->W;
+  for (int b0 = 0; b0 < p->B; b0 += run) {
+    // the samples [b0, b0 + run) as a problem of their own: every tensor is indexed by the sample first
+    FbevProblem q = *p;
+    q.B = p->B - b0 < run ? p->B - b0 : run;
+    q.image_feats = reinterpret_cast<const unsigned char*>(p->image_feats) + (size_t)b0 * tex_sample * p->C * es;
+    q.depth = reinterpret_cast<const unsigned char*>(p->depth) + (size_t)b0 * tex_sample * p->D * es;
+    q.projection = p->projection + (size_t)b0 * p->N * p->proj_stride;
+    q.feature_size = p->feature_size + (size_t)b0 * p->N * 2;
+    const void* gout = reinterpret_cast<const unsigned char*>(grad_out) + (size_t)b0 * p->Y * p->X * p->C * eso;
+    Dev d;
+    fill_dev(&q, d);
+    d.gout = gout;
+    d.flags = flags;
+    d.gfeat = gfeat_all ? gfeat_all + (size_t)b0 * tex_sample * p->C : nullptr;
+    d.gdepth = gdepth_all ? gdepth_all + (size_t)b0 * tex_sample * p->D : nullptr;
+    const Plan pl = make_plan(&q, d, true, q.image_feats, gout, f32 ? (const void*)d.gfeat : (const void*)nullptr);
+    if (sorted) {
+      if (b0 > 0 && cudaMemsetAsync(sort_base, 0, cnt_bytes + 256, st) != cudaSuccess) {  // counters of the run before
+        cudaGetLastError();
+        return FBEV_ERR_LAUNCH;
+      }
+      d.tex_count = reinterpret_cast<unsigned*>(sort_base);
+      d.ent_count = reinterpret_cast<unsigned*>(sort_base + cnt_bytes);
+      d.ent_cap = (unsigned)sort_capacity(p, flags);
+      d.ent = reinterpret_cast<uint4*>(sort_base + cnt_bytes + 256);
+      d.ent_sorted = d.ent + d.ent_cap;
+      unsigned char* after = reinterpret_cast<unsigned char*>(d.ent_sorted + d.ent_cap);
+      if (sort_carries_depth(p, flags)) {
+        d.ent_d = reinterpret_cast<float4*>(after);
+        d.ent_d_sorted = d.ent_d + d.ent_cap;
+        after = reinterpret_cast<unsigned char*>(d.ent_d_sorted + d.ent_cap);
+      }
+      d.ent_pos = reinterpret_cast<unsigned*>(after);
+    }
+    // the feature gradient has a kernel of its own, laid out like the forward
+    Dev df = d;
+    const bool wide_ok = !((flags & FBEV_BWD_DEPTH) && p->mode == FBEV_DEPTH_CATEGORICAL);
+    const Plan plf = make_plan(&q, df, false, q.image_feats, gout, d.gfeat, wide_ok);
+    int lrc;
+    switch (p->dtype) {
+      case FBEV_F32: lrc = backward_t<float>(pl, d, plf, df, st); break;
+      case FBEV_BF16: lrc = backward_t<__nv_bfloat16>(pl, d, plf, df, st); break;
+      default: lrc = backward_t<__half>(pl, d, plf, df, st); break;
+    }
+    if (lrc != FBEV_OK) return lrc;
   }
-  if (lrc != FBEV_OK) return lrc;
   if (!f32) {
     // float32 accumulation targets -> gradient tensors, both in one launch
-    const float* sa = (flags & FBEV_BWD_FEATS) ? d.gfeat : nullptr;
-    const float* sb = (flags & FBEV_BWD_DEPTH) ? d.gdepth : nullptr;
+    const float* sa = (flags & FBEV_BWD_FEATS) ? gfeat_all : nullptr;
+    const float* sb = (flags & FBEV_BWD_DEPTH) ? gdepth_all : nullptr;
     const size_t na = sa ? nf : 0, nb = sb ? nd : 0;
     const size_t units = (na + 3) / 4 + (nb + 3) / 4;
     const int threads = 256;
@@ -831,6 +901,7 @@ int fbev_probe_read(const void* buf, size_t bytes, int repeats, void* sink, void
 #define FBEV_STATIC_SCRATCH_LIMIT ((size_t)FBEV_STATIC_SCRATCH_BYTES)
 static __device__ __align__(256) unsigned char g_fbev_static_scratch[FBEV_STATIC_SCRATCH_BYTES];
 static void* g_fbev_static_scratch_addr[64] = {nullptr};  // device address of the array, per device ordinal
+static std::mutex g_fbev_static_scratch_lock;                // guards the table above
 
 int fbev_backward_static_scratch(const FbevProblem* p, const void* grad_out, void* grad_feats, void* grad_depth,
                                  int flags, void* stream) {
@@ -843,19 +914,23 @@ int fbev_backward_static_scratch(const FbevProblem* p, const void* grad_out, voi
     cudaGetLastError();
     return FBEV_ERR_NO_DEVICE;
   }
-  if (g_fbev_static_scratch_addr[dev] == nullptr) {
-    // first call on this device: resolve the array's address in this device's copy of the module
-    void* addr = nullptr;
-    if (cudaGetSymbolAddress(&addr, g_fbev_static_scratch) != cudaSuccess || addr == nullptr) {
-      cudaGetLastError();
-      return FBEV_ERR_LAUNCH;
+  void* addr = nullptr;
+  {
+    std::lock_guard<std::mutex> g(g_fbev_static_scratch_lock);
+    if (g_fbev_static_scratch_addr[dev] == nullptr) {
+      // first call on this device: resolve the array's address in this device's copy of the module
+      void* found = nullptr;
+      if (cudaGetSymbolAddress(&found, g_fbev_static_scratch) != cudaSuccess || found == nullptr) {
+        cudaGetLastError();
+        return FBEV_ERR_LAUNCH;
+      }
+      g_fbev_static_scratch_addr[dev] = found;
     }
-    g_fbev_static_scratch_addr[dev] = addr;
+    addr = g_fbev_static_scratch_addr[dev];
   }
   // fbev_backward clears the part of the scratch it accumulates into, so what an earlier call left
   // behind is never read
-  return fbev_backward(p, grad_out, grad_feats, grad_depth, g_fbev_static_scratch_addr[dev],
-                       FBEV_STATIC_SCRATCH_LIMIT, flags, stream);
+  return fbev_backward(p, grad_out, grad_feats, grad_depth, addr, FBEV_STATIC_SCRATCH_LIMIT, flags, stream);
 }
 
 }  // extern "C"

@@ -121,10 +121,12 @@ struct TileLoop {
 struct UnitLoop {
   TileLoop loop;
   bool stat;
-  int unit;  // static order: this warp's current unit
+  bool draw;  // static order for a warp's first unit only, further units from the scheduler word (FBEV_EXP_DRAW)
+  int unit;   // static order: this warp's current unit
 
   __device__ __forceinline__ void begin(const Dev& p, int* shared_slot, int warp, int nwarps) {
     stat = p.static_units != 0;
+    draw = stat && p.sched != nullptr && (p.exp & FBEV_EXP_DRAW) != 0;
     unit = blockIdx.x * nwarps + warp;
     if (!stat) loop.begin(p, shared_slot);
   }
@@ -141,15 +143,33 @@ struct UnitLoop {
     g_step = nwarps;
     return loop.current(p);
   }
-  __device__ __forceinline__ void advance(int nwarps) {
-    if (stat) {
+  __device__ __forceinline__ void advance(const Dev& p, int nwarps) {
+    if (draw) {
+      // the first round went out in the static order (neighbouring warps on neighbouring groups); what is left is
+      // handed out one unit at a time to whichever warp is free, which evens out the unequal cost of the units
+      unsigned u = 0;
+      if ((threadIdx.x & 31) == 0) u = atomicAdd(p.sched, 1u);
+      u = __shfl_sync(kFull, u, 0);
+      unit = (int)(gridDim.x * nwarps + u);
+    } else if (stat) {
       unit += gridDim.x * nwarps;
     } else {
       loop.advance();
     }
   }
-  __device__ __forceinline__ void end(const Dev& p) {
-    if (!stat) loop.end(p);
+  __device__ __forceinline__ void end(const Dev& p, int nwarps) {
+    if (draw) {
+      if ((threadIdx.x & 31) == 0) {
+        __threadfence();
+        const unsigned done = atomicAdd(p.sched + 1, 1u);  // warps that have left
+        if (done == gridDim.x * nwarps - 1) {
+          p.sched[0] = 0u;
+          p.sched[1] = 0u;
+        }
+      }
+    } else if (!stat) {
+      loop.end(p);
+    }
   }
 };
 
@@ -193,6 +213,31 @@ __device__ __forceinline__ void block_prologue(const Dev& p, const Tile& t, cons
   __syncthreads();
 }
 
+// Bit mask of the cameras (up to 32) that may see a box of cells [t.x0, t.x1) x [t.y0, t.y1) of sample t.b, whose
+// matrices are in shared memory; evaluated by every warp for itself, lane n for camera n.  A camera whose
+// feature_size entry is unusable (non-positive, larger than the tensor, or beyond what 32-bit chunk indices
+// address) is left out and reported in the status word.
+__device__ __forceinline__ unsigned box_visibility(const Dev& p, const Tile& t, const BlockHeader& h, const float vs[3],
+                                                   const float vmin[3], int image_h, int image_w) {
+  const int lane = threadIdx.x & 31;
+  bool see = false;
+  if (lane < p.N) {
+    const int fh = h.fs[lane * 2], fw = h.fs[lane * 2 + 1];
+    bool ok = fh > 0 && fw > 0 && (long long)fh * fw <= (long long)p.H * p.W;
+    if (ok && p.cpt > 0)  // the records hold 32-bit chunk indices into the feature tensor
+      ok = (unsigned long long)((size_t)t.b * p.N + lane + 1) * (unsigned long long)fh * fw * (unsigned)p.cpt < (1ull << 32);
+    if (ok) {
+      const float bx0 = centre(t.x0, vs[0], vmin[0]), bx1 = centre(t.x1 - 1, vs[0], vmin[0]);
+      const float by0 = centre(t.y0, vs[1], vmin[1]), by1 = centre(t.y1 - 1, vs[1], vmin[1]);
+      const float bz0 = centre(0, vs[2], vmin[2]), bz1 = centre(p.Z - 1, vs[2], vmin[2]);
+      see = camera_may_see(p, h.P + lane * 12, bx0, bx1, by0, by1, bz0, bz1, image_h, image_w);
+    } else if (p.status != nullptr && threadIdx.x < 32) {
+      atomicOr(p.status, (int)FBEV_DEV_BAD_FEATURE_SIZE);
+    }
+  }
+  return __ballot_sync(kFull, see);
+}
+
 // Forward-kernel prologue for up to 32 cameras.  The matrices are (re)loaded only when the tile
 // belongs to another sample than the one in shared memory (block barriers then); the camera cull is
 // evaluated by every warp for itself and returned as a bit mask, so the steady state has no barrier.
@@ -209,20 +254,7 @@ __device__ __forceinline__ unsigned tile_visibility(const Dev& p, const Tile& t,
     loaded_b = t.b;
     __syncthreads();
   }
-  const int lane = threadIdx.x & 31;
-  bool see = false;
-  if (lane < p.N) {
-    const int fh = h.fs[lane * 2], fw = h.fs[lane * 2 + 1];
-    if (fh > 0 && fw > 0 && (long long)fh * fw <= (long long)p.H * p.W) {
-      const float bx0 = centre(t.x0, vs[0], vmin[0]), bx1 = centre(t.x1 - 1, vs[0], vmin[0]);
-      const float by0 = centre(t.y0, vs[1], vmin[1]), by1 = centre(t.y1 - 1, vs[1], vmin[1]);
-      const float bz0 = centre(0, vs[2], vmin[2]), bz1 = centre(p.Z - 1, vs[2], vmin[2]);
-      see = camera_may_see(p, h.P + lane * 12, bx0, bx1, by0, by1, bz0, bz1, image_h, image_w);
-    } else if (p.status != nullptr && threadIdx.x < 32) {
-      atomicOr(p.status, (int)FBEV_DEV_BAD_FEATURE_SIZE);
-    }
-  }
-  return __ballot_sync(kFull, see);
+  return box_visibility(p, t, h, vs, vmin, image_h, image_w);
 }
 
 // List phase for one group of cells and one pass over candidates [r0, r1) of

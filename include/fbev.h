@@ -122,8 +122,8 @@ int fbev_forward(const FbevProblem* p, void* out, int32_t* valid_count, void* st
  * callers copy the whole result after the kernel.)  out_dev: device [B,Y,X,C] staging buffer; out_host:
  * page-locked host [B,Y,X,C]; both receive the rows.  The caller's stream waits for the last copy, so work
  * queued on it afterwards, or a synchronisation of it, sees the host buffer complete.  The first call on a
- * device creates the side stream and its events; make it outside any stream capture.  Calls on the same
- * device must not overlap each other in time (they share the side stream's events). */
+ * (device, stream) pair creates that pair's side stream and events under a lock; make it outside any stream
+ * capture.  Calls on different streams share nothing; calls on one stream are ordered by it. */
 int fbev_forward_to_host(const FbevProblem* p, void* out_dev, void* out_host, int row_chunks, void* stream);
 
 /* Forward whose result rows also go to other GPUs.  (No counterpart in the reference, which has no
@@ -139,9 +139,13 @@ int fbev_forward_peers(const FbevProblem* p, void* out, void* const* peer_outs, 
 
 /* Bytes of scratch fbev_backward works best with for this problem and flags: the float32 accumulation
  * targets of the 16-bit types (fbev_backward_min_scratch_bytes) plus, when the feature gradient is asked
- * for (or the depth gradient of a parametric mode), the entry lists of the sort by texel: (B*N*H*W + 1) * 4
- * bytes of counters and 36 bytes per entry (68 with a parametric depth gradient), one entry per two
- * candidates B*X*rows*N*Z (at least 4096, at most 2^26 entries). */
+ * for (or the depth gradient of a parametric mode), the entry lists of the sort by texel: counters (4 bytes
+ * per texel) and 36 bytes per entry (68 with a parametric depth gradient), one entry per two candidates
+ * X*rows*N*Z of every sample (at least 4096 entries).  The lists never exceed FBEV_SORT_BUDGET_BYTES: a batch
+ * that would need more is processed in runs of as many samples as fit, and a single sample that would need
+ * more gets lists of that size (what does not fit is added directly, slower).  (The reference backward needs
+ * no scratch at all: one atomicAdd per sample, channel and corner, flash_bevpool_cuda.cu:667-679.) */
+#define FBEV_SORT_BUDGET_BYTES ((size_t)256 << 20)
 size_t fbev_backward_scratch_bytes(const FbevProblem* p, int flags);
 
 /* The least scratch fbev_backward accepts: 0 for float32 tensors (gradients accumulate in place),
@@ -177,7 +181,8 @@ int fbev_backward(const FbevProblem* p, const void* grad_out, void* grad_feats, 
  *  - the array costs FBEV_STATIC_SCRATCH_BYTES of device memory on every GPU that loads the library,
  *    for the life of the process;
  *  - the first call on each device looks up the array's device address (cudaGetSymbolAddress, with
- *    that device current); make that first call outside any stream capture;
+ *    that device current, under a lock: host threads may race to it); make that first call outside
+ *    any stream capture;
  *  - all calls on a device share the one array.  Each call clears what it accumulates into, so
  *    leftovers of earlier calls do no harm, but two calls that overlap on the GPU (different
  *    streams, no ordering between them) corrupt each other's gradients: order them. */
@@ -230,24 +235,11 @@ int fbev_flash_bevpool_grad(int total_threads, int num_channels, int num_cameras
 int fbev_projection_matrices(const float* sensor2ego, const float* camera2imgs, const float* post_rots,
                              const float* post_trans, float* out, int count, void* stream);
 
-/* Process-wide launch tuning for experiments and tests: cells per tile in x and y, 16-byte chunks per
- * lane, warps per block, and a selector (last argument); 0 = choose automatically.  Selector values:
- *   2  forward compiled for two resident blocks per SM (128 registers) instead of three
- *   1  feature gradient by direct reductions      6  feature gradient with the per-tile sort
- *   5  record-based depth-gradient kernel also for the parametric modes without entry lists
- *   7  gradients through the global sort whatever the problem size      8  the same with a 4096-entry list
- *   9  global sort with tile_x = gather blocks per SM and tile_y = entries per gather run
- *   14 forward / list kernels always on the tile counter      15 always in the static unit order (one sample)
- * Any non-zero selector other than 7, 8, 9 also turns the global sort off. */
-void fbev_set_tuning(int tile_x, int tile_y, int chunks_per_lane, int warps, int min_blocks);
-
-/* Reads `bytes` of device memory `repeats` times with 16-byte loads (a bandwidth
- * probe for roofline denominators: L2-resident when bytes fits the L2).  sink:
- * device, >= 4 bytes. */
-int fbev_probe_read(const void* buf, size_t bytes, int repeats, void* sink, void* stream);
-
 const char* fbev_strerror(int status);
 int fbev_version(void);
+/* SHA-256 (hex) of the sources and compiler flags this library was built from; the Python binding refuses a
+ * library whose hash differs from the sources beside it.  (No counterpart in the reference.) */
+const char* fbev_source_hash(void);
 
 #ifdef __cplusplus
 }

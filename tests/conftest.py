@@ -18,3 +18,21 @@ def cuda_device():
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     return torch.device("cuda", 0)
+
+
+# Figures the parity tests want shown even when they pass (error sizes, mismatch counts): collected here and
+# printed once in the terminal summary, which "-q" keeps.
+_PARITY_LINES = []
+
+
+@pytest.fixture
+def parity_report():
+    """Callable that records one line for the "parity figures" section of the run's summary."""
+    return _PARITY_LINES.append
+
+
+def pytest_terminal_summary(terminalreporter):
+    if _PARITY_LINES:
+        terminalreporter.section("parity figures")
+        for line in _PARITY_LINES:
+            terminalreporter.write_line(line)

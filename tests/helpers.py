@@ -17,6 +17,15 @@ TOL_LOWP = 2e-3      # bfloat16 / float16 kernels vs the oracle on the same roun
 TOL_DENSE = 5e-5     # oracle vs the reference's dense PyTorch path (grid_sample re-normalises coordinates)
 
 
+def host_threads():
+    """Threads the CPU oracle may use in the full-size cases (its results do not depend on the count: the
+    float32 forward is sequential per cell, the float64 gradients are compared at 1e-5)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def rel_err(a, b):
     a = np.asarray(a, dtype=np.float64)
     b = np.asarray(b, dtype=np.float64)

@@ -1,6 +1,7 @@
 """CPU checks of the C ABI: libfbev.so loads, exports every symbol include/fbev.h declares, and
 its host-side validation returns status codes (no kernel is launched here)."""
 import ctypes
+import glob
 import os
 import re
 
@@ -13,13 +14,16 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def header_functions():
-    text = open(os.path.join(ROOT, "include", "fbev.h")).read()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(fbev_[a-z_0-9]+)\s*\(", text)))
+    """Every function declared in include/*.h (fbev.h: the operator; fbev_debug.h: experiment helpers)."""
+    names = set()
+    for path in sorted(glob.glob(os.path.join(ROOT, "include", "*.h"))):
+        text = re.sub(r"/\*.*?\*/", "", open(path).read(), flags=re.S)
+        names |= set(re.findall(r"\b(fbev_[a-z_0-9]+)\s*\(", text))
+    return sorted(names)
 
 
 def test_header_and_binding_list_the_same_functions():
-    assert header_functions() == sorted(_lib.EXPORTS)
+    assert header_functions() == sorted(_lib.EXPORTS + _lib.DEBUG_EXPORTS)
 
 
 def test_library_builds_and_exports_every_symbol():

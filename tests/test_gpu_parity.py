@@ -16,7 +16,7 @@ from flashbev_b200 import _lib, debug_indices, flash_bevpool, forward_with_count
 from flashbev_b200.flash_bevpool import status_word
 from oracle import oracle as O
 from tests.helpers import (SMALL, TOL_DENSE, TOL_F32, TOL_LOWP, golden_files, golden_inputs, golden_problem,
-                           inputs_for, op_kwargs, oracle_problem, rel_err, rel_err_quantised, to_device)
+                           host_threads, inputs_for, op_kwargs, oracle_problem, rel_err, rel_err_quantised, to_device)
 
 pytestmark = pytest.mark.gpu
 
@@ -33,7 +33,7 @@ def run_case(w, mode, device, threshold=0.0, pool=None, tol=None, dtype=None, y_
     16-bit output: 2e-3 beyond the single rounding of the result to the output type (rel_err_quantised)."""
     inp = synth.make_inputs(w, "categorical" if mode == "categorical" else "parametric", dtype=dtype)
     p = oracle_problem(inp, w, mode, threshold=threshold, pool=pool, y_range=y_range)
-    ref, ref_cnt = O.forward(p, with_count=True)
+    ref, ref_cnt = O.forward(p, with_count=True, threads=host_threads())
     out, cnt = forward_with_count(**to_device(inp, device), **op_kwargs(w, mode, threshold, pool, y_range),
                                   out_dtype=out_dtype)
     torch.cuda.synchronize()
@@ -221,7 +221,7 @@ def backward_case(w, mode, device, pool=None, dtype=None, legacy=False, threshol
     if (dtype or w.dtype) != "fp32" and not out_f32:
         go = go.to(inp["image_feats"].dtype)
     p = oracle_problem(inp, w, mode, pool=pool, threshold=threshold)
-    rf, rd = O.backward(p, go.float().numpy(), dtype=np.float64, legacy_depth_grad=legacy)
+    rf, rd = O.backward(p, go.float().numpy(), dtype=np.float64, legacy_depth_grad=legacy, threads=host_threads())
     dev = to_device(inp, device)
     dev["image_feats"].requires_grad_(True)
     dev["depth_params"].requires_grad_(True)
@@ -301,6 +301,26 @@ def test_backward_kernel_variants_agree_with_the_oracle(cuda_device, variant):
         backward_case(SMALL, "gaussian", cuda_device, legacy=True, threshold=1e-3, dtype="bf16")
     finally:
         lib.fbev_set_tuning(0, 0, 0, 0, 0)
+
+
+def test_backward_scratch_is_bounded_and_large_batches_run_in_several_passes(cuda_device):
+    """The entry lists of the sorted gradients are transient scratch: they stay within FBEV_SORT_BUDGET_BYTES
+    whatever the batch.  Here five samples would need 2.2 times the budget, so the backward takes them in runs
+    of two, two and one; the gradients must not notice."""
+    from flashbev_b200.flash_bevpool import DepthSpec, make_problem
+    lib = _lib.load()
+    w = synth.Workload("budget", B=5, N=6, C=16, H=8, W=22, D=24, X=256, Y=256, Z=16, xy_extent=40.0, d0=1.0,
+                       delta=2.5, dtype="bf16", seed=61, jitter=True)
+    inp = to_device(inputs_for(w, "laplace"), cuda_device)
+    prob, keep = make_problem(inp["depth_params"], inp["image_feats"], inp["projection_matrices"], inp["feature_size"],
+                              inp["image_size"], inp["roi_range"], inp["grid_size"], DepthSpec(1), 1e-6, 0.0)
+    per_sample = w.X * w.Y * w.N * w.Z // 2 * 68   # entries of one sample x bytes per entry (parametric depth)
+    assert per_sample * w.B > 2 * _lib.SORT_BUDGET_BYTES > 2 * per_sample
+    need = lib.fbev_backward_scratch_bytes(ctypes.byref(prob), 3)
+    floor = lib.fbev_backward_min_scratch_bytes(ctypes.byref(prob), 3)
+    assert need - floor <= _lib.SORT_BUDGET_BYTES + 4 * (2 * w.N * w.H * w.W + 1) + 1024
+    backward_case(w, "laplace", cuda_device)
+    backward_case(w, "categorical", cuda_device, pool="mean")
 
 
 def test_backward_headline_shape(cuda_device):

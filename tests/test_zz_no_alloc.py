@@ -4,8 +4,9 @@ A process that fixed its device-memory budget at start-up (or a plug-in whose ho
 pool) cannot give fbev_backward the float32 scratch it needs for 16-bit gradients.  The entry point
 under test keeps that scratch inside the library image.  Here it is called through the C ABI twice in
 a row, with different upstream gradients, and each result is compared with what fbev_backward
-produces with caller-allocated scratch: the second call shows that leftovers of the first do not leak
-into it.  The size limit is checked too.  (Collected last on purpose: a run that stops at the first
+produces with caller-allocated scratch and with the CPU oracle: the second call shows that leftovers
+of the first do not leak into it.  A float32 problem (which needs no scratch at all) goes through the
+same entry point.  The size limit is checked too.  (Collected last on purpose: a run that stops at the first
 failure has then already run every other test.)
 """
 import ctypes
@@ -16,7 +17,8 @@ import torch
 
 from flashbev_b200 import _lib, synth
 from flashbev_b200.flash_bevpool import DepthSpec, make_problem
-from tests.helpers import TOL_LOWP, rel_err_quantised
+from oracle import oracle as O
+from tests.helpers import TOL_F32, TOL_LOWP, host_threads, oracle_problem, rel_err, rel_err_quantised
 
 pytestmark = pytest.mark.gpu
 
@@ -40,7 +42,7 @@ def _grads(lib, prob, keep, go, static):
     return g_feats.float().cpu().numpy(), g_depth.float().cpu().numpy()
 
 
-@pytest.mark.parametrize("dtype,mode", [("bf16", "categorical"), ("fp16", "parametric")])
+@pytest.mark.parametrize("dtype,mode", [("bf16", "categorical"), ("fp16", "parametric"), ("fp32", "categorical")])
 def test_static_scratch_backward_matches_caller_scratch_backward(cuda_device, dtype, mode):
     lib = _lib.load()
     w = synth.Workload("noalloc", B=2, N=6, C=80, H=16, W=44, D=118, X=48, Y=40, Z=8, xy_extent=50.0, dtype=dtype,
@@ -51,12 +53,21 @@ def test_static_scratch_backward_matches_caller_scratch_backward(cuda_device, dt
                               inp["feature_size"], inp["image_size"], inp["roi_range"], inp["grid_size"], spec,
                               1e-6, 0.0)
     need = lib.fbev_backward_min_scratch_bytes(ctypes.byref(prob), 3)
-    assert 0 < need <= _lib.STATIC_SCRATCH_BYTES
+    assert (need == 0) if dtype == "fp32" else (0 < need <= _lib.STATIC_SCRATCH_BYTES)
+    cpu = oracle_problem(inp, w, "categorical" if mode == "categorical" else "laplace")
     for call in range(2):  # two calls in a row share the built-in array
         go = synth.upstream_grad(w, seed_offset=call).to(device=cuda_device, dtype=keep[0].dtype)
         ref_f, ref_d = _grads(lib, prob, keep, go, static=False)
         got_f, got_d = _grads(lib, prob, keep, go, static=True)
         assert np.isfinite(got_f).all() and np.isfinite(got_d).all()
+        # against the CPU oracle (float64 gradients of the same rounded inputs)
+        ora_f, ora_d = O.backward(cpu, go.float().cpu().numpy(), dtype=np.float64, threads=host_threads())
+        if dtype == "fp32":
+            assert rel_err(got_f, ora_f) < TOL_F32 and rel_err(got_d, ora_d) < TOL_F32, f"call {call}: vs oracle"
+            assert rel_err(got_f, ref_f) < TOL_F32 and rel_err(got_d, ref_d) < TOL_F32, f"call {call}"
+            continue
+        assert rel_err_quantised(got_f, ora_f, dtype) < TOL_LOWP, f"call {call}: d_feats vs oracle"
+        assert rel_err_quantised(got_d, ora_d, dtype) < TOL_LOWP, f"call {call}: d_depth vs oracle"
         # both sides sum with unordered float32 atomics and round once to the 16-bit type: equal up to one
         # ulp of that type plus the suite's 16-bit tolerance
         assert rel_err_quantised(got_f, ref_f, dtype, ulps=1.0) < TOL_LOWP, f"call {call}: d_feats"
