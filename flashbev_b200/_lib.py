@@ -24,7 +24,7 @@ ERR_STATIC_LIMIT = 11
 EXPORTS = (
     "fbev_forward", "fbev_forward_to_host", "fbev_forward_peers", "fbev_backward", "fbev_backward_scratch_bytes", "fbev_backward_min_scratch_bytes", "fbev_backward_static_scratch",
     "fbev_debug_indices",
-    "fbev_flash_bevpool", "fbev_flash_bevpool_grad", "fbev_projection_matrices",
+    "fbev_flash_bevpool", "fbev_flash_bevpool_grad", "fbev_projection_matrices", "fbev_pillar_pool",
     "fbev_strerror", "fbev_version", "fbev_source_hash",
 )
 # ... and include/fbev_debug.h (experiment and test helpers)
@@ -112,6 +112,8 @@ def load(build_if_missing: bool = True) -> ctypes.CDLL:
     lib.fbev_flash_bevpool_grad.restype = i32
     lib.fbev_projection_matrices.argtypes = [vp] * 5 + [i32, vp]
     lib.fbev_projection_matrices.restype = i32
+    lib.fbev_pillar_pool.argtypes = [i32, i32] + [vp] * 9 + [i32] * 4 + [f32, i32, vp, vp]
+    lib.fbev_pillar_pool.restype = i32
     lib.fbev_set_tuning.argtypes = [i32] * 5
     lib.fbev_set_tuning.restype = None
     lib.fbev_set_experiment.argtypes = [i32]

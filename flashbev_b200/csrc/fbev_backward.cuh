@@ -1199,8 +1199,7 @@ __global__ void convert2_kernel(const float* __restrict__ sa, T* __restrict__ da
     const size_t n = first ? na : nb, i = (first ? u : u - ua) * 4;
     if (i + 4 <= n && ((uintptr_t)(dst + i) % 8) == 0) {
       const float4 v = *reinterpret_cast<const float4*>(src + i);
-      T o[4] = {from_float<T>(v.x), from_float<T>(v.y), from_float<T>(v.z), from_float<T>(v.w)};
-      *reinterpret_cast<uint2*>(dst + i) = *reinterpret_cast<const uint2*>(o);
+      *reinterpret_cast<uint2*>(dst + i) = make_uint2(Chunk<T>::pack2(v.x, v.y), Chunk<T>::pack2(v.z, v.w));
     } else {
       for (size_t k = i; k < n && k < i + 4; ++k) dst[k] = from_float<T>(src[k]);
     }

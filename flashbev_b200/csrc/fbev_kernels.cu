@@ -883,6 +883,35 @@ int fbev_projection_matrices(const float* sensor2ego, const float* camera2imgs, 
   return cudaGetLastError() == cudaSuccess ? FBEV_OK : FBEV_ERR_LAUNCH;
 }
 
+int fbev_pillar_pool(int c, int n_intervals, const float* depth, const float* feat, const float* u_coords,
+                     const float* v_coords, const float* z_coords, const int* batch_camera_indices, const int* ranks_bev,
+                     const int* interval_starts, const int* interval_lengths, int batch_size, int num_cameras, int feat_h,
+                     int feat_w, float epsilon, int depth_distribution, float* out, void* stream) {
+  (void)batch_size; (void)num_cameras;  // the camera index of a sample already counts batch * cameras + camera
+  if (n_intervals == 0) return FBEV_OK;
+  if (!depth || !feat || !u_coords || !v_coords || !z_coords || !batch_camera_indices || !ranks_bev || !interval_starts ||
+      !interval_lengths || !out)
+    return FBEV_ERR_NULL;
+  if (c <= 0 || n_intervals < 0 || feat_h <= 0 || feat_w <= 0) return FBEV_ERR_SHAPE;
+  if (((uintptr_t)depth % 8) || ((uintptr_t)feat % 4) || ((uintptr_t)out % 4) || ((uintptr_t)u_coords % 4) ||
+      ((uintptr_t)v_coords % 4) || ((uintptr_t)z_coords % 4) || ((uintptr_t)batch_camera_indices % 4) ||
+      ((uintptr_t)ranks_bev % 4) || ((uintptr_t)interval_starts % 4) || ((uintptr_t)interval_lengths % 4))
+    return FBEV_ERR_ALIGN;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const bool vec = c % 4 == 0 && (uintptr_t)feat % 16 == 0;
+  const long long threads = (long long)n_intervals * (vec ? c / 4 : c);
+  if ((threads + 255) / 256 >= (1ll << 31)) return FBEV_ERR_RANGE;
+  const unsigned blocks = (unsigned)((threads + 255) / 256);
+  const int laplace = depth_distribution == 1 ? 1 : 0;
+  if (vec)
+    pillar_pool_kernel<4><<<blocks, 256, 0, st>>>(c, n_intervals, depth, feat, u_coords, v_coords, z_coords, batch_camera_indices,
+                                                  ranks_bev, interval_starts, interval_lengths, feat_h, feat_w, epsilon, laplace, out);
+  else
+    pillar_pool_kernel<1><<<blocks, 256, 0, st>>>(c, n_intervals, depth, feat, u_coords, v_coords, z_coords, batch_camera_indices,
+                                                  ranks_bev, interval_starts, interval_lengths, feat_h, feat_w, epsilon, laplace, out);
+  return cudaGetLastError() == cudaSuccess ? FBEV_OK : FBEV_ERR_LAUNCH;
+}
+
 int fbev_probe_read(const void* buf, size_t bytes, int repeats, void* sink, void* stream) {
   if (buf == nullptr || sink == nullptr) return FBEV_ERR_NULL;
   if (((uintptr_t)buf % 16) || ((uintptr_t)sink % 4)) return FBEV_ERR_ALIGN;

@@ -101,6 +101,67 @@ __global__ void projection_kernel(const float* __restrict__ s2e, const float* __
     }
 }
 
+// ---------------------------------------------------------------------------
+// Pillar pooling over pre-sorted sample lists (the reference's comparison baseline)
+// ---------------------------------------------------------------------------
+// Counterpart of sampling_vt_pillarpool_fused_kernel (flashbev/flashbevpool/src/sampling_vt_cuda.cu:24-127): the
+// caller has projected every voxel, kept the samples inside a camera's view, sorted them by BEV cell and cut the
+// sorted list into one interval per cell; the kernel pools each interval (bilinear depth parameters, likelihood
+// weight, bilinear feature, mean over the interval's samples, no weight threshold).  One thread owns an
+// interval and VEC consecutive channels (the reference: one channel), so that the four corner reads of a sample
+// are 16-byte loads when VEC = 4; the samples of an interval are walked in list order, as there.
+template <int VEC>
+__global__ void __launch_bounds__(256) pillar_pool_kernel(int c, int n_intervals, const float* __restrict__ depth,
+                                                          const float* __restrict__ feat, const float* __restrict__ u_coords,
+                                                          const float* __restrict__ v_coords, const float* __restrict__ z_coords,
+                                                          const int* __restrict__ batch_camera, const int* __restrict__ ranks_bev,
+                                                          const int* __restrict__ interval_starts,
+                                                          const int* __restrict__ interval_lengths, int feat_h, int feat_w,
+                                                          float epsilon, int laplace, float* __restrict__ out) {
+  const int per = c / VEC;  // threads per interval
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long interval = idx / per;
+  if (interval >= n_intervals) return;
+  const int c0 = (int)(idx - interval * per) * VEC;
+  const int start = __ldg(interval_starts + interval), len = __ldg(interval_lengths + interval);
+  float acc[VEC];
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) acc[k] = 0.0f;
+  int count = 0;
+  for (int i = start; i < start + len; ++i) {
+    const float fu = __ldg(u_coords + i), fv = __ldg(v_coords + i), d = __ldg(z_coords + i);
+    if (!(fu >= 0.0f && fu < (float)feat_w && fv >= 0.0f && fv < (float)feat_h && d > 0.0f)) continue;  // :65-67
+    const int u0 = (int)floorf(fu), v0 = (int)floorf(fv);
+    const int u1 = min(u0 + 1, feat_w - 1), v1 = min(v0 + 1, feat_h - 1);
+    const float wu = fu - (float)u0, wv = fv - (float)v0;
+    const float w00 = (1.0f - wu) * (1.0f - wv), w01 = wu * (1.0f - wv), w10 = (1.0f - wu) * wv, w11 = wu * wv;
+    const size_t cam = (size_t)__ldg(batch_camera + i) * feat_h * feat_w;  // texel (0, 0) of the sample's camera
+    const size_t t00 = cam + (size_t)v0 * feat_w + u0, t01 = cam + (size_t)v0 * feat_w + u1;
+    const size_t t10 = cam + (size_t)v1 * feat_w + u0, t11 = cam + (size_t)v1 * feat_w + u1;
+    const float2 p00 = __ldg(reinterpret_cast<const float2*>(depth) + t00), p01 = __ldg(reinterpret_cast<const float2*>(depth) + t01);
+    const float2 p10 = __ldg(reinterpret_cast<const float2*>(depth) + t10), p11 = __ldg(reinterpret_cast<const float2*>(depth) + t11);
+    const float mean = w00 * p00.x + w01 * p01.x + w10 * p10.x + w11 * p11.x;      // :89-97
+    const float sigma = w00 * p00.y + w01 * p01.y + w10 * p10.y + w11 * p11.y;
+    const float zs = (d - mean) / (sigma + epsilon);
+    const float wgt = laplace ? 0.5f * expf(-fabsf(zs)) / (sigma + epsilon) : expf(-0.5f * zs * zs) / (sigma + epsilon);
+    if (VEC == 4) {
+      const float4 f00 = __ldg(reinterpret_cast<const float4*>(feat + t00 * c + c0)), f01 = __ldg(reinterpret_cast<const float4*>(feat + t01 * c + c0));
+      const float4 f10 = __ldg(reinterpret_cast<const float4*>(feat + t10 * c + c0)), f11 = __ldg(reinterpret_cast<const float4*>(feat + t11 * c + c0));
+      acc[0] += wgt * (w00 * f00.x + w01 * f01.x + w10 * f10.x + w11 * f11.x);
+      acc[1 % VEC] += wgt * (w00 * f00.y + w01 * f01.y + w10 * f10.y + w11 * f11.y);
+      acc[2 % VEC] += wgt * (w00 * f00.z + w01 * f01.z + w10 * f10.z + w11 * f11.z);
+      acc[3 % VEC] += wgt * (w00 * f00.w + w01 * f01.w + w10 * f10.w + w11 * f11.w);
+    } else {
+      acc[0] += wgt * (w00 * __ldg(feat + t00 * c + c0) + w01 * __ldg(feat + t01 * c + c0) + w10 * __ldg(feat + t10 * c + c0) +
+                       w11 * __ldg(feat + t11 * c + c0));
+    }
+    ++count;
+  }
+  float* o = out + (size_t)__ldg(ranks_bev + start) * c + c0;  // the interval's BEV cell (:119-125)
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) o[k] = count > 0 ? acc[k] / (float)count : 0.0f;
+}
+
 __global__ void probe_read_kernel(const uint4* __restrict__ buf, size_t n16, int repeats, unsigned* sink) {
   unsigned acc = 0;
   const size_t stride = (size_t)gridDim.x * blockDim.x;

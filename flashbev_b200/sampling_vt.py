@@ -12,8 +12,11 @@ tools/profile_differences.py:237 rely on.
                             materialised), the comparison baseline of the reference's
                             harnesses.  Written with explicit gathers; it is a comparison
                             method, not a fallback of the fused path.
-  use_bev_pool=True      -> the reference's sort-based pillar-pool baseline
-                            (sampling_vt.py:381-447) is not provided.
+  fuse_projection=False, use_bev_pool=True
+                         -> the reference's sort-based pillar-pool baseline (sampling_vt.py:296-335,
+                            381-447): project every voxel, keep the samples a camera sees, sort them
+                            by BEV cell, pool each cell's interval with ``sampling_vt_pillarpool_fused``.
+                            A comparison method too.
 """
 from __future__ import annotations
 
@@ -21,6 +24,7 @@ import torch
 import torch.nn as nn
 
 from .flash_bevpool import flash_bevpool
+from .sampling_vt_ops import sampling_vt_pillarpool_fused
 
 
 def create_projection_matrix(sensor2ego, ego2global, camera2imgs, post_rots, post_trans, bda):
@@ -101,6 +105,41 @@ def dense_sampling_vt(features_pv, depths, projection_matrices, image_size, roi_
     return (bev / cnt.unsqueeze(1)).transpose(-1, -2).contiguous()                        # [B,C,Y,X]
 
 
+def project_voxels(projection_matrices, grid_axes, epsilon=1e-6):
+    """(u, v, d) of every voxel centre in every camera: [B,N,X,Y,Z] each (sampling_vt.py:449-466).
+    ``grid_axes``: the three 1-D tensors of voxel-centre coordinates."""
+    ax, ay, az = grid_axes
+    P = projection_matrices.to(ax.dtype)
+    # P[..., 0:3] . (x, y, z) + P[..., 3], axis by axis: no [V,4] point tensor is formed
+    px = P[..., 0].unsqueeze(-1) * ax          # [B,N,3,X]
+    py = P[..., 1].unsqueeze(-1) * ay          # [B,N,3,Y]
+    pz = P[..., 2].unsqueeze(-1) * az          # [B,N,3,Z]
+    uvd = (px[..., :, None, None] + py[..., None, :, None] + pz[..., None, None, :] +
+           P[..., 3][..., None, None, None])  # [B,N,3,X,Y,Z]
+    d = uvd[:, :, 2]
+    cd = torch.where(d >= 0, d.clamp(min=epsilon), d.clamp(max=-epsilon))
+    return uvd[:, :, 0] / cd, uvd[:, :, 1] / cd, d
+
+
+def pillar_pool_lists(u, v, d, image_size, feature_size):
+    """Sample lists of the pillar-pool baseline (sampling_vt.py:296-361): the (b, n, x, y, z) samples that fall inside
+    their camera's feature map with positive depth, ordered by BEV cell (b, x, y), and one interval per cell that
+    has any.  Returns feature-map coordinates u, v, depth, camera index b * N + n, cell rank, interval starts and
+    lengths."""
+    B, N, X, Y, Z = d.shape
+    fh, fw = feature_size
+    fu = u / image_size[1] * fw
+    fv = v / image_size[0] * fh
+    inside = (fu >= 0) & (fu < fw) & (fv >= 0) & (fv < fh) & (d > 0)
+    b, n, x, y, _ = inside.nonzero(as_tuple=True)       # row-major: camera-major, height-minor within a cell
+    rank = (b * X + x) * Y + y
+    rank, order = torch.sort(rank, stable=True)
+    cells, lengths = torch.unique_consecutive(rank, return_counts=True)
+    starts = torch.cumsum(lengths, 0) - lengths
+    pick = lambda t: t[inside][order]  # noqa: E731
+    return pick(fu), pick(fv), pick(d), (b * N + n)[order], rank, starts, lengths
+
+
 class SamplingVT(nn.Module):
     """View transformer: 1x1 context / depth heads followed by BEV pooling (sampling_vt.py:126-234)."""
 
@@ -135,6 +174,11 @@ class SamplingVT(nn.Module):
         self.register_buffer("sample_grid_size", torch.tensor(
             [(a[1] - a[0]) / a[2] for a in axes], dtype=torch.int32))
         self._grid = tuple(int(v) for v in self.sample_grid_size.tolist())
+        if not fuse_projection:
+            # buffers of the reference's unfused branches (sampling_vt.py:187-196), so that its state dicts load
+            self.register_buffer("voxel_size", torch.as_tensor([a[2] for a in axes]))
+            centres = [torch.linspace(a[0], a[1], g + 1)[:-1] + a[2] / 2.0 for a, g in zip(axes, self._grid)]
+            self.register_buffer("coords_3d", torch.stack(torch.meshgrid(*centres, indexing="ij"), dim=-1))
         # small constant inputs of the operator, built once per (device, B, N, h, w)
         self._const_cache = {}
 
@@ -203,7 +247,15 @@ class SamplingVT(nn.Module):
             )
             return bev.movedim(-1, -3)
         if self.use_bev_pool:
-            raise NotImplementedError("the sort-based pillar-pool baseline (use_bev_pool=True) is not provided; "
-                                      "use fuse_projection=True or the dense path")
+            c3 = self.coords_3d
+            u, v, d = project_voxels(projection_matrices, (c3[:, 0, 0, 0], c3[0, :, 0, 1], c3[0, 0, :, 2]))
+            fu, fv, fd, cams, ranks, starts, lengths = pillar_pool_lists(u, v, d, self.image_size, (h, w))
+            X, Y = self._grid[0], self._grid[1]
+            bev = sampling_vt_pillarpool_fused(
+                depth=depths.movedim(-3, -1), feat=features_pv.movedim(-3, -1), u_coords=fu, v_coords=fv, z_coords=fd,
+                batch_camera_indices=cams, ranks_bev=ranks, bev_feat_shape=(B, X, Y, 1, features_pv.shape[-3]),
+                interval_starts=starts, interval_lengths=lengths, batch_size=B, num_cameras=N, feat_h=h, feat_w=w,
+                epsilon=1e-6, depth_distribution=1 if self.depth_distribution == "laplace" else 0)
+            return bev.squeeze(-1).movedim(-1, -2)   # [B,C,X,Y,1] -> [B,C,Y,X]
         return dense_sampling_vt(features_pv, depths, projection_matrices, self.image_size, self.roi_ranges,
                                  self._grid, self.depth_distribution, self.depth_weight_threshold)

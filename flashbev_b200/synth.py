@@ -112,6 +112,38 @@ def rig_projection(image_size: Tuple[int, int], n_cams: int = 6, jitter_seed: Op
     return out.astype(np.float32)
 
 
+def module_inputs(B: int = 2, N: int = 6, C: int = 32, H: int = 8, W: int = 22, seed: int = 5):
+    """The seven-tensor input list of ``SamplingVT.forward`` (sampling_vt.py:225-239) for the synthetic rig, on the
+    CPU: image features [B,N,C,H,W] ~ N(0,1), sensor2ego, ego2global, camera2imgs, post_rots, post_trans, bda, and
+    the image size (16x the feature map).  Every sample's rig is jittered; post_rots / post_trans hold a small
+    seeded resize-and-shift augmentation so that the matrix builder has something to fold in."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(B, N, C, H, W, generator=g)
+    image = (16 * H, 16 * W)
+    f, cx, cy = 0.35 * image[1], image[1] / 2.0, image[0] / 2.0
+    K = torch.eye(3).repeat(B, N, 1, 1)
+    K[..., 0, 0] = K[..., 1, 1] = f
+    K[..., 0, 2], K[..., 1, 2] = cx, cy
+    s2e = torch.eye(4).repeat(B, N, 1, 1)
+    rng = np.random.RandomState(seed + 100)
+    for b in range(B):
+        for n in range(N):
+            yaw = math.radians(YAWS_DEG[n % len(YAWS_DEG)] + rng.uniform(-2.0, 2.0))
+            t = np.array([0.8 * math.cos(yaw), 0.8 * math.sin(yaw), 1.5]) + rng.uniform(-0.05, 0.05, size=3)
+            s2e[b, n, :3, 0] = torch.tensor([math.sin(yaw), -math.cos(yaw), 0.0])
+            s2e[b, n, :3, 1] = torch.tensor([0.0, 0.0, -1.0])
+            s2e[b, n, :3, 2] = torch.tensor([math.cos(yaw), math.sin(yaw), 0.0])
+            s2e[b, n, :3, 3] = torch.from_numpy(t).float()
+    post_rots = torch.eye(3).repeat(B, N, 1, 1)
+    scale = torch.from_numpy(rng.uniform(0.95, 1.05, size=(B, N))).float()
+    post_rots[..., 0, 0] = scale
+    post_rots[..., 1, 1] = scale
+    post_trans = torch.zeros(B, N, 3)
+    post_trans[..., :2] = torch.from_numpy(rng.uniform(-6.0, 6.0, size=(B, N, 2))).float()
+    inputs = [x, s2e, torch.eye(4).repeat(B, N, 1, 1), K, post_rots, post_trans, torch.eye(4).repeat(B, 1, 1)]
+    return inputs, image
+
+
 def _torch_dtype(name: str) -> torch.dtype:
     return {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}[name]
 

@@ -235,6 +235,18 @@ int fbev_flash_bevpool_grad(int total_threads, int num_channels, int num_cameras
 int fbev_projection_matrices(const float* sensor2ego, const float* camera2imgs, const float* post_rots,
                              const float* post_trans, float* out, int count, void* stream);
 
+/* Pillar pooling over pre-sorted sample lists: drop-in for the launcher of the reference's comparison baseline
+ *   void sampling_vt_pillarpool_fused(int c, int n_intervals, ...)   src/sampling_vt_cuda.cu:129-134
+ * (bound by sampling_vt_pillarpool_fused_forward, src/sampling_vt.cpp:13-55), same arguments in the same order plus
+ * the stream.  All device, float32 / int32: depth [B,N,h,w,2], feat [B,N,h,w,c]; per sample u, v (feature-map
+ * coordinates), z (camera depth), batch_camera_indices (batch * cameras + camera), ranks_bev (flat BEV cell);
+ * per interval its first sample and length.  out (flat [cells, c]) receives the mean over each interval's
+ * samples; cells without an interval are not written (the caller zero-fills, sampling_vt_ops.py:24). */
+int fbev_pillar_pool(int c, int n_intervals, const float* depth, const float* feat, const float* u_coords,
+                     const float* v_coords, const float* z_coords, const int* batch_camera_indices, const int* ranks_bev,
+                     const int* interval_starts, const int* interval_lengths, int batch_size, int num_cameras, int feat_h,
+                     int feat_w, float epsilon, int depth_distribution, float* out, void* stream);
+
 const char* fbev_strerror(int status);
 int fbev_version(void);
 /* SHA-256 (hex) of the sources and compiler flags this library was built from; the Python binding refuses a

@@ -189,3 +189,38 @@ def indices(p: Problem):
                                    va.ctypes.data, cnt.ctypes.data)
     assert rc == 0
     return {"u0": u0, "v0": v0, "kbin": kb, "valid": va, "count": cnt}
+
+
+def pillar_pool(depth, feat, u, v, z, batch_camera, ranks, starts, lengths, n_cells, laplace, epsilon=1e-6,
+                dtype=np.float64):
+    """Pillar pooling over pre-sorted sample lists, restating sampling_vt_pillarpool_fused_kernel
+    (flashbev/flashbevpool/src/sampling_vt_cuda.cu:24-127) with numpy: depth [BN,h,w,2], feat [BN,h,w,C], flat
+    per-sample u, v (feature-map coordinates), z (camera depth), camera index, BEV cell rank; per interval its
+    first sample and length.  Returns [n_cells, C]: the mean over each interval's accepted samples, zero
+    elsewhere.  Parity: pinned through the module fixtures (the dense branch of the reference module computes
+    the same mean when no weight threshold is set)."""
+    depth = np.asarray(depth, dtype)
+    feat = np.asarray(feat, dtype)
+    u, v, z = (np.asarray(a, dtype) for a in (u, v, z))
+    cam = np.asarray(batch_camera, np.int64)
+    h, w = depth.shape[1:3]
+    ok = (u >= 0) & (u < w) & (v >= 0) & (v < h) & (z > 0)                     # :65-67
+    u0 = np.floor(u).astype(np.int64).clip(0, w - 1)
+    v0 = np.floor(v).astype(np.int64).clip(0, h - 1)
+    u1, v1 = np.minimum(u0 + 1, w - 1), np.minimum(v0 + 1, h - 1)
+    wu, wv = u - u0, v - v0
+    wts = [((1 - wu) * (1 - wv), v0, u0), (wu * (1 - wv), v0, u1), ((1 - wu) * wv, v1, u0), (wu * wv, v1, u1)]
+    par = sum(wt[:, None] * depth[cam, vv, uu] for wt, vv, uu in wts)          # :89-97
+    f = sum(wt[:, None] * feat[cam, vv, uu] for wt, vv, uu in wts)             # :104-107
+    mean, sigma = par[:, 0], par[:, 1]
+    zs = (z - mean) / (sigma + epsilon)
+    wgt = 0.5 * np.exp(-np.abs(zs)) / (sigma + epsilon) if laplace else np.exp(-0.5 * zs * zs) / (sigma + epsilon)
+    wgt = np.where(ok, wgt, 0.0)
+    interval = np.repeat(np.arange(len(starts)), np.asarray(lengths, np.int64))
+    acc = np.zeros((len(starts), feat.shape[-1]), dtype)
+    np.add.at(acc, interval, wgt[:, None] * f)
+    cnt = np.bincount(interval, weights=ok.astype(dtype), minlength=len(starts))
+    out = np.zeros((n_cells, feat.shape[-1]), dtype)
+    cells = np.asarray(ranks, np.int64)[np.asarray(starts, np.int64)]
+    out[cells] = np.where(cnt[:, None] > 0, acc / np.maximum(cnt, 1)[:, None], 0.0)
+    return out

@@ -1,6 +1,6 @@
 """Generates tests/golden/*.npz from the reference's own dense PyTorch path.
 
-Run in a container that has the reference checkout (see --reference); the
+Run where the reference checkout is available (see --reference); the
 fixtures it writes are committed, this script is how they were made:
 
     python tests/golden/make_golden.py [--reference /path/to/FlashBEV]
@@ -12,6 +12,7 @@ gradient.  The reference package imports its compiled extensions at import time;
 are replaced by empty stand-in modules because only the pure-PyTorch functions are used.
 One case takes its camera rig from the reference's calibration fixture
 (inputs/calib_nuscenes.json) through the reference's ``create_projection_matrix``.
+module_dense_*.npz hold a run of the reference's ``SamplingVT`` module itself (dense branch).
 """
 import argparse
 import json
@@ -101,16 +102,49 @@ def projection_case(R):
     print("projection_synthetic", tuple(P.shape), os.path.getsize(path), "bytes")
 
 
+MODULE_GRID = {"x": [-20.0, 20.0, 1.0], "y": [-16.0, 16.0, 1.0], "z": [-4.0, 2.0, 1.0], "depth": [1.0, 60.0, 1.0]}
+
+
+def module_case(R):
+    """The reference's own module, dense branch: ``SamplingVT(fuse_projection=False, use_bev_pool=False)``
+    (sampling_vt.py:126-294) with the 1x1 heads initialised under seed 42 as tools/profile_differences.py:218
+    does.  Recorded: the seven inputs, the state dict, the BEV output and the depth head's output."""
+    inputs, image = synth.module_inputs(B=2, N=6, C=32, H=8, W=22, seed=5)
+    names = ("x", "sensor2ego", "ego2global", "camera2imgs", "post_rots", "post_trans", "bda")
+    for dist in ("laplace", "gaussian"):
+        torch.manual_seed(42)
+        m = R.SamplingVT(MODULE_GRID, image, downsample=16, in_channels=32, out_channels=16, fuse_projection=False,
+                         use_bev_pool=False, depth_distribution=dist, depth_weight_threshold=0.0).eval()
+        state = {k: v.detach().clone() for k, v in m.state_dict().items() if k.split(".")[0] in
+                 ("context_network", "depth_network")}
+        with torch.no_grad():
+            bev, depths = m([t.clone() for t in inputs])
+        path = os.path.join(HERE, f"module_dense_{dist}.npz")
+        arrays = {f"in_{n}": t.numpy() for n, t in zip(names, inputs)}
+        arrays.update({f"state_{k}": v.numpy() for k, v in state.items()})
+        np.savez_compressed(path, bev=bev.numpy(), depths=depths.numpy(), image=np.array(image, np.int32),
+                            torch_version=np.array(torch.__version__), **arrays)
+        print(f"module_dense_{dist}", tuple(bev.shape), "nonzero cells", int((bev.abs().sum(1) > 0).sum()),
+              os.path.getsize(path), "bytes")
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("FBEV_REFERENCE") or os.path.join(
+        os.path.dirname(os.path.dirname(os.path.dirname(HERE))), "reference"),
+        help="root of the reference checkout (default: $FBEV_REFERENCE, else a directory 'reference' beside this repository)")
     ap.add_argument("--only-projection", action="store_true", help="write only projection_synthetic.npz")
+    ap.add_argument("--only-module", action="store_true", help="write only module_dense_*.npz")
     args = ap.parse_args()
     R = load_reference(args.reference)
     torch.manual_seed(0)
+    if args.only_module:
+        module_case(R)
+        return
     projection_case(R)
     if args.only_projection:
         return
+    module_case(R)
 
     small = synth.Workload("golden_small", B=2, N=6, C=8, H=8, W=22, D=16, X=24, Y=20, Z=4, xy_extent=25.6,
                            d0=1.0, delta=2.0, dtype="fp32", seed=11, jitter=True)

@@ -86,12 +86,41 @@ def inputs_for(w, mode):
 
 def golden_files():
     """Operator fixtures (the calibration fixture projection_*.npz is read by projection_golden)."""
-    return sorted(f for f in glob.glob(os.path.join(GOLDEN, "*.npz")) if not os.path.basename(f).startswith("projection_"))
+    return sorted(f for f in glob.glob(os.path.join(GOLDEN, "*.npz"))
+                  if not os.path.basename(f).startswith(("projection_", "module_")))
 
 
 def projection_golden():
     """Calibration arrays and the matrices the reference's create_projection_matrix made of them."""
     return dict(np.load(os.path.join(GOLDEN, "projection_synthetic.npz")))
+
+
+MODULE_GRID = {"x": [-20.0, 20.0, 1.0], "y": [-16.0, 16.0, 1.0], "z": [-4.0, 2.0, 1.0], "depth": [1.0, 60.0, 1.0]}
+MODULE_INPUT_NAMES = ("x", "sensor2ego", "ego2global", "camera2imgs", "post_rots", "post_trans", "bda")
+
+
+def module_golden(dist):
+    """A recorded run of the reference's own SamplingVT module, dense branch (tests/golden/make_golden.py,
+    module_case): the input list, the state of the two 1x1 heads, the BEV output and the depth head's output."""
+    g = np.load(os.path.join(GOLDEN, f"module_dense_{dist}.npz"))
+    inputs = [torch.from_numpy(g[f"in_{n}"]) for n in MODULE_INPUT_NAMES]
+    state = {k[len("state_"):]: torch.from_numpy(g[k]) for k in g.files if k.startswith("state_")}
+    return inputs, state, tuple(int(v) for v in g["image"]), g["bev"], g["depths"]
+
+
+def harness_metrics(out, ref):
+    """The figures the reference's parity harness judges by (tools/profile_differences.py:17-67, 70-127):
+    MSE < 1e-6, MAE < 1e-6, mean of |diff| / max(|ref|, 1e-8) < 1e-3, cosine > 0.9999."""
+    a = np.asarray(out, np.float64).ravel()
+    b = np.asarray(ref, np.float64).ravel()
+    diff = np.abs(a - b)
+    return {"mse": float((diff ** 2).mean()), "mae": float(diff.mean()),
+            "mean_rel": float((diff / np.maximum(np.abs(b), 1e-8)).mean()),
+            "cos": float((a * b).sum() / (np.linalg.norm(a) * np.linalg.norm(b) + 1e-30))}
+
+
+def harness_pass(m):
+    return m["mse"] < 1e-6 and m["mae"] < 1e-6 and m["mean_rel"] < 1e-3 and m["cos"] > 0.9999
 
 
 def golden_problem(g):

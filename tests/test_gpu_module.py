@@ -13,30 +13,61 @@ GRID = {"x": [-20.0, 20.0, 1.0], "y": [-16.0, 16.0, 1.0], "z": [-4.0, 2.0, 1.0],
 
 
 def _module_inputs(device, B=2, N=6, C=32, H=8, W=22):
-    g = torch.Generator().manual_seed(5)
-    x = torch.randn(B, N, C, H, W, generator=g)
-    image = (16 * H, 16 * W)
-    P = torch.stack([torch.from_numpy(synth.rig_projection(image, N, jitter_seed=100 + b)) for b in range(B)])
-    # sensor2ego / intrinsics that reproduce P: K = I-like split is not needed, feed P through identity parts
-    K = torch.eye(3).repeat(B, N, 1, 1)
-    s2e = torch.eye(4).repeat(B, N, 1, 1)
-    # P = [K|0] @ inv(s2e)  with K = P[:, :, :, :3] and translation folded: solve s2e from P is overkill; instead
-    # use the rig's own pieces: f, cx, cy and the camera poses
-    import math
-    f, cx, cy = 0.35 * image[1], image[1] / 2.0, image[0] / 2.0
-    K[:, :, 0, 0] = f
-    K[:, :, 1, 1] = f
-    K[:, :, 0, 2] = cx
-    K[:, :, 1, 2] = cy
-    for n in range(N):
-        yaw = math.radians(synth.YAWS_DEG[n])
-        s2e[:, n, :3, 0] = torch.tensor([math.sin(yaw), -math.cos(yaw), 0.0])
-        s2e[:, n, :3, 1] = torch.tensor([0.0, 0.0, -1.0])
-        s2e[:, n, :3, 2] = torch.tensor([math.cos(yaw), math.sin(yaw), 0.0])
-        s2e[:, n, :3, 3] = torch.tensor([0.8 * math.cos(yaw), 0.8 * math.sin(yaw), 1.5])
-    inputs = [x, s2e, torch.eye(4).repeat(B, N, 1, 1), K, torch.eye(3).repeat(B, N, 1, 1), torch.zeros(B, N, 3),
-              torch.eye(4).repeat(B, 1, 1)]
+    inputs, image = synth.module_inputs(B=B, N=N, C=C, H=H, W=W, seed=5)
     return [t.to(device) for t in inputs], image
+
+
+@pytest.mark.parametrize("dist", ["laplace", "gaussian"])
+@pytest.mark.parametrize("method", ["fused", "pillar_pool", "dense"])
+def test_module_reproduces_a_recorded_run_of_the_reference_module(cuda_device, parity_report, dist, method):
+    """The reference's own SamplingVT (dense branch, 1x1 heads initialised under seed 42, run recorded in
+    tests/golden/module_dense_*.npz): its state dict loaded into this module, every method of this module on the
+    GPU, judged by the figures and tolerances of the reference's parity harness
+    (tools/profile_differences.py:75-77,104)."""
+    from flashbevpool import SamplingVT  # the reference's package name
+    from tests.helpers import MODULE_GRID, harness_metrics, harness_pass, module_golden
+    inputs, state, image, bev_ref, depths_ref = module_golden(dist)
+    m = SamplingVT(MODULE_GRID, image, downsample=16, in_channels=32, out_channels=16,
+                   fuse_projection=method == "fused", use_bev_pool=method == "pillar_pool", depth_distribution=dist,
+                   depth_weight_threshold=0.0)
+    missing, unexpected = m.load_state_dict(state, strict=False)
+    assert not unexpected and all(k.split(".")[0] not in ("context_network", "depth_network") for k in missing)
+    m = m.to(cuda_device).eval()
+    with torch.no_grad():
+        bev, depths = m([t.to(cuda_device) for t in inputs])
+    assert tuple(bev.shape) == bev_ref.shape
+    assert np.abs(depths.float().cpu().numpy() - depths_ref).max() < 1e-4
+    met = harness_metrics(bev.float().cpu().numpy(), bev_ref)
+    parity_report(f"module {method} {dist} vs the reference module's recorded output: mse {met['mse']:.2e} mae {met['mae']:.2e} "
+                  f"mean-rel {met['mean_rel']:.2e} cos {met['cos']:.7f}")
+    assert harness_pass(met), met
+
+
+@pytest.mark.parametrize("laplace", [True, False])
+@pytest.mark.parametrize("C", [16, 6])
+def test_pillar_pool_kernel_matches_its_restatement(cuda_device, laplace, C):
+    """fbev_pillar_pool (16-byte and scalar channel paths) against the numpy restatement on the same lists."""
+    from oracle import oracle as O
+    from flashbev_b200.sampling_vt import pillar_pool_lists, project_voxels
+    from flashbev_b200.sampling_vt_ops import sampling_vt_pillarpool_fused
+    w = synth.Workload("pillar", B=2, N=6, C=C, H=8, W=22, D=8, X=40, Y=36, Z=5, xy_extent=30.0, dtype="fp32", seed=23,
+                       jitter=True)
+    inp = synth.make_inputs(w, "parametric")
+    axes = [torch.linspace(lo, hi, g + 1)[:-1] + (hi - lo) / g / 2 for (lo, hi), g in
+            zip(((-30.0, 30.0), (-30.0, 30.0), w.z_range), w.grid)]
+    u, v, d = project_voxels(inp["projection_matrices"], axes)
+    fu, fv, fd, cams, ranks, starts, lengths = pillar_pool_lists(u, v, d, w.image_size, (w.H, w.W))
+    feat, dep = inp["image_feats"].flatten(0, 1), inp["depth_params"].flatten(0, 1)
+    ref = O.pillar_pool(dep.numpy(), feat.numpy(), fu.numpy(), fv.numpy(), fd.numpy(), cams.numpy(), ranks.numpy(),
+                        starts.numpy(), lengths.numpy(), w.B * w.X * w.Y, laplace)
+    dev = lambda t: t.to(cuda_device)  # noqa: E731
+    out = sampling_vt_pillarpool_fused(dev(dep), dev(feat), dev(fu), dev(fv), dev(fd), dev(cams), dev(ranks),
+                                       (w.B, w.X, w.Y, 1, C), dev(starts), dev(lengths), w.B, w.N, w.H, w.W, 1e-6,
+                                       1 if laplace else 0)
+    assert out.shape == (w.B, C, w.X, w.Y, 1)
+    got = out.squeeze(-1).movedim(1, -1).reshape(-1, C).cpu().numpy()
+    assert rel_err(got, ref) < 1e-5
+    assert int(starts.numel()) > 1000
 
 
 @pytest.mark.parametrize("dist", ["laplace", "gaussian"])

@@ -42,3 +42,55 @@ def test_parameter_names_match_the_reference_module():
     keys = set(make().state_dict())
     assert {"context_network.weight", "context_network.bias", "depth_network.0.weight", "depth_network.0.bias",
             "depth_bins", "roi_ranges", "output_grid_size", "sample_grid_size"} <= keys
+
+
+# ---- against a recorded run of the reference's own module (tests/golden/module_dense_*.npz) ----
+import numpy as np  # noqa: E402
+import pytest  # noqa: E402
+
+from tests.helpers import MODULE_GRID, harness_metrics, harness_pass, module_golden  # noqa: E402
+
+
+@pytest.mark.parametrize("dist", ["laplace", "gaussian"])
+def test_dense_branch_reproduces_the_reference_module(dist):
+    """State dict of the reference module (dense branch) loaded into this module's dense branch on the CPU: same
+    heads, same BEV features at the reference harness's own tolerances (tools/profile_differences.py:75-77,104)."""
+    inputs, state, image, bev_ref, depths_ref = module_golden(dist)
+    m = SamplingVT(MODULE_GRID, image, downsample=16, in_channels=32, out_channels=16, fuse_projection=False,
+                   use_bev_pool=False, depth_distribution=dist, depth_weight_threshold=0.0).eval()
+    missing, unexpected = m.load_state_dict(state, strict=False)
+    assert not unexpected and all(k.split(".")[0] not in ("context_network", "depth_network") for k in missing)
+    with torch.no_grad():
+        bev, depths = m(inputs)
+    assert bev.shape == bev_ref.shape and depths.shape == depths_ref.shape
+    assert np.abs(depths.numpy() - depths_ref).max() < 1e-5
+    met = harness_metrics(bev.numpy(), bev_ref)
+    assert harness_pass(met), met
+
+
+@pytest.mark.parametrize("dist", ["laplace", "gaussian"])
+def test_pillar_pool_lists_and_oracle_reproduce_the_reference_module(dist):
+    """The pillar-pool baseline's host side (projection of every voxel, sample lists sorted by BEV cell, intervals)
+    fed to the numpy restatement of its kernel gives the reference module's BEV features: without a weight
+    threshold the baseline and the dense branch compute the same mean.  This pins the restatement."""
+    from oracle import oracle as O
+    from flashbev_b200.sampling_vt import create_projection_matrix, pillar_pool_lists, project_voxels
+    inputs, state, image, bev_ref, _ = module_golden(dist)
+    m = SamplingVT(MODULE_GRID, image, downsample=16, in_channels=32, out_channels=16, fuse_projection=False,
+                   use_bev_pool=True, depth_distribution=dist, depth_weight_threshold=0.0).eval()
+    m.load_state_dict(state, strict=False)
+    with torch.no_grad():
+        x = inputs[0].flatten(0, 1)
+        feats = m._pointwise_conv(m.context_network, x)
+        depths = m.forward_depth(x)
+        P = create_projection_matrix(*inputs[1:7])
+        c3 = m.coords_3d
+        u, v, d = project_voxels(P, (c3[:, 0, 0, 0], c3[0, :, 0, 1], c3[0, 0, :, 2]))
+        fu, fv, fd, cams, ranks, starts, lengths = pillar_pool_lists(u, v, d, image, feats.shape[-2:])
+    B, (X, Y, _) = inputs[0].shape[0], m._grid
+    assert int(lengths.sum()) == fu.numel() and bool((ranks[1:] >= ranks[:-1]).all())
+    out = O.pillar_pool(depths.movedim(1, -1).numpy(), feats.movedim(1, -1).numpy(), fu.numpy(), fv.numpy(), fd.numpy(),
+                        cams.numpy(), ranks.numpy(), starts.numpy(), lengths.numpy(), B * X * Y, dist == "laplace")
+    bev = out.reshape(B, X, Y, -1).transpose(0, 3, 2, 1)   # [B,X,Y,C] -> [B,C,Y,X]
+    met = harness_metrics(bev, bev_ref)
+    assert harness_pass(met), met
