@@ -39,11 +39,18 @@ import torch  # noqa: E402
 
 from flashbev_b200 import synth  # noqa: E402
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one fwd_kernel launch on the default workload, from the ncu
-# capture summarised in profiles/fwd_kernel_cfg2_z8.md (the output stays in L2 until it is evicted later)
-NCU_DRAM_BYTES_PER_LAUNCH = {"cfg2": 1430656}
-# smsp__inst_executed.sum of fwd_kernel from the same ncu capture (profiles/fwd_kernel_cfg2_z8.md)
-NCU_WARP_INSTRUCTIONS_PER_LAUNCH = {"cfg2": 20070322}
+
+
+def ncu_counters(workload):
+    """Counters of the forward kernel taken with ncu (never in a timed run): DRAM bytes and executed warp
+    instructions per launch, with the commit and command of the capture.  Kept in a small tracked file so that
+    the line printed here says which build they belong to."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "ncu_counters.json")) as fh:
+            return json.load(fh).get("fwd_kernel", {}).get(workload)
+    except Exception:
+        return None
+
 METRIC = "bev_pool_forward_cells_per_s"
 UNIT = "BEV cells/s"
 
@@ -194,6 +201,61 @@ def reference_cuda_kernel_us(w):
             "mode": "float32, laplace, mean pooling, optimize_z_precompute=False, L2 flushed between launches"}
 
 
+def reference_pytorch_cpu(w, threads):
+    """The reference's own dense PyTorch path on the host cores (project_coords + sampling_vt_pytorch,
+    flashbev/flashbevpool/sampling_vt.py:449-466, 36-123), float32, parametric laplace depth, mean pooling, on the
+    same workload with (mean, sigma) taken from the same seeded distribution.  Needs a reference checkout
+    (FBEV_REFERENCE, else a directory "reference" beside this repository); reported as absent otherwise.  A second,
+    labelled CPU figure: the arm's own value stays the OpenMP port."""
+    import types
+    root = os.environ.get("FBEV_REFERENCE") or os.path.join(os.path.dirname(ROOT), "reference")
+    if not os.path.exists(os.path.join(root, "flashbev", "flashbevpool", "sampling_vt.py")):
+        return {"available": False, "why": "no reference checkout on this machine"}
+    try:
+        for n in ("flashbevpool.flashbevpool_ext", "flashbevpool.sampling_vt_ext", "flashbevpool_ext", "sampling_vt_ext"):
+            sys.modules.setdefault(n, types.ModuleType(n))  # the package imports its compiled extensions; unused here
+        saved = list(sys.path)
+        mine = {k: sys.modules.pop(k) for k in list(sys.modules) if k == "flashbevpool" or k.startswith("flashbevpool.")
+                and not k.endswith("_ext")}
+        sys.path.insert(0, os.path.join(root, "flashbev"))
+        try:
+            import flashbevpool.sampling_vt as R
+        finally:
+            sys.path[:] = saved
+            for k in [k for k in sys.modules if k == "flashbevpool" or k.startswith("flashbevpool.")]:
+                del sys.modules[k]
+            sys.modules.update(mine)
+        torch.set_num_threads(threads)
+        wp = synth.workload(w.name, dtype="fp32")
+        inp = synth.make_inputs(wp, "parametric", batch_slice=(0, 1))
+        roi = torch.tensor(wp.roi, dtype=torch.float32).view(3, 2)
+        axes = [torch.linspace(float(roi[i, 0]), float(roi[i, 1]), g + 1)[:-1] + (roi[i, 1] - roi[i, 0]) / g / 2.0
+                for i, g in enumerate(wp.grid)]
+        coords = torch.stack(torch.meshgrid(*axes, indexing="ij"), dim=-1)[None, None].expand(1, wp.N, -1, -1, -1, -1)
+        feats = inp["image_feats"].flatten(0, 1).movedim(-1, 1).contiguous()
+        depth = inp["depth_params"].flatten(0, 1).movedim(-1, 1).contiguous()
+
+        def run():
+            with torch.no_grad():
+                uvd = R.project_coords(coords_xyz=coords, projection_matrices=inp["projection_matrices"])
+                return R.sampling_vt_pytorch(image_uvd=uvd, features_pv=feats, depths=depth, B=1, N=wp.N,
+                                             image_size=wp.image_size, depth_weight_threshold=0.0,
+                                             depth_distribution="laplace", epsilon=1e-6)
+
+        run()
+        times = []
+        for _ in range(3):
+            t0 = time.perf_counter()
+            run()
+            times.append(time.perf_counter() - t0)
+        t = statistics.median(times)
+        return {"available": True, "ms_per_forward": t * 1e3, "cells_per_s": wp.X * wp.Y / t, "threads": threads,
+                "torch": torch.__version__,
+                "what": "project_coords + sampling_vt_pytorch of the reference, float32, laplace, mean pooling, one sample"}
+    except Exception as exc:  # noqa: BLE001
+        return {"available": False, "why": f"{type(exc).__name__}: {str(exc)[:160]}"}
+
+
 def reference_arm(args, rank):
     """CPU implementation of the path on the host cores (the oracle port, OpenMP over BEV rows)."""
     if rank != 0:
@@ -226,7 +288,7 @@ def reference_arm(args, rank):
                                    f"float32 oracle, OpenMP over BEV rows; host has {os.cpu_count()} logical CPUs"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
-        "extra": {"reference_cuda_kernel": ref_gpu},
+        "extra": {"reference_cuda_kernel": ref_gpu, "reference_pytorch_cpu": reference_pytorch_cpu(w, threads)},
     }
     print(json.dumps(line), flush=True)
 
@@ -242,6 +304,7 @@ def main():
     ap.add_argument("--batch-per-gpu", type=int, default=1)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip backward / e2e / L2 probe (for profiler runs)")
+    ap.add_argument("--quick", action="store_true", help="skip the extras on other workloads (cfg3, cfg4, cfg5)")
     ap.add_argument("--only-backward", type=int, default=0, metavar="FLAGS",
                     help="profiler helper: launch only fbev_backward with these flags (1 features, 2 depth, 3 both) "
                          "--steps times on the default workload, print the mean device time and exit")
@@ -382,6 +445,47 @@ def main():
             ms_g, _ = timed(graph.replay, nb, 5)
             extra["fwd_bwd_us_cuda_graph"] = ms_g * 1e3
 
+            # forward kernel with each experiment switch of fbev_debug.h (kept as a record of what each buys)
+            if Bl == 1:
+                exp_us = {}
+                for bits in (0, 1, 2, 4, 3, 6, 7):
+                    lib.fbev_set_experiment(bits)
+                    exp_us[str(bits)] = timed(fwd_raw, max(20, args.steps // 5), 5)[0] * 1e3
+                lib.fbev_set_experiment(0)
+                extra["fwd_us_by_experiment_bits"] = exp_us
+                extra["fwd_experiment_bits"] = "1 L2 prefetch at start, 2 camera cull per group of cells, 4 second round of units drawn from a counter"
+
+            # the training shape (cfg3: B=4, float32, 32x88 maps), forward and forward + backward
+            if world == 1 and not args.quick:
+                w3 = synth.workload("cfg3")
+                in3 = {k: v.to(device) for k, v in synth.make_inputs(w3, args.mode).items()}
+                prob3, keep3 = make_problem(in3["depth_params"], in3["image_feats"], in3["projection_matrices"],
+                                            in3["feature_size"], in3["image_size"], in3["roi_range"], in3["grid_size"],
+                                            DepthSpec(mode_int, **extra_kw) if args.mode == "categorical" else DepthSpec(1),
+                                            1e-6, 0.0)
+                out3 = torch.empty(w3.B, w3.Y, w3.X, w3.C, dtype=torch.float32, device=device)
+                go3 = synth.upstream_grad(w3).to(device)
+                gf3, gd3 = torch.empty_like(keep3[0]), torch.empty_like(keep3[1])
+                nb3 = lib.fbev_backward_scratch_bytes(ctypes.byref(prob3), flags)
+                sc3 = torch.empty(max(nb3, 1), dtype=torch.uint8, device=device)
+
+                def fwd3():
+                    rc = lib.fbev_forward(ctypes.byref(prob3), out3.data_ptr(), None, stream)
+                    if rc:
+                        raise RuntimeError(_lib.strerror(rc))
+
+                def fwd_bwd3():
+                    fwd3()
+                    rc = lib.fbev_backward(ctypes.byref(prob3), go3.data_ptr(), gf3.data_ptr(), gd3.data_ptr(),
+                                           sc3.data_ptr() if nb3 else None, nb3, flags, stream)
+                    if rc:
+                        raise RuntimeError(_lib.strerror(rc))
+
+                extra["cfg3_fwd_us"] = timed(fwd3, 20, 5)[0] * 1e3
+                extra["cfg3_fwd_bwd_us"] = timed(fwd_bwd3, 20, 5)[0] * 1e3
+                extra["cfg3_workload"] = workload_description(w3, w3.B, args.mode) + " + backward (both gradients)"
+                del in3, out3, go3, gf3, gd3, sc3
+
             # the reference's own mode on the same shapes (float32, parametric laplace depth, mean pooling), for
             # comparison with the reference CUDA kernel that `--impl reference` times on the same box
             wp = synth.workload(args.workload, dtype="fp32")
@@ -462,14 +566,98 @@ def main():
                         flash_bevpool(**dev_in, **const, **kw, out=host_out, host_row_chunks=chunks)
                 return step
 
+            # the three inputs packed into one page-locked buffer: one host-to-device copy instead of three
+            order = ("image_feats", "depth_params", "projection_matrices")
+            offs, total = {}, 0
+            for k in order:
+                offs[k] = total
+                total += (host[k].numel() * host[k].element_size() + 255) // 256 * 256
+            packed = torch.empty(total, dtype=torch.uint8).pin_memory()
+            for k in order:
+                n = host[k].numel() * host[k].element_size()
+                packed[offs[k]: offs[k] + n] = host[k].view(-1).view(torch.uint8)
+
+            def unpack(dev_buf):
+                return {k: dev_buf[offs[k]: offs[k] + host[k].numel() * host[k].element_size()].view(host[k].dtype)
+                        .view(host[k].shape) for k in order}
+
+            def e2e_step_packed():
+                with torch.no_grad():
+                    o = flash_bevpool(**unpack(packed.to(device, non_blocking=True)), **const, **kw)
+                    host_out.copy_(o, non_blocking=True)
+
+            def e2e_step_packed_bands():
+                with torch.no_grad():
+                    flash_bevpool(**unpack(packed.to(device, non_blocking=True)), **const, **kw, out=host_out,
+                                  host_row_chunks=4)
+
             ne = max(10, args.steps // 5)
             paths = {"device result + copy": e2e_step, "out=pinned host tensor (kernel stores to it)": e2e_step_direct,
                      "out=pinned host tensor, 4 row bands": e2e_step_bands(4),
-                     "out=pinned host tensor, 8 row bands": e2e_step_bands(8)}
+                     "out=pinned host tensor, 8 row bands": e2e_step_bands(8),
+                     "one packed input copy, device result + copy": e2e_step_packed,
+                     "one packed input copy, 4 row bands": e2e_step_packed_bands}
             times = {name: timed(fn, ne, 5)[0] for name, fn in paths.items()}
             extra["e2e_us_by_path"] = {name: t * 1e3 for name, t in times.items()}
             extra["e2e_path"] = min(times, key=times.get)
             e2e_ms_max = times[extra["e2e_path"]]
+            # the same best path by the host's clock: `ne` calls queued back to back, one synchronisation at the end
+            best_fn = paths[extra["e2e_path"]]
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(ne):
+                best_fn()
+            torch.cuda.synchronize()
+            extra["e2e_us_host_clock_pipelined"] = (time.perf_counter() - t0) / ne * 1e6
+            extra["e2e_note"] = ("e2e is device time (CUDA events around one call, L2 flushed before it); the host-clock "
+                                 "figure queues the calls back to back without a flush and synchronises once")
+            rank_e2e = torch.tensor([times[extra["e2e_path"]]], dtype=torch.float64, device=device)
+            if world > 1:
+                allr = [torch.zeros_like(rank_e2e) for _ in range(world)]
+                dist.all_gather(allr, rank_e2e)
+                extra["e2e_us_per_rank"] = [float(t[0]) * 1e3 for t in allr]
+                try:
+                    extra["rank0_cpu_affinity"] = sorted(os.sched_getaffinity(0))[:4] + ["...", len(os.sched_getaffinity(0))]
+                except AttributeError:
+                    pass
+
+            # the multi-GPU batch configuration (cfg4): 64 samples with their own rigs, 64 / N per GPU, forward and
+            # forward + backward, no collective on the data path
+            if not args.quick and 64 % world == 0:
+                B4 = 64 // world
+                w4 = synth.workload("cfg4")
+                in4 = {k: v.to(device) for k, v in synth.make_inputs(w4, "categorical", batch_slice=(rank * B4, (rank + 1) * B4)).items()}
+                prob4, keep4 = make_problem(in4["depth_params"], in4["image_feats"], in4["projection_matrices"],
+                                            in4["feature_size"], in4["image_size"], in4["roi_range"], in4["grid_size"],
+                                            DepthSpec(2, depth_bin_range=(w4.d0, w4.delta)), 1e-6, 0.0)
+                out4 = torch.empty(B4, w4.Y, w4.X, w4.C, dtype=keep4[0].dtype, device=device)
+                go4 = synth.upstream_grad(w4, B=B4).to(device=device, dtype=keep4[0].dtype)
+                gf4, gd4 = torch.empty_like(keep4[0]), torch.empty_like(keep4[1])
+                nb4 = lib.fbev_backward_scratch_bytes(ctypes.byref(prob4), flags)
+                sc4 = torch.empty(max(nb4, 1), dtype=torch.uint8, device=device)
+
+                def fwd4():
+                    rc = lib.fbev_forward(ctypes.byref(prob4), out4.data_ptr(), None, stream)
+                    if rc:
+                        raise RuntimeError(_lib.strerror(rc))
+
+                def fwd_bwd4():
+                    fwd4()
+                    rc = lib.fbev_backward(ctypes.byref(prob4), go4.data_ptr(), gf4.data_ptr(), gd4.data_ptr(),
+                                           sc4.data_ptr() if nb4 else None, nb4, flags, stream)
+                    if rc:
+                        raise RuntimeError(_lib.strerror(rc))
+
+                t4 = torch.tensor([timed(fwd4, 10, 3)[0], timed(fwd_bwd4, 10, 3)[0]], dtype=torch.float64, device=device)
+                if world > 1:
+                    dist.all_reduce(t4, op=dist.ReduceOp.MAX)
+                extra["cfg4"] = {"workload": f"cfg4: B=64 over {world} GPU(s), {B4} per GPU, per-sample rigs, bf16, categorical",
+                                 "fwd_ms": float(t4[0]), "fwd_bwd_ms": float(t4[1]),
+                                 "fwd_samples_per_s": 64 / (float(t4[0]) * 1e-3),
+                                 "fwd_bwd_samples_per_s": 64 / (float(t4[1]) * 1e-3),
+                                 "fwd_cells_per_s": 64 * w4.X * w4.Y / (float(t4[0]) * 1e-3),
+                                 "backward_scratch_mb_per_gpu": nb4 / 2 ** 20}
+                del in4, out4, go4, gf4, gd4, sc4
 
             if world > 1:
                 # one large sample (cfg5) with its BEV rows split over the ranks: all-gather of the output
@@ -478,11 +666,42 @@ def main():
                 w5 = synth.workload("cfg5")
                 in5 = {k: v.to(device) for k, v in synth.make_inputs(w5, "categorical", batch_slice=(0, 1)).items()}
                 kw5 = dict(depth_distribution=2, depth_bin_range=(w5.d0, w5.delta), depth_weight_threshold=0.0)
+                go5 = synth.upstream_grad(w5).to(device=device, dtype=in5["image_feats"].dtype)
+                y0, y1 = sharding.row_slice(w5.Y, world, rank)
+                go5_rows = go5[:, y0:y1].contiguous()
+                leaf = {k: in5[k].clone().requires_grad_(True) for k in ("image_feats", "depth_params")}
+                rest5 = {k: v for k, v in in5.items() if k not in leaf}
+
+                def train_one_gpu():
+                    for t in leaf.values():
+                        t.grad = None
+                    with torch.enable_grad():
+                        flash_bevpool(**leaf, **rest5, **kw5).backward(go5)
+
+                def train_rows_local():  # rows stay sharded; only the input gradients are summed over the ranks
+                    for t in leaf.values():
+                        t.grad = None
+                    with torch.enable_grad():
+                        sharding.flash_bevpool_rows_local(**leaf, **rest5, **kw5).backward(go5_rows)
+                    sharding.all_reduce_input_grads(*leaf.values())
+
+                def train_rows_gathered():  # whole output on every rank (all-gather) + gradient all-reduce
+                    for t in leaf.values():
+                        t.grad = None
+                    with torch.enable_grad():
+                        sharding.flash_bevpool_rows(**leaf, **rest5, **kw5).backward(go5)
+
                 variants = {
                     "rows_split_allgather_us": lambda: sharding.flash_bevpool_rows(**in5, **kw5),
                     "rows_split_peer_stores_us": lambda: sharding.flash_bevpool_rows_p2p(**in5, **kw5),
+                    "rows_split_multicast_stores_us": lambda: sharding.flash_bevpool_rows_p2p(**in5, **kw5, multicast=True),
+                    "rows_split_kept_sharded_us": lambda: sharding.flash_bevpool_rows_local(**in5, **kw5),
                     "rows_split_one_gpu_us": lambda: flash_bevpool(**in5, **kw5),
+                    "rows_split_fwd_bwd_kept_sharded_grad_allreduce_us": train_rows_local,
+                    "rows_split_fwd_bwd_allgather_grad_allreduce_us": train_rows_gathered,
+                    "rows_split_fwd_bwd_one_gpu_us": train_one_gpu,
                 }
+                import torch.distributed._symmetric_memory as symm_mem  # noqa: F401
                 with torch.no_grad():
                     for name, fn in variants.items():
                         # an extra must not cost the run its headline line: a failure is recorded, on all ranks alike
@@ -500,6 +719,11 @@ def main():
                         dist.all_reduce(tv, op=dist.ReduceOp.MAX)
                         extra[name] = float(tv[0]) * 1e3
                 extra["rows_split_workload"] = "cfg5, one sample: 512x512x16 grid, 6 cams, C=256"
+                try:
+                    st5 = sharding._p2p_buffer((1, w5.Y, w5.X, w5.C), in5["image_feats"].dtype, device, None)
+                    extra["rows_split_multicast_available"] = bool(getattr(st5["hdls"][0], "multicast_ptr", 0))
+                except Exception as exc:  # noqa: BLE001
+                    extra["rows_split_multicast_available"] = f"unknown: {str(exc)[:80]}"
 
             # L2-resident read bandwidth: 32 MiB buffer read 50 times
             buf = torch.empty(32 << 20, dtype=torch.uint8, device=device)
@@ -527,6 +751,7 @@ def main():
 
     cells_total = Bl * w.X * w.Y * world
     value = cells_total / (ms_fwd_max * 1e-3)
+    ncu = ncu_counters(args.workload) if (Bl == 1 and args.mode == "categorical") else None
     hbm_peak, peak_kind = measured_peaks()
     alg_bytes = synth.algorithmic_bytes(w, args.mode, B=Bl)
     achieved = alg_bytes / (ms_fwd * 1e-3) / 1e9
@@ -541,22 +766,38 @@ def main():
                    "parallelism": f"batch samples sharded over {world} GPU(s), no data-path collective"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                      "frac": achieved / hbm_peak,
-                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(args.workload) if Bl == 1 else None, "peak_kind": f"of {peak_kind}",
-                     "algorithmic_bytes_per_launch": alg_bytes, "kernel": "fwd_kernel"},
+                     "traffic": ncu["dram_bytes_per_launch"] if ncu else None, "peak_kind": f"of {peak_kind}",
+                     "algorithmic_bytes_per_launch": alg_bytes, "kernel": "fwd_kernel",
+                     "note": (f"traffic from an ncu capture of commit {ncu['commit']}: {ncu['command']}" if ncu else
+                              "no ncu capture on record for this workload")},
         "roofline_gather": {"bound": "l2", "achieved": gather_bytes / (ms_fwd * 1e-3) / 1e9, "peak": l2_gbs,
                             "unit": "GB/s", "frac": (gather_bytes / (ms_fwd * 1e-3) / 1e9 / l2_gbs) if l2_gbs else None,
                             "algorithmic_bytes_per_launch": gather_bytes, "accepted_samples": s_valid,
                             "peak_kind": "L2-resident 16-byte loads of a 32 MiB buffer, measured in this run"},
         "clocks": clk, "gpu_launches": args.steps, "extra": extra,
     }
-    wi = NCU_WARP_INSTRUCTIONS_PER_LAUNCH.get(args.workload) if Bl == 1 and args.mode == "categorical" else None
+    wi = ncu.get("warp_instructions_per_launch") if ncu else None
     if wi and clk.get("sm_mhz"):
         # what actually bounds the kernel: one warp instruction per scheduler and cycle, 4 schedulers on each SM
         sms = torch.cuda.get_device_properties(device).multi_processor_count
         floor_us = wi / (sms * 4) / clk["sm_mhz"]
         line["roofline_issue"] = {"bound": "instruction issue", "warp_instructions_per_launch": wi,
                                   "floor_us": floor_us, "achieved_us": ms_fwd * 1e3, "frac": floor_us / (ms_fwd * 1e3),
-                                  "note": "instructions from the ncu capture, SM clock sampled in this run"}
+                                  "note": f"instructions from the ncu capture of commit {ncu['commit']}, SM clock sampled in this run"}
+    if not args.no_extras and "fwd_bwd_us" in extra:
+        # backward alone = (forward + backward) - forward, both measured above on the same inputs
+        t_bwd = max(extra["fwd_bwd_us"] - ms_fwd * 1e3, 1e-3) * 1e-6
+        k = 1 if args.mode == "categorical" else 2
+        hbm_bwd = synth.algorithmic_bytes(w, args.mode, B=Bl, backward=True)
+        gather_bwd = gather_bytes + s_valid * (4 * w.C * es + 4 * k * es)  # + the gradient scatter per accepted sample
+        line["roofline_bwd"] = {
+            "bound": "l2", "seconds": t_bwd, "achieved": gather_bwd / t_bwd / 1e9, "peak": l2_gbs, "unit": "GB/s",
+            "frac": (gather_bwd / t_bwd / 1e9 / l2_gbs) if l2_gbs else None,
+            "algorithmic_gather_bytes": gather_bwd, "algorithmic_hbm_bytes": hbm_bwd,
+            "hbm_achieved": hbm_bwd / t_bwd / 1e9, "hbm_frac": hbm_bwd / t_bwd / 1e9 / hbm_peak,
+            "kernels": "list + depth-gradient kernel, entry scatter, gather by texel, conversion",
+            "note": "backward time = forward+backward minus forward; bytes: forward gathers re-read + one scatter per "
+                    "accepted sample and corner (features and depth), against the L2-resident read bandwidth of this run"}
     if not args.no_extras:
         line["e2e"] = {"value": cells_total / (ms_e2e_max * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
                        "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e_max}
@@ -566,7 +807,8 @@ def main():
         times = cpu_forward_rate(w, args.mode, threads, min_seconds=8.0)
         line["cpu_baseline"] = {
             "value": w.X * w.Y / statistics.median(times), "unit": UNIT, "cores": threads, "kind": "port",
-            "sample": f"{len(times)} whole forwards of one sample (median), float32 oracle, OpenMP over BEV rows"}
+            "sample": f"{len(times)} whole forwards of one sample (median), float32 oracle, OpenMP over BEV rows",
+            "reference_pytorch_path": reference_pytorch_cpu(w, threads)}
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -32,6 +32,7 @@ struct Dev {
   void* out;
   void* out_peers[7];  // further copies of the output to store to (other GPUs' buffers), n_peers of them
   int n_peers;
+  void* out_mc;        // multicast address of the output buffer (NVSwitch replicates each store to all ranks), or null
   int* count;
   int* status;
   const void* gout;  // backward: upstream gradient

@@ -131,8 +131,13 @@ __global__ void __launch_bounds__(kMaxWarps * 32, MINB) fwd_kernel(const __grid_
           for (int i = 0; i < V * E; ++i) acc[i] = cnt > 0 ? __fdiv_rn(acc[i], c) : 0.0f;
         }
         const size_t cell = ((size_t)t.b * p.Y + y) * p.X + x;
+        if (p.out_mc != nullptr) {  // one multicast store reaches this GPU's buffer and every peer's
 #pragma unroll
-        for (int j = 0; j < V; ++j) store_chunk<T>(p.out, p.out_f32, cell * cpt + lg + j * p.GL, acc + j * E);
+          for (int j = 0; j < V; ++j) store_chunk_multicast<T>(p.out_mc, p.out_f32, cell * cpt + lg + j * p.GL, acc + j * E);
+        } else {
+#pragma unroll
+          for (int j = 0; j < V; ++j) store_chunk<T>(p.out, p.out_f32, cell * cpt + lg + j * p.GL, acc + j * E);
+        }
         for (int k = 0; k < p.n_peers; ++k) {  // the same rows into the other ranks' buffers (plain peer stores)
 #pragma unroll
           for (int j = 0; j < V; ++j) store_chunk<T>(p.out_peers[k], p.out_f32, cell * cpt + lg + j * p.GL, acc + j * E);

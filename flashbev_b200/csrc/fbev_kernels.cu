@@ -457,7 +457,7 @@ using namespace fbev;
 // unknown_hw: the caller could not tell the tensor's H and W (reference launcher signature); the
 // kernels then trust feature_size, as the reference does.
 static int forward_impl(const FbevProblem* p, void* out, int32_t* valid_count, void* stream, bool unknown_hw,
-                        void* const* peers = nullptr, int n_peers = 0) {
+                        void* const* peers = nullptr, int n_peers = 0, void* out_multicast = nullptr) {
   const int rc = validate(p);
   if (rc != FBEV_OK) return rc;
   if (out == nullptr) return FBEV_ERR_NULL;
@@ -468,6 +468,8 @@ static int forward_impl(const FbevProblem* p, void* out, int32_t* valid_count, v
   d.out = out;
   d.count = valid_count;
   d.n_peers = n_peers;
+  if (out_multicast != nullptr && ((uintptr_t)out_multicast % 16 || (uintptr_t)out % 16)) return FBEV_ERR_ALIGN;
+  d.out_mc = out_multicast;
   for (int k = 0; k < n_peers; ++k) {
     if (peers[k] == nullptr) return FBEV_ERR_NULL;
     if ((uintptr_t)peers[k] % 16 != (uintptr_t)out % 16) return FBEV_ERR_ALIGN;  // same kernel, same store width
@@ -475,6 +477,7 @@ static int forward_impl(const FbevProblem* p, void* out, int32_t* valid_count, v
   }
   if (unknown_hw) d.H = d.W = 46340;  // feature_size entries up to 2^31 texels pass the in-kernel bound
   const Plan pl = make_plan(p, d, false, p->image_feats, out, nullptr);
+  if (out_multicast != nullptr && !pl.chunked) return FBEV_ERR_RANGE;  // only the 16-byte-chunk kernel stores to it
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   switch (p->dtype) {
     case FBEV_F32: return forward_t<float>(pl, d, st);
@@ -657,6 +660,11 @@ static size_t sort_bytes(const FbevProblem* p, int flags) {
 int fbev_forward_peers(const FbevProblem* p, void* out, void* const* peer_outs, int n_peers, int32_t* valid_count,
                        void* stream) {
   return forward_impl(p, out, valid_count, stream, false, peer_outs, n_peers);
+}
+
+int fbev_forward_multicast(const FbevProblem* p, void* out, void* out_multicast, int32_t* valid_count, void* stream) {
+  if (out_multicast == nullptr) return FBEV_ERR_NULL;
+  return forward_impl(p, out, valid_count, stream, false, nullptr, 0, out_multicast);
 }
 
 size_t fbev_backward_min_scratch_bytes(const FbevProblem* p, int flags) {

@@ -339,6 +339,26 @@ __device__ __forceinline__ void store_chunk(void* base, int as_f32, size_t chunk
     reinterpret_cast<uint4*>(base)[chunk] = Chunk<T>::pack(v);
   }
 }
+// The same chunk stored once to a multicast address: the NVSwitch delivers it to the buffer of every GPU bound to
+// the multicast object, this one included (multimem.st; a plain store instruction, nothing is loaded or reduced).
+__device__ __forceinline__ void multicast_store16(void* addr, float a, float b, float c, float d) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+template <typename T>
+__device__ __forceinline__ void store_chunk_multicast(void* base, int as_f32, size_t chunk, const float* v) {
+  constexpr int E = Chunk<T>::E;
+  if (E == 8 && as_f32) {
+    float4* o = reinterpret_cast<float4*>(base) + chunk * 2;
+    multicast_store16(o, v[0], v[1], v[2], v[3]);
+    multicast_store16(o + 1, v[4], v[5], v[6], v[7]);
+  } else {
+    const uint4 q = Chunk<T>::pack(v);  // any 16 bytes travel as four 32-bit words
+    multicast_store16(reinterpret_cast<uint4*>(base) + chunk, __uint_as_float(q.x), __uint_as_float(q.y),
+                      __uint_as_float(q.z), __uint_as_float(q.w));
+  }
+}
+
 template <typename T>
 __device__ __forceinline__ void load_chunk(const void* base, int as_f32, size_t chunk, float* v) {
   constexpr int E = Chunk<T>::E;

@@ -140,6 +140,30 @@ class _RowShardedPool(torch.autograd.Function):
         return out[0], out[1], None, None, None
 
 
+def flash_bevpool_rows_local(image_feats, depth_params, projection_matrices, feature_size, image_size, roi_range,
+                             grid_size, group=None, **op_kwargs) -> torch.Tensor:
+    """Row split whose result stays split: this rank's rows ``[B, rows_r, X, C]`` (``row_slice``), nothing
+    exchanged in the forward.  For a consumer that is sharded by rows too (a BEV encoder with halo exchange, a
+    per-region head).  Differentiable; the gradients of the replicated inputs it yields are this rank's partial
+    sums, which ``all_reduce_input_grads`` completes."""
+    world, rank = _world(group)
+    rows = int(_host_values(grid_size)[1])
+    y0, y1 = row_slice(rows, world, rank)
+    full = flash_bevpool(image_feats, depth_params, projection_matrices, feature_size, image_size, roi_range, grid_size,
+                         y_range=(y0, y1), **op_kwargs)
+    return full[:, y0:y1]
+
+
+def all_reduce_input_grads(*tensors, group=None) -> None:
+    """Sums the ``.grad`` of replicated inputs over the ranks (one all-reduce each), after a backward through
+    ``flash_bevpool_rows_local``."""
+    if _world(group)[0] == 1:
+        return
+    for t in tensors:
+        if t is not None and t.grad is not None:
+            dist.all_reduce(t.grad, group=group)
+
+
 def flash_bevpool_rows(image_feats, depth_params, projection_matrices, feature_size, image_size, roi_range, grid_size,
                        group=None, local_op: Optional[Callable] = None, **op_kwargs) -> torch.Tensor:
     """The operator with its BEV rows split over the ranks of ``group``; returns the whole output on every rank.
@@ -195,13 +219,17 @@ def _p2p_buffer(shape, dtype, device, group):
 
 def flash_bevpool_rows_p2p(image_feats, depth_params, projection_matrices, feature_size, image_size, roi_range,
                            grid_size, depth_distribution=0, epsilon=1e-6, depth_weight_threshold=1e-6, group=None,
-                           **spec_kwargs) -> torch.Tensor:
+                           multicast=False, **spec_kwargs) -> torch.Tensor:
     """Row-split forward whose kernel writes every rank's copy of the output (inference; no autograd).
 
     Rank r computes rows ``row_slice(Y, world, r)`` and stores them into its own and all peers' output buffers
     (``fbev_forward_peers``: plain peer stores over NVLink, the kernel waits on nothing).  One tiny NCCL
     all-reduce after the launch is the barrier: when it completes on a rank, every rank's kernel has finished
     and all rows are in this rank's buffer.  It replaces the all-gather of the whole output.
+
+    ``multicast=True`` sends every 16-byte piece once, to the multicast address of the symmetric buffer
+    (``fbev_forward_multicast``: the NVSwitch replicates it to all ranks), instead of once per peer; it falls
+    back to peer stores where the buffer has no multicast address.
 
     Two symmetric buffers alternate between calls.  A rank passes the barrier of call k+1 only after every
     rank's stream has finished everything queued before it, the consumers of result k included, so call k+2
@@ -229,9 +257,14 @@ def flash_bevpool_rows_p2p(image_feats, depth_params, projection_matrices, featu
         out, hdl = state["bufs"][which], state["hdls"][which]
         peers = [ptr for r, ptr in enumerate(hdl.buffer_ptrs) if r != rank]
         arr = (ctypes.c_void_p * len(peers))(*peers)
+        mc = int(getattr(hdl, "multicast_ptr", 0) or 0) if multicast else 0
         with torch.cuda.device(feats.device):
             stream = torch.cuda.current_stream().cuda_stream
-            rc = _lib.load().fbev_forward_peers(ctypes.byref(p), out.data_ptr(), arr, len(peers), None, stream)
-            _lib.check(rc, "fbev_forward_peers")
+            if mc:
+                rc = _lib.load().fbev_forward_multicast(ctypes.byref(p), out.data_ptr(), mc, None, stream)
+                _lib.check(rc, "fbev_forward_multicast")
+            else:
+                rc = _lib.load().fbev_forward_peers(ctypes.byref(p), out.data_ptr(), arr, len(peers), None, stream)
+                _lib.check(rc, "fbev_forward_peers")
             dist.all_reduce(state["flag"], group=group)  # barrier in stream order
     return out

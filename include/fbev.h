@@ -137,6 +137,16 @@ int fbev_forward_to_host(const FbevProblem* p, void* out_dev, void* out_host, in
 int fbev_forward_peers(const FbevProblem* p, void* out, void* const* peer_outs, int n_peers, int32_t* valid_count,
                        void* stream);
 
+/* The same exchange with one store per chunk instead of one per peer.  (No counterpart in the reference.)
+ * out: this GPU's [B,Y,X,C] buffer; out_multicast: the multicast address of that buffer, i.e. an address whose
+ * stores the NVSwitch delivers to the same offset of every GPU's buffer bound to the multicast object, this GPU's
+ * included (CUDA multicast objects, cuMulticastCreate / cuMulticastBindMem; torch.distributed._symmetric_memory
+ * hands it out as multicast_ptr).  The kernel writes out[:, y_begin:y_end] only through out_multicast
+ * (multimem.st), so each rank sends its rows over NVLink once, whatever the number of ranks.  Needs channel rows
+ * that are multiples of 16 bytes and 16-byte aligned buffers (else FBEV_ERR_RANGE / FBEV_ERR_ALIGN).  As with
+ * fbev_forward_peers the caller establishes completion across ranks after the launch. */
+int fbev_forward_multicast(const FbevProblem* p, void* out, void* out_multicast, int32_t* valid_count, void* stream);
+
 /* Bytes of scratch fbev_backward works best with for this problem and flags: the float32 accumulation
  * targets of the 16-bit types (fbev_backward_min_scratch_bytes) plus, when the feature gradient is asked
  * for (or the depth gradient of a parametric mode), the entry lists of the sort by texel: counters (4 bytes

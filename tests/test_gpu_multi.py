@@ -51,6 +51,20 @@ def _worker(rank, world, port, results):
             p2p = sharding.flash_bevpool_rows_p2p(inp["image_feats"] * scale_in, inp["depth_params"], *args, **kw)
             want = flash_bevpool(inp["image_feats"] * scale_in, inp["depth_params"], *args, **kw)
             ok_p2p = ok_p2p and bool(torch.equal(p2p, want))
+            mc = sharding.flash_bevpool_rows_p2p(inp["image_feats"] * scale_in, inp["depth_params"], *args, **kw,
+                                                 multicast=True)  # falls back to peer stores without NVLS
+            ok_p2p = ok_p2p and bool(torch.equal(mc, want))
+        # rows kept sharded: this rank's rows equal the same rows of one GPU's output; the input gradients, summed
+        # over the ranks, equal one GPU's
+        f2 = inp["image_feats"].clone().requires_grad_(True)
+        d2 = inp["depth_params"].clone().requires_grad_(True)
+        mine = sharding.flash_bevpool_rows_local(f2, d2, *args, **kw)
+        ry0, ry1 = sharding.row_slice(w.Y, world, rank)
+        ok_p2p = ok_p2p and bool(torch.equal(mine, alone[:, ry0:ry1]))
+        mine.backward(go[:, ry0:ry1])
+        sharding.all_reduce_input_grads(f2, d2)
+        ok_p2p = ok_p2p and float((f2.grad - f0.grad).abs().max()) < 1e-5 * float(f0.grad.abs().max())
+        ok_p2p = ok_p2p and float((d2.grad - d0.grad).abs().max()) < 1e-5 * float(d0.grad.abs().max())
         # device time of the two row-split forwards (informative)
         def timed(fn, n=20):
             for _ in range(3):

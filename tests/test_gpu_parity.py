@@ -417,6 +417,66 @@ def test_result_buffer_given_by_the_caller(cuda_device):
         flash_bevpool(**inp, **kw, out=host_out)
 
 
+def test_row_split_with_peer_stores_emulated_on_one_gpu(cuda_device):
+    """fbev_forward_peers as two ranks would call it, both "ranks" on this GPU (the kernel waits on nothing, so the
+    two launches simply run one after the other): rank r computes its rows and stores them into its own buffer and
+    into the other rank's.  Both buffers must end up equal to one launch over all rows, bit for bit.  (The real
+    two-GPU run of the same path is tests/test_gpu_multi.py.)"""
+    from flashbev_b200 import sharding
+    from flashbev_b200.flash_bevpool import DepthSpec, make_problem
+    lib = _lib.load()
+    w = synth.workload("cfg5", X=128, Y=96, Z=8, C=64)
+    inp = to_device(inputs_for(w, "categorical"), cuda_device)
+    kw = op_kwargs(w, "categorical")
+    full = flash_bevpool(**inp, **kw)
+    bufs = [torch.full_like(full, float("nan")) for _ in range(2)]
+    stream = torch.cuda.current_stream().cuda_stream
+    for rank in range(2):
+        spec = DepthSpec(2, depth_bin_range=(w.d0, w.delta), y_range=sharding.row_slice(w.Y, 2, rank))
+        prob, keep = make_problem(inp["depth_params"], inp["image_feats"], inp["projection_matrices"],
+                                  inp["feature_size"], inp["image_size"], inp["roi_range"], inp["grid_size"], spec,
+                                  1e-6, 0.0)
+        peers = (ctypes.c_void_p * 1)(bufs[1 - rank].data_ptr())
+        rc = lib.fbev_forward_peers(ctypes.byref(prob), bufs[rank].data_ptr(), peers, 1, None, stream)
+        assert rc == 0, _lib.strerror(rc)
+    torch.cuda.synchronize()
+    assert torch.equal(bufs[0], full) and torch.equal(bufs[1], full)
+    # argument checks: too many peers, a peer buffer with another alignment
+    many = (ctypes.c_void_p * 8)(*[bufs[0].data_ptr()] * 8)
+    assert lib.fbev_forward_peers(ctypes.byref(prob), bufs[1].data_ptr(), many, 8, None, stream) == 3
+    odd = (ctypes.c_void_p * 1)(bufs[0].data_ptr() + 4)
+    assert lib.fbev_forward_peers(ctypes.byref(prob), bufs[1].data_ptr(), odd, 1, None, stream) == 6
+
+
+def test_kernel_only_benchmark_call_pattern_of_the_reference(cuda_device):
+    """What tools/utils/benchmark_utils.py:27-42 does with the tensors of tools/utils/data_utils.py:130-219: float32,
+    depth mean = |N(0,1)| * 10 + 5 and sigma = |N(0,1)| * 2 + 0.5, projection matrices passed as [B,N,4,4], roi_range
+    and grid_size as device tensors, every argument by keyword, laplace, threshold 0, under no_grad."""
+    w = synth.Workload("kernel_only", B=1, N=6, C=32, H=16, W=44, D=2, X=100, Y=100, Z=12, xy_extent=50.0,
+                       z_range=(-4.0, 2.0), dtype="fp32", seed=52)
+    inp = inputs_for(w, "laplace")
+    g = torch.Generator().manual_seed(53)
+    dp = torch.randn(w.B, w.N, w.H, w.W, 2, generator=g)
+    dp[..., 0] = dp[..., 0].abs() * 10.0 + 5.0
+    dp[..., 1] = dp[..., 1].abs() * 2.0 + 0.5
+    inp["depth_params"] = dp
+    ref = O.forward(oracle_problem(inp, w, "laplace"), threads=host_threads())
+    p44 = torch.eye(4).repeat(w.B, w.N, 1, 1)
+    p44[:, :, :3] = inp["projection_matrices"]
+    data = to_device(dict(inp, projection_matrices=p44), cuda_device)
+    with torch.no_grad():
+        for _ in range(3):
+            out = flash_bevpool(image_feats=data["image_feats"], depth_params=data["depth_params"],
+                                projection_matrices=data["projection_matrices"], feature_size=data["feature_size"],
+                                image_size=data["image_size"], roi_range=data["roi_range"], grid_size=data["grid_size"],
+                                depth_distribution=1, use_shared_memory=False, optimize_z_precompute=True,
+                                use_warp_kernel=False, use_vectorized_load=False, epsilon=1e-6,
+                                depth_weight_threshold=0.0)
+            torch.cuda.synchronize()
+    assert out.dtype == torch.float32 and tuple(out.shape) == (1, 100, 100, 32)
+    assert rel_err(out.cpu().numpy(), ref) < TOL_F32
+
+
 def test_edge_cases(cuda_device):
     # one camera, one height bin, 1x1 grid
     w = synth.Workload("one", B=1, N=1, C=4, H=4, W=6, D=8, X=1, Y=1, Z=1, xy_extent=8.0, z_range=(0.0, 2.0),
