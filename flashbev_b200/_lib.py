@@ -11,7 +11,8 @@ import os
 from . import build as _build
 
 F32, BF16, F16 = 0, 1, 2
-DEPTH_GAUSSIAN, DEPTH_LAPLACE, DEPTH_CATEGORICAL = 0, 1, 2
+DEPTH_GAUSSIAN, DEPTH_LAPLACE, DEPTH_CATEGORICAL, DEPTH_CATEGORICAL_LOGITS = 0, 1, 2, 3
+ABI_VERSION = 2
 POOL_MEAN, POOL_SUM = 0, 1
 BWD_FEATS, BWD_DEPTH, BWD_LEGACY_DEPTH = 1, 2, 4
 DEV_BAD_FEATURE_SIZE = 1
@@ -59,6 +60,7 @@ class FbevProblem(ctypes.Structure):
         ("roi_range", ctypes.c_void_p),
         ("status", ctypes.c_void_p),
         ("workspace", ctypes.c_void_p),
+        ("depth_stats", ctypes.c_void_p),
     ]
 
 
@@ -125,8 +127,8 @@ def load(build_if_missing: bool = True) -> ctypes.CDLL:
     lib.fbev_strerror.argtypes = [i32]
     lib.fbev_strerror.restype = ctypes.c_char_p
     lib.fbev_version.restype = i32
-    if lib.fbev_version() != 1:
-        raise ImportError(f"{path}: ABI version {lib.fbev_version()} != 1")
+    if lib.fbev_version() != ABI_VERSION:
+        raise ImportError(f"{path}: ABI version {lib.fbev_version()} != {ABI_VERSION}")
     _lib = lib
     return lib
 

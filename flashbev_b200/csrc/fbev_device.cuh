@@ -25,6 +25,7 @@ constexpr unsigned kFull = 0xffffffffu;
 struct Dev {
   const void* feats;
   const void* depth;
+  const float2* dstat;  // categorical depth given as logits: per texel (max, 1 / sum exp(logit - max)); else null
   const float* proj;
   const int* fsize;
   const int* isize;
@@ -213,21 +214,34 @@ __device__ __forceinline__ float interp4(const Sample& s, float f00, float f01, 
 // Depth weight and acceptance of a geometrically valid sample.
 //   parametric  flash_bevpool_cuda.cu:161-186
 //   categorical bilinear lookup of bin floor((d - d0) / delta) with the feature weights
-// `dep` points at the (b, camera) slice of the depth tensor, [fh, fw, D].
+// `texbase`: index of texel (0, 0) of the sample's (b, camera) slice, [fh, fw, D] elements of depth from there.
 template <typename T, bool GRAD>
-__device__ __forceinline__ bool depth_weight(const Dev& p, const T* __restrict__ dep, int fw, Sample& s) {
+__device__ __forceinline__ bool depth_weight(const Dev& p, size_t texbase, int fw, Sample& s) {
   const size_t D = (size_t)p.D;
-  const T* p00 = dep + ((size_t)s.v0 * fw + s.u0) * D;
-  const T* p01 = dep + ((size_t)s.v1 * fw + s.u0) * D;
-  const T* p10 = dep + ((size_t)s.v0 * fw + s.u1) * D;
-  const T* p11 = dep + ((size_t)s.v1 * fw + s.u1) * D;
+  const T* dep = reinterpret_cast<const T*>(p.depth) + texbase * D;
+  const size_t t00 = (size_t)s.v0 * fw + s.u0, t01 = (size_t)s.v1 * fw + s.u0;
+  const size_t t10 = (size_t)s.v0 * fw + s.u1, t11 = (size_t)s.v1 * fw + s.u1;
+  const T* p00 = dep + t00 * D;
+  const T* p01 = dep + t01 * D;
+  const T* p10 = dep + t10 * D;
+  const T* p11 = dep + t11 * D;
   if (p.mode == FBEV_DEPTH_CATEGORICAL) {
     const float kf = __fdiv_rn(__fsub_rn(s.id, p.d0), p.delta);
     if (!(kf >= 0.0f && kf < __int2float_rn(p.D))) return false;
     const int k = __float2int_rz(kf);
     s.k = k;
-    s.wgt = interp4(s, to_float(__ldg(p00 + k)), to_float(__ldg(p01 + k)), to_float(__ldg(p10 + k)),
-                    to_float(__ldg(p11 + k)));
+    float e00 = to_float(__ldg(p00 + k)), e01 = to_float(__ldg(p01 + k)), e10 = to_float(__ldg(p10 + k)),
+          e11 = to_float(__ldg(p11 + k));
+    if (p.dstat != nullptr) {
+      // logits: probability of bin k = exp(logit - max) / sum, with the texel's statistics from the pre-pass
+      const float2* st = p.dstat + texbase;
+      const float2 s00 = __ldg(st + t00), s01 = __ldg(st + t01), s10 = __ldg(st + t10), s11 = __ldg(st + t11);
+      e00 = expf(e00 - s00.x) * s00.y;
+      e01 = expf(e01 - s01.x) * s01.y;
+      e10 = expf(e10 - s10.x) * s10.y;
+      e11 = expf(e11 - s11.x) * s11.y;
+    }
+    s.wgt = interp4(s, e00, e01, e10, e11);
     return !(s.wgt < p.thr);
   }
   s.k = -1;

@@ -53,6 +53,7 @@ static thread_local Tuning g_tuning = {0, 0, 0, 0, 0};
 static thread_local int g_experiment = 0;  // FBEV_EXP_* bits (fbev_debug.h)
 
 static size_t elem_size(int dtype) { return dtype == FBEV_F32 ? 4 : 2; }
+static bool is_categorical(int mode) { return mode == FBEV_DEPTH_CATEGORICAL || mode == FBEV_DEPTH_CATEGORICAL_LOGITS; }
 
 static int validate(const FbevProblem* p) {
   if (p == nullptr) return FBEV_ERR_NULL;
@@ -64,11 +65,12 @@ static int validate(const FbevProblem* p) {
     return FBEV_ERR_SHAPE;
   if (p->proj_stride != 12 && p->proj_stride != 16) return FBEV_ERR_SHAPE;
   if (p->y_begin < 0 || p->y_end > p->Y || p->y_begin > p->y_end) return FBEV_ERR_SHAPE;
-  if (p->mode != FBEV_DEPTH_GAUSSIAN && p->mode != FBEV_DEPTH_LAPLACE && p->mode != FBEV_DEPTH_CATEGORICAL)
-    return FBEV_ERR_MODE;
+  if (p->mode != FBEV_DEPTH_GAUSSIAN && p->mode != FBEV_DEPTH_LAPLACE && !is_categorical(p->mode)) return FBEV_ERR_MODE;
   if (p->pool != FBEV_POOL_MEAN && p->pool != FBEV_POOL_SUM) return FBEV_ERR_MODE;
-  if (p->mode == FBEV_DEPTH_CATEGORICAL && !(p->depth_delta > 0.0f)) return FBEV_ERR_MODE;
-  if (p->mode != FBEV_DEPTH_CATEGORICAL && p->D != 2) return FBEV_ERR_SHAPE;
+  if (is_categorical(p->mode) && !(p->depth_delta > 0.0f)) return FBEV_ERR_MODE;
+  if (!is_categorical(p->mode) && p->D != 2) return FBEV_ERR_SHAPE;
+  if (p->mode == FBEV_DEPTH_CATEGORICAL_LOGITS && p->depth_stats == nullptr) return FBEV_ERR_NULL;
+  if ((uintptr_t)p->depth_stats % 8) return FBEV_ERR_ALIGN;
   if (!p->image_feats || !p->depth || !p->projection || !p->feature_size || !p->image_size) return FBEV_ERR_NULL;
   const size_t es = elem_size(p->dtype);
   if (((uintptr_t)p->image_feats % es) || ((uintptr_t)p->depth % es) || ((uintptr_t)p->projection % 4) ||
@@ -97,7 +99,10 @@ static void fill_dev(const FbevProblem* p, Dev& d) {
   d.B = p->B; d.N = p->N; d.H = p->H; d.W = p->W; d.C = p->C; d.D = p->D;
   d.X = p->X; d.Y = p->Y; d.Z = p->Z;
   d.pstride = p->proj_stride;
-  d.mode = p->mode; d.pool = p->pool;
+  // inside the kernels logits are the categorical mode with per-texel softmax statistics at hand
+  d.mode = is_categorical(p->mode) ? (int)FBEV_DEPTH_CATEGORICAL : p->mode;
+  d.dstat = p->mode == FBEV_DEPTH_CATEGORICAL_LOGITS ? reinterpret_cast<const float2*>(p->depth_stats) : nullptr;
+  d.pool = p->pool;
   d.y0 = p->y_begin; d.y1 = p->y_end;
   d.eps = p->epsilon; d.thr = p->threshold; d.d0 = p->depth_d0; d.delta = p->depth_delta;
   for (int i = 0; i < 3; ++i) {
@@ -454,6 +459,20 @@ static int backward_t(const Plan& pl, Dev d, const Plan& plf, const Dev& df, cud
 
 using namespace fbev;
 
+// Per-texel softmax statistics of a logits depth tensor into p->depth_stats (no-op in the other modes).
+static int launch_softmax_stats(const FbevProblem* p, cudaStream_t st) {
+  if (p->mode != FBEV_DEPTH_CATEGORICAL_LOGITS) return FBEV_OK;
+  const size_t texels = (size_t)p->B * p->N * p->H * p->W;
+  const unsigned blocks = (unsigned)((texels * 32 + 255) / 256);
+  float2* stats = reinterpret_cast<float2*>(p->depth_stats);
+  switch (p->dtype) {
+    case FBEV_F32: softmax_stats_kernel<float><<<blocks, 256, 0, st>>>(reinterpret_cast<const float*>(p->depth), stats, texels, p->D); break;
+    case FBEV_BF16: softmax_stats_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(p->depth), stats, texels, p->D); break;
+    default: softmax_stats_kernel<__half><<<blocks, 256, 0, st>>>(reinterpret_cast<const __half*>(p->depth), stats, texels, p->D); break;
+  }
+  return cudaGetLastError() == cudaSuccess ? FBEV_OK : FBEV_ERR_LAUNCH;
+}
+
 // unknown_hw: the caller could not tell the tensor's H and W (reference launcher signature); the
 // kernels then trust feature_size, as the reference does.
 static int forward_impl(const FbevProblem* p, void* out, int32_t* valid_count, void* stream, bool unknown_hw,
@@ -479,6 +498,8 @@ static int forward_impl(const FbevProblem* p, void* out, int32_t* valid_count, v
   const Plan pl = make_plan(p, d, false, p->image_feats, out, nullptr);
   if (out_multicast != nullptr && !pl.chunked) return FBEV_ERR_RANGE;  // only the 16-byte-chunk kernel stores to it
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int src = launch_softmax_stats(p, st);
+  if (src != FBEV_OK) return src;
   switch (p->dtype) {
     case FBEV_F32: return forward_t<float>(pl, d, st);
     case FBEV_BF16: return forward_t<__nv_bfloat16>(pl, d, st);
@@ -502,7 +523,7 @@ const char* fbev_strerror(int status) {
     case FBEV_ERR_STRUCT: return "FbevProblem.struct_size does not match this library";
     case FBEV_ERR_SHAPE: return "a size is non-positive or inconsistent (depth last dim must be 2 for the parametric modes; proj_stride 12 or 16; 0 <= y_begin <= y_end <= Y)";
     case FBEV_ERR_DTYPE: return "unknown element type";
-    case FBEV_ERR_MODE: return "unknown depth model or pooling, or depth_delta <= 0 in the categorical mode";
+    case FBEV_ERR_MODE: return "unknown depth model or pooling, or depth_delta <= 0 in a categorical mode";
     case FBEV_ERR_ALIGN: return "a pointer is not aligned to its element size";
     case FBEV_ERR_RANGE: return "sizes exceed kernel indexing: B*N*H*W and B*Y*X must be below 2^31, N <= 1024, shared memory per block <= 200 KiB";
     case FBEV_ERR_SCRATCH: return "scratch buffer missing, misaligned or smaller than fbev_backward_min_scratch_bytes()";
@@ -627,7 +648,7 @@ static size_t scratch_min_bytes(const FbevProblem* p, int flags) {
 constexpr size_t kSortBudgetBytes = FBEV_SORT_BUDGET_BYTES;
 // the parametric depth gradient rides on the same entries (16 more bytes in each list)
 static bool sort_carries_depth(const FbevProblem* p, int flags) {
-  return (flags & FBEV_BWD_DEPTH) && p->mode != FBEV_DEPTH_CATEGORICAL;
+  return (flags & FBEV_BWD_DEPTH) && !is_categorical(p->mode);
 }
 static size_t sort_entry_bytes(const FbevProblem* p, int flags) {
   // entry and its grouped copy, position, and for the parametric depth gradient four floats in either list
@@ -688,6 +709,12 @@ int fbev_backward(const FbevProblem* p, const void* grad_out, void* grad_feats, 
   const size_t tex_all = (size_t)p->B * p->N * p->H * p->W;
   const size_t nf = tex_all * p->C, nd = tex_all * p->D;
   const bool f32 = p->dtype == FBEV_F32;
+  const bool logits = p->mode == FBEV_DEPTH_CATEGORICAL_LOGITS;
+  if (logits && (flags & FBEV_BWD_DEPTH) && ((uintptr_t)grad_depth % elem_size(p->dtype))) return FBEV_ERR_ALIGN;
+  {
+    const int src = launch_softmax_stats(p, st);
+    if (src != FBEV_OK) return src;
+  }
   // float32 accumulation targets of the whole batch: the gradient tensors themselves, or the head of the scratch
   float* gfeat_all = nullptr;
   float* gdepth_all = nullptr;
@@ -748,6 +775,7 @@ int fbev_backward(const FbevProblem* p, const void* grad_out, void* grad_feats, 
     q.depth = reinterpret_cast<const unsigned char*>(p->depth) + (size_t)b0 * tex_sample * p->D * es;
     q.projection = p->projection + (size_t)b0 * p->N * p->proj_stride;
     q.feature_size = p->feature_size + (size_t)b0 * p->N * 2;
+    if (logits) q.depth_stats = p->depth_stats + (size_t)b0 * tex_sample * 2;
     const void* gout = reinterpret_cast<const unsigned char*>(grad_out) + (size_t)b0 * p->Y * p->X * p->C * eso;
     Dev d;
     fill_dev(&q, d);
@@ -776,7 +804,7 @@ int fbev_backward(const FbevProblem* p, const void* grad_out, void* grad_feats, 
     }
     // the feature gradient has a kernel of its own, laid out like the forward
     Dev df = d;
-    const bool wide_ok = !((flags & FBEV_BWD_DEPTH) && p->mode == FBEV_DEPTH_CATEGORICAL);
+    const bool wide_ok = !((flags & FBEV_BWD_DEPTH) && is_categorical(p->mode));
     const Plan plf = make_plan(&q, df, false, q.image_feats, gout, d.gfeat, wide_ok);
     int lrc;
     switch (p->dtype) {
@@ -786,10 +814,22 @@ int fbev_backward(const FbevProblem* p, const void* grad_out, void* grad_feats, 
     }
     if (lrc != FBEV_OK) return lrc;
   }
+  if (logits && (flags & FBEV_BWD_DEPTH)) {
+    // what was accumulated is dL/dprob; through the folded softmax it becomes dL/dlogit, written in the tensor's
+    // own type (so the conversion below has only the feature gradient left)
+    const unsigned blocks = (unsigned)((tex_all * 32 + 255) / 256);
+    const float2* stats = reinterpret_cast<const float2*>(p->depth_stats);
+    switch (p->dtype) {
+      case FBEV_F32: launch_after(softmax_bwd_kernel<float>, blocks, 256, 0, st, reinterpret_cast<const float*>(p->depth), stats, (const float*)gdepth_all, reinterpret_cast<float*>(grad_depth), tex_all, p->D); break;
+      case FBEV_BF16: launch_after(softmax_bwd_kernel<__nv_bfloat16>, blocks, 256, 0, st, reinterpret_cast<const __nv_bfloat16*>(p->depth), stats, (const float*)gdepth_all, reinterpret_cast<__nv_bfloat16*>(grad_depth), tex_all, p->D); break;
+      default: launch_after(softmax_bwd_kernel<__half>, blocks, 256, 0, st, reinterpret_cast<const __half*>(p->depth), stats, (const float*)gdepth_all, reinterpret_cast<__half*>(grad_depth), tex_all, p->D); break;
+    }
+    if (cudaGetLastError() != cudaSuccess) return FBEV_ERR_LAUNCH;
+  }
   if (!f32) {
     // float32 accumulation targets -> gradient tensors, both in one launch
     const float* sa = (flags & FBEV_BWD_FEATS) ? gfeat_all : nullptr;
-    const float* sb = (flags & FBEV_BWD_DEPTH) ? gdepth_all : nullptr;
+    const float* sb = ((flags & FBEV_BWD_DEPTH) && !logits) ? gdepth_all : nullptr;
     const size_t na = sa ? nf : 0, nb = sb ? nd : 0;
     const size_t units = (na + 3) / 4 + (nb + 3) / 4;
     const int threads = 256;
@@ -814,6 +854,8 @@ int fbev_debug_indices(const FbevProblem* p, int32_t* u0, int32_t* v0, int32_t* 
   fill_dev(p, d);
   d.count = count;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int src = launch_softmax_stats(p, st);
+  if (src != FBEV_OK) return src;
   const size_t cells = (size_t)p->B * p->Y * p->X;
   const int threads = 128;
   const int blocks = (int)((cells + threads - 1) / threads);

@@ -296,7 +296,7 @@ __device__ __forceinline__ void list_phase(const Dev& p, const Tile& t, const Bl
         const float vx = centre(x, vs[0], vmin[0]), vy = centre(y, vs[1], vmin[1]), vz = centre(z, vs[2], vmin[2]);
         if (geometry(h.P + n * 12, vx, vy, vz, image_h, image_w, fh, fw, p.eps, s)) {
           const size_t texbase = ((size_t)t.b * p.N + n) * (size_t)fh * fw;
-          ok = depth_weight<T, BWD>(p, reinterpret_cast<const T*>(p.depth) + texbase * p.D, fw, s);
+          ok = depth_weight<T, BWD>(p, texbase, fw, s);
           tex00 = texbase + (size_t)s.v0 * fw + s.u0;
         }
       }
@@ -436,7 +436,7 @@ __device__ __forceinline__ void row_list_phase(const Dev& p, const Tile& t, cons
         const float vx = centre(x, vs[0], vmin[0]), vy = centre(y, vs[1], vmin[1]), vz = centre(z, vs[2], vmin[2]);
         if (geometry(h.P + n * 12, vx, vy, vz, image_h, image_w, fh, fw, p.eps, s)) {
           const size_t texbase = ((size_t)t.b * p.N + n) * (size_t)fh * fw;
-          ok = depth_weight<T, SAMPLES>(p, reinterpret_cast<const T*>(p.depth) + texbase * p.D, fw, s);
+          ok = depth_weight<T, SAMPLES>(p, texbase, fw, s);
           if (ok) {
             tex = (unsigned)(texbase + (size_t)s.v0 * fw + s.u0);
             dep00 = tex * (unsigned)p.D;

@@ -38,7 +38,7 @@ __global__ void indices_kernel(const __grid_constant__ Dev p, int* u0, int* v0, 
       unsigned char oval = 0;
       Sample s;
       if (fs_ok && geometry(P, vx, vy, centre(z, vs[2], vmin[2]), image_h, image_w, fh, fw, p.eps, s) &&
-          depth_weight<T, false>(p, reinterpret_cast<const T*>(p.depth) + texbase * p.D, fw, s)) {
+          depth_weight<T, false>(p, texbase, fw, s)) {
         ou = s.u0;
         ov = s.v0;
         ok = s.k;
@@ -99,6 +99,53 @@ __global__ void projection_kernel(const float* __restrict__ s2e, const float* __
       for (int k = 0; k < 4; ++k) a += K[r * 4 + k] * inv[k * 4 + c];
       out[(size_t)i * 12 + r * 4 + c] = (float)a;
     }
+}
+
+// ---------------------------------------------------------------------------
+// Softmax over the depth bins, folded into the operator (FBEV_DEPTH_CATEGORICAL_LOGITS)
+// ---------------------------------------------------------------------------
+// Pre-pass: per texel the largest logit and the reciprocal of sum exp(logit - max).  One warp per texel.  The
+// lookup then turns the one logit it reads into a probability (depth_weight); the probabilities are never stored.
+template <typename T>
+__global__ void __launch_bounds__(256) softmax_stats_kernel(const T* __restrict__ logits, float2* __restrict__ stats,
+                                                            size_t texels, int D) {
+  const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= texels) return;
+  const T* l = logits + warp * (size_t)D;
+  float m = -__int_as_float(0x7f800000);
+  for (int k = lane; k < D; k += 32) m = fmaxf(m, to_float(__ldg(l + k)));
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(kFull, m, off));
+  float sum = 0.0f;
+  for (int k = lane; k < D; k += 32) sum += expf(to_float(__ldg(l + k)) - m);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(kFull, sum, off);
+  if (lane == 0) stats[warp] = make_float2(m, 1.0f / sum);
+}
+
+// Backward of the folded softmax: g holds dL/dprob per (texel, bin) in float32 (what the depth-gradient kernels
+// accumulate); the gradient with respect to the logits is p_k * (g_k - sum_j g_j p_j).  One warp per texel.  For
+// float32 tensors `out` is g itself (in place: a lane rewrites only the elements it has read).
+template <typename T>
+__global__ void __launch_bounds__(256) softmax_bwd_kernel(const T* __restrict__ logits, const float2* __restrict__ stats,
+                                                          const float* g, T* out, size_t texels, int D) {
+  grid_dependency_wait();
+  const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= texels) return;
+  const T* l = logits + warp * (size_t)D;
+  const float* gt = g + warp * (size_t)D;
+  const float2 st = __ldg(stats + warp);
+  float dot = 0.0f;
+  for (int k = lane; k < D; k += 32) dot = fmaf(gt[k], expf(to_float(__ldg(l + k)) - st.x) * st.y, dot);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(kFull, dot, off);
+  T* o = out + warp * (size_t)D;
+  for (int k = lane; k < D; k += 32) {
+    const float pk = expf(to_float(__ldg(l + k)) - st.x) * st.y;
+    o[k] = from_float<T>(pk * (gt[k] - dot));
+  }
 }
 
 // ---------------------------------------------------------------------------

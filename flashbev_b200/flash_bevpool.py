@@ -41,25 +41,27 @@ _DTYPES = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16, torch.float16: _l
 class DepthSpec(int):
     """``depth_distribution`` with the extra options riding along.
 
-    It is an ``int`` (0 gaussian, 1 laplace, 2 categorical), so it fits the reference's
-    positional slot; the attributes carry what the reference has no slot for.
+    It is an ``int`` (0 gaussian, 1 laplace, 2 categorical probabilities, 3 categorical logits: the softmax over
+    the bins is folded into the operator), so it fits the reference's positional slot; the attributes carry what
+    the reference has no slot for.
     """
 
     def __new__(cls, mode: int, pool: Optional[str] = None, depth_bin_range: Optional[Tuple[float, float]] = None,
                 legacy_depth_grad: bool = False, y_range: Optional[Tuple[int, int]] = None,
                 out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None, host_row_chunks: int = 0):
         mode = int(mode)
-        if mode not in (0, 1, 2):
-            raise ValueError(f"depth_distribution must be 0 (gaussian), 1 (laplace) or 2 (categorical), got {mode}")
+        if mode not in (0, 1, 2, 3):
+            raise ValueError("depth_distribution must be 0 (gaussian), 1 (laplace), 2 (categorical probabilities) or "
+                             f"3 (categorical logits), got {mode}")
         self = super().__new__(cls, mode)
         if pool is None:
-            pool = "sum" if mode == 2 else "mean"
+            pool = "sum" if mode >= 2 else "mean"
         if pool not in ("mean", "sum"):
             raise ValueError(f"pool must be 'mean' or 'sum', got {pool!r}")
         self.pool = pool
-        if mode == 2:
+        if mode >= 2:
             if depth_bin_range is None:
-                raise ValueError("depth_distribution=2 needs depth_bin_range=(first_edge, bin_width)")
+                raise ValueError("depth_distribution=2 / 3 needs depth_bin_range=(first_edge, bin_width)")
             d0, delta = float(depth_bin_range[0]), float(depth_bin_range[1])
             if not delta > 0:
                 raise ValueError("depth_bin_range: bin width must be positive")
@@ -192,7 +194,13 @@ def make_problem(depth_params, image_feats, projection_matrices, feature_size, i
     p.feature_size, p.image_size, p.roi_range = fsize.data_ptr(), isize.data_ptr(), roi.data_ptr()
     p.status = status_word(dev).data_ptr()
     p.workspace = workspace(dev, torch.cuda.current_stream(dev).cuda_stream).data_ptr()
-    return p, (feats, depth, proj, fsize, isize, roi)
+    keep = (feats, depth, proj, fsize, isize, roi)
+    if int(spec) == _lib.DEPTH_CATEGORICAL_LOGITS:
+        # scratch for the per-texel softmax statistics; every call fills it itself
+        stats = torch.empty(B * N * H * W * 2, dtype=torch.float32, device=dev)
+        p.depth_stats = stats.data_ptr()
+        keep = keep + (stats,)
+    return p, keep
 
 
 def _out_dtype(spec: DepthSpec, feats: torch.Tensor) -> torch.dtype:
@@ -271,14 +279,14 @@ class FlashBEVPool(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, out_grad):
-        feats, depth, proj, fsize, isize, roi = ctx.saved_tensors
+        feats, depth, proj, fsize, isize, roi = ctx.saved_tensors[:6]
         spec = ctx.spec
         p = ctx.problem
         if (p.image_feats, p.depth, p.projection) != (feats.data_ptr(), depth.data_ptr(), proj.data_ptr()):
             # the saved tensors came back at other addresses (a saved-tensor hook moved them): describe them anew
             grid = torch.tensor(ctx.grid, dtype=torch.int32)  # host tensor: no synchronisation
-            p, _ = make_problem(depth, feats, proj, fsize, isize, roi, grid, spec, ctx.epsilon,
-                                ctx.depth_weight_threshold)
+            p, held = make_problem(depth, feats, proj, fsize, isize, roi, grid, spec, ctx.epsilon,
+                                   ctx.depth_weight_threshold)  # `held` keeps the call's scratch alive until launched
         else:
             p.workspace = workspace(feats.device, torch.cuda.current_stream(feats.device).cuda_stream).data_ptr()
         flags = 0
@@ -322,12 +330,13 @@ def flash_bevpool(image_feats, depth_params, projection_matrices, feature_size, 
 
     Args:
         image_feats: [B,N,H,W,C] channels-last features (float32 / bfloat16 / float16).
-        depth_params: [B,N,H,W,2] (mean, sigma) for ``depth_distribution`` 0 / 1, or [B,N,H,W,D]
-            probabilities for 2.
+        depth_params: [B,N,H,W,2] (mean, sigma) for ``depth_distribution`` 0 / 1, [B,N,H,W,D] probabilities
+            for 2, or [B,N,H,W,D] logits for 3 (softmax over D folded into the operator and its backward).
         projection_matrices: [B,N,3,4] or [B,N,4,4].
         feature_size: [B,N,2] int (h, w).  image_size: [2] int (height, width).
         roi_range: [6] xmin,xmax,ymin,ymax,zmin,zmax.  grid_size: [3] int grid_x, grid_y, grid_z.
-        depth_distribution: 0 gaussian, 1 laplace, 2 categorical (needs ``depth_bin_range``).
+        depth_distribution: 0 gaussian, 1 laplace, 2 categorical, 3 categorical from logits (2 and 3 need
+            ``depth_bin_range``).
         pool: "mean" (default for 0/1, the reference's) or "sum" (default for 2).
         depth_bin_range: (first bin edge, bin width) of the categorical mode.
         legacy_depth_grad: parametric modes only; reproduce the reference CUDA kernel's depth gradient.

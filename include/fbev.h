@@ -28,7 +28,7 @@
 extern "C" {
 #endif
 
-#define FBEV_ABI_VERSION 1
+#define FBEV_ABI_VERSION 2
 
 /* element type of features, depth, output and gradients */
 enum { FBEV_F32 = 0, FBEV_BF16 = 1, FBEV_F16 = 2 };
@@ -36,7 +36,15 @@ enum { FBEV_F32 = 0, FBEV_BF16 = 1, FBEV_F16 = 2 };
 /* depth model.  0 and 1 are the reference's (flash_bevpool.py:35,
  * flash_bevpool_cuda.cu:178-184); 2 is the depth-bin lookup into a softmaxed
  * distribution, depth tensor [B,N,H,W,D], which the reference does not have. */
-enum { FBEV_DEPTH_GAUSSIAN = 0, FBEV_DEPTH_LAPLACE = 1, FBEV_DEPTH_CATEGORICAL = 2 };
+enum {
+  FBEV_DEPTH_GAUSSIAN = 0,
+  FBEV_DEPTH_LAPLACE = 1,
+  FBEV_DEPTH_CATEGORICAL = 2,
+  /* as 2, but the depth tensor holds the depth head's LOGITS: the softmax over the D bins (in a model it is a
+   * pass of its own over the tensor, before the operator) is folded into the lookup, and its backward into the
+   * operator's backward, which then returns the gradient with respect to the logits.  Needs depth_stats. */
+  FBEV_DEPTH_CATEGORICAL_LOGITS = 3
+};
 
 /* reduction over cameras and height bins: mean over accepted samples
  * (reference, flash_bevpool_cuda.cu:212-216) or plain sum */
@@ -106,6 +114,9 @@ typedef struct FbevProblem {
                                   their tiles through an atomic counter; without it (NULL) every thread block
                                   owns one fixed tile.  Calls that may overlap on the device need a workspace
                                   each. */
+  float* depth_stats;          /* FBEV_DEPTH_CATEGORICAL_LOGITS only: device scratch, 2 floats per texel
+                                  (B*N*H*W*2, 8-byte aligned), caller-owned; every call fills it itself with each
+                                  texel's (max logit, 1 / sum of exp(logit - max)).  NULL in the other modes. */
 } FbevProblem;
 
 #define FBEV_WORKSPACE_BYTES 16

@@ -191,6 +191,22 @@ def indices(p: Problem):
     return {"u0": u0, "v0": v0, "kbin": kb, "valid": va, "count": cnt}
 
 
+def softmax_bins(logits, dtype=np.float64):
+    """Softmax over the last axis (the depth bins), evaluated in ``dtype``: what a model's depth head applies before
+    the operator, and what the operator's logits mode folds into its lookup."""
+    l = np.asarray(logits, dtype)
+    e = np.exp(l - l.max(axis=-1, keepdims=True))
+    return e / e.sum(axis=-1, keepdims=True)
+
+
+def softmax_bins_backward(prob, d_prob):
+    """Gradient with respect to the logits from the gradient with respect to the probabilities:
+    p_k * (g_k - sum_j g_j p_j) per texel."""
+    p = np.asarray(prob, np.float64)
+    g = np.asarray(d_prob, np.float64)
+    return p * (g - (g * p).sum(axis=-1, keepdims=True))
+
+
 def pillar_pool(depth, feat, u, v, z, batch_camera, ranks, starts, lengths, n_cells, laplace, epsilon=1e-6,
                 dtype=np.float64):
     """Pillar pooling over pre-sorted sample lists, restating sampling_vt_pillarpool_fused_kernel

@@ -31,13 +31,14 @@ def test_library_builds_and_exports_every_symbol():
     lib = ctypes.CDLL(build.LIB_PATH)
     for name in header_functions():
         assert hasattr(lib, name), name
-    assert _lib.load().fbev_version() == 1
+    assert _lib.load().fbev_version() == _lib.ABI_VERSION == 2
 
 
 def test_struct_layout_matches_the_header():
-    # uint32 + 20 int32/float words + 6 floats = 27 words, padded to 8 bytes, then 8 pointers (LP64)
-    assert ctypes.sizeof(_lib.FbevProblem) == 4 * 28 + 8 * 8
+    # uint32 + 20 int32/float words + 6 floats = 27 words, padded to 8 bytes, then 9 pointers (LP64)
+    assert ctypes.sizeof(_lib.FbevProblem) == 4 * 28 + 8 * 9
     assert _lib.FbevProblem.image_feats.offset == 112 and _lib.FbevProblem.workspace.offset == 168
+    assert _lib.FbevProblem.depth_stats.offset == 176
 
 
 def _problem():
@@ -73,8 +74,10 @@ def test_validation_status_codes():
     assert fwd(p) == 4
     p = _problem(); p.out_dtype = _lib.BF16                       # output narrower than the features
     assert fwd(p) == 4                                            # FBEV_ERR_DTYPE
-    p = _problem(); p.mode = 3
+    p = _problem(); p.mode = 4
     assert fwd(p) == 5                                            # FBEV_ERR_MODE
+    p = _problem(); p.mode = _lib.DEPTH_CATEGORICAL_LOGITS; p.depth_delta = 1.0   # logits need the statistics scratch
+    assert fwd(p) == 1
     p = _problem(); p.mode = _lib.DEPTH_CATEGORICAL; p.depth_delta = 0.0
     assert fwd(p) == 5
     p = _problem(); p.image_feats = 258
@@ -135,8 +138,11 @@ def test_depth_spec_rules():
     assert s.pool == "sum" and (s.d0, s.delta) == (1.0, 0.5)
     with pytest.raises(ValueError):
         DepthSpec(2)
+    assert DepthSpec(3, depth_bin_range=(1.0, 0.5)).pool == "sum"
     with pytest.raises(ValueError):
         DepthSpec(3)
+    with pytest.raises(ValueError):
+        DepthSpec(4)
     with pytest.raises(ValueError):
         DepthSpec(0, pool="max")
 

@@ -417,6 +417,45 @@ def test_result_buffer_given_by_the_caller(cuda_device):
         flash_bevpool(**inp, **kw, out=host_out)
 
 
+@pytest.mark.parametrize("name,dtype,pool,threshold", [("small", "fp32", "sum", 0.0), ("small", "fp32", "mean", 1e-3),
+                                                       ("small", "fp16", "sum", 0.0), ("cfg2", "bf16", "sum", 0.0),
+                                                       ("cfg2", "fp32", "sum", 0.0)])
+def test_logits_mode_folds_the_softmax_forward_and_backward(cuda_device, parity_report, name, dtype, pool, threshold):
+    """depth_distribution=3: the depth tensor holds logits; the operator must equal softmax-then-operator, and its
+    depth gradient the chain through that softmax.  Oracle: float64 softmax of the same (rounded) logits, the
+    categorical oracle on the probabilities, and the softmax's backward in float64."""
+    w = synth.workload(name, dtype=dtype) if name != "small" else synth.Workload(
+        "small", B=2, N=6, C=16, H=8, W=22, D=24, X=40, Y=36, Z=5, xy_extent=30.0, d0=1.0, delta=1.5, dtype=dtype,
+        seed=21, jitter=True)
+    inp = synth.make_inputs(w, "categorical")
+    g = torch.Generator().manual_seed(77)
+    logits = (torch.randn(inp["depth_params"].shape, generator=g) * 2.0).to(inp["depth_params"].dtype)
+    prob = O.softmax_bins(logits.float().numpy())
+    cpu = oracle_problem(dict(inp, depth_params=torch.from_numpy(prob.astype(np.float32))), w, "categorical",
+                         pool=pool, threshold=threshold)
+    ref, ref_cnt = O.forward(cpu, threads=host_threads(), with_count=True)
+    go = synth.upstream_grad(w)
+    if dtype != "fp32":
+        go = go.to(logits.dtype)
+    rf, rd_prob = O.backward(cpu, go.float().numpy(), dtype=np.float64, threads=host_threads())
+    rd = O.softmax_bins_backward(prob, rd_prob)
+    dev = to_device(dict(inp, depth_params=logits), cuda_device)
+    kw = dict(depth_distribution=3, depth_bin_range=(w.d0, w.delta), depth_weight_threshold=threshold, pool=pool)
+    out, cnt = forward_with_count(**dev, **kw)
+    if threshold == 0.0:
+        assert np.array_equal(cnt.cpu().numpy(), ref_cnt)
+    dev["image_feats"].requires_grad_(True)
+    dev["depth_params"].requires_grad_(True)
+    flash_bevpool(**dev, **kw).backward(go.to(cuda_device))
+    torch.cuda.synchronize()
+    tol = TOL_F32 if dtype == "fp32" else TOL_LOWP
+    for label, a, b in (("out", out, ref), ("d_feats", dev["image_feats"].grad, rf), ("d_logits", dev["depth_params"].grad, rd)):
+        a = a.float().cpu().numpy()
+        err = rel_err(a, b) if dtype == "fp32" else rel_err_quantised(a, b, dtype)
+        parity_report(f"logits mode {name} {dtype} {pool} thr={threshold:g} {label}: {err:.3e} (bar {tol:g})")
+        assert err < tol, f"{label}: {err:.3e}"
+
+
 def test_row_split_with_peer_stores_emulated_on_one_gpu(cuda_device):
     """fbev_forward_peers as two ranks would call it, both "ranks" on this GPU (the kernel waits on nothing, so the
     two launches simply run one after the other): rank r computes its rows and stores them into its own buffer and
