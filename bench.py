@@ -448,12 +448,19 @@ def main():
             # forward kernel with each experiment switch of fbev_debug.h (kept as a record of what each buys)
             if Bl == 1:
                 exp_us = {}
-                for bits in (0, 1, 2, 4, 3, 6, 7):
+                for bits in (0, 1, 2, 4, 8):
                     lib.fbev_set_experiment(bits)
                     exp_us[str(bits)] = timed(fwd_raw, max(20, args.steps // 5), 5)[0] * 1e3
                 lib.fbev_set_experiment(0)
                 extra["fwd_us_by_experiment_bits"] = exp_us
-                extra["fwd_experiment_bits"] = "1 L2 prefetch at start, 2 camera cull per group of cells, 4 second round of units drawn from a counter"
+                extra["fwd_experiment_bits"] = ("0 none (the shipped kernel), 1 L2 prefetch at start, 2 camera cull per group of "
+                                                "cells, 4 second round of units drawn from a counter, 8 gathers served from "
+                                                "shared memory (ceiling of any staging scheme; result invalid)")
+                if not args.tune:
+                    # smaller tiles with three warps per block
+                    lib.fbev_set_tuning(6, 3, 0, 3, 0)
+                    extra["fwd_us_tiles_6x3_3warps"] = timed(fwd_raw, max(20, args.steps // 5), 5)[0] * 1e3
+                    lib.fbev_set_tuning(0, 0, 0, 0, 0)
 
             # the training shape (cfg3: B=4, float32, 32x88 maps), forward and forward + backward
             if world == 1 and not args.quick:

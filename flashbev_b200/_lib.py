@@ -30,7 +30,7 @@ EXPORTS = (
 )
 # ... and include/fbev_debug.h (experiment and test helpers)
 DEBUG_EXPORTS = ("fbev_set_tuning", "fbev_set_experiment", "fbev_probe_read")
-EXP_PREFETCH, EXP_GROUP_CULL, EXP_DRAW = 1, 2, 4
+EXP_PREFETCH, EXP_GROUP_CULL, EXP_DRAW, EXP_SHARED_GATHER_CEILING = 1, 2, 4, 8
 
 
 class FbevProblem(ctypes.Structure):

@@ -215,12 +215,15 @@ __device__ __forceinline__ float interp4(const Sample& s, float f00, float f01, 
 //   parametric  flash_bevpool_cuda.cu:161-186
 //   categorical bilinear lookup of bin floor((d - d0) / delta) with the feature weights
 // `texbase`: index of texel (0, 0) of the sample's (b, camera) slice, [fh, fw, D] elements of depth from there.
-template <typename T, bool GRAD>
-__device__ __forceinline__ bool depth_weight(const Dev& p, size_t texbase, int fw, Sample& s) {
-  const size_t D = (size_t)p.D;
-  const T* dep = reinterpret_cast<const T*>(p.depth) + texbase * D;
-  const size_t t00 = (size_t)s.v0 * fw + s.u0, t01 = (size_t)s.v1 * fw + s.u0;
-  const size_t t10 = (size_t)s.v0 * fw + s.u1, t11 = (size_t)s.v1 * fw + s.u1;
+// IDX: type the element indices are computed in.  size_t always works; the chunked kernels are only chosen for
+// tensors of fewer than 2^32 depth elements (make_plan) and use unsigned, which spares them the 64-bit index
+// arithmetic of four corners per candidate.
+template <typename T, bool GRAD, typename IDX = size_t>
+__device__ __forceinline__ bool depth_weight(const Dev& p, IDX texbase, int fw, Sample& s) {
+  const IDX D = (IDX)p.D;
+  const T* dep = reinterpret_cast<const T*>(p.depth);
+  const IDX t00 = texbase + (IDX)(s.v0 * fw + s.u0), t01 = texbase + (IDX)(s.v1 * fw + s.u0);
+  const IDX t10 = texbase + (IDX)(s.v0 * fw + s.u1), t11 = texbase + (IDX)(s.v1 * fw + s.u1);
   const T* p00 = dep + t00 * D;
   const T* p01 = dep + t01 * D;
   const T* p10 = dep + t10 * D;
@@ -234,7 +237,7 @@ __device__ __forceinline__ bool depth_weight(const Dev& p, size_t texbase, int f
           e11 = to_float(__ldg(p11 + k));
     if (p.dstat != nullptr) {
       // logits: probability of bin k = exp(logit - max) / sum, with the texel's statistics from the pre-pass
-      const float2* st = p.dstat + texbase;
+      const float2* st = p.dstat;
       const float2 s00 = __ldg(st + t00), s01 = __ldg(st + t01), s10 = __ldg(st + t10), s11 = __ldg(st + t11);
       e00 = expf(e00 - s00.x) * s00.y;
       e01 = expf(e01 - s01.x) * s01.y;

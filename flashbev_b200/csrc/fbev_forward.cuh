@@ -102,8 +102,16 @@ __global__ void __launch_bounds__(kMaxWarps * 32, MINB) fwd_kernel(const __grid_
           const float2 wa1 = make_float2(__uint_as_float(r.w), __uint_as_float(r.w));
 #pragma unroll
           for (int j = 0; j < V; ++j) {
-            const uint4 q0 = ldg16(fl + (r.x + j * p.GL));
-            const uint4 q1 = ldg16(fl + (r.x + r.y + j * p.GL));
+            uint4 q0, q1;
+            if (EXPERIMENTS && (p.exp & FBEV_EXP_SHARED_GATHER_CEILING)) {
+              // timing experiment: the same two 16-byte reads, from this block's shared memory (wrong values)
+              const uint4* sm = reinterpret_cast<const uint4*>(smem);
+              q0 = sm[(r.x + j * p.GL + lg) & 1023u];
+              q1 = sm[(r.x + r.y + j * p.GL + lg) & 1023u];
+            } else {
+              q0 = ldg16(fl + (r.x + j * p.GL));
+              q1 = ldg16(fl + (r.x + r.y + j * p.GL));
+            }
             float f0[E], f1[E];
             Chunk<T>::unpack(q0, f0);
             Chunk<T>::unpack(q1, f1);

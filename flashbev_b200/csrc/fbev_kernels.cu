@@ -130,7 +130,8 @@ static Plan make_plan(const FbevProblem* p, Dev& d, bool bwd, const void* a, con
   const bool aligned = (row % 16 == 0) && ((uintptr_t)a % 16 == 0) && ((uintptr_t)b2 % 16 == 0) &&
                        ((uintptr_t)c % 16 == 0);
   const int chunks = aligned ? (int)(row / 16) : 0;
-  pl.chunked = aligned && chunks <= 128;
+  // the chunked kernels index texels, feature chunks and depth elements with 32 bits
+  pl.chunked = aligned && chunks <= 128 && (unsigned long long)p->B * p->N * p->H * p->W * (unsigned long long)p->D < (1ull << 32);
   pl.warps = g_tuning.warps > 0 ? (g_tuning.warps > kMaxWarps ? kMaxWarps : g_tuning.warps) : (bwd ? 8 : 4);
   pl.cap = 32;
   if (pl.chunked) {

@@ -224,8 +224,8 @@ __device__ __forceinline__ unsigned box_visibility(const Dev& p, const Tile& t, 
   if (lane < p.N) {
     const int fh = h.fs[lane * 2], fw = h.fs[lane * 2 + 1];
     bool ok = fh > 0 && fw > 0 && (long long)fh * fw <= (long long)p.H * p.W;
-    if (ok && p.cpt > 0)  // the records hold 32-bit chunk indices into the feature tensor
-      ok = (unsigned long long)((size_t)t.b * p.N + lane + 1) * (unsigned long long)fh * fw * (unsigned)p.cpt < (1ull << 32);
+    if (ok && p.cpt > 0)  // 32-bit chunk indices into the feature tensor, 32-bit element indices into the depth tensor
+      ok = (unsigned long long)((size_t)t.b * p.N + lane + 1) * (unsigned long long)fh * fw * (unsigned)max(p.cpt, p.D) < (1ull << 32);
     if (ok) {
       const float bx0 = centre(t.x0, vs[0], vmin[0]), bx1 = centre(t.x1 - 1, vs[0], vmin[0]);
       const float by0 = centre(t.y0, vs[1], vmin[1]), by1 = centre(t.y1 - 1, vs[1], vmin[1]);
@@ -435,10 +435,10 @@ __device__ __forceinline__ void row_list_phase(const Dev& p, const Tile& t, cons
         fw = h.fs[n * 2 + 1];
         const float vx = centre(x, vs[0], vmin[0]), vy = centre(y, vs[1], vmin[1]), vz = centre(z, vs[2], vmin[2]);
         if (geometry(h.P + n * 12, vx, vy, vz, image_h, image_w, fh, fw, p.eps, s)) {
-          const size_t texbase = ((size_t)t.b * p.N + n) * (size_t)fh * fw;
-          ok = depth_weight<T, SAMPLES>(p, texbase, fw, s);
+          const unsigned texbase = (unsigned)(t.b * p.N + n) * (unsigned)(fh * fw);  // below 2^32 / cpt (box_visibility)
+          ok = depth_weight<T, SAMPLES, unsigned>(p, texbase, fw, s);
           if (ok) {
-            tex = (unsigned)(texbase + (size_t)s.v0 * fw + s.u0);
+            tex = texbase + (unsigned)(s.v0 * fw + s.u0);
             dep00 = tex * (unsigned)p.D;
             const unsigned du = (unsigned)(s.u1 - s.u0), dvf = (unsigned)(s.v1 - s.v0);
             kk = (unsigned)cl | ((unsigned)ci << 4) | (du << 28) | (dvf << 29) | (1u << 31);

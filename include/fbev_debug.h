@@ -30,8 +30,11 @@ void fbev_set_tuning(int tile_x, int tile_y, int chunks_per_lane, int warps, int
  *   FBEV_EXP_GROUP_CULL the camera cull is evaluated for the box of the warp's own group of cells instead of
  *                      the whole tile: fewer candidates per sweep near the edges of a camera's field of view
  *   FBEV_EXP_DRAW      static unit order for a warp's first unit only; the remaining units are handed out one at
- *                      a time through the scheduler word (needs FbevProblem.workspace) */
-enum { FBEV_EXP_PREFETCH = 1, FBEV_EXP_GROUP_CULL = 2, FBEV_EXP_DRAW = 4 };
+ *                      a time through the scheduler word (needs FbevProblem.workspace)
+ *   FBEV_EXP_SHARED_GATHER_CEILING  TIMING ONLY, THE RESULT IS WRONG: the channel phase takes its texel chunks from
+ *                      the block's shared memory (whatever is there) instead of from global memory.  It shows what a
+ *                      scheme that stages feature rows in shared memory could gain at most, were the staging free */
+enum { FBEV_EXP_PREFETCH = 1, FBEV_EXP_GROUP_CULL = 2, FBEV_EXP_DRAW = 4, FBEV_EXP_SHARED_GATHER_CEILING = 8 };
 void fbev_set_experiment(int bits);
 
 /* Reads `bytes` of device memory `repeats` times with 16-byte loads (a bandwidth
