@@ -309,6 +309,7 @@ def main():
                     help="profiler helper: launch only fbev_backward with these flags (1 features, 2 depth, 3 both) "
                          "--steps times on the default workload, print the mean device time and exit")
     ap.add_argument("--tune", default=None, help="tile_x,tile_y,chunks_per_lane,warps,min_blocks (0 = automatic)")
+    ap.add_argument("--exp", type=int, default=0, help="experiment bits of fbev_debug.h for every forward launch (profiler runs)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -336,6 +337,8 @@ def main():
     lib = _lib.load()
     if args.tune:
         lib.fbev_set_tuning(*[int(v) for v in args.tune.split(",")])
+    if args.exp:
+        lib.fbev_set_experiment(args.exp)
 
     w = synth.workload(args.workload)
     Bl = args.batch_per_gpu
@@ -460,6 +463,10 @@ def main():
                     # smaller tiles with three warps per block
                     lib.fbev_set_tuning(6, 3, 0, 3, 0)
                     extra["fwd_us_tiles_6x3_3warps"] = timed(fwd_raw, max(20, args.steps // 5), 5)[0] * 1e3
+                    lib.fbev_set_tuning(0, 0, 0, 0, 3)
+                    extra["fwd_us_96_registers_5_blocks"] = timed(fwd_raw, max(20, args.steps // 5), 5)[0] * 1e3
+                    lib.fbev_set_tuning(6, 3, 0, 3, 3)
+                    extra["fwd_us_tiles_6x3_3warps_96_registers"] = timed(fwd_raw, max(20, args.steps // 5), 5)[0] * 1e3
                     lib.fbev_set_tuning(0, 0, 0, 0, 0)
 
             # the training shape (cfg3: B=4, float32, 32x88 maps), forward and forward + backward

@@ -161,6 +161,16 @@ __device__ __forceinline__ float proj_row(const float* p, float x, float y, floa
   return __fadd_rn(t, p[3]);
 }
 
+// x / d, correctly rounded.  When d is a power of two its reciprocal is exact, and x * (1 / d) rounds the same real
+// number as x / d does: the same bits for one multiplication instead of a division sequence.  (Image heights of
+// 256 or 512 and depth-bin widths of 0.5 or 1 are powers of two.)  d > 0, finite and normal.
+__device__ __forceinline__ float div_exact(float x, float d) {
+  const unsigned bits = __float_as_uint(d);
+  if ((bits & 0x007fffffu) == 0u && bits >= 0x00800000u && bits <= 0x7e800000u)
+    return __fmul_rn(x, __uint_as_float(0x7f000000u - bits));
+  return __fdiv_rn(x, d);
+}
+
 struct Sample {
   float w00, w01, w10, w11;  // bilinear weights; first index = u offset, second = v offset (:156-159)
   float wgt;                 // depth weight
@@ -182,8 +192,8 @@ __device__ __forceinline__ bool geometry(const float* P, float vx, float vy, flo
   iu = __fdiv_rn(iu, cd);
   iv = __fdiv_rn(iv, cd);
   const float fwf = __int2float_rn(fw), fhf = __int2float_rn(fh);
-  const float fu = __fmul_rn(__fdiv_rn(iu, __int2float_rn(image_w)), fwf);
-  const float fv = __fmul_rn(__fdiv_rn(iv, __int2float_rn(image_h)), fhf);
+  const float fu = __fmul_rn(div_exact(iu, __int2float_rn(image_w)), fwf);
+  const float fv = __fmul_rn(div_exact(iv, __int2float_rn(image_h)), fhf);
   if (!(fu >= 0.0f && fu < fwf && fv >= 0.0f && fv < fhf)) return false;
   int u0 = __float2int_rd(fu);
   int v0 = __float2int_rd(fv);
@@ -229,7 +239,7 @@ __device__ __forceinline__ bool depth_weight(const Dev& p, IDX texbase, int fw, 
   const T* p10 = dep + t10 * D;
   const T* p11 = dep + t11 * D;
   if (p.mode == FBEV_DEPTH_CATEGORICAL) {
-    const float kf = __fdiv_rn(__fsub_rn(s.id, p.d0), p.delta);
+    const float kf = div_exact(__fsub_rn(s.id, p.d0), p.delta);
     if (!(kf >= 0.0f && kf < __int2float_rn(p.D))) return false;
     const int k = __float2int_rz(kf);
     s.k = k;

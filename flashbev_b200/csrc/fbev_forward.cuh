@@ -13,8 +13,9 @@ namespace fbev {
 
 // EXPERIMENTS: the instantiation that honours the switches of fbev_set_experiment (Dev.exp); the ordinary one
 // carries none of their code.
-template <typename T, int V, int MINB, bool EXPERIMENTS = false>
-__global__ void __launch_bounds__(kMaxWarps * 32, MINB) fwd_kernel(const __grid_constant__ Dev p) {
+// MAXT: largest block the instantiation is launched with (with MINB it sets the register budget).
+template <typename T, int V, int MINB, bool EXPERIMENTS = false, int MAXT = kMaxWarps * 32>
+__global__ void __launch_bounds__(MAXT, MINB) fwd_kernel(const __grid_constant__ Dev p) {
   constexpr int E = Chunk<T>::E;
   extern __shared__ __align__(16) unsigned char smem[];
   const BlockHeader h = carve(smem, p.N);

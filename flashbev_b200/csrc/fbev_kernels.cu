@@ -308,6 +308,8 @@ static int forward_t(const Plan& pl, const Dev& d, cudaStream_t st) {
     case 1: return two ? launch(fwd_kernel<T, 1, 2>, pl, d, st, gpt) : launch(fwd_kernel<T, 1, 3>, pl, d, st, gpt);
     case 2:
       if (d.exp != 0 && !two) return launch(fwd_kernel<T, 2, 3, true>, pl, d, st, gpt);
+      // experiment: five resident blocks of four warps (96 registers, no spills) instead of six (80)
+      if (g_tuning.minb == 3 && pl.warps <= 4) return launch(fwd_kernel<T, 2, 5, false, 128>, pl, d, st, gpt);
       return two ? launch(fwd_kernel<T, 2, 2>, pl, d, st, gpt) : launch(fwd_kernel<T, 2, 3>, pl, d, st, gpt);
     default: return launch(fwd_kernel<T, 4, 2>, pl, d, st, gpt);
   }

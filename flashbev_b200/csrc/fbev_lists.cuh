@@ -408,6 +408,9 @@ __device__ __forceinline__ void row_list_phase(const Dev& p, const Tile& t, cons
   const int tile_cells = p.TX * p.TY;
   const int rstride = row_stride(p.cap);
   const float inv_per = 1.0f / (float)per, inv_z = 1.0f / (float)p.Z, inv_tx = 1.0f / (float)p.TX;
+  const int z_shift = (p.Z & (p.Z - 1)) == 0 ? 31 - __clz(p.Z) : -1;
+  const int row0 = t0 / p.TX;
+  const bool one_row = (t0 + p.CPW - 1) / p.TX == row0;  // all cells of the group in one row of the tile
   const unsigned lt = (1u << lane) - 1u;
   // camera of the ci-th set bit of vis, as a byte table in the unused part of sLen (cells use entries 0..7)
   unsigned char* visl = reinterpret_cast<unsigned char*>(sLen + kMaxCellsPerWarp);
@@ -425,9 +428,11 @@ __device__ __forceinline__ void row_list_phase(const Dev& p, const Tile& t, cons
     if (q < total) {
       cl = fast_div(q, inv_per);
       const int r = r0 + (q - cl * per);
-      const int ci = fast_div(r, inv_z), z = r - ci * p.Z;
+      // camera and height bin: a shift and a mask when Z is a power of two
+      const int ci = z_shift >= 0 ? (r >> z_shift) : fast_div(r, inv_z), z = r - ci * p.Z;
       const int tc = t0 + cl;
-      const int ly = fast_div(tc, inv_tx), lx = tc - ly * p.TX;
+      // row and column of the cell inside the tile: the group's own row when it lies within one
+      const int ly = one_row ? row0 : fast_div(tc, inv_tx), lx = tc - ly * p.TX;
       const int x = t.x0 + lx, y = t.y0 + ly;
       if (tc < tile_cells && x < t.x1 && y < t.y1) {
         const int n = visl[ci];  // ci-th visible camera

@@ -15,6 +15,7 @@ extern "C" {
  * threads are not affected): cells per tile in x and y, 16-byte chunks per
  * lane, warps per block, and a selector (last argument); 0 = choose automatically.  Selector values:
  *   2  forward compiled for two resident blocks per SM (128 registers) instead of three
+ *   3  forward (two chunks per lane) compiled for five resident blocks of four warps (96 registers) instead of six
  *   1  feature gradient by direct reductions      6  feature gradient with the per-tile sort
  *   5  record-based depth-gradient kernel also for the parametric modes without entry lists
  *   7  gradients through the global sort whatever the problem size      8  the same with a 4096-entry list
