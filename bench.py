@@ -615,6 +615,21 @@ def main():
             extra["e2e_us_by_path"] = {name: t * 1e3 for name, t in times.items()}
             extra["e2e_path"] = min(times, key=times.get)
             e2e_ms_max = times[extra["e2e_path"]]
+            # what the bus alone takes for this step's bytes: the copies by themselves, page-locked memory
+            dev_buf = torch.empty(total, dtype=torch.uint8, device=device)
+
+            def h2d_only():
+                dev_buf.copy_(packed, non_blocking=True)
+
+            def d2h_only():
+                host_out.copy_(out, non_blocking=True)
+
+            extra["bus_us"] = {"h2d_inputs_alone": timed(h2d_only, ne, 3)[0] * 1e3, "d2h_result_alone": timed(d2h_only, ne, 3)[0] * 1e3}
+            extra["bus_us"]["serial_floor_with_kernel"] = (extra["bus_us"]["h2d_inputs_alone"] + extra["bus_us"]["d2h_result_alone"]
+                                                           + ms_fwd * 1e3)
+            extra["bus_us"]["note"] = ("one step moves its inputs in, computes, and moves the result out, each depending on the one "
+                                       "before: copy times measured alone + the kernel = the floor of a step that overlaps nothing; "
+                                       "the row-band path overlaps the kernel with the result copy")
             # the same best path by the host's clock: `ne` calls queued back to back, one synchronisation at the end
             best_fn = paths[extra["e2e_path"]]
             torch.cuda.synchronize()

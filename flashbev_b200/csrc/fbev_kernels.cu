@@ -184,7 +184,7 @@ static Plan make_plan(const FbevProblem* p, Dev& d, bool bwd, const void* a, con
     tx = pl.CPW * (6 / pl.CPW > 1 ? 6 / pl.CPW : 1);
     ty = 4;
   }
-  const bool tile_tuned = g_tuning.minb != 9;  // 9: tile_x / tile_y steer the gather kernel instead
+  const bool tile_tuned = g_tuning.minb != 9 && g_tuning.minb != 10;  // 9 / 10: tile_x / tile_y steer the gather / scatter kernel instead
   d.TX = tile_tuned && g_tuning.tx > 0 ? g_tuning.tx : tx;
   d.TY = tile_tuned && g_tuning.ty > 0 ? g_tuning.ty : ty;
   d.tiles_x = (p->X + d.TX - 1) / d.TX;
@@ -341,7 +341,10 @@ static int sort_finish_t(const Plan& pl, const Dev& d, cudaStream_t st) {
   const int sms = sm_count();
   unsigned* total = d.ent_count + 1;  // second word of the counter block
   if (texels <= kScanInBlock) {
-    launch_after(ent_scatter_kernel<true>, sms * 8, 256, (size_t)(texels + 1) * 4, st, d, texels, total);
+    // experiments: fbev_set_tuning(blocks per SM, threads, 0, 0, 10)
+    const unsigned sb = g_tuning.minb == 10 && g_tuning.tx > 0 ? (unsigned)g_tuning.tx : 2u;
+    const unsigned stt = g_tuning.minb == 10 && g_tuning.ty > 0 ? (unsigned)g_tuning.ty : 1024u;
+    launch_after(ent_scatter_kernel<true>, sms * sb, stt, (size_t)(texels + 1) * 4, st, d, texels, total);
   } else {
     launch_after(tex_scan_kernel, 1, 1024, 0, st, d.tex_count, texels);
     launch_after(ent_scatter_kernel<false>, sms * 8, 256, 0, st, d, texels, (unsigned*)nullptr);
@@ -739,7 +742,7 @@ int fbev_backward(const FbevProblem* p, const void* grad_out, void* grad_feats, 
   // that much (fbev_backward_scratch_bytes asks for it); small problems keep the single-launch kernels: three more
   // launches cost more than they save there
   const size_t sortb = sort_bytes(p, flags), minb = scratch_min_bytes(p, flags);
-  const bool want_sort = g_tuning.minb == 7 || g_tuning.minb == 8 || g_tuning.minb == 9 ||
+  const bool want_sort = g_tuning.minb == 7 || g_tuning.minb == 8 || g_tuning.minb == 9 || g_tuning.minb == 10 ||
                          (g_tuning.minb == 0 && (size_t)p->B * p->X * (size_t)(p->y_end - p->y_begin) * p->N * p->Z >= 200000);
   const bool sorted = want_sort && sortb != 0 && scratch != nullptr && ((uintptr_t)scratch % 256) == 0 &&
                       scratch_bytes >= minb + sortb;

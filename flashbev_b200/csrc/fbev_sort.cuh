@@ -57,16 +57,17 @@ constexpr unsigned kScanInBlock = 8192;  // texels up to which every scatter blo
 // SCAN: tex_count still holds counts; every block derives the starts in shared memory (dynamic,
 // (texels + 1) * 4 bytes) and the total goes to total_out.  Otherwise tex_count holds the starts already.
 template <bool SCAN>
-__global__ void __launch_bounds__(256) ent_scatter_kernel(const Dev p, unsigned texels, unsigned* __restrict__ total_out) {
+__global__ void __launch_bounds__(1024) ent_scatter_kernel(const Dev p, unsigned texels, unsigned* __restrict__ total_out) {
   extern __shared__ unsigned s_start[];
   grid_dependency_wait();  // the emitting kernel (or the scan) has finished
   const unsigned* start = p.tex_count;
   if (SCAN) {
-    // block-wide exclusive scan: a contiguous slice per thread, shuffles inside a warp, the eight warp totals
-    // through shared memory (two barriers)
-    __shared__ unsigned warp_total[8];
-    const unsigned tid = threadIdx.x, lane = tid & 31u, wid = tid >> 5;
-    const unsigned per = (texels + 255u) / 256u;
+    // block-wide exclusive scan: a contiguous slice per thread, shuffles inside a warp, the warp totals through
+    // shared memory (two barriers).  Every block repeats it, so blocks are large and few: the scan is paid once
+    // per 1024 threads' worth of entries.
+    __shared__ unsigned warp_total[32];
+    const unsigned tid = threadIdx.x, lane = tid & 31u, wid = tid >> 5, nt = blockDim.x, nw = nt >> 5;
+    const unsigned per = (texels + nt - 1u) / nt;
     const unsigned lo = min(tid * per, texels), hi = min(lo + per, texels);
     unsigned sum = 0;
     for (unsigned i = lo; i < hi; ++i) sum += __ldg(p.tex_count + i);
@@ -79,8 +80,7 @@ __global__ void __launch_bounds__(256) ent_scatter_kernel(const Dev p, unsigned 
     if (lane == 31u) warp_total[wid] = incl;
     __syncthreads();
     unsigned before = 0, all = 0;
-#pragma unroll
-    for (unsigned k = 0; k < 8u; ++k) {
+    for (unsigned k = 0; k < nw; ++k) {
       const unsigned wt = warp_total[k];
       before += k < wid ? wt : 0u;
       all += wt;
