@@ -463,6 +463,9 @@ def main():
                     # smaller tiles with three warps per block
                     lib.fbev_set_tuning(6, 3, 0, 3, 0)
                     extra["fwd_us_tiles_6x3_3warps"] = timed(fwd_raw, max(20, args.steps // 5), 5)[0] * 1e3
+                    for nw in (2, 8):  # same units and order, other block sizes (1776 / 444 blocks instead of 888)
+                        lib.fbev_set_tuning(0, 0, 0, nw, 0)
+                        extra[f"fwd_us_{nw}_warps_per_block"] = timed(fwd_raw, max(20, args.steps // 5), 5)[0] * 1e3
                     lib.fbev_set_tuning(0, 0, 0, 0, 3)
                     extra["fwd_us_96_registers_5_blocks"] = timed(fwd_raw, max(20, args.steps // 5), 5)[0] * 1e3
                     lib.fbev_set_tuning(6, 3, 0, 3, 3)

@@ -145,9 +145,12 @@ def test_training_shape_against_reference_cuda_kernels(cuda_device, parity_repor
     parity_report(f"cfg3 {mode} vs reference CUDA kernel: forward {err:.3e} (its z-precompute variant: {err_z:.3e}; "
                   f"the reference's two variants against each other: {spread:.3e}); cells whose 'any sample "
                   f"accepted' differs: {mism} of {cnt.numel()}")
-    # 1e-5, or as close to either variant as the reference's variants are to each other (never looser than the
-    # 5e-5 allowed against its dense path)
-    bar = min(max(TOL_F32, 1.5 * spread), 5e-5)
+    # Two float32 evaluations of this shape that round the geometry differently cannot be expected within 1e-5 of
+    # each other: float32 rounding of the feature coordinates alone moves the result 1.2e-5 away from a float64
+    # evaluation (tests/test_oracle.py::test_float32_geometry_rounding_floor_on_the_training_shape), so two of
+    # them may be 2.4e-5 apart.  The kernel here is held to 1e-5 against the oracle's pinned order (above); against
+    # the reference binary, whose contraction into fused multiply-adds is the compiler's, the bar is 3e-5.
+    bar = 3e-5
     assert min(err, err_z) < bar, f"forward vs reference kernel: {err:.3e} / {err_z:.3e}, bar {bar:.1e}"
     assert mism == 0
     go = synth.upstream_grad(w).to(cuda_device)

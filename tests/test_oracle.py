@@ -179,3 +179,51 @@ def test_projection_rejects_a_singular_pose():
     s2e[0, 0, 2] = 0.0  # a zero row: the elimination meets an exact zero pivot
     with pytest.raises(ValueError):
         O.projection(s2e, g["camera2imgs"], g["post_rots"], g["post_trans"])
+
+
+def test_float32_geometry_rounding_floor_on_the_training_shape():
+    """How far ANY float32 evaluation of the operator is from exact arithmetic on the training shape (cfg3: image
+    512x1408, feature maps 32x88, one sample here).  Everything is evaluated twice with the same integer decisions
+    (texels, acceptance): in the oracle's pinned float32 order, and in float64 from the projection on.  The feature
+    coordinate reaches 88, where a float32 ulp is 7.6e-6 of a texel, and the bilinear weights inherit that: the two
+    results are about 1.2e-5 apart (max|a-b| / max|b|).  That is the floor below which two float32 implementations
+    that round the geometry differently (this library's pinned order, the reference binary's compiler-chosen
+    contraction) cannot be compared; the 1e-5 bar therefore applies against the oracle's pinned order, and the
+    comparison with the reference's CUDA kernels on this shape uses 3e-5."""
+    from flashbev_b200 import synth
+    from tests.helpers import host_threads, inputs_for, oracle_problem, rel_err
+    w = synth.workload("cfg3", B=1)
+    inp = inputs_for(w, "laplace")
+    p = oracle_problem(inp, w, "laplace", threshold=1e-6)
+    pinned = O.forward(p, threads=host_threads())[0]
+    idx = O.indices(p)
+    feats = inp["image_feats"].double().numpy()[0]
+    depth = inp["depth_params"].double().numpy()[0]
+    P = inp["projection_matrices"].double().numpy()[0]
+    X, Y, Z = w.grid
+    roi = np.array(w.roi, np.float32)
+    vs = [np.float64(np.float32((roi[2 * i + 1] - roi[2 * i]) / np.float32(g))) for i, g in enumerate((X, Y, Z))]
+    axes = [np.float64(roi[2 * i]) + (np.arange(g) + 0.5) * vs[i] for i, g in enumerate((X, Y, Z))]
+    gx, gy, gz = np.meshgrid(*axes, indexing="xy")  # [Y,X,Z]
+    ih, iw = w.image_size
+    out = np.zeros((Y, X, w.C))
+    cnt = np.zeros((Y, X))
+    for n in range(w.N):
+        u, v, d = (P[n, r, 0] * gx + P[n, r, 1] * gy + P[n, r, 2] * gz + P[n, r, 3] for r in range(3))
+        cd = np.maximum(d, 1e-6)
+        fu, fv = u / cd / iw * w.W, v / cd / ih * w.H
+        valid = idx["valid"][0, n].astype(bool)
+        u0, v0 = np.where(valid, idx["u0"][0, n], 0), np.where(valid, idx["v0"][0, n], 0)
+        du, dv = fu - u0, fv - v0
+        u1, v1 = np.minimum(u0 + 1, w.W - 1), np.minimum(v0 + 1, w.H - 1)
+        wts = [((1 - du) * (1 - dv), v0, u0), ((1 - du) * dv, v1, u0), (du * (1 - dv), v0, u1), (du * dv, v1, u1)]
+        mean = sum(wt * depth[n, vv, uu, 0] for wt, vv, uu in wts)
+        sigma = sum(wt * depth[n, vv, uu, 1] for wt, vv, uu in wts)
+        wgt = np.where(valid, 0.5 * np.exp(-np.abs((d - mean) / (sigma + 1e-6))) / (sigma + 1e-6), 0.0)
+        for z in range(Z):
+            f = sum(wt[..., z, None] * feats[n, vv[..., z], uu[..., z]] for wt, vv, uu in wts)
+            out += f * wgt[..., z, None]
+        cnt += valid.sum(-1)
+    exact = np.where(cnt[..., None] > 0, out / np.maximum(cnt, 1)[..., None], 0.0)
+    floor = rel_err(pinned, exact)
+    assert 5e-6 < floor < 2e-5, floor
