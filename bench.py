@@ -421,26 +421,44 @@ def main():
             nbytes = lib.fbev_backward_scratch_bytes(ctypes.byref(prob), flags)
             scratch = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=device)
 
-            def fwd_bwd():
-                fwd_raw()
-                rc = lib.fbev_backward(ctypes.byref(prob), go.data_ptr(), g_feats.data_ptr(), g_depth.data_ptr(),
-                                       scratch.data_ptr() if nbytes else None, nbytes, flags, stream)
+            # a training step keeps the forward's lists for the backward (FbevProblem.saved_state), as the autograd
+            # wrapper does; the variant without them rebuilds the lists in the backward
+            prob_t = type(prob).from_buffer_copy(prob)
+            nsaved = lib.fbev_saved_state_bytes(ctypes.byref(prob_t))
+            saved = torch.empty(max(nsaved, 16), dtype=torch.uint8, device=device)
+            prob_t.saved_state, prob_t.saved_state_bytes = saved.data_ptr(), nsaved
+
+            def make_step(pr):
+                def step():
+                    rc = lib.fbev_forward(ctypes.byref(pr), out.data_ptr(), None, stream)
+                    rc = rc or lib.fbev_backward(ctypes.byref(pr), go.data_ptr(), g_feats.data_ptr(), g_depth.data_ptr(),
+                                                 scratch.data_ptr() if nbytes else None, nbytes, flags, stream)
+                    if rc:
+                        raise RuntimeError(_lib.strerror(rc))
+                return step
+
+            def fwd_train():
+                rc = lib.fbev_forward(ctypes.byref(prob_t), out.data_ptr(), None, stream)
                 if rc:
                     raise RuntimeError(_lib.strerror(rc))
 
+            fwd_bwd = make_step(prob_t)
             nb = max(10, args.steps // 5)
             ms_fb, _ = timed(fwd_bwd, nb, 5)
             extra["fwd_bwd_us"] = ms_fb * 1e3
-            extra["fwd_bwd_note"] = "forward + backward (gradients for features and depth), device time, L2 flushed"
+            extra["fwd_bwd_note"] = ("forward + backward (gradients for features and depth), device time, L2 flushed; the "
+                                     "forward keeps its lists for the backward (saved state of %.1f MB)" % (nsaved / 2 ** 20))
+            extra["fwd_us_training_forward"] = timed(fwd_train, nb, 5)[0] * 1e3
+            extra["fwd_bwd_us_lists_rebuilt_in_backward"] = timed(make_step(prob), nb, 5)[0] * 1e3
 
-            # the same seven launches replayed from a CUDA graph (what a training loop with static shapes does)
+            # the same launches replayed from a CUDA graph (what a training loop with static shapes does)
             side = torch.cuda.Stream(device=device)
             with torch.cuda.stream(side):
                 graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(graph, stream=side):
                     cs = torch.cuda.current_stream().cuda_stream
-                    rc = lib.fbev_forward(ctypes.byref(prob), out.data_ptr(), None, cs)
-                    rc = rc or lib.fbev_backward(ctypes.byref(prob), go.data_ptr(), g_feats.data_ptr(), g_depth.data_ptr(),
+                    rc = lib.fbev_forward(ctypes.byref(prob_t), out.data_ptr(), None, cs)
+                    rc = rc or lib.fbev_backward(ctypes.byref(prob_t), go.data_ptr(), g_feats.data_ptr(), g_depth.data_ptr(),
                                                  scratch.data_ptr() if nbytes else None, nbytes, flags, cs)
                 if rc:
                     raise RuntimeError(_lib.strerror(rc))
@@ -483,17 +501,21 @@ def main():
                 out3 = torch.empty(w3.B, w3.Y, w3.X, w3.C, dtype=torch.float32, device=device)
                 go3 = synth.upstream_grad(w3).to(device)
                 gf3, gd3 = torch.empty_like(keep3[0]), torch.empty_like(keep3[1])
+                prob3i = type(prob3).from_buffer_copy(prob3)   # inference forward: nothing saved
+                ns3 = lib.fbev_saved_state_bytes(ctypes.byref(prob3))
+                sv3 = torch.empty(max(ns3, 16), dtype=torch.uint8, device=device)
+                prob3.saved_state, prob3.saved_state_bytes = sv3.data_ptr(), ns3
                 nb3 = lib.fbev_backward_scratch_bytes(ctypes.byref(prob3), flags)
                 sc3 = torch.empty(max(nb3, 1), dtype=torch.uint8, device=device)
 
                 def fwd3():
-                    rc = lib.fbev_forward(ctypes.byref(prob3), out3.data_ptr(), None, stream)
+                    rc = lib.fbev_forward(ctypes.byref(prob3i), out3.data_ptr(), None, stream)
                     if rc:
                         raise RuntimeError(_lib.strerror(rc))
 
                 def fwd_bwd3():
-                    fwd3()
-                    rc = lib.fbev_backward(ctypes.byref(prob3), go3.data_ptr(), gf3.data_ptr(), gd3.data_ptr(),
+                    rc = lib.fbev_forward(ctypes.byref(prob3), out3.data_ptr(), None, stream)
+                    rc = rc or lib.fbev_backward(ctypes.byref(prob3), go3.data_ptr(), gf3.data_ptr(), gd3.data_ptr(),
                                            sc3.data_ptr() if nb3 else None, nb3, flags, stream)
                     if rc:
                         raise RuntimeError(_lib.strerror(rc))
@@ -501,7 +523,8 @@ def main():
                 extra["cfg3_fwd_us"] = timed(fwd3, 20, 5)[0] * 1e3
                 extra["cfg3_fwd_bwd_us"] = timed(fwd_bwd3, 20, 5)[0] * 1e3
                 extra["cfg3_workload"] = workload_description(w3, w3.B, args.mode) + " + backward (both gradients)"
-                del in3, out3, go3, gf3, gd3, sc3
+                extra["cfg3_saved_state_mb"] = ns3 / 2 ** 20
+                del in3, out3, go3, gf3, gd3, sc3, sv3
 
             # the reference's own mode on the same shapes (float32, parametric laplace depth, mean pooling), for
             # comparison with the reference CUDA kernel that `--impl reference` times on the same box
@@ -665,17 +688,21 @@ def main():
                 out4 = torch.empty(B4, w4.Y, w4.X, w4.C, dtype=keep4[0].dtype, device=device)
                 go4 = synth.upstream_grad(w4, B=B4).to(device=device, dtype=keep4[0].dtype)
                 gf4, gd4 = torch.empty_like(keep4[0]), torch.empty_like(keep4[1])
+                prob4i = type(prob4).from_buffer_copy(prob4)   # inference forward: nothing saved
+                ns4 = lib.fbev_saved_state_bytes(ctypes.byref(prob4))
+                sv4 = torch.empty(max(ns4, 16), dtype=torch.uint8, device=device)
+                prob4.saved_state, prob4.saved_state_bytes = sv4.data_ptr(), ns4
                 nb4 = lib.fbev_backward_scratch_bytes(ctypes.byref(prob4), flags)
                 sc4 = torch.empty(max(nb4, 1), dtype=torch.uint8, device=device)
 
                 def fwd4():
-                    rc = lib.fbev_forward(ctypes.byref(prob4), out4.data_ptr(), None, stream)
+                    rc = lib.fbev_forward(ctypes.byref(prob4i), out4.data_ptr(), None, stream)
                     if rc:
                         raise RuntimeError(_lib.strerror(rc))
 
                 def fwd_bwd4():
-                    fwd4()
-                    rc = lib.fbev_backward(ctypes.byref(prob4), go4.data_ptr(), gf4.data_ptr(), gd4.data_ptr(),
+                    rc = lib.fbev_forward(ctypes.byref(prob4), out4.data_ptr(), None, stream)
+                    rc = rc or lib.fbev_backward(ctypes.byref(prob4), go4.data_ptr(), gf4.data_ptr(), gd4.data_ptr(),
                                            sc4.data_ptr() if nb4 else None, nb4, flags, stream)
                     if rc:
                         raise RuntimeError(_lib.strerror(rc))
@@ -688,8 +715,8 @@ def main():
                                  "fwd_samples_per_s": 64 / (float(t4[0]) * 1e-3),
                                  "fwd_bwd_samples_per_s": 64 / (float(t4[1]) * 1e-3),
                                  "fwd_cells_per_s": 64 * w4.X * w4.Y / (float(t4[0]) * 1e-3),
-                                 "backward_scratch_mb_per_gpu": nb4 / 2 ** 20}
-                del in4, out4, go4, gf4, gd4, sc4
+                                 "backward_scratch_mb_per_gpu": nb4 / 2 ** 20, "saved_lists_mb_per_gpu": ns4 / 2 ** 20}
+                del in4, out4, go4, gf4, gd4, sc4, sv4
 
             if world > 1:
                 # one large sample (cfg5) with its BEV rows split over the ranks: all-gather of the output

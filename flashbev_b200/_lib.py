@@ -23,7 +23,7 @@ ERR_STATIC_LIMIT = 11
 
 # every symbol include/fbev.h declares (the operator) ...
 EXPORTS = (
-    "fbev_forward", "fbev_forward_to_host", "fbev_forward_peers", "fbev_forward_multicast", "fbev_backward", "fbev_backward_scratch_bytes", "fbev_backward_min_scratch_bytes", "fbev_backward_static_scratch",
+    "fbev_forward", "fbev_forward_to_host", "fbev_forward_peers", "fbev_forward_multicast", "fbev_backward", "fbev_backward_scratch_bytes", "fbev_backward_min_scratch_bytes", "fbev_saved_state_bytes", "fbev_backward_static_scratch",
     "fbev_debug_indices",
     "fbev_flash_bevpool", "fbev_flash_bevpool_grad", "fbev_projection_matrices", "fbev_pillar_pool",
     "fbev_strerror", "fbev_version", "fbev_source_hash",
@@ -60,6 +60,8 @@ class FbevProblem(ctypes.Structure):
         ("roi_range", ctypes.c_void_p),
         ("status", ctypes.c_void_p),
         ("workspace", ctypes.c_void_p),
+        ("saved_state", ctypes.c_void_p),
+        ("saved_state_bytes", ctypes.c_uint64),
         ("depth_stats", ctypes.c_void_p),
     ]
 
@@ -102,6 +104,8 @@ def load(build_if_missing: bool = True) -> ctypes.CDLL:
     lib.fbev_forward_multicast.restype = i32
     lib.fbev_backward_scratch_bytes.argtypes = [ctypes.POINTER(FbevProblem), i32]
     lib.fbev_backward_scratch_bytes.restype = ctypes.c_size_t
+    lib.fbev_saved_state_bytes.argtypes = [ctypes.POINTER(FbevProblem)]
+    lib.fbev_saved_state_bytes.restype = ctypes.c_size_t
     lib.fbev_backward_min_scratch_bytes.argtypes = [ctypes.POINTER(FbevProblem), i32]
     lib.fbev_backward_min_scratch_bytes.restype = ctypes.c_size_t
     lib.fbev_backward.argtypes = [ctypes.POINTER(FbevProblem), vp, vp, vp, vp, ctypes.c_size_t, i32, vp]

@@ -536,9 +536,6 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_feats_sorted_kernel(con
 // once per record texel (two gathers, a dot product, a shuffle reduction over the group's lanes) and
 // then lets one lane per SAMPLE combine four T values and issue that sample's atomics.  Compared with
 // evaluating S per sample this reads 2.7 times fewer texels and spreads the atomics over all lanes.
-__host__ __device__ inline size_t depth_warp_bytes(int CPW, int cap) {
-  return 512 + (size_t)CPW * row_stride(cap) * 16 + (size_t)CPW * cap * 48;
-}
 
 // EMIT: the kernel also leaves the entries of the sorted feature gradient (emit_entries) from the same row
 // records, so that one list phase serves both gradients.
@@ -575,6 +572,8 @@ __device__ __forceinline__ void bwd_depth_body(const Dev& p) {
   // fixed cost is shared by many samples and the depth tensor is small enough for its atomics to contend);
   // measured a loss with two or three cells per warp on large feature maps
   const bool merge_bins = p.CPW >= 4;
+  // lists left by a training forward in this very layout (else they are rebuilt)
+  const bool use_saved = p.saved != nullptr && __ldg(reinterpret_cast<const unsigned*>(p.saved) + 1) == p.saved_key;
   int loaded_b = -1;
   UnitLoop sched;
   sched.begin(p, s_tile, warp, nwarps);
@@ -606,8 +605,16 @@ __device__ __forceinline__ void bwd_depth_body(const Dev& p) {
       }
       if (lane < p.CPW) sCnt[lane] = 0;
       __syncwarp();
+      const unsigned unit = (unsigned)(tile * ngroups + grp);
       if (mean_pool && !single_pass) {  // the count of all passes is needed before the first contribution
         for (int r0 = 0; r0 < ncand; r0 += p.cap) {
+          uint4 hdr;
+          const uint4* blk;
+          if (use_saved && saved_header(p, unit, r0 / p.cap, hdr, blk)) {  // the saved pass knows its sample counts
+            if (lane < p.CPW) sCnt[lane] += (int)(((lane < 4 ? hdr.z : hdr.w) >> (8 * (lane & 3))) & 0xffu);
+            __syncwarp();
+            continue;
+          }
           if (lane < p.CPW) sLen[lane] = 0;
           __syncwarp();
           row_list_phase<T, false>(p, t, h, vis, (unsigned)cpt, t0, r0, min(r0 + p.cap, ncand), vs, vmin, image_h,
@@ -628,8 +635,9 @@ __device__ __forceinline__ void bwd_depth_body(const Dev& p) {
           if (single_pass) sCnt[lane] = 0;
         }
         __syncwarp();
-        row_list_phase<T, true, true>(p, t, h, vis, (unsigned)cpt, t0, r0, min(r0 + p.cap, ncand), vs, vmin, image_h,
-                                      image_w, sLen, sCnt, recs, lane, samp, sSmp);
+        if (!(use_saved && load_pass(p, unit, r0 / p.cap, sLen, sCnt, sSmp, recs, samp, lane)))
+          row_list_phase<T, true, true>(p, t, h, vis, (unsigned)cpt, t0, r0, min(r0 + p.cap, ncand), vs, vmin, image_h,
+                                        image_w, sLen, sCnt, recs, lane, samp, sSmp);
         if (mean_pool && single_pass && lane < p.CPW) {
           const int cnt = sCnt[lane];
           inv_of_lane = cnt > 0 ? __fdiv_rn(1.0f, (float)cnt) : 0.0f;

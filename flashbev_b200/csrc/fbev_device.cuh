@@ -61,6 +61,16 @@ struct Dev {
   float4* ent_d;         // [ent_cap] parametric depth: d mean, d sigma of u0, then of u1 (else null)
   float4* ent_d_sorted;  // [ent_cap]
   unsigned ent_cap;
+  // row records and sample lists a training forward leaves for the backward (null: none; fbev_lists.cuh: SavedLists)
+  uint4* saved;          // [0] = {cursor, plan key, -, -}, then the directory, then the data area
+  unsigned saved_dir;    // directory entries (units x passes); entry e is word e of saved + 1
+  unsigned saved_cap;    // 16-byte units of data area that follow the directory
+  unsigned saved_key;    // identifies the list layout (cells per warp, records per pass, tiling): both sides must agree
+  unsigned saved_unit0;  // first unit of this launch within the saved state (backward over a slice of the batch)
+  int saved_passes;      // directory entries per unit
+  // host side only: size of the saved state, batch size it was written for, first sample of this launch in it
+  unsigned long long saved_bytes;
+  int saved_B, saved_b0;
 };
 
 // Programmatic dependent launch (sm_90+).  A kernel launched with the programmatic-serialization attribute may

@@ -14,7 +14,11 @@ namespace fbev {
 // EXPERIMENTS: the instantiation that honours the switches of fbev_set_experiment (Dev.exp); the ordinary one
 // carries none of their code.
 // MAXT: largest block the instantiation is launched with (with MINB it sets the register budget).
-template <typename T, int V, int MINB, bool EXPERIMENTS = false, int MAXT = kMaxWarps * 32>
+// TRAIN: the forward of a training step.  It runs in the lane layout and pass size of the depth-gradient kernel,
+// keeps every accepted sample beside the row records (row_list_phase with SAMPLES) and writes both to the saved
+// state (save_pass), from which the backward takes them instead of rebuilding them.  Same results as the ordinary
+// instantiation up to the grouping of the sums (the passes are half as long).
+template <typename T, int V, int MINB, bool EXPERIMENTS = false, int MAXT = kMaxWarps * 32, bool TRAIN = false>
 __global__ void __launch_bounds__(MAXT, MINB) fwd_kernel(const __grid_constant__ Dev p) {
   constexpr int E = Chunk<T>::E;
   extern __shared__ __align__(16) unsigned char smem[];
@@ -25,11 +29,14 @@ __global__ void __launch_bounds__(MAXT, MINB) fwd_kernel(const __grid_constant__
   const int image_h = __ldg(p.isize), image_w = __ldg(p.isize + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  unsigned char* wa = h.warp_area + (size_t)warp * fwd_warp_bytes(p.CPW, p.cap);
+  unsigned char* wa = h.warp_area + (size_t)warp * (TRAIN ? depth_warp_bytes(p.CPW, p.cap) : fwd_warp_bytes(p.CPW, p.cap));
   int* sLen = reinterpret_cast<int*>(wa);  // [32] records in the list of each cell
   int* sCnt = sLen + 32;                    // [32] accepted samples of each cell
-  uint4* recs = reinterpret_cast<uint4*>(wa + 256);
+  int* sSmp = sCnt + 32;                    // [32] TRAIN: sample records of each cell, this pass
+  uint4* recs = reinterpret_cast<uint4*>(wa + (TRAIN ? 512 : 256));
   const int rstride = row_stride(p.cap);
+  uint4* samp = recs + (size_t)p.CPW * rstride;  // TRAIN: three words per accepted sample
+  if (TRAIN && blockIdx.x == 0 && threadIdx.x == 0) reinterpret_cast<unsigned*>(p.saved)[1] = p.saved_key;
 
   const int g = lane / p.GL, lg = lane - g * p.GL;
   const bool lane_used = g < p.CPW;
@@ -90,10 +97,19 @@ __global__ void __launch_bounds__(MAXT, MINB) fwd_kernel(const __grid_constant__
       if (lane < p.CPW) sCnt[lane] = 0;
 
       for (int r0 = 0; r0 < ncand; r0 += p.cap) {
-        if (lane < p.CPW) sLen[lane] = 0;
+        if (lane < p.CPW) {
+          sLen[lane] = 0;
+          if (TRAIN) sSmp[lane] = 0;
+        }
         __syncwarp();
-        row_list_phase<T>(p, t, h, vis, (unsigned)cpt, t0, r0, min(r0 + p.cap, ncand), vs, vmin, image_h, image_w, sLen, sCnt, recs,
-                          lane);
+        if (TRAIN) {
+          row_list_phase<T, true, true>(p, t, h, vis, (unsigned)cpt, t0, r0, min(r0 + p.cap, ncand), vs, vmin, image_h, image_w,
+                                        sLen, sCnt, recs, lane, samp, sSmp);
+          save_pass(p, (unsigned)(tile * ngroups + grp), r0 / p.cap, sLen, sSmp, recs, samp, lane);
+        } else {
+          row_list_phase<T>(p, t, h, vis, (unsigned)cpt, t0, r0, min(r0 + p.cap, ncand), vs, vmin, image_h, image_w, sLen, sCnt,
+                            recs, lane);
+        }
         const int n = cell_ok ? sLen[g] : 0;
         const uint4* rec = recs + (size_t)g * rstride;
 #pragma unroll 2

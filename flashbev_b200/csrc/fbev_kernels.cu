@@ -95,6 +95,10 @@ static void fill_dev(const FbevProblem* p, Dev& d) {
   d.status = p->status;
   d.sched = reinterpret_cast<unsigned*>(p->workspace);
   d.exp = g_experiment;
+  d.saved = reinterpret_cast<uint4*>(p->saved_state);
+  d.saved_bytes = p->saved_state_bytes;
+  d.saved_B = p->B;
+  d.saved_b0 = 0;
   d.out_f32 = (p->out_dtype == FBEV_F32 && p->dtype != FBEV_F32) ? 1 : 0;
   d.B = p->B; d.N = p->N; d.H = p->H; d.W = p->W; d.C = p->C; d.D = p->D;
   d.X = p->X; d.Y = p->Y; d.Z = p->Z;
@@ -207,6 +211,36 @@ static Plan make_plan(const FbevProblem* p, Dev& d, bool bwd, const void* a, con
   return pl;
 }
 
+// Lays the saved list state (include/fbev.h: FbevProblem.saved_state) out for a launch whose plan is in d: directory
+// size, data capacity, plan key, first unit.  Leaves d.saved null when there is no state or it cannot even hold the
+// directory.  Forward and backward call this with the same plan, so they agree on every field.
+static void setup_saved(Dev& d, int CPW) {
+  uint4* base = d.saved;
+  d.saved = nullptr;
+  if (base == nullptr || CPW <= 0 || CPW > 8 || d.cap <= 0 || d.cap > 127) return;
+  const unsigned long long ngroups = (unsigned long long)(d.TX * d.TY + CPW - 1) / CPW;
+  const unsigned long long per_sample = (unsigned long long)d.tiles_x * d.tiles_y * ngroups;
+  const unsigned long long passes = ((unsigned long long)d.N * d.Z + d.cap - 1) / d.cap;
+  const unsigned long long dir = per_sample * (unsigned long long)d.saved_B * passes;
+  const unsigned long long units16 = d.saved_bytes / 16;
+  const unsigned long long dir16 = (dir + 3) / 4;
+  if (dir == 0 || dir >= (1ull << 32) || units16 < 1 + dir16 + 64) return;
+  unsigned long long cap16 = units16 - 1 - dir16;
+  if (cap16 > 0xfffffff0ull - dir16) cap16 = 0xfffffff0ull - dir16;  // offsets are 32-bit
+  d.saved = base;
+  d.saved_dir = (unsigned)dir;
+  d.saved_cap = (unsigned)cap16;
+  d.saved_passes = (int)passes;
+  d.saved_unit0 = (unsigned)(per_sample * (unsigned long long)d.saved_b0);
+  unsigned key = 2166136261u;  // FNV-1a over what fixes the layout of the lists
+  const int fields[] = {CPW, d.GL, d.cap, d.TX, d.TY, d.tiles_x, d.tiles_y, d.N, d.Z, d.y0, d.y1, d.X, d.saved_B, d.mode};
+  for (int f : fields) {
+    key ^= (unsigned)f;
+    key *= 16777619u;
+  }
+  d.saved_key = key | 1u;  // never 0: a cleared header matches nothing
+}
+
 static int sm_count() {
   static int cached[64] = {0};
   int dev = 0;
@@ -302,6 +336,14 @@ static cudaError_t launch_after(void (*kernel)(KArgs...), unsigned grid, unsigne
 template <typename T>
 static int forward_t(const Plan& pl, const Dev& d, cudaStream_t st) {
   if (!pl.chunked) return launch(fwd_generic_kernel<T>, pl, d, st);
+  if (d.saved != nullptr) {  // training forward: also writes the lists the backward needs
+    const int gpt = (d.TX * d.TY + pl.CPW - 1) / pl.CPW;
+    switch (pl.V) {
+      case 1: return launch(fwd_kernel<T, 1, 3, false, kMaxWarps * 32, true>, pl, d, st, gpt);
+      case 2: return launch(fwd_kernel<T, 2, 3, false, kMaxWarps * 32, true>, pl, d, st, gpt);
+      default: return launch(fwd_kernel<T, 4, 2, false, kMaxWarps * 32, true>, pl, d, st, gpt);
+    }
+  }
   const bool two = g_tuning.minb == 2;  // compiled for two resident blocks per SM (128 registers) instead of three (80)
   const int gpt = (d.TX * d.TY + pl.CPW - 1) / pl.CPW;  // groups of CPW cells per tile
   switch (pl.V) {
@@ -417,6 +459,7 @@ static int backward_t(const Plan& pl, Dev d, const Plan& plf, const Dev& df, cud
   // this latency-bound kernel needs more than it minds a second pass on tiles that three cameras see
   pld.cap = dd.cap = 16;
   pld.smem = header_bytes(dd.N) + (size_t)pld.warps * depth_warp_bytes(pld.CPW, pld.cap);
+  setup_saved(dd, pld.CPW);  // lists of a training forward, when the caller kept them
   if ((d.flags & FBEV_BWD_FEATS) && plf.chunked) {
     if (depth_on_records && df.ent != nullptr) {
       // both gradients from one list phase: the depth kernel also emits the entries of the sorted feature gradient
@@ -501,9 +544,25 @@ static int forward_impl(const FbevProblem* p, void* out, int32_t* valid_count, v
     d.out_peers[k] = peers[k];
   }
   if (unknown_hw) d.H = d.W = 46340;  // feature_size entries up to 2^31 texels pass the in-kernel bound
-  const Plan pl = make_plan(p, d, false, p->image_feats, out, nullptr);
+  if ((uintptr_t)p->saved_state % 16) return FBEV_ERR_ALIGN;
+  const bool train = p->saved_state != nullptr && !unknown_hw;
+  // a training forward runs in the depth-gradient kernel's layout (see backward_t) so that its lists can be reused
+  Plan pl = make_plan(p, d, false, p->image_feats, out, nullptr, !(train && is_categorical(p->mode)));
   if (out_multicast != nullptr && !pl.chunked) return FBEV_ERR_RANGE;  // only the 16-byte-chunk kernel stores to it
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (train && pl.chunked) {
+    pl.cap = d.cap = 16;
+    pl.smem = header_bytes(p->N) + (size_t)pl.warps * depth_warp_bytes(pl.CPW, pl.cap);
+    setup_saved(d, pl.CPW);
+  } else {
+    d.saved = nullptr;
+  }
+  if (train && d.saved == nullptr) {
+    pl = make_plan(p, d, false, p->image_feats, out, nullptr);  // no usable state after all: the ordinary forward
+  } else if (d.saved != nullptr && cudaMemsetAsync(d.saved, 0, 16, st) != cudaSuccess) {  // cursor and key
+    cudaGetLastError();
+    return FBEV_ERR_LAUNCH;
+  }
   const int src = launch_softmax_stats(p, st);
   if (src != FBEV_OK) return src;
   switch (p->dtype) {
@@ -694,6 +753,18 @@ int fbev_forward_multicast(const FbevProblem* p, void* out, void* out_multicast,
   return forward_impl(p, out, valid_count, stream, false, nullptr, 0, out_multicast);
 }
 
+size_t fbev_saved_state_bytes(const FbevProblem* p) {
+  if (p == nullptr || validate(p) != FBEV_OK) return 0;
+  // directory: one word per (group of cells, pass), sized for the smallest groups and passes the kernels use;
+  // data: 24 bytes per candidate covers the benchmark rigs (about 17 are used) with room to spare, at most 1 GiB
+  const unsigned long long cells = (unsigned long long)p->B * p->X * (unsigned long long)(p->y_end - p->y_begin);
+  const unsigned long long cand = cells * p->N * p->Z;
+  const unsigned long long dir = (cells / 2 + (unsigned long long)p->B * 4096) * (((unsigned long long)p->N * p->Z + 15) / 16);
+  unsigned long long data = cand * 24;
+  if (data > (1ull << 30)) data = 1ull << 30;
+  return (size_t)(16 + ((dir * 4 + 255) / 256) * 256 + data + 4096);
+}
+
 size_t fbev_backward_min_scratch_bytes(const FbevProblem* p, int flags) {
   return p == nullptr ? 0 : scratch_min_bytes(p, flags);
 }
@@ -709,6 +780,7 @@ int fbev_backward(const FbevProblem* p, const void* grad_out, void* grad_feats, 
   if (rc != FBEV_OK) return rc;
   if ((flags & (FBEV_BWD_FEATS | FBEV_BWD_DEPTH)) == 0) return FBEV_OK;
   if (grad_out == nullptr) return FBEV_ERR_NULL;
+  if ((uintptr_t)p->saved_state % 16) return FBEV_ERR_ALIGN;
   if ((flags & FBEV_BWD_FEATS) && grad_feats == nullptr) return FBEV_ERR_NULL;
   if ((flags & FBEV_BWD_DEPTH) && grad_depth == nullptr) return FBEV_ERR_NULL;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
@@ -787,6 +859,8 @@ int fbev_backward(const FbevProblem* p, const void* grad_out, void* grad_feats, 
     fill_dev(&q, d);
     d.gout = gout;
     d.flags = flags;
+    d.saved_B = p->B;  // the saved lists were written for the whole batch
+    d.saved_b0 = b0;
     d.gfeat = gfeat_all ? gfeat_all + (size_t)b0 * tex_sample * p->C : nullptr;
     d.gdepth = gdepth_all ? gdepth_all + (size_t)b0 * tex_sample * p->D : nullptr;
     const Plan pl = make_plan(&q, d, true, q.image_feats, gout, f32 ? (const void*)d.gfeat : (const void*)nullptr);

@@ -380,6 +380,107 @@ __device__ __forceinline__ int fast_div(int q, float inv) { return __float2int_r
 __host__ __device__ inline int row_stride(int cap) { return 2 * cap + 1; }
 __host__ __device__ inline size_t fwd_warp_bytes(int CPW, int cap) { return 256 + (size_t)CPW * row_stride(cap) * 16; }
 
+// Per-warp shared area of the kernels that also keep every accepted sample (depth gradient, training forward):
+// list lengths, sample counts, sample-record counts, the row records, then three 16-byte words per sample.
+__host__ __device__ inline size_t depth_warp_bytes(int CPW, int cap) {
+  return 512 + (size_t)CPW * row_stride(cap) * 16 + (size_t)CPW * cap * 48;
+}
+
+// Lists saved by a training forward for the backward.  The depth-gradient kernel needs exactly what the forward's
+// list phase produces, per group of cells and pass: the row records and the sample records.  Rebuilding them costs
+// the backward more than everything else it does, so a forward that knows a backward will follow writes them out:
+//   saved[0]                      {cursor: 16-byte units handed out so far, plan key, -, -}
+//   saved[1 ..]                   directory, one 32-bit word per (unit, pass): offset of the pass's block in 16-byte
+//                                 units from saved, or kSavedMissing when the data area was full
+//   block                         {list lengths of the cells (bytes 0-7), sample counts (bytes 8-15)}, the cells' row
+//                                 records back to back, the cells' sample records back to back
+// A unit is one group of cells of one tile (tile * groups + group), the same in both kernels as long as both use
+// the same tiling and lane layout, which the plan key vouches for.  A block that did not fit is simply rebuilt.
+constexpr unsigned kSavedMissing = 0xffffffffu;
+
+__device__ __forceinline__ unsigned* saved_dir_entry(const Dev& p, unsigned unit, int pass) {
+  return reinterpret_cast<unsigned*>(p.saved + 1) + ((size_t)(p.saved_unit0 + unit) * p.saved_passes + pass);
+}
+
+// Writes this warp's lists of one pass (after row_list_phase with SAMPLES) to the saved state.
+__device__ __forceinline__ void save_pass(const Dev& p, unsigned unit, int pass, const int* sLen, const int* sSmp,
+                                          const uint4* recs, const uint4* samp, int lane) {
+  const int rstride = row_stride(p.cap);
+  int nrec = 0, nsmp = 0;
+  for (int c = 0; c < p.CPW; ++c) {
+    nrec += sLen[c];
+    nsmp += sSmp[c];
+  }
+  const unsigned need = 1u + (unsigned)nrec + 3u * (unsigned)nsmp;
+  const unsigned data0 = 1u + (p.saved_dir + 3u) / 4u;
+  unsigned off = 0;
+  if (lane == 0) off = atomicAdd(reinterpret_cast<unsigned*>(p.saved), need);
+  off = __shfl_sync(kFull, off, 0);
+  const bool fits = (unsigned long long)off + need <= (unsigned long long)p.saved_cap;
+  if (lane == 0) *saved_dir_entry(p, unit, pass) = fits ? data0 + off : kSavedMissing;
+  if (!fits) return;
+  uint4* dst = p.saved + data0 + off;
+  if (lane == 0) {
+    unsigned a = 0, b = 0, c2 = 0, d = 0;  // up to eight cells: one byte each
+    for (int c = 0; c < p.CPW; ++c) {
+      const unsigned l = (unsigned)sLen[c] << (8 * (c & 3)), m = (unsigned)sSmp[c] << (8 * (c & 3));
+      if (c < 4) { a |= l; c2 |= m; } else { b |= l; d |= m; }
+    }
+    dst[0] = make_uint4(a, b, c2, d);
+  }
+  unsigned at = 1;
+  for (int c = 0; c < p.CPW; ++c) {
+    const int n = sLen[c];
+    for (int i = lane; i < n; i += 32) dst[at + i] = recs[(size_t)c * rstride + i];
+    at += (unsigned)n;
+  }
+  for (int c = 0; c < p.CPW; ++c) {
+    const int n = 3 * sSmp[c];
+    for (int i = lane; i < n; i += 32) dst[at + i] = samp[(size_t)c * p.cap * 3 + i];
+    at += (unsigned)n;
+  }
+}
+
+// Header word of a saved pass, or false when there is none.  `hdr` is warp-uniform.
+__device__ __forceinline__ bool saved_header(const Dev& p, unsigned unit, int pass, uint4& hdr, const uint4*& blk) {
+  const unsigned off = __ldg(saved_dir_entry(p, unit, pass));
+  if (off == kSavedMissing) return false;
+  blk = p.saved + off;
+  hdr = __ldg(blk);
+  return true;
+}
+
+// Reads the lists of one pass back into the warp's shared area; the counterpart of row_list_phase with SAMPLES for a
+// pass whose block exists.  Adds the pass's sample counts to sCnt, as the list phase does.
+__device__ __forceinline__ bool load_pass(const Dev& p, unsigned unit, int pass, int* sLen, int* sCnt, int* sSmp,
+                                          uint4* recs, uint4* samp, int lane) {
+  uint4 hdr;
+  const uint4* blk;
+  if (!saved_header(p, unit, pass, hdr, blk)) return false;
+  const int rstride = row_stride(p.cap);
+  if (lane < p.CPW) {
+    const unsigned lw = lane < 4 ? hdr.x : hdr.y, sw = lane < 4 ? hdr.z : hdr.w;
+    const int l = (int)((lw >> (8 * (lane & 3))) & 0xffu), m = (int)((sw >> (8 * (lane & 3))) & 0xffu);
+    sLen[lane] = l;
+    sSmp[lane] = m;
+    sCnt[lane] += m;
+  }
+  __syncwarp();
+  unsigned at = 1;
+  for (int c = 0; c < p.CPW; ++c) {
+    const int n = sLen[c];
+    for (int i = lane; i < n; i += 32) recs[(size_t)c * rstride + i] = __ldg(blk + at + i);
+    at += (unsigned)n;
+  }
+  for (int c = 0; c < p.CPW; ++c) {
+    const int n = 3 * sSmp[c];
+    for (int i = lane; i < n; i += 32) samp[(size_t)c * p.cap * 3 + i] = __ldg(blk + at + i);
+    at += (unsigned)n;
+  }
+  __syncwarp();
+  return true;
+}
+
 // List phase of the forward kernel.  As list_phase() it evaluates one candidate per lane, but it
 // emits ROW records instead of samples.  A sample touches two feature rows (v0 and v1) at the
 // columns (u0, u1); the z samples of one (cell, camera) are neighbouring lanes and mostly fall on

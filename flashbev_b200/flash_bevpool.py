@@ -48,7 +48,8 @@ class DepthSpec(int):
 
     def __new__(cls, mode: int, pool: Optional[str] = None, depth_bin_range: Optional[Tuple[float, float]] = None,
                 legacy_depth_grad: bool = False, y_range: Optional[Tuple[int, int]] = None,
-                out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None, host_row_chunks: int = 0):
+                out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None, host_row_chunks: int = 0,
+                save_lists: bool = True):
         mode = int(mode)
         if mode not in (0, 1, 2, 3):
             raise ValueError("depth_distribution must be 0 (gaussian), 1 (laplace), 2 (categorical probabilities) or "
@@ -74,6 +75,7 @@ class DepthSpec(int):
             raise ValueError("out_dtype must be None (the feature dtype) or torch.float32")
         self.out_dtype = out_dtype
         self.out = out
+        self.save_lists = bool(save_lists)
         self.host_row_chunks = int(host_row_chunks)
         if not 0 <= self.host_row_chunks <= 16:
             raise ValueError("host_row_chunks must be 0 (the kernel stores to the host buffer) or 1..16 row bands")
@@ -241,6 +243,13 @@ def _forward(depth_params, image_feats, projection_matrices, feature_size, image
     else:
         out = (torch.zeros if partial else torch.empty)(shape, dtype=_out_dtype(spec, feats), device=dev)
     lib = _lib.load()
+    if needs_grad and spec.save_lists:
+        # a backward will follow: the forward leaves it the lists it builds (FbevProblem.saved_state)
+        nbytes = lib.fbev_saved_state_bytes(ctypes.byref(p))
+        if nbytes:
+            lists = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+            p.saved_state, p.saved_state_bytes = lists.data_ptr(), nbytes
+            keep = keep + (lists,)
     with _on_device(dev):
         stream = torch.cuda.current_stream(dev).cuda_stream
         if spec.out is not None and not out.is_cuda and spec.host_row_chunks > 0:
@@ -268,7 +277,8 @@ class FlashBEVPool(torch.autograd.Function):
         out, p, keep = _forward(depth_params, image_feats, projection_matrices, feature_size, image_size, roi_range,
                                 grid_size, spec, epsilon, depth_weight_threshold,
                                 depth_params.requires_grad or image_feats.requires_grad)
-        ctx.save_for_backward(*keep)
+        ctx.save_for_backward(*keep[:6])
+        ctx.held = keep[6:]  # scratch of the call that the backward reads again (saved lists, softmax statistics)
         ctx.spec = spec
         ctx.problem = p  # the backward launches on the same tensors: same struct, as long as their addresses hold
         ctx.grid = (p.X, p.Y, p.Z)
@@ -285,8 +295,10 @@ class FlashBEVPool(torch.autograd.Function):
         if (p.image_feats, p.depth, p.projection) != (feats.data_ptr(), depth.data_ptr(), proj.data_ptr()):
             # the saved tensors came back at other addresses (a saved-tensor hook moved them): describe them anew
             grid = torch.tensor(ctx.grid, dtype=torch.int32)  # host tensor: no synchronisation
+            saved = (ctx.problem.saved_state, ctx.problem.saved_state_bytes)
             p, held = make_problem(depth, feats, proj, fsize, isize, roi, grid, spec, ctx.epsilon,
                                    ctx.depth_weight_threshold)  # `held` keeps the call's scratch alive until launched
+            p.saved_state, p.saved_state_bytes = saved
         else:
             p.workspace = workspace(feats.device, torch.cuda.current_stream(feats.device).cuda_stream).data_ptr()
         flags = 0
@@ -325,7 +337,7 @@ def flash_bevpool(image_feats, depth_params, projection_matrices, feature_size, 
                   depth_distribution=0, use_shared_memory=True, optimize_z_precompute=True, use_warp_kernel=False,
                   use_vectorized_load=False, epsilon=1e-6, depth_weight_threshold=1e-6, *, pool=None,
                   depth_bin_range=None, legacy_depth_grad=False, y_range=None, out_dtype=None, out=None,
-                  host_row_chunks=0):
+                  host_row_chunks=0, save_lists=True):
     """Fused BEV pooling; same arguments as the reference wrapper (flash_bevpool.py:139-178).
 
     Args:
@@ -348,12 +360,15 @@ def flash_bevpool(image_feats, depth_params, projection_matrices, feature_size, 
             before reading it).
         host_row_chunks: with a host ``out``: 0 lets the kernel store to it over the bus; 1..16 computes that
             many bands of rows into a device buffer and copies each band while the next is computed.
+        save_lists: when a gradient will be asked for, the forward keeps the sample lists it builds for the
+            backward (device memory of about 24 bytes per (cell, camera, height bin), freed with the graph);
+            False makes the backward rebuild them, as the reference does.
     Returns:
         BEV features [B,Y,X,C] in the dtype of ``image_feats`` (or float32, see ``out_dtype``).
     """
     spec = DepthSpec(depth_distribution, pool=pool, depth_bin_range=depth_bin_range,
                      legacy_depth_grad=legacy_depth_grad, y_range=y_range, out_dtype=out_dtype, out=out,
-                     host_row_chunks=host_row_chunks)
+                     host_row_chunks=host_row_chunks, save_lists=save_lists)
     if not (torch.is_grad_enabled() and (image_feats.requires_grad or depth_params.requires_grad)):
         return _forward(depth_params, image_feats, projection_matrices, feature_size, image_size, roi_range, grid_size,
                         spec, epsilon, depth_weight_threshold, False)[0]

@@ -114,6 +114,13 @@ typedef struct FbevProblem {
                                   their tiles through an atomic counter; without it (NULL) every thread block
                                   owns one fixed tile.  Calls that may overlap on the device need a workspace
                                   each. */
+  void* saved_state;           /* optional device memory, 16-byte aligned, that ties a forward to its backward: a
+                                  forward given it also writes the row records and sample lists it built, and a
+                                  backward given the same memory (same problem otherwise) reads them instead of
+                                  rebuilding them, which is most of its work.  fbev_saved_state_bytes() sizes it;
+                                  with less, what does not fit is rebuilt.  NULL: nothing is saved or reused (the
+                                  reference rebuilds everything in its backward, flash_bevpool_cuda.cu:477-566). */
+  uint64_t saved_state_bytes;  /* size of saved_state */
   float* depth_stats;          /* FBEV_DEPTH_CATEGORICAL_LOGITS only: device scratch, 2 floats per texel
                                   (B*N*H*W*2, 8-byte aligned), caller-owned; every call fills it itself with each
                                   texel's (max logit, 1 / sum of exp(logit - max)).  NULL in the other modes. */
@@ -157,6 +164,11 @@ int fbev_forward_peers(const FbevProblem* p, void* out, void* const* peer_outs, 
  * that are multiples of 16 bytes and 16-byte aligned buffers (else FBEV_ERR_RANGE / FBEV_ERR_ALIGN).  As with
  * fbev_forward_peers the caller establishes completion across ranks after the launch. */
 int fbev_forward_multicast(const FbevProblem* p, void* out, void* out_multicast, int32_t* valid_count, void* stream);
+
+/* Bytes of FbevProblem.saved_state that hold the lists of this problem's forward for its backward on the
+ * benchmark rigs' densities with room to spare (a directory of 4 bytes per group of cells and pass, and 24 bytes
+ * per candidate (cell, camera, height bin), at most 1 GiB).  0 for an invalid problem. */
+size_t fbev_saved_state_bytes(const FbevProblem* p);
 
 /* Bytes of scratch fbev_backward works best with for this problem and flags: the float32 accumulation
  * targets of the 16-bit types (fbev_backward_min_scratch_bytes) plus, when the feature gradient is asked

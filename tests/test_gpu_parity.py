@@ -215,7 +215,7 @@ def test_kernel_matches_reference_dense_path_fixtures(cuda_device, path):
     assert (diff ** 2).mean() < 1e-6 and np.abs(diff).mean() < 1e-6     # tools/profile_differences.py:75-77
 
 
-def backward_case(w, mode, device, pool=None, dtype=None, legacy=False, threshold=0.0, out_f32=False):
+def backward_case(w, mode, device, pool=None, dtype=None, legacy=False, threshold=0.0, out_f32=False, save_lists=True):
     inp = synth.make_inputs(w, "categorical" if mode == "categorical" else "parametric", dtype=dtype)
     go = synth.upstream_grad(w)
     if (dtype or w.dtype) != "fp32" and not out_f32:
@@ -226,7 +226,7 @@ def backward_case(w, mode, device, pool=None, dtype=None, legacy=False, threshol
     dev["image_feats"].requires_grad_(True)
     dev["depth_params"].requires_grad_(True)
     out = flash_bevpool(**dev, **op_kwargs(w, mode, threshold, pool), legacy_depth_grad=legacy,
-                        out_dtype=torch.float32 if out_f32 else None)
+                        out_dtype=torch.float32 if out_f32 else None, save_lists=save_lists)
     out.backward(go.to(device))
     torch.cuda.synchronize()
     name = dtype or w.dtype
@@ -301,6 +301,72 @@ def test_backward_kernel_variants_agree_with_the_oracle(cuda_device, variant):
         backward_case(SMALL, "gaussian", cuda_device, legacy=True, threshold=1e-3, dtype="bf16")
     finally:
         lib.fbev_set_tuning(0, 0, 0, 0, 0)
+
+
+@pytest.mark.parametrize("save_lists", [True, False])
+def test_backward_with_and_without_the_lists_saved_by_the_forward(cuda_device, save_lists):
+    """A forward that knows a backward follows leaves it its row records and sample lists; without them the
+    backward rebuilds them.  Both ways against the oracle, on shapes that take one and several passes per cell, every
+    depth model, mean and sum pooling, 16-bit and float32 (for float32 the training forward runs in the
+    depth-gradient kernel's narrower lane layout)."""
+    tall = synth.Workload("tall", B=1, N=6, C=16, H=8, W=22, D=24, X=30, Y=30, Z=40, xy_extent=30.0, d0=1.0, delta=1.5,
+                          dtype="fp32", seed=32)
+    for mode in ("categorical", "laplace", "gaussian"):
+        backward_case(SMALL, mode, cuda_device, pool="mean", save_lists=save_lists)
+        backward_case(SMALL, mode, cuda_device, pool="sum", dtype="bf16", save_lists=save_lists)
+    backward_case(tall, "categorical", cuda_device, pool="mean", save_lists=save_lists)
+    backward_case(tall, "laplace", cuda_device, save_lists=save_lists)
+    backward_case(CFG3S, "categorical", cuda_device, save_lists=save_lists)
+    backward_case(CFG3S, "categorical", cuda_device, dtype="fp16", out_f32=True, save_lists=save_lists)
+    backward_case(CFG2, "categorical", cuda_device, save_lists=save_lists)
+    backward_case(CFG2, "laplace", cuda_device, save_lists=save_lists)
+    # the forward of a training step equals the inference forward up to the grouping of its float32 sums
+    inp = to_device(inputs_for(CFG2, "categorical"), cuda_device)
+    kw = op_kwargs(CFG2, "categorical")
+    plain = flash_bevpool(**inp, **kw)
+    inp["image_feats"].requires_grad_(True)
+    train = flash_bevpool(**inp, **kw, save_lists=save_lists)
+    assert rel_err_quantised(train.detach().float().cpu().numpy(), plain.float().cpu().numpy(), "bf16", ulps=1.0) < TOL_LOWP
+
+
+@pytest.mark.parametrize("room", ["none", "directory only", "a quarter", "all"])
+def test_saved_lists_that_do_not_fit_are_rebuilt(cuda_device, room):
+    """fbev_forward / fbev_backward through the C ABI with a saved state of every size: too small for the directory
+    (ignored), no room for data (every block missing), room for some blocks, room for all.  Same gradients."""
+    from flashbev_b200.flash_bevpool import DepthSpec, make_problem
+    lib = _lib.load()
+    w = synth.workload("cfg2", X=96, Y=80)
+    inp = to_device(inputs_for(w, "categorical"), cuda_device)
+    prob, keep = make_problem(inp["depth_params"], inp["image_feats"], inp["projection_matrices"], inp["feature_size"],
+                              inp["image_size"], inp["roi_range"], inp["grid_size"],
+                              DepthSpec(2, depth_bin_range=(w.d0, w.delta)), 1e-6, 0.0)
+    full = lib.fbev_saved_state_bytes(ctypes.byref(prob))
+    assert full > 0
+    cells = w.X * w.Y
+    directory = 16 + (cells // 2 + 4096) * 3 * 4
+    size = {"none": 4096, "directory only": directory + 2048, "a quarter": directory + (full - directory) // 16,
+            "all": full}[room]
+    state = torch.empty(size, dtype=torch.uint8, device=cuda_device)
+    out = torch.empty(w.B, w.Y, w.X, w.C, dtype=keep[0].dtype, device=cuda_device)
+    go = synth.upstream_grad(w).to(device=cuda_device, dtype=keep[0].dtype)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def grads(with_state):
+        prob.saved_state, prob.saved_state_bytes = (state.data_ptr(), size) if with_state else (None, 0)
+        gf, gd = torch.full_like(keep[0], float("nan")), torch.full_like(keep[1], float("nan"))
+        need = lib.fbev_backward_scratch_bytes(ctypes.byref(prob), 3)
+        scratch = torch.empty(need, dtype=torch.uint8, device=cuda_device)
+        assert lib.fbev_forward(ctypes.byref(prob), out.data_ptr(), None, stream) == 0
+        assert lib.fbev_backward(ctypes.byref(prob), go.data_ptr(), gf.data_ptr(), gd.data_ptr(), scratch.data_ptr(),
+                                 need, 3, stream) == 0
+        torch.cuda.synchronize()
+        return out.float().cpu().numpy().copy(), gf.float().cpu().numpy(), gd.float().cpu().numpy()
+
+    ref = grads(False)
+    got = grads(True)
+    for a, b, name in zip(got, ref, ("out", "d_feats", "d_depth")):
+        assert np.isfinite(a).all(), name
+        assert rel_err_quantised(a, b, "bf16", ulps=1.0) < TOL_LOWP, f"{room}: {name}"
 
 
 def test_backward_scratch_is_bounded_and_large_batches_run_in_several_passes(cuda_device):
