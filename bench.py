@@ -308,6 +308,9 @@ def main():
     ap.add_argument("--only-backward", type=int, default=0, metavar="FLAGS",
                     help="profiler helper: launch only fbev_backward with these flags (1 features, 2 depth, 3 both) "
                          "--steps times on the default workload, print the mean device time and exit")
+    ap.add_argument("--train-step", action="store_true",
+                    help="profiler helper: launch only forward + backward of a training step (forward keeps its lists) "
+                         "--steps times on the default workload, print the mean device time and exit")
     ap.add_argument("--tune", default=None, help="tile_x,tile_y,chunks_per_lane,warps,min_blocks (0 = automatic)")
     ap.add_argument("--exp", type=int, default=0, help="experiment bits of fbev_debug.h for every forward launch (profiler runs)")
     args = ap.parse_args()
@@ -386,6 +389,29 @@ def main():
         ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
         return sum(ms) / steps, ms
 
+    if args.train_step:
+        go = synth.upstream_grad(w, B=Bl).to(device=device, dtype=inp["image_feats"].dtype)
+        g_feats, g_depth = torch.empty_like(keep[0]), torch.empty_like(keep[1])
+        nsaved = lib.fbev_saved_state_bytes(ctypes.byref(prob))
+        saved = torch.empty(max(nsaved, 16), dtype=torch.uint8, device=device)
+        prob.saved_state, prob.saved_state_bytes = saved.data_ptr(), nsaved
+        nbytes = lib.fbev_backward_scratch_bytes(ctypes.byref(prob), 3)
+        scratch = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=device)
+
+        def train_step():
+            rc = lib.fbev_forward(ctypes.byref(prob), out.data_ptr(), None, stream)
+            rc = rc or lib.fbev_backward(ctypes.byref(prob), go.data_ptr(), g_feats.data_ptr(), g_depth.data_ptr(),
+                                         scratch.data_ptr() if nbytes else None, nbytes, 3, stream)
+            if rc:
+                raise RuntimeError(_lib.strerror(rc))
+
+        ms, _ = timed(train_step, args.steps, args.warmup)
+        if rank == 0:
+            print(json.dumps({"train_step_us": ms * 1e3, "workload": workload_description(w, Bl, args.mode)}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
     if args.only_backward:
         go = synth.upstream_grad(w, B=Bl).to(device=device, dtype=inp["image_feats"].dtype)
         g_feats, g_depth = torch.empty_like(keep[0]), torch.empty_like(keep[1])
@@ -442,14 +468,15 @@ def main():
                 if rc:
                     raise RuntimeError(_lib.strerror(rc))
 
-            fwd_bwd = make_step(prob_t)
+            fwd_bwd = make_step(prob)
             nb = max(10, args.steps // 5)
             ms_fb, _ = timed(fwd_bwd, nb, 5)
             extra["fwd_bwd_us"] = ms_fb * 1e3
-            extra["fwd_bwd_note"] = ("forward + backward (gradients for features and depth), device time, L2 flushed; the "
-                                     "forward keeps its lists for the backward (saved state of %.1f MB)" % (nsaved / 2 ** 20))
-            extra["fwd_us_training_forward"] = timed(fwd_train, nb, 5)[0] * 1e3
-            extra["fwd_bwd_us_lists_rebuilt_in_backward"] = timed(make_step(prob), nb, 5)[0] * 1e3
+            extra["fwd_bwd_note"] = "forward + backward (gradients for features and depth), device time, L2 flushed"
+            # the optional variant in which the forward keeps its lists for the backward (FbevProblem.saved_state)
+            extra["fwd_bwd_us_lists_saved_by_forward"] = timed(make_step(prob_t), nb, 5)[0] * 1e3
+            extra["fwd_us_forward_that_saves_lists"] = timed(fwd_train, nb, 5)[0] * 1e3
+            extra["saved_lists_mb"] = nsaved / 2 ** 20
 
             # the same launches replayed from a CUDA graph (what a training loop with static shapes does)
             side = torch.cuda.Stream(device=device)
@@ -457,8 +484,8 @@ def main():
                 graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(graph, stream=side):
                     cs = torch.cuda.current_stream().cuda_stream
-                    rc = lib.fbev_forward(ctypes.byref(prob_t), out.data_ptr(), None, cs)
-                    rc = rc or lib.fbev_backward(ctypes.byref(prob_t), go.data_ptr(), g_feats.data_ptr(), g_depth.data_ptr(),
+                    rc = lib.fbev_forward(ctypes.byref(prob), out.data_ptr(), None, cs)
+                    rc = rc or lib.fbev_backward(ctypes.byref(prob), go.data_ptr(), g_feats.data_ptr(), g_depth.data_ptr(),
                                                  scratch.data_ptr() if nbytes else None, nbytes, flags, cs)
                 if rc:
                     raise RuntimeError(_lib.strerror(rc))
@@ -504,7 +531,8 @@ def main():
                 prob3i = type(prob3).from_buffer_copy(prob3)   # inference forward: nothing saved
                 ns3 = lib.fbev_saved_state_bytes(ctypes.byref(prob3))
                 sv3 = torch.empty(max(ns3, 16), dtype=torch.uint8, device=device)
-                prob3.saved_state, prob3.saved_state_bytes = sv3.data_ptr(), ns3
+                prob3s = type(prob3).from_buffer_copy(prob3)
+                prob3s.saved_state, prob3s.saved_state_bytes = sv3.data_ptr(), ns3
                 nb3 = lib.fbev_backward_scratch_bytes(ctypes.byref(prob3), flags)
                 sc3 = torch.empty(max(nb3, 1), dtype=torch.uint8, device=device)
 
@@ -523,6 +551,14 @@ def main():
                 extra["cfg3_fwd_us"] = timed(fwd3, 20, 5)[0] * 1e3
                 extra["cfg3_fwd_bwd_us"] = timed(fwd_bwd3, 20, 5)[0] * 1e3
                 extra["cfg3_workload"] = workload_description(w3, w3.B, args.mode) + " + backward (both gradients)"
+                def fwd_bwd3_saved():
+                    rc = lib.fbev_forward(ctypes.byref(prob3s), out3.data_ptr(), None, stream)
+                    rc = rc or lib.fbev_backward(ctypes.byref(prob3s), go3.data_ptr(), gf3.data_ptr(), gd3.data_ptr(),
+                                                 sc3.data_ptr() if nb3 else None, nb3, flags, stream)
+                    if rc:
+                        raise RuntimeError(_lib.strerror(rc))
+
+                extra["cfg3_fwd_bwd_us_lists_saved_by_forward"] = timed(fwd_bwd3_saved, 20, 5)[0] * 1e3
                 extra["cfg3_saved_state_mb"] = ns3 / 2 ** 20
                 del in3, out3, go3, gf3, gd3, sc3, sv3
 
@@ -689,9 +725,6 @@ def main():
                 go4 = synth.upstream_grad(w4, B=B4).to(device=device, dtype=keep4[0].dtype)
                 gf4, gd4 = torch.empty_like(keep4[0]), torch.empty_like(keep4[1])
                 prob4i = type(prob4).from_buffer_copy(prob4)   # inference forward: nothing saved
-                ns4 = lib.fbev_saved_state_bytes(ctypes.byref(prob4))
-                sv4 = torch.empty(max(ns4, 16), dtype=torch.uint8, device=device)
-                prob4.saved_state, prob4.saved_state_bytes = sv4.data_ptr(), ns4
                 nb4 = lib.fbev_backward_scratch_bytes(ctypes.byref(prob4), flags)
                 sc4 = torch.empty(max(nb4, 1), dtype=torch.uint8, device=device)
 
@@ -715,8 +748,8 @@ def main():
                                  "fwd_samples_per_s": 64 / (float(t4[0]) * 1e-3),
                                  "fwd_bwd_samples_per_s": 64 / (float(t4[1]) * 1e-3),
                                  "fwd_cells_per_s": 64 * w4.X * w4.Y / (float(t4[0]) * 1e-3),
-                                 "backward_scratch_mb_per_gpu": nb4 / 2 ** 20, "saved_lists_mb_per_gpu": ns4 / 2 ** 20}
-                del in4, out4, go4, gf4, gd4, sc4, sv4
+                                 "backward_scratch_mb_per_gpu": nb4 / 2 ** 20}
+                del in4, out4, go4, gf4, gd4, sc4
 
             if world > 1:
                 # one large sample (cfg5) with its BEV rows split over the ranks: all-gather of the output

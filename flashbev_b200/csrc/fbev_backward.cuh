@@ -21,6 +21,7 @@ __device__ __forceinline__ void red_add4(float* addr, float a, float b, float c,
 __device__ __forceinline__ float group_sum(float v, int lg, int GL) {
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) {
+    if (off >= GL) continue;  // uniform: no lane of the group is that far away
     const float o = __shfl_down_sync(kFull, v, off);
     if (lg + off < GL) v += o;
   }
@@ -540,9 +541,17 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_feats_sorted_kernel(con
 // EMIT: the kernel also leaves the entries of the sorted feature gradient (emit_entries) from the same row
 // records, so that one list phase serves both gradients.
 // CAT: categorical depth (compile-time so that each of the two kernels below carries only its own sample pass).
-template <typename T, int V, bool EMIT, bool CAT>
+// SAVED: the lists come from the saved state of a training forward (load_pass) and the instantiation carries no
+// list-phase code at all, which is most of the other one's registers.  Whether the state is usable is decided once
+// per launch (saved_usable); the host launches both instantiations when it has a state to offer and exactly one of
+// them does the work: this one when the state is complete and in its layout, the rebuilding one otherwise.
+template <typename T, int V, bool EMIT, bool CAT, bool SAVED = false>
 __device__ __forceinline__ void bwd_depth_body(const Dev& p) {
   constexpr int E = Chunk<T>::E;
+  if (saved_usable(p) != SAVED) {  // the other instantiation's launch does the work
+    grid_dependency_trigger();
+    return;
+  }
   extern __shared__ __align__(16) unsigned char smem[];
   const BlockHeader h = carve(smem, p.N);
   __shared__ int s_tile[2];
@@ -572,8 +581,7 @@ __device__ __forceinline__ void bwd_depth_body(const Dev& p) {
   // fixed cost is shared by many samples and the depth tensor is small enough for its atomics to contend);
   // measured a loss with two or three cells per warp on large feature maps
   const bool merge_bins = p.CPW >= 4;
-  // lists left by a training forward in this very layout (else they are rebuilt)
-  const bool use_saved = p.saved != nullptr && __ldg(reinterpret_cast<const unsigned*>(p.saved) + 1) == p.saved_key;
+  int* sOff = sSmp + 32;                    // [2 x 9] SAVED: start offsets of the cells' lists in a saved block
   int loaded_b = -1;
   UnitLoop sched;
   sched.begin(p, s_tile, warp, nwarps);
@@ -608,17 +616,17 @@ __device__ __forceinline__ void bwd_depth_body(const Dev& p) {
       const unsigned unit = (unsigned)(tile * ngroups + grp);
       if (mean_pool && !single_pass) {  // the count of all passes is needed before the first contribution
         for (int r0 = 0; r0 < ncand; r0 += p.cap) {
-          uint4 hdr;
-          const uint4* blk;
-          if (use_saved && saved_header(p, unit, r0 / p.cap, hdr, blk)) {  // the saved pass knows its sample counts
-            if (lane < p.CPW) sCnt[lane] += (int)(((lane < 4 ? hdr.z : hdr.w) >> (8 * (lane & 3))) & 0xffu);
+          if (SAVED) {  // the saved pass knows its sample counts
+            const uint4 entry = __ldg(saved_dir_entry(p, unit, r0 / p.cap));
+            if (lane < p.CPW) sCnt[lane] += saved_cnt(entry, lane);
             __syncwarp();
             continue;
           }
           if (lane < p.CPW) sLen[lane] = 0;
           __syncwarp();
-          row_list_phase<T, false>(p, t, h, vis, (unsigned)cpt, t0, r0, min(r0 + p.cap, ncand), vs, vmin, image_h,
-                                   image_w, sLen, sCnt, recs, lane);
+          if (!SAVED)
+            row_list_phase<T, false>(p, t, h, vis, (unsigned)cpt, t0, r0, min(r0 + p.cap, ncand), vs, vmin, image_h,
+                                     image_w, sLen, sCnt, recs, lane);
         }
       }
       // inverse count per cell of the group, kept by lane c for cell c
@@ -635,7 +643,9 @@ __device__ __forceinline__ void bwd_depth_body(const Dev& p) {
           if (single_pass) sCnt[lane] = 0;
         }
         __syncwarp();
-        if (!(use_saved && load_pass(p, unit, r0 / p.cap, sLen, sCnt, sSmp, recs, samp, lane)))
+        if (SAVED)
+          load_pass(p, unit, r0 / p.cap, sLen, sCnt, sSmp, sOff, recs, samp, lane);
+        else
           row_list_phase<T, true, true>(p, t, h, vis, (unsigned)cpt, t0, r0, min(r0 + p.cap, ncand), vs, vmin, image_h,
                                         image_w, sLen, sCnt, recs, lane, samp, sSmp);
         if (mean_pool && single_pass && lane < p.CPW) {
@@ -899,13 +909,13 @@ __device__ __forceinline__ void bwd_depth_body(const Dev& p) {
 // The two depth-gradient kernels.  Categorical: 96 registers, five resident blocks per SM (no spills; measured 4 %
 // ahead of 80 registers / six blocks on the benchmark shape, 9 % on cfg4).  Parametric: 80 registers / six blocks,
 // which its shared-memory sample pass prefers (96 registers cost it 8 % on the benchmark shape).
-template <typename T, int V, bool EMIT>
+template <typename T, int V, bool EMIT, bool SAVED = false>
 __global__ void __maxnreg__(96) bwd_depth_kernel(const __grid_constant__ Dev p) {
-  bwd_depth_body<T, V, EMIT, true>(p);
+  bwd_depth_body<T, V, EMIT, true, SAVED>(p);
 }
-template <typename T, int V, bool EMIT>
+template <typename T, int V, bool EMIT, bool SAVED = false>
 __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_depth_param_kernel(const __grid_constant__ Dev p) {
-  bwd_depth_body<T, V, EMIT, false>(p);
+  bwd_depth_body<T, V, EMIT, false, SAVED>(p);
 }
 
 // Gradient kernel.  Same decomposition as the forward.  For every accepted sample

@@ -63,11 +63,13 @@ struct Dev {
   unsigned ent_cap;
   // row records and sample lists a training forward leaves for the backward (null: none; fbev_lists.cuh: SavedLists)
   uint4* saved;          // [0] = {cursor, plan key, -, -}, then the directory, then the data area
-  unsigned saved_dir;    // directory entries (units x passes); entry e is word e of saved + 1
+  unsigned saved_dir;    // directory entries (units x passes), 16 bytes each, from saved + 1
   unsigned saved_cap;    // 16-byte units of data area that follow the directory
   unsigned saved_key;    // identifies the list layout (cells per warp, records per pass, tiling): both sides must agree
   unsigned saved_unit0;  // first unit of this launch within the saved state (backward over a slice of the batch)
   int saved_passes;      // directory entries per unit
+  unsigned saved_sub_rec;  // backward over a slice of the batch: what to subtract from the saved chunk indices
+  unsigned saved_sub_dep;  // ... and from the saved depth element indices (the slice's tensors start at its first sample)
   // host side only: size of the saved state, batch size it was written for, first sample of this launch in it
   unsigned long long saved_bytes;
   int saved_B, saved_b0;

@@ -217,13 +217,13 @@ static Plan make_plan(const FbevProblem* p, Dev& d, bool bwd, const void* a, con
 static void setup_saved(Dev& d, int CPW) {
   uint4* base = d.saved;
   d.saved = nullptr;
-  if (base == nullptr || CPW <= 0 || CPW > 8 || d.cap <= 0 || d.cap > 127) return;
+  if (base == nullptr || CPW <= 0 || CPW > 8 || d.cap <= 0 || d.cap > 16) return;  // counts are packed in 6 / 5 bits
   const unsigned long long ngroups = (unsigned long long)(d.TX * d.TY + CPW - 1) / CPW;
   const unsigned long long per_sample = (unsigned long long)d.tiles_x * d.tiles_y * ngroups;
   const unsigned long long passes = ((unsigned long long)d.N * d.Z + d.cap - 1) / d.cap;
   const unsigned long long dir = per_sample * (unsigned long long)d.saved_B * passes;
   const unsigned long long units16 = d.saved_bytes / 16;
-  const unsigned long long dir16 = (dir + 3) / 4;
+  const unsigned long long dir16 = dir;  // one 16-byte entry per (unit, pass)
   if (dir == 0 || dir >= (1ull << 32) || units16 < 1 + dir16 + 64) return;
   unsigned long long cap16 = units16 - 1 - dir16;
   if (cap16 > 0xfffffff0ull - dir16) cap16 = 0xfffffff0ull - dir16;  // offsets are 32-bit
@@ -232,6 +232,10 @@ static void setup_saved(Dev& d, int CPW) {
   d.saved_cap = (unsigned)cap16;
   d.saved_passes = (int)passes;
   d.saved_unit0 = (unsigned)(per_sample * (unsigned long long)d.saved_b0);
+  // the saved indices count from the first sample of the forward's batch; this launch's tensors start at sample b0
+  const unsigned long long tex0 = (unsigned long long)d.saved_b0 * d.N * d.H * d.W;
+  d.saved_sub_rec = (unsigned)(tex0 * (unsigned long long)d.cpt);
+  d.saved_sub_dep = (unsigned)(tex0 * (unsigned long long)d.D);
   unsigned key = 2166136261u;  // FNV-1a over what fixes the layout of the lists
   const int fields[] = {CPW, d.GL, d.cap, d.TX, d.TY, d.tiles_x, d.tiles_y, d.N, d.Z, d.y0, d.y1, d.X, d.saved_B, d.mode};
   for (int f : fields) {
@@ -443,8 +447,32 @@ static int backward_feats_t(const Plan& pl, const Dev& d, cudaStream_t st) {
   }
 }
 
-// pl / d: plan of the per-sample kernel (depth gradient, or both gradients when the feature-gradient
-// kernel cannot take the shape); plf / df: plan of the feature-gradient kernel.
+// Launches the record-based depth-gradient kernel for plan pld / problem dd.  With a saved state to offer, the
+// instantiation that reads the forward's lists goes first and the rebuilding one after it; each looks at the state
+// (saved_usable) and exactly one of them does the work, so an incomplete or foreign state costs one empty launch.
+template <typename T, int V, bool EMIT>
+static int launch_depth_v(const Plan& pld, const Dev& dd, cudaStream_t st) {
+  const int gpt = (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW;
+  const bool cat = dd.mode == FBEV_DEPTH_CATEGORICAL;
+  if (dd.saved != nullptr) {
+    const int rc = cat ? launch(bwd_depth_kernel<T, V, EMIT, true>, pld, dd, st, gpt)
+                       : launch(bwd_depth_param_kernel<T, V, EMIT, true>, pld, dd, st, gpt);
+    if (rc != FBEV_OK) return rc;
+  }
+  return cat ? launch(bwd_depth_kernel<T, V, EMIT, false>, pld, dd, st, gpt)
+             : launch(bwd_depth_param_kernel<T, V, EMIT, false>, pld, dd, st, gpt);
+}
+template <typename T, bool EMIT>
+static int launch_depth(const Plan& pld, const Dev& dd, cudaStream_t st) {
+  switch (pld.V) {
+    case 1: return launch_depth_v<T, 1, EMIT>(pld, dd, st);
+    case 2: return launch_depth_v<T, 2, EMIT>(pld, dd, st);
+    default: return launch_depth_v<T, 4, EMIT>(pld, dd, st);
+  }
+}
+
+// pl / d: plan of the per-sample kernel (depth gradient, or both gradients when the feature-gradient kernel cannot
+// take the shape); plf / df: plan of the feature-gradient kernel.
 template <typename T>
 static int backward_t(const Plan& pl, Dev d, const Plan& plf, const Dev& df, cudaStream_t st) {
   if (!pl.chunked) return launch(bwd_generic_kernel<T>, pl, d, st);
@@ -464,12 +492,7 @@ static int backward_t(const Plan& pl, Dev d, const Plan& plf, const Dev& df, cud
     if (depth_on_records && df.ent != nullptr) {
       // both gradients from one list phase: the depth kernel also emits the entries of the sorted feature gradient
       dd.flags = d.flags;
-      int rc;
-      switch (pld.V) {
-        case 1: rc = (dd.mode == FBEV_DEPTH_CATEGORICAL ? launch(bwd_depth_kernel<T, 1, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW) : launch(bwd_depth_param_kernel<T, 1, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW)); break;
-        case 2: rc = (dd.mode == FBEV_DEPTH_CATEGORICAL ? launch(bwd_depth_kernel<T, 2, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW) : launch(bwd_depth_param_kernel<T, 2, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW)); break;
-        default: rc = (dd.mode == FBEV_DEPTH_CATEGORICAL ? launch(bwd_depth_kernel<T, 4, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW) : launch(bwd_depth_param_kernel<T, 4, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW)); break;
-      }
+      const int rc = launch_depth<T, true>(pld, dd, st);
       return rc != FBEV_OK ? rc : sort_finish_t<T>(pld, dd, st);
     }
     const int rc = backward_feats_t<T>(plf, df, st);
@@ -480,22 +503,13 @@ static int backward_t(const Plan& pl, Dev d, const Plan& plf, const Dev& df, cud
   if (depth_on_records && df.ent_d != nullptr) {
     // parametric depth gradient alone: its per-texel sums travel through the entry lists
     dd.flags = d.flags;
-    int rc;
-    switch (pld.V) {
-      case 1: rc = (dd.mode == FBEV_DEPTH_CATEGORICAL ? launch(bwd_depth_kernel<T, 1, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW) : launch(bwd_depth_param_kernel<T, 1, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW)); break;
-      case 2: rc = (dd.mode == FBEV_DEPTH_CATEGORICAL ? launch(bwd_depth_kernel<T, 2, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW) : launch(bwd_depth_param_kernel<T, 2, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW)); break;
-      default: rc = (dd.mode == FBEV_DEPTH_CATEGORICAL ? launch(bwd_depth_kernel<T, 4, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW) : launch(bwd_depth_param_kernel<T, 4, true>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW)); break;
-    }
+    const int rc = launch_depth<T, true>(pld, dd, st);
     return rc != FBEV_OK ? rc : sort_finish_t<T>(pld, dd, st);
   }
   if (depth_on_records) {
     // depth gradient alone: per-texel dot products on the forward's row records
     dd.flags = d.flags;
-    switch (pld.V) {
-      case 1: return (dd.mode == FBEV_DEPTH_CATEGORICAL ? launch(bwd_depth_kernel<T, 1, false>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW) : launch(bwd_depth_param_kernel<T, 1, false>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW));
-      case 2: return (dd.mode == FBEV_DEPTH_CATEGORICAL ? launch(bwd_depth_kernel<T, 2, false>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW) : launch(bwd_depth_param_kernel<T, 2, false>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW));
-      default: return (dd.mode == FBEV_DEPTH_CATEGORICAL ? launch(bwd_depth_kernel<T, 4, false>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW) : launch(bwd_depth_param_kernel<T, 4, false>, pld, dd, st, (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW));
-    }
+    return launch_depth<T, false>(pld, dd, st);
   }
   switch (pl.V) {
     case 1: return launch(bwd_kernel<T, 1>, pl, d, st);
@@ -755,14 +769,14 @@ int fbev_forward_multicast(const FbevProblem* p, void* out, void* out_multicast,
 
 size_t fbev_saved_state_bytes(const FbevProblem* p) {
   if (p == nullptr || validate(p) != FBEV_OK) return 0;
-  // directory: one word per (group of cells, pass), sized for the smallest groups and passes the kernels use;
+  // directory: 16 bytes per (group of cells, pass), sized for the smallest groups and passes the kernels use;
   // data: 24 bytes per candidate covers the benchmark rigs (about 17 are used) with room to spare, at most 1 GiB
   const unsigned long long cells = (unsigned long long)p->B * p->X * (unsigned long long)(p->y_end - p->y_begin);
   const unsigned long long cand = cells * p->N * p->Z;
   const unsigned long long dir = (cells / 2 + (unsigned long long)p->B * 4096) * (((unsigned long long)p->N * p->Z + 15) / 16);
   unsigned long long data = cand * 24;
   if (data > (1ull << 30)) data = 1ull << 30;
-  return (size_t)(16 + ((dir * 4 + 255) / 256) * 256 + data + 4096);
+  return (size_t)(16 + dir * 16 + data + 4096);
 }
 
 size_t fbev_backward_min_scratch_bytes(const FbevProblem* p, int flags) {

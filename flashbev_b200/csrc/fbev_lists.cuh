@@ -390,16 +390,40 @@ __host__ __device__ inline size_t depth_warp_bytes(int CPW, int cap) {
 // list phase produces, per group of cells and pass: the row records and the sample records.  Rebuilding them costs
 // the backward more than everything else it does, so a forward that knows a backward will follow writes them out:
 //   saved[0]                      {cursor: 16-byte units handed out so far, plan key, -, -}
-//   saved[1 ..]                   directory, one 32-bit word per (unit, pass): offset of the pass's block in 16-byte
-//                                 units from saved, or kSavedMissing when the data area was full
-//   block                         {list lengths of the cells (bytes 0-7), sample counts (bytes 8-15)}, the cells' row
-//                                 records back to back, the cells' sample records back to back
+//   saved[1 + e]                  directory entry of (unit, pass) e, 16 bytes: the offset of the pass's block in
+//                                 16-byte units from saved (kSavedMissing when the data area was full), and the
+//                                 cells' list lengths (6 bits each) and sample counts (5 bits each), see pack_counts
+//   block                         the cells' row records back to back, then the cells' sample records back to back
 // A unit is one group of cells of one tile (tile * groups + group), the same in both kernels as long as both use
 // the same tiling and lane layout, which the plan key vouches for.  A block that did not fit is simply rebuilt.
+// The directory entry carries the counts so that a reader needs one round trip to memory for them and one for all
+// of the block's words, which it requests together.
 constexpr unsigned kSavedMissing = 0xffffffffu;
 
-__device__ __forceinline__ unsigned* saved_dir_entry(const Dev& p, unsigned unit, int pass) {
-  return reinterpret_cast<unsigned*>(p.saved + 1) + ((size_t)(p.saved_unit0 + unit) * p.saved_passes + pass);
+__device__ __forceinline__ uint4* saved_dir_entry(const Dev& p, unsigned unit, int pass) {
+  return p.saved + 1 + ((size_t)(p.saved_unit0 + unit) * p.saved_passes + pass);
+}
+
+// Up to eight cells with at most 33 records and 16 samples each per pass: 48 bits of lengths (y and the low half of
+// z) and 40 bits of counts (w and the high half of z).
+__device__ __forceinline__ void pack_counts(const int* sLen, const int* sSmp, int CPW, unsigned& y, unsigned& z, unsigned& w) {
+  y = z = w = 0u;
+  unsigned long long len = 0, cnt = 0;
+  for (int c = 0; c < CPW; ++c) {
+    len |= (unsigned long long)(unsigned)sLen[c] << (6 * c);  // <= 33 < 64
+    cnt |= (unsigned long long)(unsigned)sSmp[c] << (5 * c);  // <= 16 < 32
+  }
+  y = (unsigned)len;
+  z = (unsigned)(len >> 32) | ((unsigned)(cnt >> 32) << 16);
+  w = (unsigned)cnt;
+}
+__device__ __forceinline__ int saved_len(const uint4& e, int c) {
+  const unsigned long long len = (unsigned long long)e.y | ((unsigned long long)(e.z & 0xffffu) << 32);
+  return (int)((len >> (6 * c)) & 63u);
+}
+__device__ __forceinline__ int saved_cnt(const uint4& e, int c) {
+  const unsigned long long cnt = (unsigned long long)e.w | ((unsigned long long)(e.z >> 16) << 32);
+  return (int)((cnt >> (5 * c)) & 31u);
 }
 
 // Writes this warp's lists of one pass (after row_list_phase with SAMPLES) to the saved state.
@@ -411,24 +435,21 @@ __device__ __forceinline__ void save_pass(const Dev& p, unsigned unit, int pass,
     nrec += sLen[c];
     nsmp += sSmp[c];
   }
-  const unsigned need = 1u + (unsigned)nrec + 3u * (unsigned)nsmp;
-  const unsigned data0 = 1u + (p.saved_dir + 3u) / 4u;
+  const unsigned need = (unsigned)nrec + 3u * (unsigned)nsmp;
+  const unsigned data0 = 1u + p.saved_dir;
   unsigned off = 0;
   if (lane == 0) off = atomicAdd(reinterpret_cast<unsigned*>(p.saved), need);
   off = __shfl_sync(kFull, off, 0);
   const bool fits = (unsigned long long)off + need <= (unsigned long long)p.saved_cap;
-  if (lane == 0) *saved_dir_entry(p, unit, pass) = fits ? data0 + off : kSavedMissing;
+  if (lane == 0) {
+    unsigned y, z, w;
+    pack_counts(sLen, sSmp, p.CPW, y, z, w);
+    *saved_dir_entry(p, unit, pass) = make_uint4(fits ? data0 + off : kSavedMissing, y, z, w);
+    if (!fits) reinterpret_cast<unsigned*>(p.saved)[2] = 1u;  // the state is incomplete: the backward rebuilds
+  }
   if (!fits) return;
   uint4* dst = p.saved + data0 + off;
-  if (lane == 0) {
-    unsigned a = 0, b = 0, c2 = 0, d = 0;  // up to eight cells: one byte each
-    for (int c = 0; c < p.CPW; ++c) {
-      const unsigned l = (unsigned)sLen[c] << (8 * (c & 3)), m = (unsigned)sSmp[c] << (8 * (c & 3));
-      if (c < 4) { a |= l; c2 |= m; } else { b |= l; d |= m; }
-    }
-    dst[0] = make_uint4(a, b, c2, d);
-  }
-  unsigned at = 1;
+  unsigned at = 0;
   for (int c = 0; c < p.CPW; ++c) {
     const int n = sLen[c];
     for (int i = lane; i < n; i += 32) dst[at + i] = recs[(size_t)c * rstride + i];
@@ -441,44 +462,82 @@ __device__ __forceinline__ void save_pass(const Dev& p, unsigned unit, int pass,
   }
 }
 
-// Header word of a saved pass, or false when there is none.  `hdr` is warp-uniform.
-__device__ __forceinline__ bool saved_header(const Dev& p, unsigned unit, int pass, uint4& hdr, const uint4*& blk) {
-  const unsigned off = __ldg(saved_dir_entry(p, unit, pass));
-  if (off == kSavedMissing) return false;
-  blk = p.saved + off;
-  hdr = __ldg(blk);
-  return true;
+// Directory entry of a saved pass, or false when there is none.  Warp-uniform.
+__device__ __forceinline__ bool saved_entry(const Dev& p, unsigned unit, int pass, uint4& e) {
+  e = __ldg(saved_dir_entry(p, unit, pass));
+  return e.x != kSavedMissing;
 }
 
-// Reads the lists of one pass back into the warp's shared area; the counterpart of row_list_phase with SAMPLES for a
-// pass whose block exists.  Adds the pass's sample counts to sCnt, as the list phase does.
-__device__ __forceinline__ bool load_pass(const Dev& p, unsigned unit, int pass, int* sLen, int* sCnt, int* sSmp,
-                                          uint4* recs, uint4* samp, int lane) {
-  uint4 hdr;
-  const uint4* blk;
-  if (!saved_header(p, unit, pass, hdr, blk)) return false;
+// True when the saved state at p.saved was written completely, in this launch's layout.  Uniform over the grid.
+__device__ __forceinline__ bool saved_usable(const Dev& p) {
+  if (p.saved == nullptr) return false;
+  const volatile unsigned* head = reinterpret_cast<const volatile unsigned*>(p.saved);  // written by the forward kernel
+  return head[1] == p.saved_key && head[2] == 0u;
+}
+
+// Reads the lists of one pass back into the warp's shared area; the counterpart of row_list_phase with SAMPLES.
+// Adds the pass's sample counts to sCnt, as the list phase does.  All words of the block are requested together
+// (four loads in flight per lane), so the pass costs two round trips to memory: the directory entry, then the
+// block.  sOff: 2 x (kMaxCellsPerWarp + 1) ints of the warp's shared area for the cells' start offsets.
+__device__ __forceinline__ void load_pass(const Dev& p, unsigned unit, int pass, int* sLen, int* sCnt, int* sSmp,
+                                          int* sOff, uint4* recs, uint4* samp, int lane) {
+  const uint4 e = __ldg(saved_dir_entry(p, unit, pass));
+  const uint4* blk = p.saved + e.x;
   const int rstride = row_stride(p.cap);
+  // exclusive prefix sums of the cells' record counts and sample words, by the first lanes
+  const int l = lane < p.CPW ? saved_len(e, lane) : 0, m = lane < p.CPW ? saved_cnt(e, lane) : 0;
+  int pl = l, pm = 3 * m;
+#pragma unroll
+  for (int d = 1; d < kMaxCellsPerWarp; d <<= 1) {
+    const int a = __shfl_up_sync(kFull, pl, d), b = __shfl_up_sync(kFull, pm, d);
+    if (lane >= d) {
+      pl += a;
+      pm += b;
+    }
+  }
+  if (lane < kMaxCellsPerWarp) {
+    sOff[lane + 1] = pl;
+    sOff[kMaxCellsPerWarp + 1 + lane + 1] = pm;
+    if (lane == 0) sOff[0] = sOff[kMaxCellsPerWarp + 1] = 0;
+  }
   if (lane < p.CPW) {
-    const unsigned lw = lane < 4 ? hdr.x : hdr.y, sw = lane < 4 ? hdr.z : hdr.w;
-    const int l = (int)((lw >> (8 * (lane & 3))) & 0xffu), m = (int)((sw >> (8 * (lane & 3))) & 0xffu);
     sLen[lane] = l;
     sSmp[lane] = m;
     sCnt[lane] += m;
   }
   __syncwarp();
-  unsigned at = 1;
-  for (int c = 0; c < p.CPW; ++c) {
-    const int n = sLen[c];
-    for (int i = lane; i < n; i += 32) recs[(size_t)c * rstride + i] = __ldg(blk + at + i);
-    at += (unsigned)n;
-  }
-  for (int c = 0; c < p.CPW; ++c) {
-    const int n = 3 * sSmp[c];
-    for (int i = lane; i < n; i += 32) samp[(size_t)c * p.cap * 3 + i] = __ldg(blk + at + i);
-    at += (unsigned)n;
+  const int* rec0 = sOff;
+  const int* smp0 = sOff + kMaxCellsPerWarp + 1;
+  const int nrec = rec0[kMaxCellsPerWarp], total = nrec + smp0[kMaxCellsPerWarp];
+  constexpr int U = 4;
+  for (int base = 0; base < total; base += 32 * U) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int i = base + u * 32 + lane;
+      if (i < total) v[u] = __ldg(blk + i);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int i = base + u * 32 + lane;
+      if (i >= total) continue;
+      const bool is_rec = i < nrec;
+      const int* start = is_rec ? rec0 : smp0;
+      const int j = is_rec ? i : i - nrec;
+      int c = 0;
+#pragma unroll
+      for (int k = 1; k < kMaxCellsPerWarp; ++k) c += j >= start[k] ? 1 : 0;
+      const int off = j - start[c];
+      if (is_rec) {
+        v[u].x -= p.saved_sub_rec;  // chunk index of the record's texel, counted from the first sample of this launch
+        recs[(size_t)c * rstride + off] = v[u];
+      } else {
+        if (off % 3 == 1) v[u].x -= p.saved_sub_dep;  // second word of a sample: its depth element index
+        samp[(size_t)c * p.cap * 3 + off] = v[u];
+      }
+    }
   }
   __syncwarp();
-  return true;
 }
 
 // List phase of the forward kernel.  As list_phase() it evaluates one candidate per lane, but it

@@ -166,7 +166,7 @@ int fbev_forward_peers(const FbevProblem* p, void* out, void* const* peer_outs, 
 int fbev_forward_multicast(const FbevProblem* p, void* out, void* out_multicast, int32_t* valid_count, void* stream);
 
 /* Bytes of FbevProblem.saved_state that hold the lists of this problem's forward for its backward on the
- * benchmark rigs' densities with room to spare (a directory of 4 bytes per group of cells and pass, and 24 bytes
+ * benchmark rigs' densities with room to spare (a directory of 16 bytes per group of cells and pass, and 24 bytes
  * per candidate (cell, camera, height bin), at most 1 GiB).  0 for an invalid problem. */
 size_t fbev_saved_state_bytes(const FbevProblem* p);
 

@@ -215,7 +215,7 @@ def test_kernel_matches_reference_dense_path_fixtures(cuda_device, path):
     assert (diff ** 2).mean() < 1e-6 and np.abs(diff).mean() < 1e-6     # tools/profile_differences.py:75-77
 
 
-def backward_case(w, mode, device, pool=None, dtype=None, legacy=False, threshold=0.0, out_f32=False, save_lists=True):
+def backward_case(w, mode, device, pool=None, dtype=None, legacy=False, threshold=0.0, out_f32=False, save_lists=False):
     inp = synth.make_inputs(w, "categorical" if mode == "categorical" else "parametric", dtype=dtype)
     go = synth.upstream_grad(w)
     if (dtype or w.dtype) != "fp32" and not out_f32:
@@ -343,7 +343,7 @@ def test_saved_lists_that_do_not_fit_are_rebuilt(cuda_device, room):
     full = lib.fbev_saved_state_bytes(ctypes.byref(prob))
     assert full > 0
     cells = w.X * w.Y
-    directory = 16 + (cells // 2 + 4096) * 3 * 4
+    directory = 16 + (cells // 2 + 4096) * 3 * 16   # what fbev_saved_state_bytes reserves for the directory
     size = {"none": 4096, "directory only": directory + 2048, "a quarter": directory + (full - directory) // 16,
             "all": full}[room]
     state = torch.empty(size, dtype=torch.uint8, device=cuda_device)
