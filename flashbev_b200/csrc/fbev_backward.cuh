@@ -21,7 +21,6 @@ __device__ __forceinline__ void red_add4(float* addr, float a, float b, float c,
 __device__ __forceinline__ float group_sum(float v, int lg, int GL) {
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) {
-    if (off >= GL) continue;  // uniform: no lane of the group is that far away
     const float o = __shfl_down_sync(kFull, v, off);
     if (lg + off < GL) v += o;
   }
