@@ -52,6 +52,7 @@ class FbevProblem(ctypes.Structure):
         ("y_begin", ctypes.c_int32), ("y_end", ctypes.c_int32),
         ("voxel_size", ctypes.c_float * 3),
         ("voxel_min", ctypes.c_float * 3),
+        ("compact_rows", ctypes.c_int32),
         ("image_feats", ctypes.c_void_p),
         ("depth", ctypes.c_void_p),
         ("projection", ctypes.c_void_p),

@@ -166,7 +166,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_feats_kernel(const __gr
       float go[V * E];
 #pragma unroll
       for (int i = 0; i < V * E; ++i) go[i] = 0.0f;
-      const size_t cell = ((size_t)t.b * p.Y + y) * p.X + x;
+      const size_t cell = out_cell(p, t.b, y, x);
       if (!EMIT && cell_ok) {
 #pragma unroll
         for (int j = 0; j < V; ++j) load_chunk<T>(p.gout, p.out_f32, cell * cpt + lg + j * p.GL, go + j * E);
@@ -429,7 +429,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_feats_sorted_kernel(con
             } else {
               // direct: this lane alone adds g * w to the record's texel(s), chunk by chunk
               const int ly = fast_div(tc, inv_tx), lx = tc - ly * p.TX;
-              const size_t cell = ((size_t)t.b * p.Y + t.y0 + ly) * p.X + t.x0 + lx;
+              const size_t cell = out_cell(p, t.b, t.y0 + ly, t.x0 + lx);
               for (int ch = 0; ch < cpt; ++ch) {
                 float gv[E];
                 load_chunk<T>(p.gout, p.out_f32, cell * cpt + ch, gv);
@@ -494,7 +494,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_feats_sorted_kernel(con
         const int tc = (int)(en.x >> 16);
         const float w = __uint_as_float(en.y);
         const int ly = fast_div(tc, inv_tx), lx = tc - ly * p.TX;
-        const size_t cell = ((size_t)t.b * p.Y + t.y0 + ly) * p.X + t.x0 + lx;
+        const size_t cell = out_cell(p, t.b, t.y0 + ly, t.x0 + lx);
 #pragma unroll
         for (int j = 0; j < V; ++j) {
           float gv[E];
@@ -606,7 +606,7 @@ __device__ __forceinline__ void bwd_depth_body(const Dev& p) {
 #pragma unroll
       for (int i = 0; i < V * E; ++i) go[i] = 0.0f;
       if (cell_ok) {
-        const size_t cell = ((size_t)t.b * p.Y + y) * p.X + x;
+        const size_t cell = out_cell(p, t.b, y, x);
 #pragma unroll
         for (int j = 0; j < V; ++j) load_chunk<T>(p.gout, p.out_f32, cell * cpt + lg + j * p.GL, go + j * E);
       }
@@ -657,7 +657,7 @@ __device__ __forceinline__ void bwd_depth_body(const Dev& p) {
         if (EMIT) {
           const float inv_cell = __shfl_sync(kFull, inv_of_lane, g < p.CPW ? g : 0);
           const uint4* rec_e = recs + (size_t)g * rstride;
-          const size_t cell = ((size_t)t.b * p.Y + y) * p.X + x;
+          const size_t cell = out_cell(p, t.b, y, x);
           emitted = emit_entries(p, rec_e, n, g, lg, lane, (unsigned)cell, inv_cell, sLen, (unsigned)cpt, &first_slot);
           if (!emitted && (p.flags & FBEV_BWD_FEATS)) {
             float gs[V * E];
@@ -984,7 +984,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32) bwd_kernel(const __grid_consta
 #pragma unroll
     for (int i = 0; i < V * E; ++i) go[i] = 0.0f;
     if (cell_ok) {
-      const size_t cell = ((size_t)t.b * p.Y + y) * p.X + x;
+      const size_t cell = out_cell(p, t.b, y, x);
 #pragma unroll
       for (int j = 0; j < V; ++j) load_chunk<T>(p.gout, p.out_f32, cell * cpt + lg + j * p.GL, go + j * E);
     }
@@ -1121,7 +1121,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32) bwd_generic_kernel(const __gri
       const int ly = tc / p.TX, lx = tc - ly * p.TX;
       const int x = t.x0 + lx, y = t.y0 + ly;
       if (!(x < t.x1 && y < t.y1)) continue;  // uniform per warp
-      const size_t cell = ((size_t)t.b * p.Y + y) * p.X + x;
+      const size_t cell = out_cell(p, t.b, y, x);
       float inv = 1.0f;
       if (p.pool == FBEV_POOL_MEAN) {
         int cnt = 0;

@@ -40,6 +40,7 @@ struct Dev {
   float* gfeat;      // backward: float32 accumulation target [B,N,H,W,C]
   float* gdepth;     // backward: float32 accumulation target [B,N,H,W,D]
   int B, N, H, W, C, D, X, Y, Z, pstride, mode, pool, y0, y1;
+  int out_rows, out_y0;  // rows the output / upstream gradient / count tensors hold per sample, and the first of them
   float eps, thr, d0, delta;
   float vs[3], vmin[3];
   int TX, TY, tiles_x, tiles_y;
@@ -74,6 +75,12 @@ struct Dev {
   unsigned long long saved_bytes;
   int saved_B, saved_b0;
 };
+
+// Cell (b, y, x) in the output, the upstream gradient and the count tensor, which hold all Y rows of a sample or only
+// the rows [y_begin, y_end) of the call (FbevProblem.compact_rows).
+__device__ __forceinline__ size_t out_cell(const Dev& p, int b, int y, int x) {
+  return ((size_t)b * p.out_rows + (y - p.out_y0)) * p.X + x;
+}
 
 // Programmatic dependent launch (sm_90+).  A kernel launched with the programmatic-serialization attribute may
 // start while the kernel before it in the stream is still draining; grid_dependency_wait() returns once that

@@ -155,7 +155,7 @@ __global__ void __launch_bounds__(MAXT, MINB) fwd_kernel(const __grid_constant__
 #pragma unroll
           for (int i = 0; i < V * E; ++i) acc[i] = cnt > 0 ? __fdiv_rn(acc[i], c) : 0.0f;
         }
-        const size_t cell = ((size_t)t.b * p.Y + y) * p.X + x;
+        const size_t cell = out_cell(p, t.b, y, x);
         if (p.out_mc != nullptr) {  // one multicast store reaches this GPU's buffer and every peer's
 #pragma unroll
           for (int j = 0; j < V; ++j) store_chunk_multicast<T>(p.out_mc, p.out_f32, cell * cpt + lg + j * p.GL, acc + j * E);
@@ -207,7 +207,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32) fwd_generic_kernel(const __gri
     const int ly = tc / p.TX, lx = tc - ly * p.TX;
     const int x = t.x0 + lx, y = t.y0 + ly;
     if (!(x < t.x1 && y < t.y1)) continue;  // uniform per warp
-    const size_t cell = ((size_t)t.b * p.Y + y) * p.X + x;
+    const size_t cell = out_cell(p, t.b, y, x);
     int cnt = 0;
     for (int r0 = 0; r0 < ncand; r0 += p.cap) {  // count first (mean pooling divides every block)
       list_phase<T, false, true>(p, t, h, nvis, tc, r0, min(r0 + p.cap, ncand), vs, vmin, image_h, image_w, sLen,

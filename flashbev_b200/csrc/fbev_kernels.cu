@@ -108,6 +108,8 @@ static void fill_dev(const FbevProblem* p, Dev& d) {
   d.dstat = p->mode == FBEV_DEPTH_CATEGORICAL_LOGITS ? reinterpret_cast<const float2*>(p->depth_stats) : nullptr;
   d.pool = p->pool;
   d.y0 = p->y_begin; d.y1 = p->y_end;
+  d.out_rows = p->compact_rows ? p->y_end - p->y_begin : p->Y;
+  d.out_y0 = p->compact_rows ? p->y_begin : 0;
   d.eps = p->epsilon; d.thr = p->threshold; d.d0 = p->depth_d0; d.delta = p->depth_delta;
   for (int i = 0; i < 3; ++i) {
     d.vs[i] = p->voxel_size[i];
@@ -545,6 +547,7 @@ static int forward_impl(const FbevProblem* p, void* out, int32_t* valid_count, v
   if (out == nullptr) return FBEV_ERR_NULL;
   if (((uintptr_t)out % elem_size(p->out_dtype)) || ((uintptr_t)valid_count % 4)) return FBEV_ERR_ALIGN;
   if (n_peers < 0 || n_peers > 7 || (n_peers > 0 && peers == nullptr)) return FBEV_ERR_SHAPE;
+  if (p->compact_rows && (n_peers > 0 || out_multicast != nullptr)) return FBEV_ERR_SHAPE;  // peers hold whole grids
   Dev d;
   fill_dev(p, d);
   d.out = out;
@@ -661,7 +664,7 @@ int fbev_forward_to_host(const FbevProblem* p, void* out_dev, void* out_host, in
   const int rc = validate(p);
   if (rc != FBEV_OK) return rc;
   if (out_dev == nullptr || out_host == nullptr) return FBEV_ERR_NULL;
-  if (row_chunks < 1 || row_chunks > 16) return FBEV_ERR_SHAPE;
+  if (row_chunks < 1 || row_chunks > 16 || p->compact_rows) return FBEV_ERR_SHAPE;
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) {
     cudaGetLastError();
@@ -868,7 +871,8 @@ int fbev_backward(const FbevProblem* p, const void* grad_out, void* grad_feats, 
     q.projection = p->projection + (size_t)b0 * p->N * p->proj_stride;
     q.feature_size = p->feature_size + (size_t)b0 * p->N * 2;
     if (logits) q.depth_stats = p->depth_stats + (size_t)b0 * tex_sample * 2;
-    const void* gout = reinterpret_cast<const unsigned char*>(grad_out) + (size_t)b0 * p->Y * p->X * p->C * eso;
+    const size_t out_rows = p->compact_rows ? (size_t)(p->y_end - p->y_begin) : (size_t)p->Y;
+    const void* gout = reinterpret_cast<const unsigned char*>(grad_out) + (size_t)b0 * out_rows * p->X * p->C * eso;
     Dev d;
     fill_dev(&q, d);
     d.gout = gout;
@@ -944,6 +948,7 @@ int fbev_debug_indices(const FbevProblem* p, int32_t* u0, int32_t* v0, int32_t* 
   const int rc = validate(p);
   if (rc != FBEV_OK) return rc;
   if (!u0 || !v0 || !kbin || !valid || !count) return FBEV_ERR_NULL;
+  if (p->compact_rows) return FBEV_ERR_SHAPE;  // the index dump covers whole grids
   Dev d;
   fill_dev(p, d);
   d.count = count;

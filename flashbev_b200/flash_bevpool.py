@@ -49,7 +49,7 @@ class DepthSpec(int):
     def __new__(cls, mode: int, pool: Optional[str] = None, depth_bin_range: Optional[Tuple[float, float]] = None,
                 legacy_depth_grad: bool = False, y_range: Optional[Tuple[int, int]] = None,
                 out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None, host_row_chunks: int = 0,
-                save_lists: bool = False):
+                save_lists: bool = False, compact_rows: bool = False):
         mode = int(mode)
         if mode not in (0, 1, 2, 3):
             raise ValueError("depth_distribution must be 0 (gaussian), 1 (laplace), 2 (categorical probabilities) or "
@@ -76,6 +76,9 @@ class DepthSpec(int):
         self.out_dtype = out_dtype
         self.out = out
         self.save_lists = bool(save_lists)
+        self.compact_rows = bool(compact_rows)
+        if self.compact_rows and y_range is None:
+            raise ValueError("compact_rows needs y_range")
         self.host_row_chunks = int(host_row_chunks)
         if not 0 <= self.host_row_chunks <= 16:
             raise ValueError("host_row_chunks must be 0 (the kernel stores to the host buffer) or 1..16 row bands")
@@ -192,6 +195,7 @@ def make_problem(depth_params, image_feats, projection_matrices, feature_size, i
     p.depth_d0, p.depth_delta = spec.d0, spec.delta
     yb, ye = spec.y_range if spec.y_range is not None else (0, Y)
     p.y_begin, p.y_end = yb, ye
+    p.compact_rows = 1 if spec.compact_rows else 0
     p.image_feats, p.depth, p.projection = feats.data_ptr(), depth.data_ptr(), proj.data_ptr()
     p.feature_size, p.image_size, p.roi_range = fsize.data_ptr(), isize.data_ptr(), roi.data_ptr()
     p.status = status_word(dev).data_ptr()
@@ -236,8 +240,8 @@ def _forward(depth_params, image_feats, projection_matrices, feature_size, image
                            roi_range, grid_size, spec, epsilon, depth_weight_threshold)
     feats = keep[0]
     dev = feats.device
-    shape = (p.B, p.Y, p.X, p.C)
-    partial = (p.y_begin, p.y_end) != (0, p.Y)
+    shape = (p.B, p.y_end - p.y_begin if spec.compact_rows else p.Y, p.X, p.C)
+    partial = (p.y_begin, p.y_end) != (0, p.Y) and not spec.compact_rows
     if spec.out is not None:
         out = _check_out(spec.out, shape, _out_dtype(spec, feats), dev, partial, needs_grad)
     else:
@@ -337,7 +341,7 @@ def flash_bevpool(image_feats, depth_params, projection_matrices, feature_size, 
                   depth_distribution=0, use_shared_memory=True, optimize_z_precompute=True, use_warp_kernel=False,
                   use_vectorized_load=False, epsilon=1e-6, depth_weight_threshold=1e-6, *, pool=None,
                   depth_bin_range=None, legacy_depth_grad=False, y_range=None, out_dtype=None, out=None,
-                  host_row_chunks=0, save_lists=False):
+                  host_row_chunks=0, save_lists=False, compact_rows=False):
     """Fused BEV pooling; same arguments as the reference wrapper (flash_bevpool.py:139-178).
 
     Args:
@@ -353,6 +357,8 @@ def flash_bevpool(image_feats, depth_params, projection_matrices, feature_size, 
         depth_bin_range: (first bin edge, bin width) of the categorical mode.
         legacy_depth_grad: parametric modes only; reproduce the reference CUDA kernel's depth gradient.
         y_range: (begin, end) BEV rows to compute; the other rows of the output are zero.
+        compact_rows: with ``y_range``: the result (and the upstream gradient of its backward) holds only those
+            rows, [B, end - begin, X, C]: a row shard that stays a shard.
         out_dtype: None (output in the feature dtype) or torch.float32 (what the reference returns for
             any input dtype).
         out: result buffer to fill and return instead of a new tensor: on the device, or page-locked host
@@ -369,7 +375,7 @@ def flash_bevpool(image_feats, depth_params, projection_matrices, feature_size, 
     """
     spec = DepthSpec(depth_distribution, pool=pool, depth_bin_range=depth_bin_range,
                      legacy_depth_grad=legacy_depth_grad, y_range=y_range, out_dtype=out_dtype, out=out,
-                     host_row_chunks=host_row_chunks, save_lists=save_lists)
+                     host_row_chunks=host_row_chunks, save_lists=save_lists, compact_rows=compact_rows)
     if not (torch.is_grad_enabled() and (image_feats.requires_grad or depth_params.requires_grad)):
         return _forward(depth_params, image_feats, projection_matrices, feature_size, image_size, roi_range, grid_size,
                         spec, epsilon, depth_weight_threshold, False)[0]

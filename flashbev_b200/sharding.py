@@ -149,9 +149,8 @@ def flash_bevpool_rows_local(image_feats, depth_params, projection_matrices, fea
     world, rank = _world(group)
     rows = int(_host_values(grid_size)[1])
     y0, y1 = row_slice(rows, world, rank)
-    full = flash_bevpool(image_feats, depth_params, projection_matrices, feature_size, image_size, roi_range, grid_size,
-                         y_range=(y0, y1), **op_kwargs)
-    return full[:, y0:y1]
+    return flash_bevpool(image_feats, depth_params, projection_matrices, feature_size, image_size, roi_range, grid_size,
+                         y_range=(y0, y1), compact_rows=True, **op_kwargs)
 
 
 def all_reduce_input_grads(*tensors, group=None) -> None:

@@ -102,6 +102,9 @@ typedef struct FbevProblem {
   int32_t y_begin, y_end;      /* BEV rows computed by this call (row sharding); 0, Y for all */
   float voxel_size[3];         /* used when roi_range is NULL: (max-min)/grid, flash_bevpool.py:62-64 */
   float voxel_min[3];          /* used when roi_range is NULL: xmin, ymin, zmin, flash_bevpool.py:65-67 */
+  int32_t compact_rows;        /* 0: out, grad_out and valid_count are [B,Y,...] tensors of which this call touches
+                                  rows y_begin..y_end.  Non-zero: they hold only those rows, [B, y_end - y_begin, ...]
+                                  (a row shard that stays a shard: nothing to zero-fill, nothing to slice) */
   const void* image_feats;     /* device [B,N,H,W,C] */
   const void* depth;           /* device [B,N,H,W,D] */
   const float* projection;     /* device [B,N,proj_stride] float32 */

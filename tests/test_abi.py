@@ -35,10 +35,10 @@ def test_library_builds_and_exports_every_symbol():
 
 
 def test_struct_layout_matches_the_header():
-    # uint32 + 20 int32/float words + 6 floats = 27 words, padded to 8 bytes, then 8 pointers, saved_state and its
+    # uint32 + 20 int32/float words + 6 floats + compact_rows = 28 words, then 8 pointers, saved_state and its
     # 64-bit size, depth_stats (LP64)
     assert ctypes.sizeof(_lib.FbevProblem) == 4 * 28 + 8 * 11
-    assert _lib.FbevProblem.image_feats.offset == 112 and _lib.FbevProblem.workspace.offset == 168
+    assert _lib.FbevProblem.compact_rows.offset == 108 and _lib.FbevProblem.image_feats.offset == 112 and _lib.FbevProblem.workspace.offset == 168
     assert _lib.FbevProblem.saved_state.offset == 176 and _lib.FbevProblem.depth_stats.offset == 192
 
 

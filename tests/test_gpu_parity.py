@@ -146,6 +146,33 @@ def test_forward_row_ranges_compose(cuda_device):
     run_case(w, "categorical", cuda_device, y_range=(37, 90))
 
 
+@pytest.mark.parametrize("mode,dtype", [("categorical", "bf16"), ("laplace", "fp32")])
+def test_row_shard_that_stays_a_shard(cuda_device, mode, dtype):
+    """y_range with compact_rows: output, upstream gradient and gradients of a call that holds only its rows equal
+    the same rows of the whole-grid call (forward bit for bit; the gradients are sums over the shard's rows)."""
+    w = synth.workload("cfg4", B=3, dtype=dtype)
+    kw = op_kwargs(w, mode)
+    go = synth.upstream_grad(w).to(device=cuda_device)
+    y0, y1 = 44, 120
+    whole = to_device(inputs_for(w, mode), cuda_device)
+    whole["image_feats"].requires_grad_(True)
+    whole["depth_params"].requires_grad_(True)
+    full = flash_bevpool(**whole, **kw)
+    masked = torch.zeros_like(go)
+    masked[:, y0:y1] = go[:, y0:y1]
+    full.backward(masked.to(full.dtype))
+    part = to_device(inputs_for(w, mode), cuda_device)
+    part["image_feats"].requires_grad_(True)
+    part["depth_params"].requires_grad_(True)
+    rows = flash_bevpool(**part, **kw, y_range=(y0, y1), compact_rows=True)
+    assert tuple(rows.shape) == (w.B, y1 - y0, w.X, w.C)
+    assert torch.equal(rows, full[:, y0:y1])
+    rows.backward(go[:, y0:y1].to(rows.dtype).contiguous())
+    tol = TOL_F32 if dtype == "fp32" else 2 * TOL_LOWP
+    for k in ("image_feats", "depth_params"):
+        assert rel_err(part[k].grad.float().cpu().numpy(), whole[k].grad.float().cpu().numpy()) < tol, k
+
+
 def test_forward_batch_samples_are_independent(cuda_device):
     """Batch sharding property at the multi-GPU configuration's shapes: a slice of the batch run alone
     equals the same rows of the whole batch, bit for bit."""
