@@ -689,6 +689,13 @@ def main():
             extra["bus_us"] = {"h2d_inputs_alone": timed(h2d_only, ne, 3)[0] * 1e3, "d2h_result_alone": timed(d2h_only, ne, 3)[0] * 1e3}
             extra["bus_us"]["serial_floor_with_kernel"] = (extra["bus_us"]["h2d_inputs_alone"] + extra["bus_us"]["d2h_result_alone"]
                                                            + ms_fwd * 1e3)
+            if world > 1:  # every rank copies at the same moment: what the shared host links leave each of them
+                tb = torch.tensor([extra["bus_us"]["h2d_inputs_alone"], extra["bus_us"]["d2h_result_alone"]],
+                                  dtype=torch.float64, device=device)
+                allb = [torch.zeros_like(tb) for _ in range(world)]
+                dist.all_gather(allb, tb)
+                extra["bus_us"]["h2d_by_rank"] = [round(float(t[0]), 1) for t in allb]
+                extra["bus_us"]["d2h_by_rank"] = [round(float(t[1]), 1) for t in allb]
             extra["bus_us"]["note"] = ("one step moves its inputs in, computes, and moves the result out, each depending on the one "
                                        "before: copy times measured alone + the kernel = the floor of a step that overlaps nothing; "
                                        "the row-band path overlaps the kernel with the result copy")

@@ -141,14 +141,18 @@ class _RowShardedPool(torch.autograd.Function):
 
 
 def flash_bevpool_rows_local(image_feats, depth_params, projection_matrices, feature_size, image_size, roi_range,
-                             grid_size, group=None, **op_kwargs) -> torch.Tensor:
+                             grid_size, group=None, local_op: Optional[Callable] = None, **op_kwargs) -> torch.Tensor:
     """Row split whose result stays split: this rank's rows ``[B, rows_r, X, C]`` (``row_slice``), nothing
     exchanged in the forward.  For a consumer that is sharded by rows too (a BEV encoder with halo exchange, a
     per-region head).  Differentiable; the gradients of the replicated inputs it yields are this rank's partial
-    sums, which ``all_reduce_input_grads`` completes."""
+    sums, which ``all_reduce_input_grads`` completes.  ``local_op`` replaces ``flash_bevpool`` as the per-rank
+    compute (CPU tests of the plumbing)."""
     world, rank = _world(group)
     rows = int(_host_values(grid_size)[1])
     y0, y1 = row_slice(rows, world, rank)
+    if local_op is not None:
+        return local_op(image_feats, depth_params, projection_matrices, feature_size, image_size, roi_range, grid_size,
+                        y_range=(y0, y1), **op_kwargs)[:, y0:y1]
     return flash_bevpool(image_feats, depth_params, projection_matrices, feature_size, image_size, roi_range, grid_size,
                          y_range=(y0, y1), compact_rows=True, **op_kwargs)
 

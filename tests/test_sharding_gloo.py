@@ -69,6 +69,17 @@ def _worker(rank, world, port, results):
                                           inp["roi_range"], inp["grid_size"], local_op=oracle_op)
         go = synth.upstream_grad(w)
         out.backward(go)
+        # ---- rows that stay sharded: this rank's rows only, gradients of the replicated inputs summed afterwards ----
+        f2 = inp["image_feats"].clone().requires_grad_(True)
+        d2 = inp["depth_params"].clone().requires_grad_(True)
+        mine = sharding.flash_bevpool_rows_local(f2, d2, inp["projection_matrices"], inp["feature_size"],
+                                                 inp["image_size"], inp["roi_range"], inp["grid_size"], local_op=oracle_op)
+        ry0, ry1 = sharding.row_slice(w.Y, world, rank)
+        local_ok = bool(torch.equal(mine, out.detach()[:, ry0:ry1]))
+        mine.backward(go[:, ry0:ry1])
+        sharding.all_reduce_input_grads(f2, d2)
+        local_ok = local_ok and bool(torch.allclose(f2.grad, f.grad, rtol=0, atol=1e-5 * float(f.grad.abs().max())))
+        local_ok = local_ok and bool(torch.allclose(d2.grad, d.grad, rtol=0, atol=1e-5 * float(d.grad.abs().max())))
         # ---- batch split over the ranks, gathered ----
         b0, b1 = sharding.batch_slice(w.B, world, rank)
         part = synth.make_inputs(w, "categorical", batch_slice=(b0, b1))
@@ -81,7 +92,7 @@ def _worker(rank, world, port, results):
         ragged = sharding.gather_rows(rows[:, y0:y1].contiguous(), 35)
         if rank == 0:
             results.put((out.detach().numpy(), f.grad.numpy(), d.grad.numpy(), whole.numpy(),
-                         bool(torch.equal(ragged, rows))))
+                         bool(torch.equal(ragged, rows)) and local_ok))
     finally:
         dist.destroy_process_group()
 
