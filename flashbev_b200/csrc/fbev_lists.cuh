@@ -462,12 +462,6 @@ __device__ __forceinline__ void save_pass(const Dev& p, unsigned unit, int pass,
   }
 }
 
-// Directory entry of a saved pass, or false when there is none.  Warp-uniform.
-__device__ __forceinline__ bool saved_entry(const Dev& p, unsigned unit, int pass, uint4& e) {
-  e = __ldg(saved_dir_entry(p, unit, pass));
-  return e.x != kSavedMissing;
-}
-
 // True when the saved state at p.saved was written completely, in this launch's layout.  Uniform over the grid.
 __device__ __forceinline__ bool saved_usable(const Dev& p) {
   if (p.saved == nullptr) return false;

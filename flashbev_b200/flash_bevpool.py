@@ -92,7 +92,11 @@ _host_cache = {}
 
 def _host_values(t: torch.Tensor) -> tuple:
     """Values of a small tensor on the host.  Synchronises only the first time a given
-    (tensor, version) is seen; the reference synchronises on every call (flash_bevpool.py:58-67)."""
+    (tensor, version) is seen; the reference synchronises on every call (flash_bevpool.py:58-67).
+    A caller that builds a new device ``grid_size`` tensor for every call (as the reference's
+    tools/utils/data_utils.py:208-209 does once per benchmark) pays that one synchronisation per
+    call and leaves no entry behind (the weak reference removes it with the tensor); keeping the
+    tensor, or passing a host tensor, avoids it."""
     if t.device.type == "cpu":
         return tuple(t.tolist())
     key = id(t)
