@@ -523,6 +523,21 @@ def main():
             extra["fwd_us_forward_that_saves_lists"] = timed(fwd_train, nb, 5)[0] * 1e3
             extra["saved_lists_mb"] = nsaved / 2 ** 20
 
+            # bitwise reproducible gradients (FBEV_BWD_DETERMINISTIC: fixed-point sums, a measuring launch first)
+            flags_det = flags | _lib.BWD_DETERMINISTIC
+            nbytes_det = lib.fbev_backward_scratch_bytes(ctypes.byref(prob), flags_det)
+            scratch_det = torch.empty(max(nbytes_det, 1), dtype=torch.uint8, device=device)
+
+            def fwd_bwd_det():
+                rc = lib.fbev_forward(ctypes.byref(prob), out.data_ptr(), None, stream)
+                rc = rc or lib.fbev_backward(ctypes.byref(prob), go.data_ptr(), g_feats.data_ptr(), g_depth.data_ptr(),
+                                             scratch_det.data_ptr(), nbytes_det, flags_det, stream)
+                if rc:
+                    raise RuntimeError(_lib.strerror(rc))
+
+            extra["fwd_bwd_us_deterministic"] = timed(fwd_bwd_det, nb, 3)[0] * 1e3
+            del scratch_det
+
             # the same launches replayed from a CUDA graph (what a training loop with static shapes does)
             side = torch.cuda.Stream(device=device)
             with torch.cuda.stream(side):
@@ -604,6 +619,18 @@ def main():
                         raise RuntimeError(_lib.strerror(rc))
 
                 extra["cfg3_fwd_bwd_us_lists_saved_by_forward"] = timed(fwd_bwd3_saved, 20, 5)[0] * 1e3
+                nb3d = lib.fbev_backward_scratch_bytes(ctypes.byref(prob3), flags | _lib.BWD_DETERMINISTIC)
+                sc3d = torch.empty(max(nb3d, 1), dtype=torch.uint8, device=device)
+
+                def fwd_bwd3_det():
+                    rc = lib.fbev_forward(ctypes.byref(prob3), out3.data_ptr(), None, stream)
+                    rc = rc or lib.fbev_backward(ctypes.byref(prob3), go3.data_ptr(), gf3.data_ptr(), gd3.data_ptr(),
+                                                 sc3d.data_ptr(), nb3d, flags | _lib.BWD_DETERMINISTIC, stream)
+                    if rc:
+                        raise RuntimeError(_lib.strerror(rc))
+
+                extra["cfg3_fwd_bwd_us_deterministic"] = timed(fwd_bwd3_det, 10, 3)[0] * 1e3
+                del sc3d
                 extra["cfg3_saved_state_mb"] = ns3 / 2 ** 20
                 del in3, out3, go3, gf3, gd3, sc3, sv3
 

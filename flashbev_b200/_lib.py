@@ -14,11 +14,12 @@ F32, BF16, F16 = 0, 1, 2
 DEPTH_GAUSSIAN, DEPTH_LAPLACE, DEPTH_CATEGORICAL, DEPTH_CATEGORICAL_LOGITS = 0, 1, 2, 3
 ABI_VERSION = 2
 POOL_MEAN, POOL_SUM = 0, 1
-BWD_FEATS, BWD_DEPTH, BWD_LEGACY_DEPTH = 1, 2, 4
+BWD_FEATS, BWD_DEPTH, BWD_LEGACY_DEPTH, BWD_DETERMINISTIC = 1, 2, 4, 8
 DEV_BAD_FEATURE_SIZE = 1
 WORKSPACE_BYTES = 16
 STATIC_SCRATCH_BYTES = 16 << 20
 SORT_BUDGET_BYTES = 256 << 20
+ERR_SCRATCH = 8
 ERR_STATIC_LIMIT = 11
 
 # every symbol include/fbev.h declares (the operator) ...

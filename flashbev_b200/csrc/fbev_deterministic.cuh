@@ -1,0 +1,248 @@
+// Bitwise reproducible backward (FBEV_BWD_DETERMINISTIC).
+//
+// The gradients are sums over samples that many warps produce in an order that changes from run to run; float32
+// addition is not associative, so the default kernels (atomics, and a sort whose segments are filled in drawn order)
+// differ between two runs in the last bits, as the reference's per-sample atomicAdd does
+// (flash_bevpool_cuda.cu:667-679).  Here every contribution is turned into a 64-bit fixed-point integer and added
+// with an integer atomic: integer addition is associative and commutative, so the sum does not depend on the order,
+// and every contribution itself is computed by one warp in a fixed order.
+//
+// The fixed-point scale is a power of two chosen from the data: a first launch of the same kernel (MEASURE) only
+// records the largest magnitude any single contribution takes, per gradient; det_scale_kernel turns that into
+// scale = 2^(62 - bits - e) with 2^e above that magnitude and 2^bits above the number of contributions one element
+// can receive (4 * rows * X * Z: every candidate of the texel's camera, four corners each), so no sum can leave
+// 63 bits, and a contribution keeps at least 62 - bits binary digits below the largest one (38 for a 512 x 512 x 16
+// grid).  det_finish_kernel converts the sums back.  NaN or infinite inputs give meaningless (but still repeatable)
+// gradients.
+//
+// One kernel serves every shape the row-record list phase takes (up to 32 cameras, fewer than 2^32 depth elements),
+// any channel count and alignment: one cell per warp, lanes stride over the channels.  Per cell it builds the
+// forward's merged row records and the sample list (row_list_phase), adds the records' feature contributions
+//   d_feats[texel, c] += g_c * inv * weight                                     (flash_bevpool_cuda.cu:665,676-679)
+// computes T = <g, texel> once per record texel and lets one lane per sample form S = sum_ij w_ij T_ij and add
+// the sample's depth contributions, exactly the arithmetic of bwd_depth_kernel.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "fbev.h"
+#include "fbev_lists.cuh"
+
+namespace fbev {
+
+// Head of the deterministic scratch (256 bytes reserved).
+struct DetHeader {
+  unsigned max_f, max_d;  // bit patterns of the largest |contribution| to d_feats / d_depth (non-negative floats order as integers)
+  float scale_f, inv_f;   // fixed-point scale of d_feats and its inverse
+  float scale_d, inv_d;   // the same for d_depth
+};
+
+__device__ __forceinline__ void det_add(long long* base, size_t idx, float v, float scale) {
+  atomicAdd(reinterpret_cast<unsigned long long*>(base) + idx, (unsigned long long)__float2ll_rn(v * scale));
+}
+
+// Dev fields as this kernel reads them: gfeat / gdepth point at int64 arrays of the tensors' shapes, tex_count at
+// the DetHeader; CPW = 1, cpt = 1 (record texel fields are plain texel indices), cap = 32.
+template <typename T, bool MEASURE>
+__global__ void __launch_bounds__(kMaxWarps * 32) bwd_det_kernel(const __grid_constant__ Dev p) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  const BlockHeader h = carve(smem, p.N);
+  __shared__ int s_tile[2];
+  float vs[3], vmin[3];
+  voxel_frame(p, vs, vmin);
+  const int image_h = __ldg(p.isize), image_w = __ldg(p.isize + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  unsigned char* wa = h.warp_area + (size_t)warp * depth_warp_bytes(1, p.cap);
+  int* sLen = reinterpret_cast<int*>(wa);
+  int* sCnt = sLen + 32;
+  int* sSmp = sCnt + 32;
+  uint4* recs = reinterpret_cast<uint4*>(wa + 512);
+  uint4* samp = recs + row_stride(p.cap);
+
+  DetHeader* hdr = reinterpret_cast<DetHeader*>(p.tex_count);
+  long long* gf = reinterpret_cast<long long*>(p.gfeat);
+  long long* gd = reinterpret_cast<long long*>(p.gdepth);
+  const float scale_f = MEASURE ? 1.0f : hdr->scale_f, scale_d = MEASURE ? 1.0f : hdr->scale_d;
+  float mf = 0.0f, md = 0.0f;  // MEASURE: largest magnitudes seen by this lane
+
+  const T* fbase = reinterpret_cast<const T*>(p.feats);
+  const bool want_feats = (p.flags & FBEV_BWD_FEATS) != 0;
+  const bool want_depth = (p.flags & FBEV_BWD_DEPTH) != 0;
+  const bool legacy = (p.flags & FBEV_BWD_LEGACY_DEPTH) != 0;
+  const bool cat = p.mode == FBEV_DEPTH_CATEGORICAL;
+  const bool mean_pool = p.pool == FBEV_POOL_MEAN;
+  const int tile_cells = p.TX * p.TY;
+  const size_t C = (size_t)p.C;
+  int loaded_b = -1;
+  TileLoop loop;
+  loop.begin(p, s_tile);
+  for (int tile; (tile = loop.current(p)) >= 0; loop.advance()) {
+    const Tile t = tile_of(p, tile);
+    const unsigned vis = tile_visibility(p, t, h, vs, vmin, image_h, image_w, loaded_b);
+    const int ncand = __popc(vis) * p.Z;
+    for (int tc = warp; tc < tile_cells; tc += nwarps) {
+      const int ly = tc / p.TX, lx = tc - ly * p.TX;
+      const int x = t.x0 + lx, y = t.y0 + ly;
+      if (!(x < t.x1 && y < t.y1)) continue;  // uniform over the warp
+      const size_t cell = out_cell(p, t.b, y, x);
+      float inv = 1.0f;
+      if (mean_pool) {  // the count of all passes comes first
+        if (lane == 0) sCnt[0] = 0;
+        __syncwarp();
+        for (int r0 = 0; r0 < ncand; r0 += p.cap) {
+          if (lane == 0) sLen[0] = 0;
+          __syncwarp();
+          row_list_phase<T, false>(p, t, h, vis, 1u, tc, r0, min(r0 + p.cap, ncand), vs, vmin, image_h, image_w, sLen,
+                                   sCnt, recs, lane);
+        }
+        const int cnt = sCnt[0];
+        inv = cnt > 0 ? __fdiv_rn(1.0f, (float)cnt) : 0.0f;
+        __syncwarp();
+      }
+      for (int r0 = 0; r0 < ncand; r0 += p.cap) {
+        if (lane == 0) sLen[0] = sCnt[0] = sSmp[0] = 0;
+        __syncwarp();
+        row_list_phase<T, true, true>(p, t, h, vis, 1u, tc, r0, min(r0 + p.cap, ncand), vs, vmin, image_h, image_w, sLen,
+                                      sCnt, recs, lane, samp, sSmp);
+        const int n = sLen[0], ns = sSmp[0];
+        // ---- per row record: its feature contributions, and T = <g, texel> for its two texels ----
+        for (int i = 0; i < n; ++i) {
+          const uint4 r = recs[i];
+          const size_t tex0 = (size_t)r.x, tex1 = tex0 + r.y;  // r.y = u1 - u0 (0 in the last column)
+          const float w0 = __uint_as_float(r.z) * inv, w1 = __uint_as_float(r.w) * inv;
+          float t0 = 0.0f, t1 = 0.0f;
+          for (int c = lane; c < p.C; c += 32) {
+            const float gc = p.out_f32 ? __ldg(reinterpret_cast<const float*>(p.gout) + cell * C + c)
+                                       : to_float(__ldg(reinterpret_cast<const T*>(p.gout) + cell * C + c));
+            if (want_depth) {
+              t0 = fmaf(gc, to_float(__ldg(fbase + tex0 * C + c)), t0);
+              t1 = fmaf(gc, to_float(__ldg(fbase + tex1 * C + c)), t1);
+            }
+            if (want_feats) {
+              const float a0 = gc * w0, a1 = gc * w1;
+              if (MEASURE) {
+                mf = fmaxf(mf, fmaxf(fabsf(a0), fabsf(a1)));
+              } else {
+                det_add(gf, tex0 * C + c, a0, scale_f);
+                det_add(gf, tex1 * C + c, a1, scale_f);
+              }
+            }
+          }
+          if (want_depth) {
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+              t0 += __shfl_xor_sync(kFull, t0, off);
+              t1 += __shfl_xor_sync(kFull, t1, off);
+            }
+            __syncwarp();
+            if (lane == 0) {
+              recs[i].z = __float_as_uint(t0);
+              recs[i].w = __float_as_uint(t1);
+            }
+          }
+        }
+        __syncwarp();
+        // ---- one lane per sample: S from four T values, then the sample's depth contributions ----
+        if (want_depth) {
+          for (int idx = lane; idx < ns; idx += 32) {
+            const uint4* sr = samp + (size_t)idx * 3;
+            const uint4 sw = sr[0], sa = sr[1], sp = sr[2];
+            const float w00 = __uint_as_float(sw.x), w01 = __uint_as_float(sw.y), w10 = __uint_as_float(sw.z),
+                        w11 = __uint_as_float(sw.w);
+            const uint4 ra = recs[sp.x & 0xffffu], rb = recs[sp.x >> 16];
+            float S = w00 * __uint_as_float(ra.z);
+            S = fmaf(w10, __uint_as_float(ra.w), S);
+            S = fmaf(w01, __uint_as_float(rb.z), S);
+            S = fmaf(w11, __uint_as_float(rb.w), S);
+            const float sd = S * inv;
+            const float v00 = sd * w00, v01 = sd * w01, v10 = sd * w10, v11 = sd * w11;
+            // element indices of the four corners' depth rows: (v0,u0), (v0,u1), (v1,u0), (v1,u1)
+            const size_t e00 = (size_t)sa.x, e10 = e00 + sa.y, e01 = e00 + sa.z, e11 = e01 + sa.y;
+            if (cat) {
+              const size_t k = (size_t)sa.w;
+              if (MEASURE) {
+                md = fmaxf(md, fmaxf(fmaxf(fabsf(v00), fabsf(v01)), fmaxf(fabsf(v10), fabsf(v11))));
+              } else {
+                det_add(gd, e00 + k, v00, scale_d);
+                det_add(gd, e01 + k, v01, scale_d);
+                det_add(gd, e10 + k, v10, scale_d);
+                det_add(gd, e11 + k, v11, scale_d);
+              }
+            } else {
+              const float wgt = __uint_as_float(sp.y);
+              const float cm = legacy ? wgt : __uint_as_float(sp.z);
+              const float cs = legacy ? wgt : __uint_as_float(sp.w);
+              if (MEASURE) {
+                const float vmax = fmaxf(fmaxf(fabsf(v00), fabsf(v01)), fmaxf(fabsf(v10), fabsf(v11)));
+                md = fmaxf(md, vmax * fmaxf(fabsf(cm), fabsf(cs)));
+              } else {
+                det_add(gd, e00, cm * v00, scale_d);
+                det_add(gd, e00 + 1, cs * v00, scale_d);
+                det_add(gd, e01, cm * v01, scale_d);
+                det_add(gd, e01 + 1, cs * v01, scale_d);
+                det_add(gd, e10, cm * v10, scale_d);
+                det_add(gd, e10 + 1, cs * v10, scale_d);
+                det_add(gd, e11, cm * v11, scale_d);
+                det_add(gd, e11 + 1, cs * v11, scale_d);
+              }
+            }
+          }
+        }
+        __syncwarp();
+      }
+    }
+  }  // tiles
+  loop.end(p);
+  if (MEASURE) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      mf = fmaxf(mf, __shfl_xor_sync(kFull, mf, off));
+      md = fmaxf(md, __shfl_xor_sync(kFull, md, off));
+    }
+    if (lane == 0) {
+      // a maximum does not depend on the order either; NaN never wins a fmaxf, infinity saturates the scale
+      if (mf > 0.0f) atomicMax(&hdr->max_f, __float_as_uint(mf));
+      if (md > 0.0f) atomicMax(&hdr->max_d, __float_as_uint(md));
+    }
+  }
+}
+
+// scale = 2^(shift - e) with 2^e above the measured magnitude; shift = 62 - bits of the contribution count.
+__global__ void det_scale_kernel(DetHeader* hdr, int shift) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  const unsigned bits[2] = {hdr->max_f, hdr->max_d};
+  float scale[2], inv[2];
+  for (int k = 0; k < 2; ++k) {
+    int e = 0;
+    const float m = __uint_as_float(bits[k]);
+    if (m > 0.0f && m <= 3.0e38f) (void)frexpf(m, &e);  // m = f * 2^e, 0.5 <= f < 1
+    if (!(m <= 3.0e38f)) e = 128;
+    int s = shift - e;
+    s = s > 100 ? 100 : (s < -100 ? -100 : s);  // both the scale and its inverse stay normal numbers
+    scale[k] = ldexpf(1.0f, s);
+    inv[k] = ldexpf(1.0f, -s);
+  }
+  hdr->scale_f = scale[0];
+  hdr->inv_f = inv[0];
+  hdr->scale_d = scale[1];
+  hdr->inv_d = inv[1];
+}
+
+// Fixed-point sums -> gradient tensors; two arrays (either may be empty) in one launch.  which_b: the second
+// array uses the depth scale.  (A sum converts to float32 with one rounding; times a power of two is exact.)
+template <typename TA, typename TB>
+__global__ void det_finish_kernel(const DetHeader* __restrict__ hdr, const long long* __restrict__ sa, TA* __restrict__ da,
+                                  size_t na, const long long* __restrict__ sb, TB* __restrict__ db, size_t nb) {
+  const float inv_f = hdr->inv_f, inv_d = hdr->inv_d;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < na + nb; i += stride) {
+    if (i < na)
+      da[i] = from_float<TA>(__ll2float_rn(sa[i]) * inv_f);
+    else
+      db[i - na] = from_float<TB>(__ll2float_rn(sb[i - na]) * inv_d);
+  }
+}
+
+}  // namespace fbev

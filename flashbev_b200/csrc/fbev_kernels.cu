@@ -38,6 +38,7 @@
 #include "fbev_backward.cuh"
 #include "fbev_sort.cuh"
 #include "fbev_misc.cuh"
+#include "fbev_deterministic.cuh"
 
 namespace fbev {
 
@@ -713,7 +714,22 @@ int fbev_forward_to_host(const FbevProblem* p, void* out_dev, void* out_host, in
 }
 
 // float32 accumulation targets of the 16-bit types: what fbev_backward cannot do without
+// Deterministic backward: a 256-byte head (DetHeader), 64-bit fixed-point sums for the requested gradients and,
+// for logits, the float32 gradient with respect to the probabilities that the softmax backward consumes.
+static size_t round256(size_t n) { return ((n + 255) / 256) * 256; }
+static size_t det_scratch_bytes(const FbevProblem* p, int flags) {
+  const size_t tex = (size_t)p->B * p->N * p->H * p->W;
+  size_t n = 256;
+  if (flags & FBEV_BWD_FEATS) n += round256(tex * p->C * 8);
+  if (flags & FBEV_BWD_DEPTH) {
+    n += round256(tex * p->D * 8);
+    if (p->mode == FBEV_DEPTH_CATEGORICAL_LOGITS) n += round256(tex * p->D * 4);
+  }
+  return n;
+}
+
 static size_t scratch_min_bytes(const FbevProblem* p, int flags) {
+  if (flags & FBEV_BWD_DETERMINISTIC) return det_scratch_bytes(p, flags);
   if (p->dtype == FBEV_F32) return 0;
   size_t n = 0;
   const size_t tex = (size_t)p->B * p->N * p->H * p->W;
@@ -754,6 +770,7 @@ static size_t sort_capacity(const FbevProblem* p, int flags) {
   return cand < top ? (cand < 4096 ? 4096 : cand) : top;
 }
 static size_t sort_bytes(const FbevProblem* p, int flags) {
+  if (flags & FBEV_BWD_DETERMINISTIC) return 0;  // no sort: fixed-point sums need no order
   if (!(flags & FBEV_BWD_FEATS) && !sort_carries_depth(p, flags)) return 0;
   const size_t tex = (size_t)sort_batch_run(p, flags) * p->N * p->H * p->W;
   if (tex >= 0xfffffff0ull || (size_t)p->B * p->Y * p->X >= 0xfffffff0ull) return 0;
@@ -791,6 +808,110 @@ size_t fbev_backward_scratch_bytes(const FbevProblem* p, int flags) {
   return scratch_min_bytes(p, flags) + sort_bytes(p, flags);
 }
 
+// FBEV_BWD_DETERMINISTIC: measure launch, scale, accumulation launch, conversion (fbev_deterministic.cuh).
+extern "C++" {
+template <typename T>
+static int backward_deterministic_t(const FbevProblem* p, Dev d, const Plan& pl, DetHeader* hdr, int shift, void* grad_feats,
+                                    void* grad_depth, float* dprob, size_t nf, size_t nd, cudaStream_t st) {
+  int rc = launch(bwd_det_kernel<T, true>, pl, d, st);
+  if (rc != FBEV_OK) return rc;
+  det_scale_kernel<<<1, 32, 0, st>>>(hdr, shift);
+  if (cudaGetLastError() != cudaSuccess) return FBEV_ERR_LAUNCH;
+  rc = launch(bwd_det_kernel<T, false>, pl, d, st);
+  if (rc != FBEV_OK) return rc;
+  const long long* gf = reinterpret_cast<const long long*>(d.gfeat);
+  const long long* gd = reinterpret_cast<const long long*>(d.gdepth);
+  const size_t na = (d.flags & FBEV_BWD_FEATS) ? nf : 0, nb = (d.flags & FBEV_BWD_DEPTH) ? nd : 0;
+  const size_t want = (na + nb + 255) / 256;
+  const int blocks = (int)(want < (size_t)sm_count() * 16 ? (want ? want : 1) : (size_t)sm_count() * 16);
+  if (dprob != nullptr)
+    det_finish_kernel<T, float><<<blocks, 256, 0, st>>>(hdr, gf, reinterpret_cast<T*>(grad_feats), na, gd, dprob, nb);
+  else
+    det_finish_kernel<T, T><<<blocks, 256, 0, st>>>(hdr, gf, reinterpret_cast<T*>(grad_feats), na, gd,
+                                                    reinterpret_cast<T*>(grad_depth), nb);
+  return cudaGetLastError() == cudaSuccess ? FBEV_OK : FBEV_ERR_LAUNCH;
+}
+}  // extern "C++"
+
+static int backward_deterministic(const FbevProblem* p, const void* grad_out, void* grad_feats, void* grad_depth,
+                                  void* scratch, size_t scratch_bytes, int flags, cudaStream_t st) {
+  const size_t tex_all = (size_t)p->B * p->N * p->H * p->W;
+  const size_t nf = tex_all * p->C, nd = tex_all * p->D;
+  // the row-record list phase keeps the visible cameras in a 32-bit mask and 32-bit depth element indices
+  if (p->N > 32 || (unsigned long long)nd >= (1ull << 32)) return FBEV_ERR_RANGE;
+  const size_t need = det_scratch_bytes(p, flags);
+  if (scratch == nullptr || scratch_bytes < need || ((uintptr_t)scratch % 256)) return FBEV_ERR_SCRATCH;
+  const bool logits = p->mode == FBEV_DEPTH_CATEGORICAL_LOGITS;
+  unsigned char* s = reinterpret_cast<unsigned char*>(scratch);
+  DetHeader* hdr = reinterpret_cast<DetHeader*>(s);
+  s += 256;
+  long long* gf = nullptr;
+  long long* gd = nullptr;
+  float* dprob = nullptr;
+  if (flags & FBEV_BWD_FEATS) {
+    gf = reinterpret_cast<long long*>(s);
+    s += round256(nf * 8);
+  }
+  if (flags & FBEV_BWD_DEPTH) {
+    gd = reinterpret_cast<long long*>(s);
+    s += round256(nd * 8);
+    if (logits) dprob = reinterpret_cast<float*>(s);
+  }
+  const size_t clear = 256 + (gf ? round256(nf * 8) : 0) + (gd ? round256(nd * 8) : 0);
+  if (cudaMemsetAsync(scratch, 0, clear, st) != cudaSuccess) {
+    cudaGetLastError();
+    return FBEV_ERR_LAUNCH;
+  }
+  Dev d;
+  fill_dev(p, d);
+  d.saved = nullptr;
+  d.gout = grad_out;
+  d.flags = flags;
+  d.gfeat = reinterpret_cast<float*>(gf);   // the kernel reads these two as int64 arrays
+  d.gdepth = reinterpret_cast<float*>(gd);
+  d.tex_count = reinterpret_cast<unsigned*>(hdr);
+  d.GL = 32;
+  d.CPW = 1;
+  d.cpt = 1;  // record texel fields are plain texel indices
+  d.cap = 32;
+  d.TX = 8;
+  d.TY = 4;
+  d.tiles_x = (p->X + d.TX - 1) / d.TX;
+  d.tiles_y = (p->y_end - p->y_begin + d.TY - 1) / d.TY;
+  Plan pl{};
+  pl.chunked = false;
+  pl.GL = 32;
+  pl.CPW = 1;
+  pl.warps = kMaxWarps;
+  pl.cap = d.cap;
+  pl.smem = header_bytes(p->N) + (size_t)pl.warps * depth_warp_bytes(1, pl.cap);
+  pl.blocks = d.tiles_x * d.tiles_y * p->B;
+  // 2^bits above the number of contributions one element can receive: four corners of every candidate of its camera
+  const unsigned long long cnt = 4ull * (unsigned long long)(p->y_end - p->y_begin) * p->X * p->Z;
+  int bits = 0;
+  while (bits < 48 && (1ull << bits) < cnt) ++bits;
+  const int shift = 62 - bits;
+  int rc;
+  switch (p->dtype) {
+    case FBEV_F32: rc = backward_deterministic_t<float>(p, d, pl, hdr, shift, grad_feats, grad_depth, dprob, nf, nd, st); break;
+    case FBEV_BF16: rc = backward_deterministic_t<__nv_bfloat16>(p, d, pl, hdr, shift, grad_feats, grad_depth, dprob, nf, nd, st); break;
+    default: rc = backward_deterministic_t<__half>(p, d, pl, hdr, shift, grad_feats, grad_depth, dprob, nf, nd, st); break;
+  }
+  if (rc != FBEV_OK) return rc;
+  if (dprob != nullptr) {
+    // dL/dprob -> dL/dlogit through the folded softmax: one thread order per texel, nothing is drawn
+    const unsigned blocks = (unsigned)((tex_all * 32 + 255) / 256);
+    const float2* stats = reinterpret_cast<const float2*>(p->depth_stats);
+    switch (p->dtype) {
+      case FBEV_F32: launch_after(softmax_bwd_kernel<float>, blocks, 256, 0, st, reinterpret_cast<const float*>(p->depth), stats, (const float*)dprob, reinterpret_cast<float*>(grad_depth), tex_all, p->D); break;
+      case FBEV_BF16: launch_after(softmax_bwd_kernel<__nv_bfloat16>, blocks, 256, 0, st, reinterpret_cast<const __nv_bfloat16*>(p->depth), stats, (const float*)dprob, reinterpret_cast<__nv_bfloat16*>(grad_depth), tex_all, p->D); break;
+      default: launch_after(softmax_bwd_kernel<__half>, blocks, 256, 0, st, reinterpret_cast<const __half*>(p->depth), stats, (const float*)dprob, reinterpret_cast<__half*>(grad_depth), tex_all, p->D); break;
+    }
+    if (cudaGetLastError() != cudaSuccess) return FBEV_ERR_LAUNCH;
+  }
+  return FBEV_OK;
+}
+
 int fbev_backward(const FbevProblem* p, const void* grad_out, void* grad_feats, void* grad_depth, void* scratch,
                   size_t scratch_bytes, int flags, void* stream) {
   const int rc = validate(p);
@@ -810,6 +931,8 @@ int fbev_backward(const FbevProblem* p, const void* grad_out, void* grad_feats, 
     const int src = launch_softmax_stats(p, st);
     if (src != FBEV_OK) return src;
   }
+  if (flags & FBEV_BWD_DETERMINISTIC)
+    return backward_deterministic(p, grad_out, grad_feats, grad_depth, scratch, scratch_bytes, flags, st);
   // float32 accumulation targets of the whole batch: the gradient tensors themselves, or the head of the scratch
   float* gfeat_all = nullptr;
   float* gdepth_all = nullptr;

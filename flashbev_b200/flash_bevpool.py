@@ -15,8 +15,8 @@ Differences, all additive or host-side:
   * float32, bfloat16 and float16 features are processed natively (float32 accumulation)
     and the output has the feature dtype; the reference up-casts to float32 (:47-49);
   * ``depth_distribution=2`` selects the categorical depth mode (depth = probabilities
-    [B,N,H,W,D]); ``pool``, ``depth_bin_range``, ``legacy_depth_grad`` and ``y_range``
-    are keyword-only extras of the wrapper;
+    [B,N,H,W,D]); ``pool``, ``depth_bin_range``, ``legacy_depth_grad``, ``deterministic`` and
+    ``y_range`` are keyword-only extras of the wrapper;
   * the kernel-variant flags (``use_shared_memory``, ``optimize_z_precompute``,
     ``use_warp_kernel``, ``use_vectorized_load``) are accepted and ignored: they select
     between reference kernels that compute the same thing;
@@ -49,7 +49,7 @@ class DepthSpec(int):
     def __new__(cls, mode: int, pool: Optional[str] = None, depth_bin_range: Optional[Tuple[float, float]] = None,
                 legacy_depth_grad: bool = False, y_range: Optional[Tuple[int, int]] = None,
                 out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None, host_row_chunks: int = 0,
-                save_lists: bool = False, compact_rows: bool = False):
+                save_lists: bool = False, compact_rows: bool = False, deterministic: bool = False):
         mode = int(mode)
         if mode not in (0, 1, 2, 3):
             raise ValueError("depth_distribution must be 0 (gaussian), 1 (laplace), 2 (categorical probabilities) or "
@@ -70,6 +70,7 @@ class DepthSpec(int):
             d0, delta = 0.0, 1.0
         self.d0, self.delta = d0, delta
         self.legacy_depth_grad = bool(legacy_depth_grad)
+        self.deterministic = bool(deterministic)
         self.y_range = None if y_range is None else (int(y_range[0]), int(y_range[1]))
         if out_dtype not in (None, torch.float32):
             raise ValueError("out_dtype must be None (the feature dtype) or torch.float32")
@@ -316,6 +317,8 @@ class FlashBEVPool(torch.autograd.Function):
             flags |= _lib.BWD_DEPTH
         if spec.legacy_depth_grad:
             flags |= _lib.BWD_LEGACY_DEPTH
+        if spec.deterministic:
+            flags |= _lib.BWD_DETERMINISTIC
         grad_feats = grad_depth = None
         if flags & (_lib.BWD_FEATS | _lib.BWD_DEPTH):
             go = _on(out_grad, feats.device, _out_dtype(spec, feats))
@@ -345,7 +348,7 @@ def flash_bevpool(image_feats, depth_params, projection_matrices, feature_size, 
                   depth_distribution=0, use_shared_memory=True, optimize_z_precompute=True, use_warp_kernel=False,
                   use_vectorized_load=False, epsilon=1e-6, depth_weight_threshold=1e-6, *, pool=None,
                   depth_bin_range=None, legacy_depth_grad=False, y_range=None, out_dtype=None, out=None,
-                  host_row_chunks=0, save_lists=False, compact_rows=False):
+                  host_row_chunks=0, save_lists=False, compact_rows=False, deterministic=False):
     """Fused BEV pooling; same arguments as the reference wrapper (flash_bevpool.py:139-178).
 
     Args:
@@ -360,6 +363,8 @@ def flash_bevpool(image_feats, depth_params, projection_matrices, feature_size, 
         pool: "mean" (default for 0/1, the reference's) or "sum" (default for 2).
         depth_bin_range: (first bin edge, bin width) of the categorical mode.
         legacy_depth_grad: parametric modes only; reproduce the reference CUDA kernel's depth gradient.
+        deterministic: backward with bitwise reproducible gradients (fixed-point sums instead of float atomics;
+            several times slower, same tolerances; at most 32 cameras).  The forward is reproducible anyway.
         y_range: (begin, end) BEV rows to compute; the other rows of the output are zero.
         compact_rows: with ``y_range``: the result (and the upstream gradient of its backward) holds only those
             rows, [B, end - begin, X, C]: a row shard that stays a shard.
@@ -379,7 +384,8 @@ def flash_bevpool(image_feats, depth_params, projection_matrices, feature_size, 
     """
     spec = DepthSpec(depth_distribution, pool=pool, depth_bin_range=depth_bin_range,
                      legacy_depth_grad=legacy_depth_grad, y_range=y_range, out_dtype=out_dtype, out=out,
-                     host_row_chunks=host_row_chunks, save_lists=save_lists, compact_rows=compact_rows)
+                     host_row_chunks=host_row_chunks, save_lists=save_lists, compact_rows=compact_rows,
+                     deterministic=deterministic)
     if not (torch.is_grad_enabled() and (image_feats.requires_grad or depth_params.requires_grad)):
         return _forward(depth_params, image_feats, projection_matrices, feature_size, image_size, roi_range, grid_size,
                         spec, epsilon, depth_weight_threshold, False)[0]

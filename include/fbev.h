@@ -75,9 +75,18 @@ enum {
 enum {
   FBEV_BWD_FEATS = 1,        /* compute grad_feats */
   FBEV_BWD_DEPTH = 2,        /* compute grad_depth */
-  FBEV_BWD_LEGACY_DEPTH = 4  /* parametric modes: reproduce the reference kernel's depth gradient
+  FBEV_BWD_LEGACY_DEPTH = 4, /* parametric modes: reproduce the reference kernel's depth gradient
                                 (same value into mean and sigma, flash_bevpool_cuda.cu:665-674)
                                 instead of the analytic one */
+  FBEV_BWD_DETERMINISTIC = 8 /* bitwise reproducible gradients: every contribution is added as a 64-bit
+                                fixed-point integer (integer addition does not depend on the order the
+                                warps arrive in), at a power-of-two scale taken from a first, measuring
+                                launch.  Same tolerances as the default path, several times slower.
+                                Needs N <= 32 and B*N*H*W*D < 2^32 (FBEV_ERR_RANGE otherwise) and scratch
+                                for every element type: fbev_backward_min_scratch_bytes() with this flag
+                                (256 bytes + 8 per element of each requested gradient, + 4 per depth
+                                element for logits).  The reference has no counterpart: its backward
+                                adds float atomics in arrival order (flash_bevpool_cuda.cu:667-679). */
 };
 
 /*
@@ -185,7 +194,8 @@ size_t fbev_saved_state_bytes(const FbevProblem* p);
 size_t fbev_backward_scratch_bytes(const FbevProblem* p, int flags);
 
 /* The least scratch fbev_backward accepts: 0 for float32 tensors (gradients accumulate in place),
- * otherwise room for float32 copies of the requested gradients.  With less than
+ * otherwise room for float32 copies of the requested gradients; with FBEV_BWD_DETERMINISTIC the
+ * fixed-point sums described at that flag, for every element type.  With less than
  * fbev_backward_scratch_bytes() the feature gradient falls back to its single-launch kernels
  * (direct float reductions), about 1.6 times slower on the benchmark shape. */
 size_t fbev_backward_min_scratch_bytes(const FbevProblem* p, int flags);
