@@ -7,13 +7,25 @@
 // with an integer atomic: integer addition is associative and commutative, so the sum does not depend on the order,
 // and every contribution itself is computed by one warp in a fixed order.
 //
-// The fixed-point scale is a power of two chosen from the data: a first launch of the same kernel (MEASURE) only
-// records the largest magnitude any single contribution takes, per gradient; det_scale_kernel turns that into
-// scale = 2^(62 - bits - e) with 2^e above that magnitude and 2^bits above the number of contributions one element
-// can receive (4 * rows * X * Z: every candidate of the texel's camera, four corners each), so no sum can leave
-// 63 bits, and a contribution keeps at least 62 - bits binary digits below the largest one (38 for a 512 x 512 x 16
-// grid).  det_finish_kernel converts the sums back.  NaN or infinite inputs give meaningless (but still repeatable)
-// gradients.
+// The fixed-point scale is a power of two chosen from the data before anything is added.  det_bounds_kernel reduces
+// the inputs to four maxima (each order-independent): G = max |g|, Gn = max over cells of ||g_cell||_2, Fn = max over
+// texels of ||f_texel||_2, and the largest depth weight any sample can have: max |probability| in the categorical
+// mode (1 for logits), max 1 / (sigma + eps) in the parametric modes (a bilinear interpolation is a convex
+// combination, so the interpolated value stays inside the corner values' range).  From these follow bounds that
+// hold whatever the geometry does:
+//   a contribution to d_feats is g_c * inv * (sum of at most 2 Z sample weights w_ij * weight, w_ij <= 1), doubled
+//     where the two texels of a record coincide                                  =>  |.| <= 4 Z * Wmax * G
+//   a contribution to d_depth is S * inv * w_ij (* d weight / d parameter), S = sum_ij w_ij <g, f_ij> a convex
+//     combination of dot products, |<g, f>| <= ||g|| ||f||, `merged` of them summed before they are added (1 in
+//     the kernel below)                                                        =>  |.| <= merged * Gn * Fn * Dmax
+//   with Dmax = 1 (categorical), 1 / (sigma + eps)_min (legacy parametric gradient) or its square (analytic one:
+//   |z| exp(-z^2 / 2) < 1, |z^2 - 1| exp(-z^2 / 2) <= 1, and the Laplace counterparts are below 1 / 2).
+// det_scale_kernel sets scale = 2^(62 - bits - e) with 2^e above the bound and 2^bits above the number of
+// contributions one element can receive (4 * rows * X * Z: every candidate of the texel's camera, four corners
+// each), so no sum can leave 63 bits.  The bounds are loose by a few binary digits, the count by many; what is left
+// is still finer than float32 (on the benchmark shapes a contribution keeps more than 30 digits below the largest
+// one, and the sums themselves are exact).  det_finish_kernel converts the sums back.  sigma + eps <= 0 somewhere, NaN
+// or infinite inputs give meaningless (but still repeatable) gradients.
 //
 // One kernel serves every shape the row-record list phase takes (up to 32 cameras, fewer than 2^32 depth elements),
 // any channel count and alignment: one cell per warp, lanes stride over the channels.  Per cell it builds the
@@ -32,12 +44,72 @@
 
 namespace fbev {
 
-// Head of the deterministic scratch (256 bytes reserved).
+// Head of the deterministic scratch (256 bytes reserved).  The maxima are kept as bit patterns: non-negative floats
+// (infinity included) order like unsigned integers, so atomicMax combines them in any order.
 struct DetHeader {
-  unsigned max_f, max_d;  // bit patterns of the largest |contribution| to d_feats / d_depth (non-negative floats order as integers)
+  unsigned g_max;    // max |g|
+  unsigned g_norm2;  // max over cells of sum_c g_c^2
+  unsigned f_norm2;  // max over texels of sum_c f_c^2
+  unsigned d_max;    // categorical: max |depth value|; parametric: max 1 / (sigma + eps), infinity when that is <= 0
   float scale_f, inv_f;   // fixed-point scale of d_feats and its inverse
   float scale_d, inv_d;   // the same for d_depth
 };
+
+// One warp per row: the cells of the upstream gradient, the texels of the features, and the depth tensor in rows of
+// D values (categorical) or (mean, sigma) pairs (parametric).
+template <typename T>
+__global__ void __launch_bounds__(256) det_bounds_kernel(DetHeader* __restrict__ hdr, const void* __restrict__ gout, int gout_f32,
+                                                         size_t cells, const T* __restrict__ feats, size_t texels, int C,
+                                                         const T* __restrict__ depth, int D, int categorical, float eps) {
+  const int lane = threadIdx.x & 31;
+  const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
+  float gmax = 0.0f, gn2 = 0.0f, fn2 = 0.0f, dmax = 0.0f;
+  for (size_t row = warp; row < cells + texels; row += nwarps) {
+    const bool is_g = row < cells;
+    float m = 0.0f, q = 0.0f;
+    for (int c = lane; c < C; c += 32) {
+      float v;
+      if (is_g)
+        v = gout_f32 ? __ldg(reinterpret_cast<const float*>(gout) + row * (size_t)C + c)
+                     : to_float(__ldg(reinterpret_cast<const T*>(gout) + row * (size_t)C + c));
+      else
+        v = to_float(__ldg(feats + (row - cells) * (size_t)C + c));
+      m = fmaxf(m, fabsf(v));
+      q = fmaf(v, v, q);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) q += __shfl_xor_sync(0xffffffffu, q, off);  // same value in every lane, every run
+    if (is_g) {
+      gmax = fmaxf(gmax, m);
+      gn2 = fmaxf(gn2, q);
+    } else {
+      fn2 = fmaxf(fn2, q);
+    }
+  }
+  const size_t nd = categorical ? texels * (size_t)D : texels;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nd; i += (size_t)gridDim.x * blockDim.x) {
+    if (categorical) {
+      dmax = fmaxf(dmax, fabsf(to_float(__ldg(depth + i))));
+    } else {
+      const float se = to_float(__ldg(depth + i * 2 + 1)) + eps;
+      dmax = fmaxf(dmax, se > 0.0f ? 1.0f / se : __int_as_float(0x7f800000));
+    }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    gmax = fmaxf(gmax, __shfl_xor_sync(0xffffffffu, gmax, off));
+    gn2 = fmaxf(gn2, __shfl_xor_sync(0xffffffffu, gn2, off));
+    fn2 = fmaxf(fn2, __shfl_xor_sync(0xffffffffu, fn2, off));
+    dmax = fmaxf(dmax, __shfl_xor_sync(0xffffffffu, dmax, off));
+  }
+  if (lane == 0) {  // NaN never wins a fmaxf; zero needs no update
+    if (gmax > 0.0f) atomicMax(&hdr->g_max, __float_as_uint(gmax));
+    if (gn2 > 0.0f) atomicMax(&hdr->g_norm2, __float_as_uint(gn2));
+    if (fn2 > 0.0f) atomicMax(&hdr->f_norm2, __float_as_uint(fn2));
+    if (dmax > 0.0f) atomicMax(&hdr->d_max, __float_as_uint(dmax));
+  }
+}
 
 __device__ __forceinline__ void det_add(long long* base, size_t idx, float v, float scale) {
   atomicAdd(reinterpret_cast<unsigned long long*>(base) + idx, (unsigned long long)__float2ll_rn(v * scale));
@@ -45,7 +117,7 @@ __device__ __forceinline__ void det_add(long long* base, size_t idx, float v, fl
 
 // Dev fields as this kernel reads them: gfeat / gdepth point at int64 arrays of the tensors' shapes, tex_count at
 // the DetHeader; CPW = 1, cpt = 1 (record texel fields are plain texel indices), cap = 32.
-template <typename T, bool MEASURE>
+template <typename T>
 __global__ void __launch_bounds__(kMaxWarps * 32) bwd_det_kernel(const __grid_constant__ Dev p) {
   extern __shared__ __align__(16) unsigned char smem[];
   const BlockHeader h = carve(smem, p.N);
@@ -64,8 +136,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32) bwd_det_kernel(const __grid_co
   DetHeader* hdr = reinterpret_cast<DetHeader*>(p.tex_count);
   long long* gf = reinterpret_cast<long long*>(p.gfeat);
   long long* gd = reinterpret_cast<long long*>(p.gdepth);
-  const float scale_f = MEASURE ? 1.0f : hdr->scale_f, scale_d = MEASURE ? 1.0f : hdr->scale_d;
-  float mf = 0.0f, md = 0.0f;  // MEASURE: largest magnitudes seen by this lane
+  const float scale_f = hdr->scale_f, scale_d = hdr->scale_d;
 
   const T* fbase = reinterpret_cast<const T*>(p.feats);
   const bool want_feats = (p.flags & FBEV_BWD_FEATS) != 0;
@@ -121,13 +192,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32) bwd_det_kernel(const __grid_co
               t1 = fmaf(gc, to_float(__ldg(fbase + tex1 * C + c)), t1);
             }
             if (want_feats) {
-              const float a0 = gc * w0, a1 = gc * w1;
-              if (MEASURE) {
-                mf = fmaxf(mf, fmaxf(fabsf(a0), fabsf(a1)));
-              } else {
-                det_add(gf, tex0 * C + c, a0, scale_f);
-                det_add(gf, tex1 * C + c, a1, scale_f);
-              }
+              det_add(gf, tex0 * C + c, gc * w0, scale_f);
+              det_add(gf, tex1 * C + c, gc * w1, scale_f);
             }
           }
           if (want_depth) {
@@ -162,31 +228,22 @@ __global__ void __launch_bounds__(kMaxWarps * 32) bwd_det_kernel(const __grid_co
             const size_t e00 = (size_t)sa.x, e10 = e00 + sa.y, e01 = e00 + sa.z, e11 = e01 + sa.y;
             if (cat) {
               const size_t k = (size_t)sa.w;
-              if (MEASURE) {
-                md = fmaxf(md, fmaxf(fmaxf(fabsf(v00), fabsf(v01)), fmaxf(fabsf(v10), fabsf(v11))));
-              } else {
-                det_add(gd, e00 + k, v00, scale_d);
-                det_add(gd, e01 + k, v01, scale_d);
-                det_add(gd, e10 + k, v10, scale_d);
-                det_add(gd, e11 + k, v11, scale_d);
-              }
+              det_add(gd, e00 + k, v00, scale_d);
+              det_add(gd, e01 + k, v01, scale_d);
+              det_add(gd, e10 + k, v10, scale_d);
+              det_add(gd, e11 + k, v11, scale_d);
             } else {
               const float wgt = __uint_as_float(sp.y);
               const float cm = legacy ? wgt : __uint_as_float(sp.z);
               const float cs = legacy ? wgt : __uint_as_float(sp.w);
-              if (MEASURE) {
-                const float vmax = fmaxf(fmaxf(fabsf(v00), fabsf(v01)), fmaxf(fabsf(v10), fabsf(v11)));
-                md = fmaxf(md, vmax * fmaxf(fabsf(cm), fabsf(cs)));
-              } else {
-                det_add(gd, e00, cm * v00, scale_d);
-                det_add(gd, e00 + 1, cs * v00, scale_d);
-                det_add(gd, e01, cm * v01, scale_d);
-                det_add(gd, e01 + 1, cs * v01, scale_d);
-                det_add(gd, e10, cm * v10, scale_d);
-                det_add(gd, e10 + 1, cs * v10, scale_d);
-                det_add(gd, e11, cm * v11, scale_d);
-                det_add(gd, e11 + 1, cs * v11, scale_d);
-              }
+              det_add(gd, e00, cm * v00, scale_d);
+              det_add(gd, e00 + 1, cs * v00, scale_d);
+              det_add(gd, e01, cm * v01, scale_d);
+              det_add(gd, e01 + 1, cs * v01, scale_d);
+              det_add(gd, e10, cm * v10, scale_d);
+              det_add(gd, e10 + 1, cs * v10, scale_d);
+              det_add(gd, e11, cm * v11, scale_d);
+              det_add(gd, e11 + 1, cs * v11, scale_d);
             }
           }
         }
@@ -195,32 +252,28 @@ __global__ void __launch_bounds__(kMaxWarps * 32) bwd_det_kernel(const __grid_co
     }
   }  // tiles
   loop.end(p);
-  if (MEASURE) {
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-      mf = fmaxf(mf, __shfl_xor_sync(kFull, mf, off));
-      md = fmaxf(md, __shfl_xor_sync(kFull, md, off));
-    }
-    if (lane == 0) {
-      // a maximum does not depend on the order either; NaN never wins a fmaxf, infinity saturates the scale
-      if (mf > 0.0f) atomicMax(&hdr->max_f, __float_as_uint(mf));
-      if (md > 0.0f) atomicMax(&hdr->max_d, __float_as_uint(md));
-    }
-  }
 }
 
-// scale = 2^(shift - e) with 2^e above the measured magnitude; shift = 62 - bits of the contribution count.
-__global__ void det_scale_kernel(DetHeader* hdr, int shift) {
+// The bounds of the file comment -> scale = 2^(shift - e) with 2^e above the bound; shift = 62 - bits of the
+// contribution count.  depth_kind: 0 categorical probabilities, 1 logits (probabilities <= 1), 2 parametric with
+// the analytic depth gradient, 3 parametric with the legacy one.
+__global__ void det_scale_kernel(DetHeader* hdr, int shift, int Z, int depth_kind, int merged) {
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
-  const unsigned bits[2] = {hdr->max_f, hdr->max_d};
+  const double g = (double)__uint_as_float(hdr->g_max);
+  const double gn = sqrt((double)__uint_as_float(hdr->g_norm2)), fn = sqrt((double)__uint_as_float(hdr->f_norm2));
+  const double d = (double)__uint_as_float(hdr->d_max);
+  const double slack = 1.01;  // float32 rounding inside the reductions and the kernels' own products
+  const double wmax = depth_kind == 1 ? 1.0 : d;
+  const double dpar = depth_kind <= 1 ? 1.0 : (depth_kind == 3 ? d : d * d);
+  const double bound[2] = {4.0 * (double)Z * wmax * g * slack, (double)merged * gn * fn * dpar * slack};
   float scale[2], inv[2];
   for (int k = 0; k < 2; ++k) {
     int e = 0;
-    const float m = __uint_as_float(bits[k]);
-    if (m > 0.0f && m <= 3.0e38f) (void)frexpf(m, &e);  // m = f * 2^e, 0.5 <= f < 1
-    if (!(m <= 3.0e38f)) e = 128;
+    const double m = bound[k];
+    if (m > 0.0 && m < 1.0e300) (void)frexp(m, &e);  // m = f * 2^e, 0.5 <= f < 1
+    if (!(m < 1.0e300)) e = 1024;
     int s = shift - e;
-    s = s > 100 ? 100 : (s < -100 ? -100 : s);  // both the scale and its inverse stay normal numbers
+    s = s > 100 ? 100 : (s < -100 ? -100 : s);  // both the scale and its inverse stay normal float32 numbers
     scale[k] = ldexpf(1.0f, s);
     inv[k] = ldexpf(1.0f, -s);
   }

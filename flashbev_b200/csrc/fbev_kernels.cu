@@ -808,16 +808,21 @@ size_t fbev_backward_scratch_bytes(const FbevProblem* p, int flags) {
   return scratch_min_bytes(p, flags) + sort_bytes(p, flags);
 }
 
-// FBEV_BWD_DETERMINISTIC: measure launch, scale, accumulation launch, conversion (fbev_deterministic.cuh).
+// FBEV_BWD_DETERMINISTIC: bounds of the inputs, scale, accumulation launch, conversion (fbev_deterministic.cuh).
 extern "C++" {
 template <typename T>
 static int backward_deterministic_t(const FbevProblem* p, Dev d, const Plan& pl, DetHeader* hdr, int shift, void* grad_feats,
                                     void* grad_depth, float* dprob, size_t nf, size_t nd, cudaStream_t st) {
-  int rc = launch(bwd_det_kernel<T, true>, pl, d, st);
-  if (rc != FBEV_OK) return rc;
-  det_scale_kernel<<<1, 32, 0, st>>>(hdr, shift);
+  const size_t cells = (size_t)p->B * d.out_rows * p->X, texels = (size_t)p->B * p->N * p->H * p->W;
+  const bool cat = is_categorical(p->mode);
+  det_bounds_kernel<T><<<sm_count() * 8, 256, 0, st>>>(hdr, d.gout, d.out_f32, cells, reinterpret_cast<const T*>(p->image_feats),
+                                                       texels, p->C, reinterpret_cast<const T*>(p->depth), p->D, cat ? 1 : 0,
+                                                       p->epsilon);
   if (cudaGetLastError() != cudaSuccess) return FBEV_ERR_LAUNCH;
-  rc = launch(bwd_det_kernel<T, false>, pl, d, st);
+  const int kind = p->mode == FBEV_DEPTH_CATEGORICAL_LOGITS ? 1 : (cat ? 0 : ((d.flags & FBEV_BWD_LEGACY_DEPTH) ? 3 : 2));
+  det_scale_kernel<<<1, 32, 0, st>>>(hdr, shift, p->Z, kind, 1);
+  if (cudaGetLastError() != cudaSuccess) return FBEV_ERR_LAUNCH;
+  int rc = launch(bwd_det_kernel<T>, pl, d, st);
   if (rc != FBEV_OK) return rc;
   const long long* gf = reinterpret_cast<const long long*>(d.gfeat);
   const long long* gd = reinterpret_cast<const long long*>(d.gdepth);
