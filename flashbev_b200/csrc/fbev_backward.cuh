@@ -60,6 +60,34 @@ __device__ __forceinline__ void add_records_direct(const Dev& p, const uint4* re
   }
 }
 
+// The contributions of one cell's row records as 64-bit fixed-point integers (reproducible backward, for the warps
+// that find the entry list full): p.gfeat holds int64 sums, go the lane's chunks of the cell's upstream gradient as
+// loaded, lg the lane's position in its group, scale the fixed-point scale of d_feats.  Every term is formed exactly
+// as the entry path forms it -- emit_entries' weight (times 1 / count, both weights merged when the record has one
+// texel), times the scale, times g, rounded to an integer -- because which warps end up here depends on the order
+// the warps drew their slots in, and the result must not.
+template <typename T, int V>
+__device__ __forceinline__ void add_records_fixed(const Dev& p, const uint4* rec, int n, const float* go, float inv_cell,
+                                                  int lg, float scale) {
+  constexpr int E = Chunk<T>::E;
+  unsigned long long* gf = reinterpret_cast<unsigned long long*>(p.gfeat);
+  for (int i = 0; i < n; ++i) {
+    const uint4 r = rec[i];
+    const float a = __uint_as_float(r.z) * inv_cell, b = __uint_as_float(r.w) * inv_cell;
+    const bool two = r.y != 0u;
+    const float w0 = (two ? a : a + b) * scale, w1 = (two ? b : 0.0f) * scale;
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      const size_t e0 = (size_t)(r.x + j * p.GL + lg) * E, e1 = (size_t)(r.x + r.y + j * p.GL + lg) * E;
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        atomicAdd(gf + e0 + e, (unsigned long long)__float2ll_rn(w0 * go[j * E + e]));
+        if (two) atomicAdd(gf + e1 + e, (unsigned long long)__float2ll_rn(w1 * go[j * E + e]));
+      }
+    }
+  }
+}
+
 // Entry emission of the sorted gradients, for the whole warp: every row record of the warp's cells leaves one
 // entry {texel of (row, u0), cell, weight of u0 * inv, weight of u1 * inv} in p.ent and, in p.ent_pos, the
 // position it drew inside its texel's segment.  Slots come from p.ent_count (one atomic per call), positions
@@ -544,7 +572,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_feats_sorted_kernel(con
 // list-phase code at all, which is most of the other one's registers.  Whether the state is usable is decided once
 // per launch (saved_usable); the host launches both instantiations when it has a state to offer and exactly one of
 // them does the work: this one when the state is complete and in its layout, the rebuilding one otherwise.
-template <typename T, int V, bool EMIT, bool CAT, bool SAVED = false>
+// DET: reproducible sums (fbev_deterministic.cuh): p.gfeat / p.gdepth are int64 fixed-point arrays, every addition to
+// them is an integer atomic at the scales in p.det, and the parametric depth gradient takes the per-sample path (the
+// per-record one sums in shared memory with float atomics, whose order inside a warp instruction is not specified).
+template <typename T, int V, bool EMIT, bool CAT, bool SAVED = false, bool DET = false>
 __device__ __forceinline__ void bwd_depth_body(const Dev& p) {
   constexpr int E = Chunk<T>::E;
   if (saved_usable(p) != SAVED) {  // the other instantiation's launch does the work
@@ -575,7 +606,9 @@ __device__ __forceinline__ void bwd_depth_body(const Dev& p) {
   const uint4* fl = reinterpret_cast<const uint4*>(p.feats) + lg;
   const bool legacy = (p.flags & FBEV_BWD_LEGACY_DEPTH) != 0;
   const bool mean_pool = p.pool == FBEV_POOL_MEAN;
-  const bool by_record = (p.flags & FBEV_BWD_DEPTH) != 0 && (!EMIT || p.ent_d != nullptr);
+  const bool by_record = !DET && (p.flags & FBEV_BWD_DEPTH) != 0 && (!EMIT || p.ent_d != nullptr);
+  const float scale_f = DET ? p.det->scale_f : 0.0f, scale_d = DET ? p.det->scale_d : 0.0f;
+  long long* gd64 = reinterpret_cast<long long*>(p.gdepth);
   // categorical: sum equal (texel, bin) neighbours before the atomics.  Pays with six cells per warp (the scan's
   // fixed cost is shared by many samples and the depth tensor is small enough for its atomics to contend);
   // measured a loss with two or three cells per warp on large feature maps
@@ -663,7 +696,10 @@ __device__ __forceinline__ void bwd_depth_body(const Dev& p) {
             float gs[V * E];
 #pragma unroll
             for (int k = 0; k < V * E; ++k) gs[k] = go[k] * inv_cell;
-            add_records_direct<T, V>(p, rec_e, n, gs, p.gfeat + (size_t)lg * E);
+            if (DET)
+              add_records_fixed<T, V>(p, rec_e, n, go, inv_cell, lg, scale_f);
+            else
+              add_records_direct<T, V>(p, rec_e, n, gs, p.gfeat + (size_t)lg * E);
           }
           __syncwarp();
         }
@@ -854,13 +890,22 @@ __device__ __forceinline__ void bwd_depth_body(const Dev& p) {
           float* d10 = d00 + sa.y;
           float* d01 = d00 + sa.z;
           float* d11 = d01 + sa.y;
+          // the same four corners as element indices of the fixed-point array
+          const size_t e00 = (size_t)sa.x, e10 = e00 + sa.y, e01 = e00 + sa.z, e11 = e01 + sa.y;
           if (CAT && !merge_bins) {
             if (active) {
               const int k = (int)sa.w;
-              atomicAdd(d00 + k, v00);
-              atomicAdd(d01 + k, v01);
-              atomicAdd(d10 + k, v10);
-              atomicAdd(d11 + k, v11);
+              if (DET) {
+                det_add(gd64, e00 + k, v00, scale_d);
+                det_add(gd64, e01 + k, v01, scale_d);
+                det_add(gd64, e10 + k, v10, scale_d);
+                det_add(gd64, e11 + k, v11, scale_d);
+              } else {
+                atomicAdd(d00 + k, v00);
+                atomicAdd(d01 + k, v01);
+                atomicAdd(d10 + k, v10);
+                atomicAdd(d11 + k, v11);
+              }
             }
           } else if (CAT) {
             const unsigned key = active ? sa.x + sa.w : 0xffffffffu - (unsigned)lane;  // element index of (texel, bin)
@@ -878,20 +923,38 @@ __device__ __forceinline__ void bwd_depth_body(const Dev& p) {
             const bool tail = active && (lane == 31 || ((headm >> (lane + 1)) & 1u) || !((actm >> (lane + 1)) & 1u));
             if (tail) {
               const int k = (int)sa.w;
-              atomicAdd(d00 + k, v00);
-              atomicAdd(d01 + k, v01);
-              atomicAdd(d10 + k, v10);
-              atomicAdd(d11 + k, v11);
+              if (DET) {  // the run's sums were formed by fixed lanes in a fixed order
+                det_add(gd64, e00 + k, v00, scale_d);
+                det_add(gd64, e01 + k, v01, scale_d);
+                det_add(gd64, e10 + k, v10, scale_d);
+                det_add(gd64, e11 + k, v11, scale_d);
+              } else {
+                atomicAdd(d00 + k, v00);
+                atomicAdd(d01 + k, v01);
+                atomicAdd(d10 + k, v10);
+                atomicAdd(d11 + k, v11);
+              }
             }
           } else if (active) {
-            atomicAdd(d00 + 0, cm * v00);
-            atomicAdd(d00 + 1, cs * v00);
-            atomicAdd(d01 + 0, cm * v01);
-            atomicAdd(d01 + 1, cs * v01);
-            atomicAdd(d10 + 0, cm * v10);
-            atomicAdd(d10 + 1, cs * v10);
-            atomicAdd(d11 + 0, cm * v11);
-            atomicAdd(d11 + 1, cs * v11);
+            if (DET) {
+              det_add(gd64, e00, cm * v00, scale_d);
+              det_add(gd64, e00 + 1, cs * v00, scale_d);
+              det_add(gd64, e01, cm * v01, scale_d);
+              det_add(gd64, e01 + 1, cs * v01, scale_d);
+              det_add(gd64, e10, cm * v10, scale_d);
+              det_add(gd64, e10 + 1, cs * v10, scale_d);
+              det_add(gd64, e11, cm * v11, scale_d);
+              det_add(gd64, e11 + 1, cs * v11, scale_d);
+            } else {
+              atomicAdd(d00 + 0, cm * v00);
+              atomicAdd(d00 + 1, cs * v00);
+              atomicAdd(d01 + 0, cm * v01);
+              atomicAdd(d01 + 1, cs * v01);
+              atomicAdd(d10 + 0, cm * v10);
+              atomicAdd(d10 + 1, cs * v10);
+              atomicAdd(d11 + 0, cm * v11);
+              atomicAdd(d11 + 1, cs * v11);
+            }
           }
         }
         __syncwarp();
@@ -908,13 +971,13 @@ __device__ __forceinline__ void bwd_depth_body(const Dev& p) {
 // The two depth-gradient kernels.  Categorical: 96 registers, five resident blocks per SM (no spills; measured 4 %
 // ahead of 80 registers / six blocks on the benchmark shape, 9 % on cfg4).  Parametric: 80 registers / six blocks,
 // which its shared-memory sample pass prefers (96 registers cost it 8 % on the benchmark shape).
-template <typename T, int V, bool EMIT, bool SAVED = false>
+template <typename T, int V, bool EMIT, bool SAVED = false, bool DET = false>
 __global__ void __maxnreg__(96) bwd_depth_kernel(const __grid_constant__ Dev p) {
-  bwd_depth_body<T, V, EMIT, true, SAVED>(p);
+  bwd_depth_body<T, V, EMIT, true, SAVED, DET>(p);
 }
-template <typename T, int V, bool EMIT, bool SAVED = false>
+template <typename T, int V, bool EMIT, bool SAVED = false, bool DET = false>
 __global__ void __launch_bounds__(kMaxWarps * 32, 3) bwd_depth_param_kernel(const __grid_constant__ Dev p) {
-  bwd_depth_body<T, V, EMIT, false, SAVED>(p);
+  bwd_depth_body<T, V, EMIT, false, SAVED, DET>(p);
 }
 
 // Gradient kernel.  Same decomposition as the forward.  For every accepted sample

@@ -17,7 +17,7 @@
 //     where the two texels of a record coincide                                  =>  |.| <= 4 Z * Wmax * G
 //   a contribution to d_depth is S * inv * w_ij (* d weight / d parameter), S = sum_ij w_ij <g, f_ij> a convex
 //     combination of dot products, |<g, f>| <= ||g|| ||f||, `merged` of them summed before they are added (1 in
-//     the kernel below)                                                        =>  |.| <= merged * Gn * Fn * Dmax
+//     the kernel below, up to a warp's 32 in bwd_depth_kernel)                 =>  |.| <= merged * Gn * Fn * Dmax
 //   with Dmax = 1 (categorical), 1 / (sigma + eps)_min (legacy parametric gradient) or its square (analytic one:
 //   |z| exp(-z^2 / 2) < 1, |z^2 - 1| exp(-z^2 / 2) <= 1, and the Laplace counterparts are below 1 / 2).
 // det_scale_kernel sets scale = 2^(62 - bits - e) with 2^e above the bound and 2^bits above the number of
@@ -27,12 +27,18 @@
 // one, and the sums themselves are exact).  det_finish_kernel converts the sums back.  sigma + eps <= 0 somewhere, NaN
 // or infinite inputs give meaningless (but still repeatable) gradients.
 //
-// One kernel serves every shape the row-record list phase takes (up to 32 cameras, fewer than 2^32 depth elements),
-// any channel count and alignment: one cell per warp, lanes stride over the channels.  Per cell it builds the
-// forward's merged row records and the sample list (row_list_phase), adds the records' feature contributions
+// Two ways lead to the sums.  Large problems whose channel rows are whole 16-byte chunks, given room for the entry
+// lists, run through the default backward's own kernels in their fixed-point instantiations: bwd_depth_kernel<DET>
+// (list phase, entries of the feature gradient, depth contributions as integer atomics), the scatter by texel, and
+// feats_gather_fixed_kernel (integer accumulators in registers, one integer atomic per channel when the texel
+// changes).  The order in which entries land inside a texel's segment still varies from launch to launch; the sums
+// do not.  Everything else takes bwd_det_kernel below: one cell per warp, lanes stride over the channels, any
+// channel count and alignment (up to 32 cameras, fewer than 2^32 depth elements).  Per cell it builds the forward's
+// merged row records and the sample list (row_list_phase), adds the records' feature contributions
 //   d_feats[texel, c] += g_c * inv * weight                                     (flash_bevpool_cuda.cu:665,676-679)
 // computes T = <g, texel> once per record texel and lets one lane per sample form S = sum_ij w_ij T_ij and add
-// the sample's depth contributions, exactly the arithmetic of bwd_depth_kernel.
+// the sample's depth contributions, the arithmetic of bwd_depth_kernel.  Which way a call takes depends on its
+// shape and scratch only, never on timing.
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -43,17 +49,6 @@
 #include "fbev_lists.cuh"
 
 namespace fbev {
-
-// Head of the deterministic scratch (256 bytes reserved).  The maxima are kept as bit patterns: non-negative floats
-// (infinity included) order like unsigned integers, so atomicMax combines them in any order.
-struct DetHeader {
-  unsigned g_max;    // max |g|
-  unsigned g_norm2;  // max over cells of sum_c g_c^2
-  unsigned f_norm2;  // max over texels of sum_c f_c^2
-  unsigned d_max;    // categorical: max |depth value|; parametric: max 1 / (sigma + eps), infinity when that is <= 0
-  float scale_f, inv_f;   // fixed-point scale of d_feats and its inverse
-  float scale_d, inv_d;   // the same for d_depth
-};
 
 // One warp per row: the cells of the upstream gradient, the texels of the features, and the depth tensor in rows of
 // D values (categorical) or (mean, sigma) pairs (parametric).
@@ -111,12 +106,8 @@ __global__ void __launch_bounds__(256) det_bounds_kernel(DetHeader* __restrict__
   }
 }
 
-__device__ __forceinline__ void det_add(long long* base, size_t idx, float v, float scale) {
-  atomicAdd(reinterpret_cast<unsigned long long*>(base) + idx, (unsigned long long)__float2ll_rn(v * scale));
-}
-
-// Dev fields as this kernel reads them: gfeat / gdepth point at int64 arrays of the tensors' shapes, tex_count at
-// the DetHeader; CPW = 1, cpt = 1 (record texel fields are plain texel indices), cap = 32.
+// Dev fields as this kernel reads them: gfeat / gdepth point at int64 arrays of the tensors' shapes, det at the
+// DetHeader; CPW = 1, cpt = 1 (record texel fields are plain texel indices), cap = 32.
 template <typename T>
 __global__ void __launch_bounds__(kMaxWarps * 32) bwd_det_kernel(const __grid_constant__ Dev p) {
   extern __shared__ __align__(16) unsigned char smem[];
@@ -133,7 +124,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32) bwd_det_kernel(const __grid_co
   uint4* recs = reinterpret_cast<uint4*>(wa + 512);
   uint4* samp = recs + row_stride(p.cap);
 
-  DetHeader* hdr = reinterpret_cast<DetHeader*>(p.tex_count);
+  const DetHeader* hdr = p.det;
   long long* gf = reinterpret_cast<long long*>(p.gfeat);
   long long* gd = reinterpret_cast<long long*>(p.gdepth);
   const float scale_f = hdr->scale_f, scale_d = hdr->scale_d;

@@ -21,6 +21,23 @@ namespace fbev {
 
 constexpr unsigned kFull = 0xffffffffu;
 
+// Head of the scratch of the reproducible backward (fbev_deterministic.cuh; 256 bytes reserved).  The maxima are kept
+// as bit patterns: non-negative floats (infinity included) order like unsigned integers, so atomicMax combines them
+// in any order.
+struct DetHeader {
+  unsigned g_max;    // max |g|
+  unsigned g_norm2;  // max over cells of sum_c g_c^2
+  unsigned f_norm2;  // max over texels of sum_c f_c^2
+  unsigned d_max;    // categorical: max |depth value|; parametric: max 1 / (sigma + eps), infinity when that is <= 0
+  float scale_f, inv_f;   // fixed-point scale of d_feats and its inverse
+  float scale_d, inv_d;   // the same for d_depth
+};
+
+// One contribution to a 64-bit fixed-point sum: an integer atomic, so the sum does not depend on the order.
+__device__ __forceinline__ void det_add(long long* base, size_t idx, float v, float scale) {
+  atomicAdd(reinterpret_cast<unsigned long long*>(base) + idx, (unsigned long long)__float2ll_rn(v * scale));
+}
+
 // Kernel-side view of one call (passed by value as a __grid_constant__).
 struct Dev {
   const void* feats;
@@ -74,6 +91,8 @@ struct Dev {
   // host side only: size of the saved state, batch size it was written for, first sample of this launch in it
   unsigned long long saved_bytes;
   int saved_B, saved_b0;
+  // reproducible backward: gfeat / gdepth then point at int64 fixed-point sums instead of float32 (else null)
+  const DetHeader* det;
 };
 
 // Cell (b, y, x) in the output, the upstream gradient and the count tensor, which hold all Y rows of a sample or only

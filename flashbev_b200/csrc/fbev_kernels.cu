@@ -365,7 +365,7 @@ static int forward_t(const Plan& pl, const Dev& d, cudaStream_t st) {
 }
 
 template <typename T>
-static int sort_finish_t(const Plan& pl, const Dev& d, cudaStream_t st);
+static int sort_finish_t(const Plan& pl, const Dev& d, cudaStream_t st, bool fixed = false);
 
 // Feature gradient through the global sort: emission (list phase only), scan, scatter, gather.
 template <typename T>
@@ -384,8 +384,9 @@ static int backward_feats_sort_t(const Plan& pl, const Dev& d_in, cudaStream_t s
 }
 
 // Scan, scatter and gather of the sorted gradients, after a kernel that called emit_entries.
+// fixed: the reproducible backward's gather (64-bit fixed-point sums in d.gfeat).
 template <typename T>
-static int sort_finish_t(const Plan& pl, const Dev& d, cudaStream_t st) {
+static int sort_finish_t(const Plan& pl, const Dev& d, cudaStream_t st, bool fixed) {
   const unsigned texels = (unsigned)((size_t)d.B * d.N * d.H * d.W);
   const int sms = sm_count();
   unsigned* total = d.ent_count + 1;  // second word of the counter block
@@ -403,6 +404,16 @@ static int sort_finish_t(const Plan& pl, const Dev& d, cudaStream_t st) {
   const unsigned run_len = g_tuning.minb == 9 && g_tuning.ty > 0 ? (unsigned)g_tuning.ty : 32u;
   const int gb = sms * (g_tuning.minb == 9 && g_tuning.tx > 0 ? g_tuning.tx : 8);
   const bool pd = d.ent_d_sorted != nullptr;
+  if (fixed) {
+#define FBEV_GATHER_FIXED(VV, GF) launch_after(feats_gather_fixed_kernel<T, VV, GF>, gb, 128, 0, st, d, (const unsigned*)total, run_len)
+    switch (pl.V) {
+      case 1: if (d.out_f32) FBEV_GATHER_FIXED(1, true); else FBEV_GATHER_FIXED(1, false); break;
+      case 2: if (d.out_f32) FBEV_GATHER_FIXED(2, true); else FBEV_GATHER_FIXED(2, false); break;
+      default: if (d.out_f32) FBEV_GATHER_FIXED(4, true); else FBEV_GATHER_FIXED(4, false); break;
+    }
+#undef FBEV_GATHER_FIXED
+    return cudaGetLastError() == cudaSuccess ? FBEV_OK : FBEV_ERR_LAUNCH;
+  }
 #define FBEV_GATHER(VV, GF, PD) launch_after(feats_gather_kernel<T, VV, GF, PD>, gb, 128, 0, st, d, (const unsigned*)total, run_len)
 #define FBEV_GATHER_V(GF, PD)                 \
   switch (pl.V) {                             \
@@ -465,6 +476,22 @@ static int launch_depth_v(const Plan& pld, const Dev& dd, cudaStream_t st) {
   return cat ? launch(bwd_depth_kernel<T, V, EMIT, false>, pld, dd, st, gpt)
              : launch(bwd_depth_param_kernel<T, V, EMIT, false>, pld, dd, st, gpt);
 }
+// The reproducible backward's instantiations: entries for the feature gradient, fixed-point depth sums, lists rebuilt.
+template <typename T, int V>
+static int launch_depth_fixed_v(const Plan& pld, const Dev& dd, cudaStream_t st) {
+  const int gpt = (dd.TX * dd.TY + pld.CPW - 1) / pld.CPW;
+  return dd.mode == FBEV_DEPTH_CATEGORICAL ? launch(bwd_depth_kernel<T, V, true, false, true>, pld, dd, st, gpt)
+                                           : launch(bwd_depth_param_kernel<T, V, true, false, true>, pld, dd, st, gpt);
+}
+template <typename T>
+static int launch_depth_fixed(const Plan& pld, const Dev& dd, cudaStream_t st) {
+  switch (pld.V) {
+    case 1: return launch_depth_fixed_v<T, 1>(pld, dd, st);
+    case 2: return launch_depth_fixed_v<T, 2>(pld, dd, st);
+    default: return launch_depth_fixed_v<T, 4>(pld, dd, st);
+  }
+}
+
 template <typename T, bool EMIT>
 static int launch_depth(const Plan& pld, const Dev& dd, cudaStream_t st) {
   switch (pld.V) {
@@ -714,22 +741,19 @@ int fbev_forward_to_host(const FbevProblem* p, void* out_dev, void* out_host, in
 }
 
 // float32 accumulation targets of the 16-bit types: what fbev_backward cannot do without
-// Deterministic backward: a 256-byte head (DetHeader), 64-bit fixed-point sums for the requested gradients and,
-// for logits, the float32 gradient with respect to the probabilities that the softmax backward consumes.
+// Reproducible backward: a 256-byte head (DetHeader), 64-bit fixed-point sums for both gradients (the kernels always
+// form both; only the requested ones are converted) and, for logits, the float32 gradient with respect to the
+// probabilities that the softmax backward consumes.
 static size_t round256(size_t n) { return ((n + 255) / 256) * 256; }
-static size_t det_scratch_bytes(const FbevProblem* p, int flags) {
+static size_t det_scratch_bytes(const FbevProblem* p) {
   const size_t tex = (size_t)p->B * p->N * p->H * p->W;
-  size_t n = 256;
-  if (flags & FBEV_BWD_FEATS) n += round256(tex * p->C * 8);
-  if (flags & FBEV_BWD_DEPTH) {
-    n += round256(tex * p->D * 8);
-    if (p->mode == FBEV_DEPTH_CATEGORICAL_LOGITS) n += round256(tex * p->D * 4);
-  }
+  size_t n = 256 + round256(tex * p->C * 8) + round256(tex * p->D * 8);
+  if (p->mode == FBEV_DEPTH_CATEGORICAL_LOGITS) n += round256(tex * p->D * 4);
   return n;
 }
 
 static size_t scratch_min_bytes(const FbevProblem* p, int flags) {
-  if (flags & FBEV_BWD_DETERMINISTIC) return det_scratch_bytes(p, flags);
+  if (flags & FBEV_BWD_DETERMINISTIC) return det_scratch_bytes(p);
   if (p->dtype == FBEV_F32) return 0;
   size_t n = 0;
   const size_t tex = (size_t)p->B * p->N * p->H * p->W;
@@ -770,7 +794,7 @@ static size_t sort_capacity(const FbevProblem* p, int flags) {
   return cand < top ? (cand < 4096 ? 4096 : cand) : top;
 }
 static size_t sort_bytes(const FbevProblem* p, int flags) {
-  if (flags & FBEV_BWD_DETERMINISTIC) return 0;  // no sort: fixed-point sums need no order
+  if (flags & FBEV_BWD_DETERMINISTIC) flags = FBEV_BWD_FEATS;  // entries of the feature gradient only, whatever was asked for
   if (!(flags & FBEV_BWD_FEATS) && !sort_carries_depth(p, flags)) return 0;
   const size_t tex = (size_t)sort_batch_run(p, flags) * p->N * p->H * p->W;
   if (tex >= 0xfffffff0ull || (size_t)p->B * p->Y * p->X >= 0xfffffff0ull) return 0;
@@ -808,31 +832,130 @@ size_t fbev_backward_scratch_bytes(const FbevProblem* p, int flags) {
   return scratch_min_bytes(p, flags) + sort_bytes(p, flags);
 }
 
-// FBEV_BWD_DETERMINISTIC: bounds of the inputs, scale, accumulation launch, conversion (fbev_deterministic.cuh).
+// FBEV_BWD_DETERMINISTIC (fbev_deterministic.cuh): bounds of the inputs, scale, accumulation, conversion.  Shapes the
+// chunked kernels take, given room for the entry lists, accumulate through the default pipeline's kernels in their
+// fixed-point instantiations (list phase + entries + depth sums, scatter, gather); everything else through the
+// one-cell-per-warp kernel.
+struct DetLayout {
+  DetHeader* hdr;
+  long long* gf;
+  long long* gd;
+  float* dprob;          // logits only
+  unsigned char* sort;   // entry lists, or null
+};
+
 extern "C++" {
 template <typename T>
-static int backward_deterministic_t(const FbevProblem* p, Dev d, const Plan& pl, DetHeader* hdr, int shift, void* grad_feats,
-                                    void* grad_depth, float* dprob, size_t nf, size_t nd, cudaStream_t st) {
-  const size_t cells = (size_t)p->B * d.out_rows * p->X, texels = (size_t)p->B * p->N * p->H * p->W;
+static int backward_deterministic_t(const FbevProblem* p, const void* grad_out, void* grad_feats, void* grad_depth,
+                                    const DetLayout& L, int flags, cudaStream_t st) {
+  const size_t tex_sample = (size_t)p->N * p->H * p->W, tex_all = tex_sample * p->B;
+  const size_t nf = tex_all * p->C, nd = tex_all * p->D;
+  const size_t out_rows = p->compact_rows ? (size_t)(p->y_end - p->y_begin) : (size_t)p->Y;
+  const size_t es = elem_size(p->dtype), eso = elem_size(p->out_dtype);
   const bool cat = is_categorical(p->mode);
-  det_bounds_kernel<T><<<sm_count() * 8, 256, 0, st>>>(hdr, d.gout, d.out_f32, cells, reinterpret_cast<const T*>(p->image_feats),
-                                                       texels, p->C, reinterpret_cast<const T*>(p->depth), p->D, cat ? 1 : 0,
+  const int work = (flags & FBEV_BWD_LEGACY_DEPTH) | FBEV_BWD_FEATS | FBEV_BWD_DEPTH;  // both gradients are always formed
+  const int sort_flags = FBEV_BWD_FEATS;
+  // 2^bits above the number of contributions one element can receive: four corners of every candidate of its camera
+  const unsigned long long cnt = 4ull * (unsigned long long)(p->y_end - p->y_begin) * p->X * p->Z;
+  int bits = 0;
+  while (bits < 48 && (1ull << bits) < cnt) ++bits;
+  const int shift = 62 - bits;
+
+  // which way: the plan of the first run of samples decides for all of them
+  const int run = L.sort != nullptr ? sort_batch_run(p, sort_flags) : p->B;
+  bool fast = false;
+  if (L.sort != nullptr) {
+    FbevProblem q = *p;
+    q.B = run < p->B ? run : p->B;
+    Dev probe;
+    fill_dev(&q, probe);
+    const Plan plf = make_plan(&q, probe, false, q.image_feats, grad_out, L.gf, !cat);
+    fast = plf.chunked;
+  }
+
+  det_bounds_kernel<T><<<sm_count() * 8, 256, 0, st>>>(L.hdr, grad_out, (p->out_dtype == FBEV_F32 && p->dtype != FBEV_F32) ? 1 : 0,
+                                                       (size_t)p->B * out_rows * p->X, reinterpret_cast<const T*>(p->image_feats),
+                                                       tex_all, p->C, reinterpret_cast<const T*>(p->depth), p->D, cat ? 1 : 0,
                                                        p->epsilon);
   if (cudaGetLastError() != cudaSuccess) return FBEV_ERR_LAUNCH;
-  const int kind = p->mode == FBEV_DEPTH_CATEGORICAL_LOGITS ? 1 : (cat ? 0 : ((d.flags & FBEV_BWD_LEGACY_DEPTH) ? 3 : 2));
-  det_scale_kernel<<<1, 32, 0, st>>>(hdr, shift, p->Z, kind, 1);
+  const int kind = p->mode == FBEV_DEPTH_CATEGORICAL_LOGITS ? 1 : (cat ? 0 : ((flags & FBEV_BWD_LEGACY_DEPTH) ? 3 : 2));
+  // the chunked depth kernel sums up to a warp's worth of equal (texel, bin) neighbours before it adds them
+  det_scale_kernel<<<1, 32, 0, st>>>(L.hdr, shift, p->Z, kind, fast ? 32 : 1);
   if (cudaGetLastError() != cudaSuccess) return FBEV_ERR_LAUNCH;
-  int rc = launch(bwd_det_kernel<T>, pl, d, st);
-  if (rc != FBEV_OK) return rc;
-  const long long* gf = reinterpret_cast<const long long*>(d.gfeat);
-  const long long* gd = reinterpret_cast<const long long*>(d.gdepth);
-  const size_t na = (d.flags & FBEV_BWD_FEATS) ? nf : 0, nb = (d.flags & FBEV_BWD_DEPTH) ? nd : 0;
+
+  if (!fast) {
+    Dev d;
+    fill_dev(p, d);
+    d.saved = nullptr;
+    d.gout = grad_out;
+    d.flags = work;
+    d.gfeat = reinterpret_cast<float*>(L.gf);   // read as int64 arrays by the kernel
+    d.gdepth = reinterpret_cast<float*>(L.gd);
+    d.det = L.hdr;
+    d.GL = 32;
+    d.CPW = 1;
+    d.cpt = 1;  // record texel fields are plain texel indices
+    d.cap = 32;
+    d.TX = 8;
+    d.TY = 4;
+    d.tiles_x = (p->X + d.TX - 1) / d.TX;
+    d.tiles_y = (p->y_end - p->y_begin + d.TY - 1) / d.TY;
+    Plan pl{};
+    pl.chunked = false;
+    pl.GL = 32;
+    pl.CPW = 1;
+    pl.warps = kMaxWarps;
+    pl.cap = d.cap;
+    pl.smem = header_bytes(p->N) + (size_t)pl.warps * depth_warp_bytes(1, pl.cap);
+    pl.blocks = d.tiles_x * d.tiles_y * p->B;
+    const int rc = launch(bwd_det_kernel<T>, pl, d, st);
+    if (rc != FBEV_OK) return rc;
+  } else {
+    const size_t tex_run = (size_t)run * tex_sample;
+    const size_t cnt_bytes = round256((tex_run + 1) * 4);
+    for (int b0 = 0; b0 < p->B; b0 += run) {
+      FbevProblem q = *p;  // the samples [b0, b0 + run) as a problem of their own
+      q.B = p->B - b0 < run ? p->B - b0 : run;
+      q.image_feats = reinterpret_cast<const unsigned char*>(p->image_feats) + (size_t)b0 * tex_sample * p->C * es;
+      q.depth = reinterpret_cast<const unsigned char*>(p->depth) + (size_t)b0 * tex_sample * p->D * es;
+      q.projection = p->projection + (size_t)b0 * p->N * p->proj_stride;
+      q.feature_size = p->feature_size + (size_t)b0 * p->N * 2;
+      if (p->mode == FBEV_DEPTH_CATEGORICAL_LOGITS) q.depth_stats = p->depth_stats + (size_t)b0 * tex_sample * 2;
+      const void* gout = reinterpret_cast<const unsigned char*>(grad_out) + (size_t)b0 * out_rows * p->X * p->C * eso;
+      Dev d;
+      fill_dev(&q, d);
+      d.saved = nullptr;
+      d.gout = gout;
+      d.flags = work;
+      d.gfeat = reinterpret_cast<float*>(L.gf + (size_t)b0 * tex_sample * p->C);
+      d.gdepth = reinterpret_cast<float*>(L.gd + (size_t)b0 * tex_sample * p->D);
+      d.det = L.hdr;
+      if (cudaMemsetAsync(L.sort, 0, cnt_bytes + 256, st) != cudaSuccess) {
+        cudaGetLastError();
+        return FBEV_ERR_LAUNCH;
+      }
+      d.tex_count = reinterpret_cast<unsigned*>(L.sort);
+      d.ent_count = reinterpret_cast<unsigned*>(L.sort + cnt_bytes);
+      d.ent_cap = (unsigned)sort_capacity(p, sort_flags);
+      d.ent = reinterpret_cast<uint4*>(L.sort + cnt_bytes + 256);
+      d.ent_sorted = d.ent + d.ent_cap;
+      d.ent_pos = reinterpret_cast<unsigned*>(d.ent_sorted + d.ent_cap);
+      Plan pld = make_plan(&q, d, false, q.image_feats, gout, d.gfeat, !cat);
+      if (!pld.chunked) return FBEV_ERR_RANGE;  // cannot happen: a slice of the batch fits where the first run did
+      pld.cap = d.cap = 16;  // as the default backward: half the shared memory, twice the resident warps
+      pld.smem = header_bytes(d.N) + (size_t)pld.warps * depth_warp_bytes(pld.CPW, pld.cap);
+      int rc = launch_depth_fixed<T>(pld, d, st);
+      if (rc == FBEV_OK) rc = sort_finish_t<T>(pld, d, st, true);
+      if (rc != FBEV_OK) return rc;
+    }
+  }
+  const size_t na = (flags & FBEV_BWD_FEATS) ? nf : 0, nb = (flags & FBEV_BWD_DEPTH) ? nd : 0;
   const size_t want = (na + nb + 255) / 256;
   const int blocks = (int)(want < (size_t)sm_count() * 16 ? (want ? want : 1) : (size_t)sm_count() * 16);
-  if (dprob != nullptr)
-    det_finish_kernel<T, float><<<blocks, 256, 0, st>>>(hdr, gf, reinterpret_cast<T*>(grad_feats), na, gd, dprob, nb);
+  if (L.dprob != nullptr)
+    det_finish_kernel<T, float><<<blocks, 256, 0, st>>>(L.hdr, L.gf, reinterpret_cast<T*>(grad_feats), na, L.gd, L.dprob, nb);
   else
-    det_finish_kernel<T, T><<<blocks, 256, 0, st>>>(hdr, gf, reinterpret_cast<T*>(grad_feats), na, gd,
+    det_finish_kernel<T, T><<<blocks, 256, 0, st>>>(L.hdr, L.gf, reinterpret_cast<T*>(grad_feats), na, L.gd,
                                                     reinterpret_cast<T*>(grad_depth), nb);
   return cudaGetLastError() == cudaSuccess ? FBEV_OK : FBEV_ERR_LAUNCH;
 }
@@ -844,73 +967,43 @@ static int backward_deterministic(const FbevProblem* p, const void* grad_out, vo
   const size_t nf = tex_all * p->C, nd = tex_all * p->D;
   // the row-record list phase keeps the visible cameras in a 32-bit mask and 32-bit depth element indices
   if (p->N > 32 || (unsigned long long)nd >= (1ull << 32)) return FBEV_ERR_RANGE;
-  const size_t need = det_scratch_bytes(p, flags);
+  const size_t need = det_scratch_bytes(p);
   if (scratch == nullptr || scratch_bytes < need || ((uintptr_t)scratch % 256)) return FBEV_ERR_SCRATCH;
   const bool logits = p->mode == FBEV_DEPTH_CATEGORICAL_LOGITS;
   unsigned char* s = reinterpret_cast<unsigned char*>(scratch);
-  DetHeader* hdr = reinterpret_cast<DetHeader*>(s);
+  DetLayout L{};
+  L.hdr = reinterpret_cast<DetHeader*>(s);
   s += 256;
-  long long* gf = nullptr;
-  long long* gd = nullptr;
-  float* dprob = nullptr;
-  if (flags & FBEV_BWD_FEATS) {
-    gf = reinterpret_cast<long long*>(s);
-    s += round256(nf * 8);
-  }
-  if (flags & FBEV_BWD_DEPTH) {
-    gd = reinterpret_cast<long long*>(s);
-    s += round256(nd * 8);
-    if (logits) dprob = reinterpret_cast<float*>(s);
-  }
-  const size_t clear = 256 + (gf ? round256(nf * 8) : 0) + (gd ? round256(nd * 8) : 0);
-  if (cudaMemsetAsync(scratch, 0, clear, st) != cudaSuccess) {
+  L.gf = reinterpret_cast<long long*>(s);
+  s += round256(nf * 8);
+  L.gd = reinterpret_cast<long long*>(s);
+  s += round256(nd * 8);
+  if (logits && (flags & FBEV_BWD_DEPTH)) L.dprob = reinterpret_cast<float*>(s);
+  // the entry lists of the sort by texel lie beyond, when the caller gave that much and the problem is large enough
+  // for three more launches to pay (the default path's rule)
+  const size_t sortb = sort_bytes(p, flags);
+  const bool want_sort = g_tuning.minb == 7 || g_tuning.minb == 8 ||
+                         (g_tuning.minb == 0 && (size_t)p->B * p->X * (size_t)(p->y_end - p->y_begin) * p->N * p->Z >= 200000);
+  if (want_sort && sortb != 0 && scratch_bytes >= need + sortb) L.sort = reinterpret_cast<unsigned char*>(scratch) + need;
+  if (cudaMemsetAsync(scratch, 0, 256 + round256(nf * 8) + round256(nd * 8), st) != cudaSuccess) {
     cudaGetLastError();
     return FBEV_ERR_LAUNCH;
   }
-  Dev d;
-  fill_dev(p, d);
-  d.saved = nullptr;
-  d.gout = grad_out;
-  d.flags = flags;
-  d.gfeat = reinterpret_cast<float*>(gf);   // the kernel reads these two as int64 arrays
-  d.gdepth = reinterpret_cast<float*>(gd);
-  d.tex_count = reinterpret_cast<unsigned*>(hdr);
-  d.GL = 32;
-  d.CPW = 1;
-  d.cpt = 1;  // record texel fields are plain texel indices
-  d.cap = 32;
-  d.TX = 8;
-  d.TY = 4;
-  d.tiles_x = (p->X + d.TX - 1) / d.TX;
-  d.tiles_y = (p->y_end - p->y_begin + d.TY - 1) / d.TY;
-  Plan pl{};
-  pl.chunked = false;
-  pl.GL = 32;
-  pl.CPW = 1;
-  pl.warps = kMaxWarps;
-  pl.cap = d.cap;
-  pl.smem = header_bytes(p->N) + (size_t)pl.warps * depth_warp_bytes(1, pl.cap);
-  pl.blocks = d.tiles_x * d.tiles_y * p->B;
-  // 2^bits above the number of contributions one element can receive: four corners of every candidate of its camera
-  const unsigned long long cnt = 4ull * (unsigned long long)(p->y_end - p->y_begin) * p->X * p->Z;
-  int bits = 0;
-  while (bits < 48 && (1ull << bits) < cnt) ++bits;
-  const int shift = 62 - bits;
   int rc;
   switch (p->dtype) {
-    case FBEV_F32: rc = backward_deterministic_t<float>(p, d, pl, hdr, shift, grad_feats, grad_depth, dprob, nf, nd, st); break;
-    case FBEV_BF16: rc = backward_deterministic_t<__nv_bfloat16>(p, d, pl, hdr, shift, grad_feats, grad_depth, dprob, nf, nd, st); break;
-    default: rc = backward_deterministic_t<__half>(p, d, pl, hdr, shift, grad_feats, grad_depth, dprob, nf, nd, st); break;
+    case FBEV_F32: rc = backward_deterministic_t<float>(p, grad_out, grad_feats, grad_depth, L, flags, st); break;
+    case FBEV_BF16: rc = backward_deterministic_t<__nv_bfloat16>(p, grad_out, grad_feats, grad_depth, L, flags, st); break;
+    default: rc = backward_deterministic_t<__half>(p, grad_out, grad_feats, grad_depth, L, flags, st); break;
   }
   if (rc != FBEV_OK) return rc;
-  if (dprob != nullptr) {
+  if (L.dprob != nullptr) {
     // dL/dprob -> dL/dlogit through the folded softmax: one thread order per texel, nothing is drawn
     const unsigned blocks = (unsigned)((tex_all * 32 + 255) / 256);
     const float2* stats = reinterpret_cast<const float2*>(p->depth_stats);
     switch (p->dtype) {
-      case FBEV_F32: launch_after(softmax_bwd_kernel<float>, blocks, 256, 0, st, reinterpret_cast<const float*>(p->depth), stats, (const float*)dprob, reinterpret_cast<float*>(grad_depth), tex_all, p->D); break;
-      case FBEV_BF16: launch_after(softmax_bwd_kernel<__nv_bfloat16>, blocks, 256, 0, st, reinterpret_cast<const __nv_bfloat16*>(p->depth), stats, (const float*)dprob, reinterpret_cast<__nv_bfloat16*>(grad_depth), tex_all, p->D); break;
-      default: launch_after(softmax_bwd_kernel<__half>, blocks, 256, 0, st, reinterpret_cast<const __half*>(p->depth), stats, (const float*)dprob, reinterpret_cast<__half*>(grad_depth), tex_all, p->D); break;
+      case FBEV_F32: launch_after(softmax_bwd_kernel<float>, blocks, 256, 0, st, reinterpret_cast<const float*>(p->depth), stats, (const float*)L.dprob, reinterpret_cast<float*>(grad_depth), tex_all, p->D); break;
+      case FBEV_BF16: launch_after(softmax_bwd_kernel<__nv_bfloat16>, blocks, 256, 0, st, reinterpret_cast<const __nv_bfloat16*>(p->depth), stats, (const float*)L.dprob, reinterpret_cast<__nv_bfloat16*>(grad_depth), tex_all, p->D); break;
+      default: launch_after(softmax_bwd_kernel<__half>, blocks, 256, 0, st, reinterpret_cast<const __half*>(p->depth), stats, (const float*)L.dprob, reinterpret_cast<__half*>(grad_depth), tex_all, p->D); break;
     }
     if (cudaGetLastError() != cudaSuccess) return FBEV_ERR_LAUNCH;
   }

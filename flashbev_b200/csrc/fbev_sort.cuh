@@ -234,4 +234,98 @@ __global__ void __launch_bounds__(128, (PDEPTH || GF32) ? 3 : 4)
   grid_dependency_trigger();
 }
 
+// The gather for the reproducible backward: the same walk over the grouped entries, but every product weight * g is
+// turned into a 64-bit fixed-point integer before it is added, in registers and then (one integer atomic per channel
+// when the texel changes or the run ends) in p.gfeat, which holds int64 sums.  The position an entry drew inside its
+// texel's segment and the way segments split into runs change from launch to launch; integer sums do not care.
+template <typename T, int V, bool GF32>
+__global__ void __launch_bounds__(128, 2)
+    feats_gather_fixed_kernel(const __grid_constant__ Dev p, const unsigned* __restrict__ n_entries, unsigned run_len) {
+  constexpr int E = Chunk<T>::E;
+  constexpr int R = (GF32 && E == 8) ? 2 : 1;  // 16-byte loads per chunk of E channels
+  constexpr int U = 2;                         // entries in flight per lane
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int g = lane / p.GL, lg = lane - g * p.GL;
+  grid_dependency_wait();
+  if (g >= p.CPW) {
+    grid_dependency_trigger();
+    return;
+  }
+  const unsigned n = *n_entries;
+  const unsigned cpt = (unsigned)(p.GL * V);
+  const unsigned groups = gridDim.x * nwarps * p.CPW;
+  const uint4* gl = reinterpret_cast<const uint4*>(p.gout) + (size_t)lg * R;
+  const float scale = p.det->scale_f;
+  unsigned long long* gf = reinterpret_cast<unsigned long long*>(p.gfeat);
+  for (unsigned run = (blockIdx.x * nwarps + warp) * p.CPW + g; (unsigned long long)run * run_len < n; run += groups) {
+    const unsigned i0 = run * run_len, i1 = min(i0 + run_len, n);
+    long long acc0[V * E], acc1[V * E];  // sums for texel `cur` and its right neighbour
+    bool any1 = false;
+#pragma unroll
+    for (int k = 0; k < V * E; ++k) acc0[k] = acc1[k] = 0;
+    auto flush = [&](unsigned tex, const long long* acc) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        unsigned long long* d = gf + ((size_t)tex * cpt + lg + j * p.GL) * E;
+#pragma unroll
+        for (int e = 0; e < E; ++e) atomicAdd(d + e, (unsigned long long)acc[j * E + e]);
+      }
+    };
+    unsigned cur = __ldg(&p.ent_sorted[i0].x);
+    for (unsigned i = i0; i < i1; i += U) {
+      uint4 en[U];
+      uint4 q[U][V][R];
+#pragma unroll
+      for (int u = 0; u < U; ++u) en[u] = __ldg(p.ent_sorted + min(i + u, i1 - 1));
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int j = 0; j < V; ++j)
+#pragma unroll
+          for (int r = 0; r < R; ++r) q[u][j][r] = ldg16(gl + ((size_t)en[u].y * cpt + j * p.GL) * R + r);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (i + u >= i1) break;
+        const unsigned t = en[u].x;
+        if (t != cur) {
+          flush(cur, acc0);
+          if (t == cur + 1u) {
+#pragma unroll
+            for (int k = 0; k < V * E; ++k) acc0[k] = acc1[k];
+          } else {
+            if (any1) flush(cur + 1u, acc1);
+#pragma unroll
+            for (int k = 0; k < V * E; ++k) acc0[k] = 0;
+          }
+#pragma unroll
+          for (int k = 0; k < V * E; ++k) acc1[k] = 0;
+          any1 = false;
+          cur = t;
+        }
+        // weight times a power of two is exact; every term rounds to an integer by itself
+        const float w0 = __uint_as_float(en[u].z) * scale, w1 = __uint_as_float(en[u].w) * scale;
+        any1 = any1 || w1 != 0.0f;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          float f[E];
+          if (R == 2) {
+            Chunk<float>::unpack(q[u][j][0], f);
+            Chunk<float>::unpack(q[u][j][R - 1], f + 4);
+          } else {
+            Chunk<T>::unpack(q[u][j][0], f);
+          }
+#pragma unroll
+          for (int e = 0; e < E; ++e) {
+            acc0[j * E + e] += __float2ll_rn(w0 * f[e]);
+            acc1[j * E + e] += __float2ll_rn(w1 * f[e]);
+          }
+        }
+      }
+    }
+    flush(cur, acc0);
+    if (any1) flush(cur + 1u, acc1);
+  }
+  grid_dependency_trigger();
+}
+
 }  // namespace fbev

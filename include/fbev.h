@@ -80,13 +80,15 @@ enum {
                                 instead of the analytic one */
   FBEV_BWD_DETERMINISTIC = 8 /* bitwise reproducible gradients: every contribution is added as a 64-bit
                                 fixed-point integer (integer addition does not depend on the order the
-                                warps arrive in), at a power-of-two scale taken from a first, measuring
-                                launch.  Same tolerances as the default path, several times slower.
+                                warps arrive in), at a power-of-two scale taken from bounds of the inputs.
+                                Same tolerances as the default path, slower.
                                 Needs N <= 32 and B*N*H*W*D < 2^32 (FBEV_ERR_RANGE otherwise) and scratch
-                                for every element type: fbev_backward_min_scratch_bytes() with this flag
-                                (256 bytes + 8 per element of each requested gradient, + 4 per depth
-                                element for logits).  The reference has no counterpart: its backward
-                                adds float atomics in arrival order (flash_bevpool_cuda.cu:667-679). */
+                                for every element type: at least fbev_backward_min_scratch_bytes() with
+                                this flag (256 bytes + 8 per element of both gradients, + 4 per depth
+                                element for logits), better fbev_backward_scratch_bytes(), which adds the
+                                entry lists that let large problems run through the sort by texel.  The
+                                reference has no counterpart: its backward adds float atomics in arrival
+                                order (flash_bevpool_cuda.cu:667-679). */
 };
 
 /*

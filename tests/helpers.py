@@ -1,7 +1,9 @@
 """Shared pieces of the parity tests: problem construction for the CPU oracle and the CUDA
 operator from the same seeded inputs, and the error measure the tolerances refer to."""
+import contextlib
 import glob
 import os
+import threading
 
 import numpy as np
 import torch
@@ -10,6 +12,37 @@ from flashbev_b200 import synth
 from oracle import oracle as O
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+
+@contextlib.contextmanager
+def tuning(lib, *values):
+    """fbev_set_tuning(*values) for the calls inside the block, put back to zeros after it.  The tuning is kept per
+    host thread, and autograd normally runs a CUDA operator's backward on a worker thread of its own, which would
+    not see it: inside the block autograd's worker threads are off, so the backward runs on the calling thread
+    (checked with a probe function)."""
+    class _Probe(torch.autograd.Function):
+        ident = None
+
+        @staticmethod
+        def forward(ctx, x):
+            return x.clone()
+
+        @staticmethod
+        def backward(ctx, g):
+            _Probe.ident = threading.get_ident()
+            return g
+
+    with torch.autograd.set_multithreading_enabled(False):
+        if torch.cuda.is_available():
+            x = torch.ones(1, device="cuda", requires_grad=True)
+            _Probe.apply(x).sum().backward()
+            assert _Probe.ident == threading.get_ident(), "autograd ran the backward on another thread"
+        lib.fbev_set_tuning(*values)
+        try:
+            yield
+        finally:
+            lib.fbev_set_tuning(0, 0, 0, 0, 0)
 
 # Tolerances (relative error = max|a-b| / max|b| per tensor):
 TOL_F32 = 1e-5       # float32 kernels vs the float32/float64 oracle

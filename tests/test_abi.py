@@ -122,13 +122,15 @@ def test_backward_scratch_size_and_checks():
     # 16-bit gradients without scratch are refused before anything is launched
     assert lib.fbev_backward(ctypes.byref(p), 256, 256, 256, None, 0, 3, None) == 8   # FBEV_ERR_SCRATCH
     assert lib.fbev_backward(ctypes.byref(p), 256, 256, 256, None, 0, 0, None) == 0   # nothing requested
-    # deterministic backward: 256-byte head + 64-bit fixed-point sums, whatever the element type; no sort lists
+    # deterministic backward: 256-byte head + 64-bit fixed-point sums, whatever the element type
     det = _lib.BWD_DETERMINISTIC
     for dtype in (_lib.BF16, _lib.F32):
         p.dtype = p.out_dtype = dtype
-        assert lib.fbev_backward_min_scratch_bytes(ctypes.byref(p), 3 | det) == 256 + tex * 8 * 8 + tex * 2 * 8
-        assert lib.fbev_backward_scratch_bytes(ctypes.byref(p), 3 | det) == 256 + tex * 8 * 8 + tex * 2 * 8
-        assert lib.fbev_backward_min_scratch_bytes(ctypes.byref(p), 2 | det) == 256 + tex * 2 * 8
+        least = 256 + tex * 8 * 8 + tex * 2 * 8   # both gradients are always formed
+        assert lib.fbev_backward_min_scratch_bytes(ctypes.byref(p), 3 | det) == least
+        assert lib.fbev_backward_min_scratch_bytes(ctypes.byref(p), 2 | det) == least
+        # + the entry lists of the feature gradient's sort (no depth values ride on them in this mode)
+        assert lib.fbev_backward_scratch_bytes(ctypes.byref(p), 3 | det) == least + 256 + 256 + 4096 * 36
         assert lib.fbev_backward(ctypes.byref(p), 256, 256, 256, None, 0, 3 | det, None) == 8
 
 

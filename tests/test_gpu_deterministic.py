@@ -1,5 +1,10 @@
 """Bitwise reproducible backward (``deterministic=True`` -> FBEV_BWD_DETERMINISTIC of the C ABI).
 
+Two ways lead to the fixed-point sums: large problems whose channel rows are whole 16-byte chunks go through the
+default pipeline's kernels (list phase + entries, sort by texel, gather) in their fixed-point instantiations, all
+others through a one-cell-per-warp kernel.  The small shapes below take the second way by themselves and the first
+one under the tuning switch that forces the sort.
+
 Two things are checked on the GPU: the gradients of repeated runs are equal bit for bit (the default path adds
 float32 values in arrival order and is not), and they meet the same bars against the CPU oracle as the default
 path: float32 within 1e-5, 16-bit types within 2e-3 beyond their one rounding, as max|a-b| / max|b| per tensor.
@@ -14,7 +19,7 @@ from flashbev_b200 import _lib, flash_bevpool, synth
 from flashbev_b200.flash_bevpool import DepthSpec, make_problem
 from oracle import oracle as O
 from tests.helpers import (SMALL, TOL_F32, TOL_LOWP, host_threads, op_kwargs, oracle_problem, rel_err,
-                           rel_err_quantised, to_device)
+                           rel_err_quantised, to_device, tuning)
 
 pytestmark = pytest.mark.gpu
 
@@ -59,6 +64,33 @@ def deterministic_case(w, mode, device, report, pool=None, dtype=None, legacy=Fa
 @pytest.mark.parametrize("pool", ["mean", "sum"])
 def test_small_shapes_every_mode_and_pooling(cuda_device, parity_report, mode, pool):
     deterministic_case(SMALL, mode, cuda_device, parity_report, pool=pool)
+
+
+@pytest.mark.parametrize("mode", ["gaussian", "laplace", "categorical"])
+def test_small_shapes_through_the_sorted_pipeline(cuda_device, parity_report, mode):
+    lib = _lib.load()
+    with tuning(lib, 0, 0, 0, 0, 7):
+        deterministic_case(SMALL, mode, cuda_device, parity_report, pool="mean")
+        deterministic_case(SMALL, mode, cuda_device, parity_report, pool="sum", dtype="bf16")
+        deterministic_case(SMALL, mode, cuda_device, parity_report, legacy=mode != "categorical", threshold=1e-3, dtype="fp16")
+
+
+def test_full_entry_list_changes_no_bit(cuda_device):
+    """With room for only 4096 entries nearly every warp finds the list full and adds its records itself; which
+    warps do depends on the order they arrive in.  Every term is formed the same way on both routes, so the
+    gradients must equal those of a run with room for all entries, bit for bit, and each other."""
+    lib = _lib.load()
+    w = synth.workload("cfg3", B=2, X=96, Y=80)
+    for mode, dtype in (("categorical", "bf16"), ("laplace", "fp32")):
+        inp = synth.make_inputs(w, "categorical" if mode == "categorical" else "parametric", dtype=dtype)
+        go = synth.upstream_grad(w).to(inp["image_feats"].dtype)
+        kw = dict(op_kwargs(w, mode), deterministic=True)
+        with tuning(lib, 0, 0, 0, 0, 7):
+            roomy = grads(inp, cuda_device, go, **kw)
+        with tuning(lib, 0, 0, 0, 0, 8):
+            tight = [grads(inp, cuda_device, go, **kw) for _ in range(2)]
+        for gf, gd in tight:
+            assert torch.equal(gf, roomy[0]) and torch.equal(gd, roomy[1]), mode
 
 
 def test_legacy_depth_gradient_threshold_and_row_range(cuda_device, parity_report):
@@ -141,8 +173,8 @@ def test_more_than_32_cameras_are_refused(cuda_device):
 
 
 def test_scratch_sizes_of_the_c_abi(cuda_device):
-    """256 bytes + 8 per element of each requested gradient (rounded up to 256), + 4 per depth element for logits;
-    less than that is refused."""
+    """Least scratch: 256 bytes + 8 per element of both gradients (rounded up to 256 each; both are always formed),
+    + 4 per depth element for logits; the entry lists of the sort come on top; less than the least is refused."""
     w = SMALL
     inp = to_device(synth.make_inputs(w, "categorical"), cuda_device)
     lib = _lib.load()
@@ -151,14 +183,26 @@ def test_scratch_sizes_of_the_c_abi(cuda_device):
                            DepthSpec(2, depth_bin_range=(w.d0, w.delta)), 1e-6, 0.0)
     tex = w.B * w.N * w.H * w.W
     r256 = lambda n: (n + 255) // 256 * 256  # noqa: E731
-    both = _lib.BWD_FEATS | _lib.BWD_DEPTH | _lib.BWD_DETERMINISTIC
-    assert lib.fbev_backward_min_scratch_bytes(ctypes.byref(p), both) == 256 + r256(tex * w.C * 8) + r256(tex * w.D * 8)
-    assert lib.fbev_backward_scratch_bytes(ctypes.byref(p), both) == lib.fbev_backward_min_scratch_bytes(ctypes.byref(p), both)
+    least = 256 + r256(tex * w.C * 8) + r256(tex * w.D * 8)
+    for flags in (_lib.BWD_FEATS | _lib.BWD_DEPTH, _lib.BWD_FEATS, _lib.BWD_DEPTH):
+        assert lib.fbev_backward_min_scratch_bytes(ctypes.byref(p), flags | _lib.BWD_DETERMINISTIC) == least
+        lists = lib.fbev_backward_scratch_bytes(ctypes.byref(p), _lib.BWD_FEATS) \
+            - lib.fbev_backward_min_scratch_bytes(ctypes.byref(p), _lib.BWD_FEATS)
+        assert lib.fbev_backward_scratch_bytes(ctypes.byref(p), flags | _lib.BWD_DETERMINISTIC) == least + lists
     only_f = _lib.BWD_FEATS | _lib.BWD_DETERMINISTIC
-    assert lib.fbev_backward_min_scratch_bytes(ctypes.byref(p), only_f) == 256 + r256(tex * w.C * 8)
     go = synth.upstream_grad(w).to(cuda_device)
     gf = torch.empty_like(inp["image_feats"])
     small = torch.empty(1024, dtype=torch.uint8, device=cuda_device)
     rc = lib.fbev_backward(ctypes.byref(p), go.data_ptr(), gf.data_ptr(), None, small.data_ptr(), small.numel(), only_f,
                            torch.cuda.current_stream().cuda_stream)
-    assert rc == _lib.ERR_SCRATCH, _lib.load().fbev_strerror(rc)
+    assert rc == _lib.ERR_SCRATCH, _lib.strerror(rc)
+    # the least scratch alone is enough (one-cell-per-warp kernel), and gives what the full scratch gives on this
+    # small shape, which takes that kernel anyway
+    ok = torch.empty(least, dtype=torch.uint8, device=cuda_device)
+    rc = lib.fbev_backward(ctypes.byref(p), go.data_ptr(), gf.data_ptr(), None, ok.data_ptr(), ok.numel(), only_f,
+                           torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, _lib.strerror(rc)
+    ref = grads(synth.make_inputs(w, "categorical"), cuda_device, synth.upstream_grad(w),
+                **dict(op_kwargs(w, "categorical"), deterministic=True))[0]
+    torch.cuda.synchronize()
+    assert torch.equal(gf, ref)

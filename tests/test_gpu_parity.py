@@ -16,7 +16,7 @@ from flashbev_b200 import _lib, debug_indices, flash_bevpool, forward_with_count
 from flashbev_b200.flash_bevpool import status_word
 from oracle import oracle as O
 from tests.helpers import (SMALL, TOL_DENSE, TOL_F32, TOL_LOWP, golden_files, golden_inputs, golden_problem,
-                           host_threads, inputs_for, op_kwargs, oracle_problem, rel_err, rel_err_quantised, to_device)
+                           host_threads, inputs_for, op_kwargs, oracle_problem, rel_err, rel_err_quantised, to_device, tuning)
 
 pytestmark = pytest.mark.gpu
 
@@ -66,12 +66,9 @@ def test_random_shapes_forward_and_backward(cuda_device, seed):
     pool = ["mean", "sum"][int(rng.integers(0, 2))]
     threshold = [0.0, 1e-3][int(rng.integers(0, 2))]
     lib = _lib.load()
-    try:
-        lib.fbev_set_tuning(0, 0, 0, 0, 7 if seed & 1 else 0)
+    with tuning(lib, 0, 0, 0, 0, 7 if seed & 1 else 0):
         run_case(w, mode, cuda_device, threshold=threshold, pool=pool)
         backward_case(w, mode, cuda_device, pool=pool, threshold=threshold)
-    finally:
-        lib.fbev_set_tuning(0, 0, 0, 0, 0)
 
 
 @pytest.mark.parametrize("mode", ["gaussian", "laplace", "categorical"])
@@ -313,8 +310,7 @@ def test_backward_kernel_variants_agree_with_the_oracle(cuda_device, variant):
     lib = _lib.load()
     tall = synth.Workload("tall", B=1, N=6, C=16, H=8, W=22, D=24, X=30, Y=30, Z=40, xy_extent=30.0, d0=1.0, delta=1.5,
                           dtype="fp32", seed=32)
-    try:
-        lib.fbev_set_tuning(0, 0, 0, 0, variant)
+    with tuning(lib, 0, 0, 0, 0, variant):
         for mode in ("categorical", "laplace", "gaussian"):
             backward_case(SMALL, mode, cuda_device, pool="mean")
             backward_case(SMALL, mode, cuda_device, pool="sum", dtype="bf16")
@@ -326,8 +322,6 @@ def test_backward_kernel_variants_agree_with_the_oracle(cuda_device, variant):
         backward_case(SMALL, "laplace", cuda_device, dtype="fp16", out_f32=True, pool="mean")
         backward_case(SMALL, "laplace", cuda_device, legacy=True)
         backward_case(SMALL, "gaussian", cuda_device, legacy=True, threshold=1e-3, dtype="bf16")
-    finally:
-        lib.fbev_set_tuning(0, 0, 0, 0, 0)
 
 
 @pytest.mark.parametrize("save_lists", [True, False])
