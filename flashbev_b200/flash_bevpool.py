@@ -363,8 +363,9 @@ def flash_bevpool(image_feats, depth_params, projection_matrices, feature_size, 
         pool: "mean" (default for 0/1, the reference's) or "sum" (default for 2).
         depth_bin_range: (first bin edge, bin width) of the categorical mode.
         legacy_depth_grad: parametric modes only; reproduce the reference CUDA kernel's depth gradient.
-        deterministic: backward with bitwise reproducible gradients (fixed-point sums instead of float atomics;
-            several times slower, same tolerances; at most 32 cameras).  The forward is reproducible anyway.
+        deterministic: backward with bitwise reproducible gradients (fixed-point sums instead of float sums in
+            arrival order; 1.4 to 1.8 times the default backward's time on the benchmark shapes, same tolerances; at
+            most 32 cameras).  The forward is reproducible anyway.
         y_range: (begin, end) BEV rows to compute; the other rows of the output are zero.
         compact_rows: with ``y_range``: the result (and the upstream gradient of its backward) holds only those
             rows, [B, end - begin, X, C]: a row shard that stays a shard.
