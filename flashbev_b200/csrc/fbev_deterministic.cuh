@@ -20,7 +20,7 @@
 //     the kernel below, up to a warp's 32 in bwd_depth_kernel)                 =>  |.| <= merged * Gn * Fn * Dmax
 //   with Dmax = 1 (categorical), 1 / (sigma + eps)_min (legacy parametric gradient) or its square (analytic one:
 //   |z| exp(-z^2 / 2) < 1, |z^2 - 1| exp(-z^2 / 2) <= 1, and the Laplace counterparts are below 1 / 2).
-// det_scale_kernel sets scale = 2^(62 - bits - e) with 2^e above the bound and 2^bits above the number of
+// det_set_scales (run by the last block of det_bounds_kernel) sets scale = 2^(62 - bits - e) with 2^e above the bound and 2^bits above the number of
 // contributions one element can receive (4 * rows * X * Z: every candidate of the texel's camera, four corners
 // each), so no sum can leave 63 bits.  The bounds are loose by a few binary digits, the count by many; what is left
 // is still finer than float32 (on the benchmark shapes a contribution keeps more than 30 digits below the largest
@@ -50,36 +50,86 @@
 
 namespace fbev {
 
+// The bounds of the file comment -> scale = 2^(shift - e) with 2^e above the bound; shift = 62 - bits of the
+// contribution count.  depth_kind: 0 categorical probabilities, 1 logits (probabilities <= 1), 2 parametric with
+// the analytic depth gradient, 3 parametric with the legacy one.  merged: how many depth contributions a kernel
+// sums before it adds them.  One thread.
+__device__ inline void det_set_scales(DetHeader* hdr, int shift, int Z, int depth_kind, int merged) {
+  const volatile unsigned* mx = &hdr->g_max;  // the four maxima, as the other blocks' atomics left them in memory
+  const double g = (double)__uint_as_float(mx[0]);
+  const double gn = sqrt((double)__uint_as_float(mx[1])), fn = sqrt((double)__uint_as_float(mx[2]));
+  const double d = (double)__uint_as_float(mx[3]);
+  const double slack = 1.01;  // float32 rounding inside the reductions and the kernels' own products
+  const double wmax = depth_kind == 1 ? 1.0 : d;
+  const double dpar = depth_kind <= 1 ? 1.0 : (depth_kind == 3 ? d : d * d);
+  const double bound[2] = {4.0 * (double)Z * wmax * g * slack, (double)merged * gn * fn * dpar * slack};
+  float scale[2], inv[2];
+  for (int k = 0; k < 2; ++k) {
+    int e = 0;
+    const double m = bound[k];
+    if (m > 0.0 && m < 1.0e300) (void)frexp(m, &e);  // m = f * 2^e, 0.5 <= f < 1
+    if (!(m < 1.0e300)) e = 1024;
+    int s = shift - e;
+    s = s > 100 ? 100 : (s < -100 ? -100 : s);  // both the scale and its inverse stay normal float32 numbers
+    scale[k] = ldexpf(1.0f, s);
+    inv[k] = ldexpf(1.0f, -s);
+  }
+  hdr->scale_f = scale[0];
+  hdr->inv_f = inv[0];
+  hdr->scale_d = scale[1];
+  hdr->inv_d = inv[1];
+}
+
 // One warp per row: the cells of the upstream gradient, the texels of the features, and the depth tensor in rows of
-// D values (categorical) or (mean, sigma) pairs (parametric).
+// D values (categorical) or (mean, sigma) pairs (parametric).  A block combines its warps' maxima in shared memory
+// and adds them with one atomic each (thousands of warps firing at four words would queue up at the L2); the block
+// that finds all others done turns the maxima into the scales.
 template <typename T>
 __global__ void __launch_bounds__(256) det_bounds_kernel(DetHeader* __restrict__ hdr, const void* __restrict__ gout, int gout_f32,
                                                          size_t cells, const T* __restrict__ feats, size_t texels, int C,
-                                                         const T* __restrict__ depth, int D, int categorical, float eps) {
-  const int lane = threadIdx.x & 31;
+                                                         const T* __restrict__ depth, int D, int categorical, float eps,
+                                                         int shift, int Z, int depth_kind, int merged) {
+  __shared__ float s_max[4][8];
+  __shared__ bool s_last;
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
   float gmax = 0.0f, gn2 = 0.0f, fn2 = 0.0f, dmax = 0.0f;
-  for (size_t row = warp; row < cells + texels; row += nwarps) {
-    const bool is_g = row < cells;
-    float m = 0.0f, q = 0.0f;
-    for (int c = lane; c < C; c += 32) {
-      float v;
-      if (is_g)
-        v = gout_f32 ? __ldg(reinterpret_cast<const float*>(gout) + row * (size_t)C + c)
-                     : to_float(__ldg(reinterpret_cast<const T*>(gout) + row * (size_t)C + c));
-      else
-        v = to_float(__ldg(feats + (row - cells) * (size_t)C + c));
-      m = fmaxf(m, fabsf(v));
-      q = fmaf(v, v, q);
+  // four rows at a time, so that their loads are in flight together (the kernel is bound by their latency)
+  constexpr int R = 4;
+  for (size_t row0 = warp; row0 < cells + texels; row0 += nwarps * R) {
+    float m[R], q[R];
+#pragma unroll
+    for (int k = 0; k < R; ++k) {
+      m[k] = q[k] = 0.0f;
+      const size_t row = row0 + (size_t)k * nwarps;
+      if (row >= cells + texels) continue;
+      const bool is_g = row < cells;
+      for (int c = lane; c < C; c += 32) {
+        float v;
+        if (is_g)
+          v = gout_f32 ? __ldg(reinterpret_cast<const float*>(gout) + row * (size_t)C + c)
+                       : to_float(__ldg(reinterpret_cast<const T*>(gout) + row * (size_t)C + c));
+        else
+          v = to_float(__ldg(feats + (row - cells) * (size_t)C + c));
+        m[k] = fmaxf(m[k], fabsf(v));
+        q[k] = fmaf(v, v, q[k]);
+      }
     }
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) q += __shfl_xor_sync(0xffffffffu, q, off);  // same value in every lane, every run
-    if (is_g) {
-      gmax = fmaxf(gmax, m);
-      gn2 = fmaxf(gn2, q);
-    } else {
-      fn2 = fmaxf(fn2, q);
+    for (int off = 16; off > 0; off >>= 1) {  // same value in every lane, every run
+#pragma unroll
+      for (int k = 0; k < R; ++k) q[k] += __shfl_xor_sync(0xffffffffu, q[k], off);
+    }
+#pragma unroll
+    for (int k = 0; k < R; ++k) {
+      const size_t row = row0 + (size_t)k * nwarps;
+      if (row < cells) {
+        gmax = fmaxf(gmax, m[k]);
+        gn2 = fmaxf(gn2, q[k]);
+      } else {
+        fn2 = fmaxf(fn2, q[k]);  // 0 for rows beyond the end
+      }
     }
   }
   const size_t nd = categorical ? texels * (size_t)D : texels;
@@ -98,11 +148,26 @@ __global__ void __launch_bounds__(256) det_bounds_kernel(DetHeader* __restrict__
     fn2 = fmaxf(fn2, __shfl_xor_sync(0xffffffffu, fn2, off));
     dmax = fmaxf(dmax, __shfl_xor_sync(0xffffffffu, dmax, off));
   }
-  if (lane == 0) {  // NaN never wins a fmaxf; zero needs no update
-    if (gmax > 0.0f) atomicMax(&hdr->g_max, __float_as_uint(gmax));
-    if (gn2 > 0.0f) atomicMax(&hdr->g_norm2, __float_as_uint(gn2));
-    if (fn2 > 0.0f) atomicMax(&hdr->f_norm2, __float_as_uint(fn2));
-    if (dmax > 0.0f) atomicMax(&hdr->d_max, __float_as_uint(dmax));
+  if (lane == 0) {
+    s_max[0][wib] = gmax;
+    s_max[1][wib] = gn2;
+    s_max[2][wib] = fn2;
+    s_max[3][wib] = dmax;
+  }
+  __syncthreads();
+  if (threadIdx.x < 4) {  // NaN never wins a fmaxf; zero needs no update
+    float m = 0.0f;
+    for (int k = 0; k < (int)(blockDim.x >> 5); ++k) m = fmaxf(m, s_max[threadIdx.x][k]);
+    unsigned* word = threadIdx.x == 0 ? &hdr->g_max : threadIdx.x == 1 ? &hdr->g_norm2 : threadIdx.x == 2 ? &hdr->f_norm2 : &hdr->d_max;
+    if (m > 0.0f) atomicMax(word, __float_as_uint(m));
+    __threadfence();  // this block's maxima are in place before it reports itself done
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(&hdr->blocks_done, 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (s_last && threadIdx.x == 0) {
+    __threadfence();
+    det_set_scales(hdr, shift, Z, depth_kind, merged);
   }
 }
 
@@ -243,35 +308,6 @@ __global__ void __launch_bounds__(kMaxWarps * 32) bwd_det_kernel(const __grid_co
     }
   }  // tiles
   loop.end(p);
-}
-
-// The bounds of the file comment -> scale = 2^(shift - e) with 2^e above the bound; shift = 62 - bits of the
-// contribution count.  depth_kind: 0 categorical probabilities, 1 logits (probabilities <= 1), 2 parametric with
-// the analytic depth gradient, 3 parametric with the legacy one.
-__global__ void det_scale_kernel(DetHeader* hdr, int shift, int Z, int depth_kind, int merged) {
-  if (threadIdx.x != 0 || blockIdx.x != 0) return;
-  const double g = (double)__uint_as_float(hdr->g_max);
-  const double gn = sqrt((double)__uint_as_float(hdr->g_norm2)), fn = sqrt((double)__uint_as_float(hdr->f_norm2));
-  const double d = (double)__uint_as_float(hdr->d_max);
-  const double slack = 1.01;  // float32 rounding inside the reductions and the kernels' own products
-  const double wmax = depth_kind == 1 ? 1.0 : d;
-  const double dpar = depth_kind <= 1 ? 1.0 : (depth_kind == 3 ? d : d * d);
-  const double bound[2] = {4.0 * (double)Z * wmax * g * slack, (double)merged * gn * fn * dpar * slack};
-  float scale[2], inv[2];
-  for (int k = 0; k < 2; ++k) {
-    int e = 0;
-    const double m = bound[k];
-    if (m > 0.0 && m < 1.0e300) (void)frexp(m, &e);  // m = f * 2^e, 0.5 <= f < 1
-    if (!(m < 1.0e300)) e = 1024;
-    int s = shift - e;
-    s = s > 100 ? 100 : (s < -100 ? -100 : s);  // both the scale and its inverse stay normal float32 numbers
-    scale[k] = ldexpf(1.0f, s);
-    inv[k] = ldexpf(1.0f, -s);
-  }
-  hdr->scale_f = scale[0];
-  hdr->inv_f = inv[0];
-  hdr->scale_d = scale[1];
-  hdr->inv_d = inv[1];
 }
 
 // Fixed-point sums -> gradient tensors; two arrays (either may be empty) in one launch.  which_b: the second

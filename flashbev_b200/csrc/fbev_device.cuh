@@ -31,6 +31,7 @@ struct DetHeader {
   unsigned d_max;    // categorical: max |depth value|; parametric: max 1 / (sigma + eps), infinity when that is <= 0
   float scale_f, inv_f;   // fixed-point scale of d_feats and its inverse
   float scale_d, inv_d;   // the same for d_depth
+  unsigned blocks_done;   // blocks of det_bounds_kernel that have added their maxima; the last one sets the scales
 };
 
 // One contribution to a 64-bit fixed-point sum: an integer atomic, so the sum does not depend on the order.

@@ -873,14 +873,12 @@ static int backward_deterministic_t(const FbevProblem* p, const void* grad_out, 
     fast = plf.chunked;
   }
 
+  const int kind = p->mode == FBEV_DEPTH_CATEGORICAL_LOGITS ? 1 : (cat ? 0 : ((flags & FBEV_BWD_LEGACY_DEPTH) ? 3 : 2));
+  // the chunked depth kernel sums up to a warp's worth of equal (texel, bin) neighbours before it adds them
   det_bounds_kernel<T><<<sm_count() * 8, 256, 0, st>>>(L.hdr, grad_out, (p->out_dtype == FBEV_F32 && p->dtype != FBEV_F32) ? 1 : 0,
                                                        (size_t)p->B * out_rows * p->X, reinterpret_cast<const T*>(p->image_feats),
                                                        tex_all, p->C, reinterpret_cast<const T*>(p->depth), p->D, cat ? 1 : 0,
-                                                       p->epsilon);
-  if (cudaGetLastError() != cudaSuccess) return FBEV_ERR_LAUNCH;
-  const int kind = p->mode == FBEV_DEPTH_CATEGORICAL_LOGITS ? 1 : (cat ? 0 : ((flags & FBEV_BWD_LEGACY_DEPTH) ? 3 : 2));
-  // the chunked depth kernel sums up to a warp's worth of equal (texel, bin) neighbours before it adds them
-  det_scale_kernel<<<1, 32, 0, st>>>(L.hdr, shift, p->Z, kind, fast ? 32 : 1);
+                                                       p->epsilon, shift, p->Z, kind, fast ? 32 : 1);
   if (cudaGetLastError() != cudaSuccess) return FBEV_ERR_LAUNCH;
 
   if (!fast) {
