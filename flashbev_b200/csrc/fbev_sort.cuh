@@ -239,7 +239,7 @@ __global__ void __launch_bounds__(128, (PDEPTH || GF32) ? 3 : 4)
 // when the texel changes or the run ends) in p.gfeat, which holds int64 sums.  The position an entry drew inside its
 // texel's segment and the way segments split into runs change from launch to launch; integer sums do not care.
 template <typename T, int V, bool GF32>
-__global__ void __launch_bounds__(128, 2)
+__global__ void __launch_bounds__(128, V == 4 ? 2 : 3)
     feats_gather_fixed_kernel(const __grid_constant__ Dev p, const unsigned* __restrict__ n_entries, unsigned run_len) {
   constexpr int E = Chunk<T>::E;
   constexpr int R = (GF32 && E == 8) ? 2 : 1;  // 16-byte loads per chunk of E channels
@@ -271,18 +271,26 @@ __global__ void __launch_bounds__(128, 2)
         for (int e = 0; e < E; ++e) atomicAdd(d + e, (unsigned long long)acc[j * E + e]);
       }
     };
-    unsigned cur = __ldg(&p.ent_sorted[i0].x);
+    // entries one step ahead, so that their latency overlaps the gathers of this step
+    uint4 nx[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) nx[u] = __ldg(p.ent_sorted + min(i0 + u, i1 - 1));
+    unsigned cur = nx[0].x;
     for (unsigned i = i0; i < i1; i += U) {
       uint4 en[U];
       uint4 q[U][V][R];
 #pragma unroll
-      for (int u = 0; u < U; ++u) en[u] = __ldg(p.ent_sorted + min(i + u, i1 - 1));
+      for (int u = 0; u < U; ++u) en[u] = nx[u];
 #pragma unroll
       for (int u = 0; u < U; ++u)
 #pragma unroll
         for (int j = 0; j < V; ++j)
 #pragma unroll
           for (int r = 0; r < R; ++r) q[u][j][r] = ldg16(gl + ((size_t)en[u].y * cpt + j * p.GL) * R + r);
+      if (i + U < i1) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) nx[u] = __ldg(p.ent_sorted + min(i + U + u, i1 - 1));
+      }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         if (i + u >= i1) break;
