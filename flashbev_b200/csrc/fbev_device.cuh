@@ -72,7 +72,9 @@ struct Dev {
   int static_units;   // forward, one sample: warps stride over (tile, group) units, no barrier, no atomic
   int exp;            // experiment bits (fbev_debug.h: fbev_set_experiment); 0 in normal use
   // gradients through a global sort by texel (null / 0 when not in use)
-  unsigned* tex_count;   // [texels + 1] entries per texel; after the scan: start of the texel's segment, total last
+  unsigned* tex_count;   // [texels + 1] entries per texel (the scatter and gather kernels of large feature maps are
+                         // handed tex_start in this field: start of every texel's segment, total last)
+  unsigned* tex_start;   // [texels + 1] target of tex_scan_kernel, for feature maps too large to scan inside a block
   unsigned* ent_count;   // [1] entries emitted so far
   uint4* ent;            // [ent_cap] {texel of (row, u0), cell, weight of u0, weight of u1} in emission order
   unsigned* ent_pos;     // [ent_cap] position the entry drew inside its texel's segment

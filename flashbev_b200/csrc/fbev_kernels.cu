@@ -396,9 +396,14 @@ static int sort_finish_t(const Plan& pl, const Dev& d, cudaStream_t st, bool fix
     const unsigned stt = g_tuning.minb == 10 && g_tuning.ty > 0 ? (unsigned)g_tuning.ty : 1024u;
     launch_after(ent_scatter_kernel<true>, sms * sb, stt, (size_t)(texels + 1) * 4, st, d, texels, total);
   } else {
-    launch_after(tex_scan_kernel, 1, 1024, 0, st, d.tex_count, texels);
-    launch_after(ent_scatter_kernel<false>, sms * 8, 256, 0, st, d, texels, (unsigned*)nullptr);
-    total = d.tex_count + texels;
+    // at most 128 blocks of 1024 threads, `per` counters per thread
+    const unsigned per = (texels + 1024u * 128u - 1u) / (1024u * 128u);
+    const unsigned sblocks = (texels + per * 1024u - 1u) / (per * 1024u);
+    launch_after(tex_scan_kernel, sblocks, 1024, 0, st, (const unsigned*)d.tex_count, d.tex_start, texels, per);
+    Dev ds = d;
+    ds.tex_count = d.tex_start;  // what the scatter kernel reads as segment starts
+    launch_after(ent_scatter_kernel<false>, sms * 8, 256, 0, st, ds, texels, (unsigned*)nullptr);
+    total = d.tex_start + texels;
   }
   // entries one lane group walks per run, blocks per SM (experiments: fbev_set_tuning tile_y / tile_x with min_blocks 9)
   const unsigned run_len = g_tuning.minb == 9 && g_tuning.ty > 0 ? (unsigned)g_tuning.ty : 32u;
@@ -798,7 +803,9 @@ static size_t sort_bytes(const FbevProblem* p, int flags) {
   if (!(flags & FBEV_BWD_FEATS) && !sort_carries_depth(p, flags)) return 0;
   const size_t tex = (size_t)sort_batch_run(p, flags) * p->N * p->H * p->W;
   if (tex >= 0xfffffff0ull || (size_t)p->B * p->Y * p->X >= 0xfffffff0ull) return 0;
-  return (((tex + 1) * 4 + 255) / 256) * 256 + 256 + sort_capacity(p, flags) * sort_entry_bytes(p, flags);
+  const size_t cnt = (((tex + 1) * 4 + 255) / 256) * 256;
+  // feature maps too large for the in-block scan keep the segment starts in an array of their own
+  return cnt + 256 + sort_capacity(p, flags) * sort_entry_bytes(p, flags) + (tex > kScanInBlock ? cnt : 0);
 }
 
 int fbev_forward_peers(const FbevProblem* p, void* out, void* const* peer_outs, int n_peers, int32_t* valid_count,
@@ -938,6 +945,7 @@ static int backward_deterministic_t(const FbevProblem* p, const void* grad_out, 
       d.ent = reinterpret_cast<uint4*>(L.sort + cnt_bytes + 256);
       d.ent_sorted = d.ent + d.ent_cap;
       d.ent_pos = reinterpret_cast<unsigned*>(d.ent_sorted + d.ent_cap);
+      d.tex_start = d.ent_pos + d.ent_cap;
       Plan pld = make_plan(&q, d, false, q.image_feats, gout, d.gfeat, !cat);
       if (!pld.chunked) return FBEV_ERR_RANGE;  // cannot happen: a slice of the batch fits where the first run did
       pld.cap = d.cap = 16;  // as the default backward: half the shared memory, twice the resident warps
@@ -1118,6 +1126,7 @@ int fbev_backward(const FbevProblem* p, const void* grad_out, void* grad_feats, 
         after = reinterpret_cast<unsigned char*>(d.ent_d_sorted + d.ent_cap);
       }
       d.ent_pos = reinterpret_cast<unsigned*>(after);
+      d.tex_start = d.ent_pos + d.ent_cap;
     }
     // the feature gradient has a kernel of its own, laid out like the forward
     Dev df = d;

@@ -17,37 +17,57 @@ namespace fbev {
 // d_feats = W^T * dO with W the sparse [cells x texels] matrix of record weights.  A list-phase kernel
 // (bwd_feats_kernel<EMIT> or bwd_depth_kernel<EMIT>) writes W as one entry per row record and counts the
 // entries per texel (of u0); the counts become segment starts (inside ent_scatter_kernel for small feature
-// maps, else tex_scan_kernel); ent_scatter_kernel moves every entry to its texel's segment;
+// maps, else tex_scan_kernel into a second array); ent_scatter_kernel moves every entry to its texel's segment;
 // feats_gather_kernel walks the grouped list, gathers each entry's dO row from L2 once and accumulates it,
 // in float32 registers, for the entry's two neighbouring texels -- one 16-byte reduction per chunk when the
 // texel changes instead of one per record, which is some 20 times fewer reductions than the direct scatter,
 // whose rate at the L2 is what bounds bwd_feats_kernel.  The parametric depth gradient (two floats per
 // texel, hopelessly contended as atomics) travels with the entries and is summed the same way.
 
-// Exclusive prefix sum of count[0, n) in place; count[n] receives the total.  One block.
-__global__ void __launch_bounds__(1024) tex_scan_kernel(unsigned* __restrict__ count, unsigned n) {
+// Exclusive prefix sum of count[0, n) into start[0, n); start[n] receives the total.  Block b owns the slice
+// [b * S, (b + 1) * S), S = per * 1024: it first adds up everything before its slice (all its threads, independent
+// coalesced loads from L2: the counters are a few hundred KB), then scans its slice.  No block waits for another;
+// the price is that the counters are read gridDim.x / 2 times over, which for the at most 128 blocks the host
+// launches stays in the megabytes.  (A single block walking 67 K counters took 60 us on the training shape.)
+__global__ void __launch_bounds__(1024) tex_scan_kernel(const unsigned* __restrict__ count, unsigned* __restrict__ start, unsigned n,
+                                                        unsigned per) {
   grid_dependency_wait();
-  __shared__ unsigned part[1024];
-  const unsigned tid = threadIdx.x, nt = blockDim.x;
-  const unsigned per = (n + nt - 1) / nt;
-  const unsigned lo = min(tid * per, n), hi = min(lo + per, n);
+  __shared__ unsigned part[32];
+  const unsigned tid = threadIdx.x, lane = tid & 31u, wid = tid >> 5;
+  const unsigned slice0 = min(blockIdx.x * per * 1024u, n);
   unsigned sum = 0;
-  for (unsigned i = lo; i < hi; ++i) sum += count[i];
-  part[tid] = sum;
+  for (unsigned i = tid; i < slice0; i += 1024u) sum += __ldg(count + i);
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+  if (lane == 0u) part[wid] = sum;
   __syncthreads();
-  for (unsigned d = 1; d < nt; d <<= 1) {
-    const unsigned v = tid >= d ? part[tid - d] : 0u;
-    __syncthreads();
-    part[tid] += v;
-    __syncthreads();
+  unsigned before = 0;
+  for (unsigned k = 0; k < 32u; ++k) before += part[k];
+  __syncthreads();
+  // the slice: `per` consecutive counters per thread, shuffles inside a warp, the warp totals through shared memory
+  const unsigned lo = min(slice0 + tid * per, n), hi = min(lo + per, n);
+  unsigned own = 0;
+  for (unsigned i = lo; i < hi; ++i) own += __ldg(count + i);
+  unsigned incl = own;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const unsigned v = __shfl_up_sync(0xffffffffu, incl, d);
+    if (lane >= (unsigned)d) incl += v;
   }
-  unsigned run = part[tid] - sum;
+  if (lane == 31u) part[wid] = incl;
+  __syncthreads();
+  unsigned warps_before = 0, all = 0;
+  for (unsigned k = 0; k < 32u; ++k) {
+    const unsigned wt = part[k];
+    warps_before += k < wid ? wt : 0u;
+    all += wt;
+  }
+  unsigned run = before + warps_before + incl - own;
   for (unsigned i = lo; i < hi; ++i) {
-    const unsigned c = count[i];
-    count[i] = run;
-    run += c;
+    start[i] = run;
+    run += __ldg(count + i);
   }
-  if (tid == nt - 1) count[n] = part[tid];
+  if (blockIdx.x == gridDim.x - 1 && tid == 0u) start[n] = before + all;
   grid_dependency_trigger();
 }
 
