@@ -127,6 +127,15 @@ def test_headline_and_training_shapes_at_full_size(cuda_device, parity_report):
     deterministic_case(synth.workload("cfg3"), "laplace", cuda_device, parity_report, repeats=2)
 
 
+def test_batch_taken_in_several_runs(cuda_device, parity_report):
+    """Five samples whose entry lists would need 2.2 times the scratch budget go through the sort in runs of two, two
+    and one sample; the fixed-point sums of the whole batch live side by side and must not notice."""
+    w = synth.Workload("budget", B=5, N=6, C=16, H=8, W=22, D=24, X=256, Y=256, Z=16, xy_extent=40.0, d0=1.0,
+                       delta=2.5, dtype="bf16", seed=61, jitter=True)
+    assert w.X * w.Y * w.N * w.Z // 2 * 36 * w.B > 2 * _lib.SORT_BUDGET_BYTES
+    deterministic_case(w, "categorical", cuda_device, parity_report, pool="mean", repeats=2)
+
+
 def test_logits_mode(cuda_device, parity_report):
     """depth_distribution=3: the chain through the folded softmax is reproducible too."""
     w = synth.Workload("small", B=2, N=6, C=16, H=8, W=22, D=24, X=40, Y=36, Z=5, xy_extent=30.0, d0=1.0, delta=1.5,
