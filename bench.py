@@ -739,12 +739,37 @@ def main():
                     flash_bevpool(**unpack(packed.to(device, non_blocking=True)), **const, **kw, out=host_out,
                                   host_row_chunks=4)
 
+            # the same step against include/fbev.h directly, every buffer allocated once (a serving loop in C would look
+            # like this): one copy of the packed inputs, fbev_forward_to_host with `bands` bands of rows
+            class AbiSlot:
+                def __init__(self):
+                    self.dev_buf = torch.empty(total, dtype=torch.uint8, device=device)
+                    self.staging = torch.empty(out.shape, dtype=out.dtype, device=device)
+                    self.host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+                    t = unpack(self.dev_buf)
+                    self.prob, self.keep = make_problem(t["depth_params"], t["image_feats"], t["projection_matrices"],
+                                                        const["feature_size"], const["image_size"], const["roi_range"],
+                                                        const["grid_size"], spec, 1e-6, 0.0)
+
+            abi_slots = [AbiSlot(), AbiSlot()]
+
+            def abi_step(slot, bands, cuda_stream):
+                slot.dev_buf.copy_(packed, non_blocking=True)  # on torch's current stream, which is cuda_stream
+                rc = lib.fbev_forward_to_host(ctypes.byref(slot.prob), slot.staging.data_ptr(), slot.host_out.data_ptr(),
+                                              bands, cuda_stream)
+                if rc:
+                    raise RuntimeError(_lib.strerror(rc))
+
             ne = max(10, args.steps // 5)
             paths = {"device result + copy": e2e_step, "out=pinned host tensor (kernel stores to it)": e2e_step_direct,
                      "out=pinned host tensor, 4 row bands": e2e_step_bands(4),
                      "out=pinned host tensor, 8 row bands": e2e_step_bands(8),
                      "one packed input copy, device result + copy": e2e_step_packed,
-                     "one packed input copy, 4 row bands": e2e_step_packed_bands}
+                     "one packed input copy, 4 row bands": e2e_step_packed_bands,
+                     "C ABI, buffers allocated once: one packed input copy, fbev_forward_to_host, 2 row bands":
+                         lambda: abi_step(abi_slots[0], 2, stream),
+                     "C ABI, buffers allocated once: one packed input copy, fbev_forward_to_host, 4 row bands":
+                         lambda: abi_step(abi_slots[0], 4, stream)}
             times = {name: timed(fn, ne, 5)[0] for name, fn in paths.items()}
             extra["e2e_us_by_path"] = {name: t * 1e3 for name, t in times.items()}
             extra["e2e_path"] = min(times, key=times.get)
@@ -781,6 +806,28 @@ def main():
             extra["e2e_us_host_clock_pipelined"] = (time.perf_counter() - t0) / ne * 1e6
             extra["e2e_note"] = ("e2e is device time (CUDA events around one call, L2 flushed before it); the host-clock "
                                  "figure queues the calls back to back without a flush and synchronises once")
+            # two steps in flight, as a double-buffered serving loop runs them: consecutive steps alternate between two
+            # streams and two sets of buffers (C ABI path above), so that one step's result travels out while the next
+            # step's inputs travel in and its kernel runs.  Every step still copies its own inputs in and its own result
+            # out.  Host clock over all steps.  Not the e2e figure of the JSON line, which stays one step at a time.
+            two = [torch.cuda.Stream(device=device), torch.cuda.Stream(device=device)]
+
+            def steps_two_in_flight(n):
+                for i in range(n):
+                    with torch.cuda.stream(two[i & 1]):
+                        abi_step(abi_slots[i & 1], 2, two[i & 1].cuda_stream)
+
+            steps_two_in_flight(6)
+            torch.cuda.synchronize()
+            n2 = 4 * ne
+            t0 = time.perf_counter()
+            steps_two_in_flight(n2)
+            torch.cuda.synchronize()
+            extra["e2e_us_two_steps_in_flight_host_clock"] = (time.perf_counter() - t0) / n2 * 1e6
+            ref_out = flash_bevpool(**{k: inp[k] for k in order}, **const, **kw)
+            torch.cuda.synchronize()
+            if not all(torch.equal(sl.host_out, ref_out.cpu()) for sl in abi_slots):
+                raise RuntimeError("C ABI end-to-end path: result differs from the operator's")
             rank_e2e = torch.tensor([times[extra["e2e_path"]]], dtype=torch.float64, device=device)
             if world > 1:
                 allr = [torch.zeros_like(rank_e2e) for _ in range(world)]
