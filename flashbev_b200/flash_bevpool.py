@@ -218,6 +218,22 @@ def _out_dtype(spec: DepthSpec, feats: torch.Tensor) -> torch.dtype:
     return torch.float32 if spec.out_dtype == torch.float32 else feats.dtype
 
 
+# host tensors already found page-locked, keyed by the identity of the tensor object (Tensor.is_pinned asks the
+# driver about the address, tens of microseconds every time); the weak reference drops the entry with the tensor
+_pinned_seen = {}
+
+
+def _is_pinned(t: torch.Tensor) -> bool:
+    key = id(t)
+    hit = _pinned_seen.get(key)
+    if hit is not None and hit[0]() is t and hit[1] == t.data_ptr():
+        return True
+    if not t.is_pinned():
+        return False
+    _pinned_seen[key] = (weakref.ref(t, lambda _r, k=key: _pinned_seen.pop(k, None)), t.data_ptr())
+    return True
+
+
 def _check_out(out, shape, dtype, device, partial, needs_grad):
     """A caller-provided result buffer: a tensor on the operator's device, or page-locked host memory that
     the kernel writes through the bus directly (the device-to-host copy of the result disappears)."""
@@ -229,7 +245,7 @@ def _check_out(out, shape, dtype, device, partial, needs_grad):
         if partial:
             out.zero_()
         return out
-    if not out.is_pinned():
+    if not _is_pinned(out):
         raise ValueError("a host out tensor must be page-locked (tensor.pin_memory())")
     if partial:
         raise ValueError("y_range with a host out tensor is not supported")
