@@ -606,7 +606,8 @@ __device__ __forceinline__ void bwd_depth_body(const Dev& p) {
   const uint4* fl = reinterpret_cast<const uint4*>(p.feats) + lg;
   const bool legacy = (p.flags & FBEV_BWD_LEGACY_DEPTH) != 0;
   const bool mean_pool = p.pool == FBEV_POOL_MEAN;
-  const bool by_record = !DET && (p.flags & FBEV_BWD_DEPTH) != 0 && (!EMIT || p.ent_d != nullptr);
+  const bool depth_entries = p.ent_d != nullptr;
+  const bool by_record = !DET && (p.flags & FBEV_BWD_DEPTH) != 0 && (!EMIT || depth_entries || (p.flags & kBwdRecordAtomics) != 0);
   const float scale_f = DET ? p.det->scale_f : 0.0f, scale_d = DET ? p.det->scale_d : 0.0f;
   long long* gd64 = reinterpret_cast<long long*>(p.gdepth);
   // categorical: sum equal (texel, bin) neighbours before the atomics.  Pays with six cells per warp (the scan's
@@ -754,7 +755,7 @@ __device__ __forceinline__ void bwd_depth_body(const Dev& p) {
             }
           }
           __syncwarp();
-          if (emitted) {
+          if (emitted && depth_entries) {
             // the records' texel fields went into the entries already, so all four words of a record can hold
             // sums: d mean / d sigma of u0, d mean / d sigma of u1 -- one walk over the samples instead of two.
             // Which of my records have a second texel is remembered in a register first.
@@ -830,7 +831,7 @@ __device__ __forceinline__ void bwd_depth_body(const Dev& p) {
               const uint4 r = rec[i];
               const float v0 = __uint_as_float(r.z), v1 = __uint_as_float(r.w);
               const bool two = r.y != 0u;
-              if (emitted) {
+              if (emitted && depth_entries) {
                 float* e = reinterpret_cast<float*>(p.ent_d + first_slot + (unsigned)i);
                 e[which] = two ? v0 : v0 + v1;
                 e[2 + which] = two ? v1 : 0.0f;

@@ -20,6 +20,9 @@
 namespace fbev {
 
 constexpr unsigned kFull = 0xffffffffu;
+// Dev.flags bit beside the FBEV_BWD_* ones (internal): the parametric depth sums per record texel leave the depth
+// kernel as atomics although it emits entries for the feature gradient
+constexpr int kBwdRecordAtomics = 16;
 
 // Head of the scratch of the reproducible backward (fbev_deterministic.cuh; 256 bytes reserved).  The maxima are kept
 // as bit patterns: non-negative floats (infinity included) order like unsigned integers, so atomicMax combines them

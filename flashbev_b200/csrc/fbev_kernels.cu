@@ -524,10 +524,11 @@ static int launch_depth(const Plan& pld, const Dev& dd, cudaStream_t st) {
 template <typename T>
 static int backward_t(const Plan& pl, Dev d, const Plan& plf, const Dev& df, cudaStream_t st) {
   if (!pl.chunked) return launch(bwd_generic_kernel<T>, pl, d, st);
-  // the record-based depth kernel (categorical depth only: the parametric modes have two gradient slots per
-  // texel, and one lane per sample firing at them contends more than the per-group issue of bwd_kernel)
+  // the record-based depth kernel: categorical depth always; the parametric modes (two gradient slots per texel,
+  // where one lane per sample firing at them contends more than the per-group issue of bwd_kernel) when their
+  // per-record sums can ride on the entry lists or leave as one atomic per record texel beside them
   const bool depth_on_records = (d.flags & FBEV_BWD_DEPTH) && plf.chunked &&
-                                (d.mode == FBEV_DEPTH_CATEGORICAL || g_tuning.minb == 5 || df.ent_d != nullptr) &&
+                                (d.mode == FBEV_DEPTH_CATEGORICAL || g_tuning.minb == 5 || df.ent != nullptr) &&
                                 (unsigned long long)df.B * df.N * df.H * df.W * (unsigned long long)df.D < (1ull << 32);
   Plan pld = plf;
   Dev dd = df;
@@ -539,7 +540,8 @@ static int backward_t(const Plan& pl, Dev d, const Plan& plf, const Dev& df, cud
   if ((d.flags & FBEV_BWD_FEATS) && plf.chunked) {
     if (depth_on_records && df.ent != nullptr) {
       // both gradients from one list phase: the depth kernel also emits the entries of the sorted feature gradient
-      dd.flags = d.flags;
+      // parametric depth without room in the entries: per-record sums leave as atomics (sort_carries_depth)
+      dd.flags = d.flags | (d.mode != FBEV_DEPTH_CATEGORICAL && df.ent_d == nullptr ? kBwdRecordAtomics : 0);
       const int rc = launch_depth<T, true>(pld, dd, st);
       return rc != FBEV_OK ? rc : sort_finish_t<T>(pld, dd, st);
     }
@@ -786,9 +788,15 @@ static size_t scratch_min_bytes(const FbevProblem* p, int flags) {
 // not fit is processed in runs of as many samples as do (sort_batch_run); one sample that does not fit by itself
 // gets the capped list and its overflow takes the direct path.
 constexpr size_t kSortBudgetBytes = FBEV_SORT_BUDGET_BYTES;
-// the parametric depth gradient rides on the same entries (16 more bytes in each list)
+// The parametric depth gradient (two values per texel) rides on the same entries, 16 more bytes in each list, when
+// the feature map is small: few texels mean many records per texel, and their sums as atomics on two words per
+// texel queue up.  From 8192 texels per sample on the sums leave the depth kernel as one atomic per record texel
+// instead (measured, both gradients: 16x44 maps 121 us on the entries against 159 us by atomics; 32x88 maps 571
+// against 574 us on a 200x200x8 grid and 2393 against 1841 us on a 512x512x16 grid with 256 channels).
 static bool sort_carries_depth(const FbevProblem* p, int flags) {
-  return (flags & FBEV_BWD_DEPTH) && !is_categorical(p->mode);
+  if (!(flags & FBEV_BWD_DEPTH) || is_categorical(p->mode)) return false;
+  if (g_tuning.minb == 12) return false;  // experiments: never / (13) always
+  return g_tuning.minb == 13 || (size_t)p->N * p->H * p->W < 8192;
 }
 static size_t sort_entry_bytes(const FbevProblem* p, int flags) {
   // entry and its grouped copy, position, and for the parametric depth gradient four floats in either list
@@ -1071,7 +1079,7 @@ int fbev_backward(const FbevProblem* p, const void* grad_out, void* grad_feats, 
   // that much (fbev_backward_scratch_bytes asks for it); small problems keep the single-launch kernels: three more
   // launches cost more than they save there
   const size_t sortb = sort_bytes(p, flags), minb = scratch_min_bytes(p, flags);
-  const bool want_sort = g_tuning.minb == 7 || g_tuning.minb == 8 || g_tuning.minb == 9 || g_tuning.minb == 10 ||
+  const bool want_sort = g_tuning.minb == 7 || g_tuning.minb == 8 || g_tuning.minb == 9 || g_tuning.minb == 10 || g_tuning.minb == 12 || g_tuning.minb == 13 ||
                          (g_tuning.minb == 0 && (size_t)p->B * p->X * (size_t)(p->y_end - p->y_begin) * p->N * p->Z >= 200000);
   const bool sorted = want_sort && sortb != 0 && scratch != nullptr && ((uintptr_t)scratch % 256) == 0 &&
                       scratch_bytes >= minb + sortb;

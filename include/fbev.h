@@ -186,9 +186,10 @@ size_t fbev_saved_state_bytes(const FbevProblem* p);
 
 /* Bytes of scratch fbev_backward works best with for this problem and flags: the float32 accumulation
  * targets of the 16-bit types (fbev_backward_min_scratch_bytes) plus, when the feature gradient is asked
- * for (or the depth gradient of a parametric mode), the entry lists of the sort by texel: counters (4 bytes
- * per texel, 8 where a run of samples has more than 8192 texels) and 36 bytes per entry (68 with a parametric depth gradient), one entry per two candidates
- * X*rows*N*Z of every sample (at least 4096 entries).  The lists never exceed FBEV_SORT_BUDGET_BYTES: a batch
+ * for (or the depth gradient of a parametric mode on feature maps of fewer than 8192 texels per sample),
+ * the entry lists of the sort by texel: counters (4 bytes per texel, 8 where a run of samples has more
+ * than 8192 texels) and 36 bytes per entry (68 when that parametric depth gradient rides on them), one
+ * entry per two candidates X*rows*N*Z of every sample (at least 4096 entries).  The lists never exceed FBEV_SORT_BUDGET_BYTES: a batch
  * that would need more is processed in runs of as many samples as fit, and a single sample that would need
  * more gets lists of that size (what does not fit is added directly, slower).  (The reference backward needs
  * no scratch at all: one atomicAdd per sample, channel and corner, flash_bevpool_cuda.cu:667-679.) */

@@ -303,7 +303,7 @@ def test_backward_channel_counts_without_16_byte_rows(cuda_device, C, dtype):
     backward_case(w, "laplace", cuda_device)
 
 
-@pytest.mark.parametrize("variant", [1, 5, 6, 7, 8])
+@pytest.mark.parametrize("variant", [1, 5, 6, 7, 8, 12, 13])
 def test_backward_kernel_variants_agree_with_the_oracle(cuda_device, variant):
     """The library picks between two feature-gradient kernels (direct reductions / texel-stationary gather) and
     two depth-gradient kernels by shape; the tuning switch forces each of them on shapes it would not get."""
