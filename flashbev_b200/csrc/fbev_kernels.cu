@@ -191,7 +191,7 @@ static Plan make_plan(const FbevProblem* p, Dev& d, bool bwd, const void* a, con
     tx = pl.CPW * (6 / pl.CPW > 1 ? 6 / pl.CPW : 1);
     ty = 4;
   }
-  const bool tile_tuned = g_tuning.minb != 9 && g_tuning.minb != 10;  // 9 / 10: tile_x / tile_y steer the gather / scatter kernel instead
+  const bool tile_tuned = g_tuning.minb != 9 && g_tuning.minb != 10 && g_tuning.minb != 16;  // 9 / 10: tile_x / tile_y steer the gather / scatter kernel instead
   d.TX = tile_tuned && g_tuning.tx > 0 ? g_tuning.tx : tx;
   d.TY = tile_tuned && g_tuning.ty > 0 ? g_tuning.ty : ty;
   d.tiles_x = (p->X + d.TX - 1) / d.TX;
@@ -425,13 +425,17 @@ static int sort_finish_t(const Plan& pl, const Dev& d, cudaStream_t st, bool fix
   // The entries do not depend on the lane layout that emitted them.  A float32 list phase that ran with four
   // chunks per lane is gathered with two: eight accumulators per texel side instead of sixteen, and twice the
   // lane groups (measured on the training shape: 94 against 102 us).
-  const bool narrow = !fixed && sizeof(T) == 4 && pl.V == 4 && d.GL * 2 <= 32 && g_tuning.minb != 9;
+  const bool narrow = !fixed && sizeof(T) == 4 && pl.V == 4 && g_tuning.minb != 9;
+  int gather_v = narrow ? 2 : pl.V;
+  if (!fixed && g_tuning.minb == 16 && (g_tuning.tx == 1 || g_tuning.tx == 2 || g_tuning.tx == 4)) gather_v = g_tuning.tx;  // experiments
   Dev dn = d;
-  if (narrow) {
-    dn.GL = d.GL * 2;
+  const int cpt = d.GL * pl.V;
+  if (gather_v != pl.V && cpt % gather_v == 0 && cpt / gather_v <= 32) {
+    dn.GL = cpt / gather_v;
     dn.CPW = 32 / dn.GL < kMaxCellsPerWarp ? 32 / dn.GL : kMaxCellsPerWarp;
+  } else {
+    gather_v = pl.V;
   }
-  const int gather_v = narrow ? 2 : pl.V;
   if (fixed) {
 #define FBEV_GATHER_FIXED(VV, GF) launch_after(feats_gather_fixed_kernel<T, VV, GF>, gb, 128, 0, st, d, (const unsigned*)total, run_len)
     switch (pl.V) {
@@ -1089,7 +1093,7 @@ int fbev_backward(const FbevProblem* p, const void* grad_out, void* grad_feats, 
   // that much (fbev_backward_scratch_bytes asks for it); small problems keep the single-launch kernels: three more
   // launches cost more than they save there
   const size_t sortb = sort_bytes(p, flags), minb = scratch_min_bytes(p, flags);
-  const bool want_sort = g_tuning.minb == 7 || g_tuning.minb == 8 || g_tuning.minb == 9 || g_tuning.minb == 10 || g_tuning.minb == 12 || g_tuning.minb == 13 ||
+  const bool want_sort = g_tuning.minb == 7 || g_tuning.minb == 8 || g_tuning.minb == 9 || g_tuning.minb == 10 || g_tuning.minb == 12 || g_tuning.minb == 13 || g_tuning.minb == 16 ||
                          (g_tuning.minb == 0 && (size_t)p->B * p->X * (size_t)(p->y_end - p->y_begin) * p->N * p->Z >= 200000);
   const bool sorted = want_sort && sortb != 0 && scratch != nullptr && ((uintptr_t)scratch % 256) == 0 &&
                       scratch_bytes >= minb + sortb;

@@ -22,8 +22,9 @@ extern "C" {
  *   9  global sort with tile_x = gather blocks per SM and tile_y = entries per gather run
  *   10 global sort with tile_x = scatter blocks per SM and tile_y = threads per scatter block
  *   12 global sort, the parametric depth gradient never on the entry lists      13 always on them
+ *   16 global sort with tile_x = 16-byte chunks per lane of the gather kernel (1, 2 or 4)
  *   14 forward / list kernels always on the tile counter      15 always in the static unit order (one sample)
- * Any non-zero selector other than 7, 8, 9, 10, 12, 13 also turns the global sort off. */
+ * Any non-zero selector other than 7, 8, 9, 10, 12, 13, 16 also turns the global sort off. */
 void fbev_set_tuning(int tile_x, int tile_y, int chunks_per_lane, int warps, int min_blocks);
 
 /* Experiment switches of the forward kernel, per host thread like the tuning above; a bit mask, 0 = off.
