@@ -20,9 +20,9 @@
 //     the kernel below, up to a warp's 32 in bwd_depth_kernel)                 =>  |.| <= merged * Gn * Fn * Dmax
 //   with Dmax = 1 (categorical), 1 / (sigma + eps)_min (legacy parametric gradient) or its square (analytic one:
 //   |z| exp(-z^2 / 2) < 1, |z^2 - 1| exp(-z^2 / 2) <= 1, and the Laplace counterparts are below 1 / 2).
-// det_set_scales (run by the last block of det_bounds_kernel) sets scale = 2^(62 - bits - e) with 2^e above the bound and 2^bits above the number of
-// contributions one element can receive (4 * rows * X * Z: every candidate of the texel's camera, four corners
-// each), so no sum can leave 63 bits.  The bounds are loose by a few binary digits, the count by many; what is left
+// det_set_scales (run by the last block of det_bounds_kernel) sets scale = 2^(62 - bits - e) with 2^e above the bound
+// and 2^bits above the number of contributions one element can receive (4 * rows * X * Z: every candidate of the
+// texel's camera, four corners each), so no sum can leave 63 bits.  The bounds are loose by a few binary digits, the count by many; what is left
 // is still finer than float32 (on the benchmark shapes a contribution keeps more than 30 digits below the largest
 // one, and the sums themselves are exact).  det_finish_kernel converts the sums back.  sigma + eps <= 0 somewhere, NaN
 // or infinite inputs give meaningless (but still repeatable) gradients.
