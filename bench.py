@@ -651,6 +651,32 @@ def main():
             ms_p, _ = timed(fwd_param, max(10, args.steps // 5), 5)
             extra["fwd_us_reference_mode_fp32_laplace_mean"] = ms_p * 1e3
 
+            # the same shapes on the reference's nuScenes calibration (matrices its create_projection_matrix built from
+            # inputs/calib_nuscenes.json, kept in a test fixture): fewer candidates land in a camera than on the synthetic rig
+            nus = os.path.join(ROOT, "tests", "golden", "nuscenes_laplace_thr0.npz")
+            if Bl == 1 and w.N == 6 and os.path.exists(nus):
+                import numpy as np
+                proj_n = torch.from_numpy(np.load(nus)["proj"]).to(device)
+                if tuple(proj_n.shape) == tuple(inp["projection_matrices"].shape):
+                    inp_n = dict(inp, projection_matrices=proj_n)
+                    prob_n, keep_n = make_problem(inp_n["depth_params"], inp_n["image_feats"], inp_n["projection_matrices"],
+                                                  inp_n["feature_size"], inp_n["image_size"], inp_n["roi_range"],
+                                                  inp_n["grid_size"], spec, 1e-6, 0.0)
+
+                    def fwd_nus():
+                        rc = lib.fbev_forward(ctypes.byref(prob_n), out.data_ptr(), None, stream)
+                        if rc:
+                            raise RuntimeError(_lib.strerror(rc))
+
+                    cnt_n = forward_with_count(**{k: inp_n[k] for k in ("image_feats", "depth_params", "projection_matrices",
+                                                                         "feature_size", "image_size", "roi_range", "grid_size")},
+                                               **kw)[1]
+                    acc = int(cnt_n.sum().item())
+                    extra["nuscenes_rig"] = {"fwd_us": timed(fwd_nus, max(10, args.steps // 5), 5)[0] * 1e3,
+                                             "accepted_samples": acc,
+                                             "of_candidates": acc / float(w.X * w.Y * w.N * w.Z),
+                                             "note": "cfg2 tensors, projection matrices of the nuScenes calibration record; one launch between its own events, L2 flushed"}
+
             # back-to-back launches with warm L2 (what a model sees when the features were just produced)
             for _ in range(20):
                 fwd_raw()
