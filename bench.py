@@ -672,6 +672,7 @@ def main():
                                                                          "feature_size", "image_size", "roi_range", "grid_size")},
                                                **kw)[1]
                     acc = int(cnt_n.sum().item())
+                    lib.fbev_set_experiment(args.exp)  # the loop over the experiment switches above left it at 0
                     extra["nuscenes_rig"] = {"fwd_us": timed(fwd_nus, max(10, args.steps // 5), 5)[0] * 1e3,
                                              "accepted_samples": acc,
                                              "of_candidates": acc / float(w.X * w.Y * w.N * w.Z),
