@@ -134,6 +134,29 @@ def test_backward_scratch_size_and_checks():
         assert lib.fbev_backward(ctypes.byref(p), 256, 256, 256, None, 0, 3 | det, None) == 8
 
 
+def test_backward_scratch_of_large_feature_maps():
+    """From 8192 texels per sample on, the texel counters are scanned into a second array (8 bytes per texel
+    instead of 4) and the parametric depth gradient no longer rides on the entries (36 bytes per entry, not 68)."""
+    lib = _lib.load()
+    r256 = lambda n: (n + 255) // 256 * 256  # noqa: E731
+    p = _problem()
+    p.N, p.H, p.W = 2, 64, 64            # 8192 texels per sample
+    p.X, p.Y, p.Z, p.y_end = 64, 64, 4, 64
+    entries = p.X * p.Y * p.N * p.Z // 2
+    cnt = r256((p.N * p.H * p.W + 1) * 4)
+    assert lib.fbev_backward_scratch_bytes(ctypes.byref(p), 3) == cnt + 256 + entries * 36   # 8192 texels: one array
+    p.H = 65                              # 8320 texels per sample
+    cnt = r256((p.N * p.H * p.W + 1) * 4)
+    assert lib.fbev_backward_scratch_bytes(ctypes.byref(p), 3) == 2 * cnt + 256 + entries * 36
+    assert lib.fbev_backward_scratch_bytes(ctypes.byref(p), 2) == 0      # depth alone: no lists at this size
+    p.H = 32                              # 4096 texels per sample: the depth gradient rides on the entries
+    cnt = r256((p.N * p.H * p.W + 1) * 4)
+    assert lib.fbev_backward_scratch_bytes(ctypes.byref(p), 3) == cnt + 256 + entries * 68
+    p.B = 3                               # 12288 texels in the run of three samples: second array again
+    cnt = r256((p.B * p.N * p.H * p.W + 1) * 4)
+    assert lib.fbev_backward_scratch_bytes(ctypes.byref(p), 3) == 2 * cnt + 256 + 3 * entries * 68
+
+
 def test_operator_refuses_cpu_tensors():
     from flashbev_b200 import flash_bevpool
     from flashbev_b200 import synth
