@@ -523,6 +523,32 @@ def main():
             extra["fwd_us_forward_that_saves_lists"] = timed(fwd_train, nb, 5)[0] * 1e3
             extra["saved_lists_mb"] = nsaved / 2 ** 20
 
+            # the same step through the Python autograd function, by the host's clock (steps issued back to back, one
+            # synchronisation): what a training loop without CUDA graphs sees, with autograd's device thread and without
+            if Bl == 1:
+                leaf = {k: inp[k].detach().clone().requires_grad_(True) for k in ("image_feats", "depth_params")}
+                rest = {k: inp[k] for k in ("projection_matrices", "feature_size", "image_size", "roi_range", "grid_size")}
+
+                def autograd_step():
+                    leaf["image_feats"].grad = None
+                    leaf["depth_params"].grad = None
+                    flash_bevpool(**leaf, **rest, **kw).backward(go)
+
+                def host_clock(n):
+                    for _ in range(10):
+                        autograd_step()
+                    torch.cuda.synchronize()
+                    t0 = time.perf_counter()
+                    for _ in range(n):
+                        autograd_step()
+                    torch.cuda.synchronize()
+                    return (time.perf_counter() - t0) / n * 1e6
+
+                extra["fwd_bwd_us_python_autograd_host_clock"] = host_clock(4 * nb)
+                with torch.autograd.set_multithreading_enabled(False):
+                    extra["fwd_bwd_us_python_autograd_host_clock_single_thread"] = host_clock(4 * nb)
+                del leaf
+
             # bitwise reproducible gradients (FBEV_BWD_DETERMINISTIC: fixed-point sums, a measuring launch first)
             flags_det = flags | _lib.BWD_DETERMINISTIC
             nbytes_det = lib.fbev_backward_scratch_bytes(ctypes.byref(prob), flags_det)
