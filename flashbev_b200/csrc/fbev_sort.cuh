@@ -36,7 +36,15 @@ __global__ void __launch_bounds__(1024) tex_scan_kernel(const unsigned* __restri
   const unsigned tid = threadIdx.x, lane = tid & 31u, wid = tid >> 5;
   const unsigned slice0 = min(blockIdx.x * per * 1024u, n);
   unsigned sum = 0;
-  for (unsigned i = tid; i < slice0; i += 1024u) sum += __ldg(count + i);
+  if (blockIdx.x * per * 1024u <= n) {  // a multiple of 1024 counters, 16 bytes at a time (the array is 256-byte aligned)
+    const uint4* c4 = reinterpret_cast<const uint4*>(count);
+    for (unsigned i = tid; i < slice0 / 4u; i += 1024u) {
+      const uint4 v = __ldg(c4 + i);
+      sum += v.x + v.y + v.z + v.w;
+    }
+  } else {
+    for (unsigned i = tid; i < slice0; i += 1024u) sum += __ldg(count + i);
+  }
 #pragma unroll
   for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
   if (lane == 0u) part[wid] = sum;
